@@ -1,0 +1,1282 @@
+// The kernels of the block-FP8 tensor-parallel decode path and their C ABI
+// (declared in include/iqb200.h), built on the streaming engine of stream_core.cuh:
+//
+//   iq_linear    row-parallel block-FP8 product (+ fused all-reduce tail)
+//   iq_router    bf16 router GEMV + top-k selection in one launch
+//   iq_moe_gate  grouped expert Gate/Up + SiLU, each distinct expert streamed once
+//   iq_moe_down  grouped expert Down (+ fused all-reduce tail)
+//   iq_tail      the all-reduce + residual + RMSNorm epilogue on its own
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <mutex>
+#include <utility>
+#include <vector>
+
+#include "stream_core.cuh"
+
+namespace iqb {
+
+// ------------------------------------------------------------------------------------
+// Scratch layout (bytes): status @0, ticket @64, tile counters @256, partials after.
+constexpr size_t kScrTicket = 64;
+constexpr size_t kScrCounters = 256;
+constexpr int kMaxTiles = 16384;
+constexpr size_t kScrPartials = kScrCounters + sizeof(uint32_t) * kMaxTiles;
+constexpr int kMaxGrid = 256;
+constexpr size_t kScrDebug = kScrPartials + sizeof(float) * kMaxGrid * 2 * 128 * 8;
+constexpr size_t kScrBytes = kScrDebug + sizeof(uint64_t) * kMaxGrid * 8;   // + timestamps (debug)
+
+__host__ __device__ inline StreamScratch scratch_of(void* base) {
+  StreamScratch s;
+  uint8_t* b = static_cast<uint8_t*>(base);
+  s.status = reinterpret_cast<int*>(b);
+  s.ticket = reinterpret_cast<uint32_t*>(b + kScrTicket);
+  s.tile_counter = reinterpret_cast<uint32_t*>(b + kScrCounters);
+  s.partials = reinterpret_cast<float*>(b + kScrPartials);
+  return s;
+}
+
+__host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Shared-memory carve-up after StreamSmem: activation scales, staged activations, ring.
+template <class G>
+struct Carve {
+  StreamSmem<G>* sm;
+  float* xs;
+  uint8_t* xq;
+  uint8_t* ring;
+};
+template <class G>
+__host__ __device__ inline size_t smem_fixed_bytes(int x_rows, int x_blocks, int x_pitch) {
+  size_t off = align_up(sizeof(StreamSmem<G>), 16);
+  off += align_up(sizeof(float) * x_rows * x_blocks, 16);
+  off += static_cast<size_t>(x_rows) * x_pitch;
+  return align_up(off, 128);
+}
+template <class G>
+__device__ inline Carve<G> carve(uint8_t* base, const StreamShape& sh) {
+  Carve<G> c;
+  c.sm = reinterpret_cast<StreamSmem<G>*>(base);
+  size_t off = align_up(sizeof(StreamSmem<G>), 16);
+  c.xs = reinterpret_cast<float*>(base + off);
+  off += align_up(sizeof(float) * sh.x_rows * sh.x_blocks, 16);
+  c.xq = base + off;
+  c.ring = base + smem_fixed_bytes<G>(sh.x_rows, sh.x_blocks, sh.x_pitch);
+  return c;
+}
+
+// ------------------------------------------------------------------------------------
+// Activation staging (consumer threads only, tid in [0, 256)).
+
+// Both routines issue a batch of independent 16-byte global loads before touching any of
+// them, so a row set costs about one memory latency instead of one per group.
+constexpr int kStageBatch = 8;
+
+// Raw e4m3 rows (16-byte vectors) + their scales (or 1).
+__device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape& sh,
+                                       const uint8_t* src, size_t src_pitch,
+                                       const float* src_scale, int rows, int k, int tid) {
+  const int vec = k / 16, nvec = rows * vec;
+  for (int v0 = 0; v0 < nvec; v0 += kConsumerThreads * kStageBatch) {
+    uint4 raw[kStageBatch];
+#pragma unroll
+    for (int j = 0; j < kStageBatch; ++j) {
+      const int i = v0 + j * kConsumerThreads + tid;
+      if (i < nvec) {
+        const int r = i / vec, v = i - r * vec;
+        raw[j] = __ldg(reinterpret_cast<const uint4*>(src + r * src_pitch + v * 16));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kStageBatch; ++j) {
+      const int i = v0 + j * kConsumerThreads + tid;
+      if (i < nvec) {
+        const int r = i / vec, v = i - r * vec;
+        *reinterpret_cast<uint4*>(xq + r * sh.x_pitch + v * 16) = raw[j];
+      }
+    }
+  }
+  for (int i = tid; i < rows * sh.x_blocks; i += kConsumerThreads)
+    xs[i] = src_scale ? src_scale[i] : 1.0f;
+}
+
+// bf16 rows quantised per 1x128 group: scale = amax/448 (1 for an all-zero group), value
+// = e4m3(x * (1 / scale)).  A thread holds eight consecutive elements, so a group is sixteen
+// consecutive lanes.  With `split2` row r becomes staged rows 2r (the e4m3 value) and
+// 2r+1 (the e4m3 of what the first term missed), both under the same scale.
+__device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const StreamShape& sh,
+                                              const __nv_bfloat16* src, size_t src_pitch,
+                                              int rows, int k, bool split2, int tid) {
+  const int vec = k / 8, nvec = rows * vec;
+  for (int v0 = 0; v0 < nvec; v0 += kConsumerThreads * kStageBatch) {
+    uint4 raw[kStageBatch];
+#pragma unroll
+    for (int j = 0; j < kStageBatch; ++j) {
+      const int i = v0 + j * kConsumerThreads + tid;
+      raw[j] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < nvec) {
+        const int r = i / vec, v = i - r * vec;
+        raw[j] = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * src_pitch + v * 8));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kStageBatch; ++j) {
+      const int i = v0 + j * kConsumerThreads + tid;   // uniform trip count: shuffles below
+      const bool live = i < nvec;
+      const int ii = live ? i : 0;
+      const int r = ii / vec, v = ii - r * vec;
+      float f[8];
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 t = __bfloat1622float2(p[q]);
+        f[2 * q] = t.x;
+        f[2 * q + 1] = t.y;
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
+#pragma unroll
+      for (int o = 8; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      if (!live) continue;               // after the shuffles: dead lanes skip the math
+      const float s = amax > 0.f ? amax / 448.0f : 1.0f;
+      const float rcp = 1.0f / s;        // one division per vector; values use x * (1/s)
+      uint32_t q0[2] = {0u, 0u}, q1[2] = {0u, 0u};
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float xn = f[q] * rcp;
+        const uint8_t a = f32_to_e4m3_sat(xn);
+        q0[q >> 2] |= static_cast<uint32_t>(a) << (8 * (q & 3));
+        if (split2)
+          q1[q >> 2] |= static_cast<uint32_t>(f32_to_e4m3_sat(xn - e4m3_to_f32(a))) << (8 * (q & 3));
+      }
+      const int blk = v >> 4;
+      if (split2) {
+        *reinterpret_cast<uint2*>(xq + (2 * r) * sh.x_pitch + v * 8) = make_uint2(q0[0], q0[1]);
+        *reinterpret_cast<uint2*>(xq + (2 * r + 1) * sh.x_pitch + v * 8) = make_uint2(q1[0], q1[1]);
+        if ((v & 15) == 0) {
+          xs[(2 * r) * sh.x_blocks + blk] = s;
+          xs[(2 * r + 1) * sh.x_blocks + blk] = s;
+        }
+      } else {
+        *reinterpret_cast<uint2*>(xq + r * sh.x_pitch + v * 8) = make_uint2(q0[0], q0[1]);
+        if ((v & 15) == 0) xs[r * sh.x_blocks + blk] = s;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// The tail: all-reduce of the ranks' bf16 rows, residual add and RMSNorm(s).
+struct TailParams {
+  iq_tail_args a;
+};
+
+__device__ inline void bf16x8_to_f32(const U4& u, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(p[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+__device__ inline U4 f32_to_bf16x8(const float (&f)[8]) {
+  U4 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) p[j] = __float22bfloat162_rn(make_float2(f[2 * j], f[2 * j + 1]));
+  return u;
+}
+__device__ inline float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// Sum of squares per row across the block: `part[m]` from every thread -> `out[m]` on all.
+// `red` holds 8 x nwarps floats.  Fixed summation order.
+__device__ inline void block_row_sums(float (&part)[8], int m, float* red, float (&out)[8]) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  __syncthreads();
+  for (int r = 0; r < m; ++r) {
+    const float s = warp_sum(part[r]);
+    if (lane == 0) red[r * nwarps + warp] = s;
+  }
+  __syncthreads();
+  for (int r = 0; r < m; ++r) {
+    float s = 0.f;
+    for (int w = 0; w < nwarps; ++w) s += red[r * nwarps + w];
+    out[r] = s;
+  }
+}
+
+// Runs on every thread of one CTA.  `rows_s` is shared memory for m*h bf16 and `red` for
+// 8 * (blockDim/32) floats.  Rows written by other CTAs of this launch must already be
+// visible (the caller passed the ticket).
+__device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* rows_s, float* red,
+                         int* sflag) {
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int m = a.m, h = a.h, vec_per_row = h / 8;
+  const int nvec = m * vec_per_row;
+
+  // ---- cross-rank readiness
+  if (a.world > 1) {
+    if (tid == 0) {
+      const uint32_t target = (*a.epoch + 1u) * static_cast<uint32_t>(a.world);
+      __threadfence_system();
+      if (a.arrive_mc) {
+        multimem_red_add_release_u32(a.arrive_mc, 1u);
+      } else {
+        for (int p = 0; p < a.world; ++p)
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_arrive[p]), "r"(1u)
+                       : "memory");
+      }
+      const uint64_t budget = 1000000ull * (a.timeout_ms ? a.timeout_ms : 2000u);
+      const uint64_t t0 = globaltimer_ns();
+      int ok = 1;
+      while (static_cast<int32_t>(ld_acquire_sys_u32(a.arrive) - target) < 0) {
+        if (globaltimer_ns() - t0 > budget) { ok = 0; break; }
+      }
+      if (!ok) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
+      *sflag = ok;
+    }
+    __syncthreads();
+    if (!*sflag) {
+      // Peers are missing: leave the outputs untouched and let the host read the status.
+      if (tid == 0) *a.epoch = *a.epoch + 1u;
+      return;
+    }
+  }
+
+  // ---- reduced rows into shared memory (bf16, the switch's rounding point)
+  for (int v = tid; v < nvec; v += nthr) {
+    U4 u;
+    const size_t off = static_cast<size_t>(v) * 8;
+    if (a.world == 1) {
+      const uint4 t = __ldcg(reinterpret_cast<const uint4*>(
+          static_cast<const __nv_bfloat16*>(a.partial) + off));
+      u = U4{t.x, t.y, t.z, t.w};
+    } else if (a.partial_mc) {
+      u = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(a.partial_mc) + off);
+    } else {
+      float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int p = 0; p < a.world; ++p) {
+        const U4 t = ld_global_u4(static_cast<const __nv_bfloat16*>(a.peer_partials[p]) + off);
+        float f[8];
+        bf16x8_to_f32(t, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) accv[j] += f[j];
+      }
+      u = f32_to_bf16x8(accv);
+    }
+    *reinterpret_cast<U4*>(rows_s + off) = u;
+  }
+
+  float part[8], tot[8], inv[8];
+  const float inv_h = 1.0f / static_cast<float>(h);
+  if (a.kind == IQ_TAIL_ATTN) {
+    // first RMSNorm statistics on the reduced rows
+#pragma unroll
+    for (int r = 0; r < 8; ++r) part[r] = 0.f;
+    __syncthreads();
+    for (int v = tid; v < nvec; v += nthr) {
+      float f[8];
+      bf16x8_to_f32(*reinterpret_cast<const U4*>(rows_s + static_cast<size_t>(v) * 8), f);
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s = fmaf(f[j], f[j], s);
+      const int r = v / vec_per_row;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) part[q] += (q == r) ? s : 0.f;
+    }
+    block_row_sums(part, m, red, tot);
+    for (int r = 0; r < m; ++r) inv[r] = rsqrtf(tot[r] * inv_h + a.eps);
+  }
+
+  // ---- h = residual + (ATTN: bf16(bf16(w1*(ao*inv))*scale) | MLP: bf16(m*scale))
+#pragma unroll
+  for (int r = 0; r < 8; ++r) part[r] = 0.f;
+  if (a.kind != IQ_TAIL_ATTN) __syncthreads();
+  for (int v = tid; v < nvec; v += nthr) {
+    const int r = v / vec_per_row, c0 = (v - r * vec_per_row) * 8;
+    const size_t off = static_cast<size_t>(v) * 8;
+    float f[8], res[8], hv[8];
+    bf16x8_to_f32(*reinterpret_cast<const U4*>(rows_s + off), f);
+    if (a.residual_fp32) {
+      const float4 r0 = *reinterpret_cast<const float4*>(static_cast<const float*>(a.residual) + off);
+      const float4 r1 =
+          *reinterpret_cast<const float4*>(static_cast<const float*>(a.residual) + off + 4);
+      res[0] = r0.x; res[1] = r0.y; res[2] = r0.z; res[3] = r0.w;
+      res[4] = r1.x; res[5] = r1.y; res[6] = r1.z; res[7] = r1.w;
+    } else {
+      const uint4 t =
+          *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.residual) + off);
+      bf16x8_to_f32(U4{t.x, t.y, t.z, t.w}, res);
+    }
+    if (a.kind == IQ_TAIL_ATTN) {
+      const float4 w0 = *reinterpret_cast<const float4*>(a.w_first + c0);
+      const float4 w1 = *reinterpret_cast<const float4*>(a.w_first + c0 + 4);
+      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float nrm = bf16_round(w[j] * (f[j] * inv[r]));
+        const float sc = bf16_round(nrm * a.scale);
+        hv[j] = sc + res[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) hv[j] = res[j] + bf16_round(f[j] * a.scale);
+    }
+    float s = 0.f;
+    if (a.residual_fp32) {
+      float* ho = static_cast<float*>(a.h_out) + off;
+      *reinterpret_cast<float4*>(ho) = make_float4(hv[0], hv[1], hv[2], hv[3]);
+      *reinterpret_cast<float4*>(ho + 4) = make_float4(hv[4], hv[5], hv[6], hv[7]);
+      // The fp32 stream is normalised unrounded; shared memory keeps a bf16 copy only
+      // when it is the stream itself, so recompute from registers below.
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s = fmaf(hv[j], hv[j], s);
+      // Stash fp32 h for the norm pass in place of the reduced row (two bf16 slots per
+      // value are not available), so the fp32 path normalises in this same pass instead.
+      const U4 hb = f32_to_bf16x8(hv);
+      *reinterpret_cast<U4*>(rows_s + off) = hb;
+    } else {
+      const U4 hb = f32_to_bf16x8(hv);
+      *reinterpret_cast<U4*>(rows_s + off) = hb;
+      *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.h_out) + off) = hb;
+      float hr[8];
+      bf16x8_to_f32(hb, hr);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s = fmaf(hr[j], hr[j], s);
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) part[q] += (q == r) ? s : 0.f;
+  }
+  block_row_sums(part, m, red, tot);
+  for (int r = 0; r < m; ++r) inv[r] = rsqrtf(tot[r] * inv_h + a.eps);
+  if (a.inv_out && tid < m) {
+    float t = inv[0];
+    for (int r = 1; r < m; ++r) t = (tid == r) ? inv[r] : t;
+    a.inv_out[tid] = t;
+  }
+
+  // ---- norm_out = bf16(w_norm * (h * inv)) (+ e4m3 copy, unscaled or per 1x128 group)
+  for (int v0 = 0; v0 < nvec; v0 += nthr) {
+    const int v = v0 + tid;
+    const bool live = v < nvec;
+    const int vv = live ? v : 0;
+    const int r = vv / vec_per_row, c0 = (vv - r * vec_per_row) * 8;
+    const size_t off = static_cast<size_t>(vv) * 8;
+    float hr[8], o[8];
+    if (a.residual_fp32) {
+      const float* hp = static_cast<const float*>(a.h_out) + off;   // written by this thread
+      const float4 h0 = *reinterpret_cast<const float4*>(hp);
+      const float4 h1 = *reinterpret_cast<const float4*>(hp + 4);
+      hr[0] = h0.x; hr[1] = h0.y; hr[2] = h0.z; hr[3] = h0.w;
+      hr[4] = h1.x; hr[5] = h1.y; hr[6] = h1.z; hr[7] = h1.w;
+    } else {
+      bf16x8_to_f32(*reinterpret_cast<const U4*>(rows_s + off), hr);
+    }
+    const float4 w0 = *reinterpret_cast<const float4*>(a.w_norm + c0);
+    const float4 w1 = *reinterpret_cast<const float4*>(a.w_norm + c0 + 4);
+    const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[j] = bf16_round(w[j] * (hr[j] * inv[r]));
+      amax = fmaxf(amax, fabsf(o[j]));
+    }
+    if (live) *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.norm_out) + off) = f32_to_bf16x8(o);
+    if (a.norm_fp8) {
+      float s = 1.0f;
+      if (a.norm_fp8_scale) {
+        // A 128-element group is sixteen consecutive vectors = sixteen consecutive lanes.
+#pragma unroll
+        for (int o2 = 8; o2; o2 >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o2));
+        s = amax > 0.f ? amax / 448.0f : 1.0f;
+        if (live && (vv & 15) == 0) a.norm_fp8_scale[vv >> 4] = s;
+      }
+      const float rcp = 1.0f / s;
+      uint32_t q0 = 0, q1 = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        q0 |= static_cast<uint32_t>(f32_to_e4m3_sat(o[j] * rcp)) << (8 * j);
+        q1 |= static_cast<uint32_t>(f32_to_e4m3_sat(o[j + 4] * rcp)) << (8 * j);
+      }
+      if (live) *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.norm_fp8) + off) = make_uint2(q0, q1);
+    }
+  }
+  if (a.world > 1 && tid == 0) *a.epoch = *a.epoch + 1u;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) tail_kernel(const TailParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  float* red = reinterpret_cast<float*>(smem);
+  int* sflag = reinterpret_cast<int*>(smem + 512);
+  run_tail(p.a, reinterpret_cast<__nv_bfloat16*>(smem + 1024), red, sflag);
+}
+
+// ------------------------------------------------------------------------------------
+// iq_linear
+struct LinearParams {
+  CUtensorMap map0, map1;   // weight tensor maps (unused for whole-row stages)
+  StreamShape sh;
+  const void* x;
+  const float* x_scale;
+  int x_kind, m, k, n;
+  const uint8_t* w;
+  const float* w_scale;
+  __nv_bfloat16* out;
+  void* scratch;
+  int has_tail;
+  iq_tail_args tail;
+};
+
+template <class G>
+__global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_constant__ LinearParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const StreamShape& sh = p.sh;
+  const Carve<G> cv = carve<G>(smem, sh);
+  const StreamScratch scr = scratch_of(p.scratch);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const long long total =
+      static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
+  const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
+  const int cta = blockIdx.x;
+  uint64_t* dbg = (sh.debug & 4)
+      ? reinterpret_cast<uint64_t*>(static_cast<uint8_t*>(p.scratch) + kScrDebug) + cta * 8 : nullptr;
+  if (dbg && tid == 0) dbg[0] = globaltimer_ns();
+  pdl_launch_dependents();
+  stream_init<G>(sh, cv.sm);
+  if (tid == 0) {
+    GroupDesc& g = cv.sm->groups[0];
+    g.w = p.w;
+    g.scale = p.w_scale;
+    g.row_base = 0;
+    g.map_id = 0;
+    for (int c = 0; c < kMaxCols; ++c) {
+      g.col_row[c] = c < sh.x_rows ? c : -1;
+      g.col_mul[c] = 1.0f;
+      g.col_out[c] = static_cast<int16_t>(c);
+    }
+  }
+  __syncthreads();
+  if (cta < grid) {
+    const long long it0 = item_begin(total, grid, cta), it1 = item_begin(total, grid, cta + 1);
+    if (warp == kConsumerWarps) {
+      // Weights never change: start streaming before the predecessor kernel has finished.
+      if (dbg && tid == kConsumerThreads) dbg[4] = globaltimer_ns();
+      produce<G>(sh, cv.sm, cv.ring, it0, it1, scr.status, &p.map0, &p.map1);
+      if (dbg && tid == kConsumerThreads) dbg[5] = globaltimer_ns();
+      pdl_wait();
+    } else {
+      pdl_wait();
+      if (dbg && tid == 0) dbg[1] = globaltimer_ns();
+      if (p.x_kind == IQ_X_BF16_GROUPQ || p.x_kind == IQ_X_BF16_SPLIT2)
+        stage_rows_bf16_groupq(cv.xq, cv.xs, sh, static_cast<const __nv_bfloat16*>(p.x), p.k, p.m,
+                               p.k, p.x_kind == IQ_X_BF16_SPLIT2, tid);
+      else
+        stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.x), p.k,
+                        p.x_kind == IQ_X_E4M3_GROUP ? p.x_scale : nullptr, p.m, p.k, tid);
+      named_bar_sync(1, kConsumerThreads);
+      if (dbg && tid == 0) dbg[2] = globaltimer_ns();
+      const bool split2 = p.x_kind == IQ_X_BF16_SPLIT2;
+      const int m = p.m, n = p.n;
+      __nv_bfloat16* out = p.out;
+      auto emit = [&](const ItemCoord& c, int r, int col, const float (&val)[G::RT]) {
+#pragma unroll
+        for (int sub = 0; sub < G::RT; ++sub) {
+          const int row = c.tile_in_group * G::ROWS + sub * 16 + r;
+          if (split2) {
+            // columns 2j and 2j+1 are the two terms of row j: fold them on the even lane
+            const float other = __shfl_xor_sync(0xffffffffu, val[sub], 1);
+            if ((col & 1) == 0 && (col >> 1) < m)
+              out[static_cast<size_t>(col >> 1) * n + row] = __float2bfloat16_rn(val[sub] + other);
+          } else if (col < m) {
+            out[static_cast<size_t>(col) * n + row] = __float2bfloat16_rn(val[sub]);
+          }
+        }
+      };
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, it0, it1, total, grid, cta, scr, emit);
+      if (dbg && tid == 0) dbg[3] = globaltimer_ns();
+    }
+  } else {
+    pdl_wait();
+  }
+  if (!p.has_tail) {
+    stream_drain_on_abort<G>(cv.sm);
+    return;
+  }
+  if (last_cta<G>(cv.sm, scr, gridDim.x)) {
+    // The ring is idle now: its first bytes hold the reduced rows.
+    float* red = reinterpret_cast<float*>(cv.sm->red);
+    run_tail(p.tail, reinterpret_cast<__nv_bfloat16*>(cv.ring), red, &cv.sm->is_last_tile);
+  }
+  stream_drain_on_abort<G>(cv.sm);
+}
+
+// ------------------------------------------------------------------------------------
+// iq_router: bf16 GEMV into fp32 logits, then top-k on the last CTA (one warp per row).
+struct RouterParams {
+  CUtensorMap map0, map1;   // weight tensor maps (unused for whole-row stages)
+  StreamShape sh;
+  const __nv_bfloat16* x;
+  const uint8_t* w;
+  int m, h, e, top_k, score;
+  int* sel;
+  float* wt;
+  float* logits;
+  void* scratch;
+};
+
+// Monotone key for finite fp32 with -0 == +0.
+__device__ inline uint32_t ordered_key(float v) {
+  uint32_t b = __float_as_uint(v);
+  if ((b & 0x7fffffffu) == 0) b = 0;
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// One warp selects row `row`: top_k rounds of (largest key, then smallest id), softmax
+// or renormalised sigmoid summed in descending-value order, pairs stored by ascending id.
+__device__ void select_row(const float* logits, int e, int top_k, int score, int row, int* sel,
+                           float* wt) {
+  const int lane = threadIdx.x & 31;
+  constexpr int kMaxPerLane = 16;            // e <= 512
+  uint32_t key[kMaxPerLane];
+  const int per = (e + 31) / 32;
+#pragma unroll
+  for (int j = 0; j < kMaxPerLane; ++j) {
+    const int id = lane + 32 * j;
+    key[j] = (j < per && id < e) ? ordered_key(__ldcg(logits + static_cast<size_t>(row) * e + id)) : 0u;
+  }
+  int my_id = 0x7fffffff;
+  float my_val = 0.f, top_val = 0.f, sum = 0.f, my_p = 0.f;
+  for (int t = 0; t < top_k; ++t) {
+    uint32_t best = 0;
+    int best_id = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int id = lane + 32 * j;
+      if (key[j] > best) { best = key[j]; best_id = id; }   // ascending id: first max wins
+    }
+    const uint32_t wmax = __reduce_max_sync(0xffffffffu, best);
+    const int cand = (best == wmax && best != 0u) ? best_id : 0x7fffffff;
+    const int win = __reduce_min_sync(0xffffffffu, cand);
+    if (win == 0x7fffffff) break;            // fewer than top_k finite logits
+    const uint32_t kbits = wmax;
+    const uint32_t raw = (kbits & 0x80000000u) ? (kbits & 0x7fffffffu) : ~kbits;
+    const float val = __uint_as_float(raw);
+    if (t == 0) top_val = val;
+    const float p = score == IQ_ROUTE_SOFTMAX ? expf(__fsub_rn(val, top_val))
+                                              : 1.0f / (1.0f + expf(-val));
+    sum = __fadd_rn(sum, p);
+    if (lane == t) { my_id = win; my_val = val; my_p = p; }
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j)
+      if ((win & 31) == lane && (win >> 5) == j) key[j] = 0u;
+  }
+  (void)my_val;
+  // rank of my id among the selected ids
+  int rank = 0;
+  for (int t = 0; t < top_k; ++t) {
+    const int other = __shfl_sync(0xffffffffu, my_id, t);
+    rank += (other < my_id) ? 1 : 0;
+  }
+  if (lane < top_k && my_id != 0x7fffffff) {
+    sel[row * top_k + rank] = my_id;
+    wt[row * top_k + rank] = my_p / sum;
+  }
+}
+
+template <class G>
+__global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_constant__ RouterParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const StreamShape& sh = p.sh;
+  const Carve<G> cv = carve<G>(smem, sh);
+  const StreamScratch scr = scratch_of(p.scratch);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const long long total =
+      static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
+  const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
+  const int cta = blockIdx.x;
+  pdl_launch_dependents();
+  stream_init<G>(sh, cv.sm);
+  if (tid == 0) {
+    GroupDesc& g = cv.sm->groups[0];
+    g.w = p.w;
+    g.scale = nullptr;
+    g.row_base = 0;
+    g.map_id = 0;
+    for (int c = 0; c < kMaxCols; ++c) {
+      g.col_row[c] = c < p.m ? c : -1;
+      g.col_mul[c] = 1.0f;
+      g.col_out[c] = static_cast<int16_t>(c);
+    }
+  }
+  __syncthreads();
+  if (cta < grid) {
+    const long long it0 = item_begin(total, grid, cta), it1 = item_begin(total, grid, cta + 1);
+    if (warp == kConsumerWarps) {
+      produce<G>(sh, cv.sm, cv.ring, it0, it1, scr.status, &p.map0, &p.map1);
+      pdl_wait();
+    } else {
+      pdl_wait();
+      const int vec = p.h / 8;   // 16-byte vectors per bf16 row
+      for (int i = tid; i < p.m * vec; i += kConsumerThreads) {
+        const int r = i / vec, v = i - r * vec;
+        *reinterpret_cast<uint4*>(cv.xq + r * sh.x_pitch + v * 16) =
+            *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(r) * p.h + v * 8);
+      }
+      named_bar_sync(1, kConsumerThreads);
+      const int m = p.m, e = p.e;
+      float* logits = p.logits;
+      auto emit = [&](const ItemCoord& c, int r, int col, const float (&val)[G::RT]) {
+#pragma unroll
+        for (int sub = 0; sub < G::RT; ++sub)
+          if (col < m)
+            logits[static_cast<size_t>(col) * e + c.tile_in_group * G::ROWS + sub * 16 + r] = val[sub];
+      };
+      consume<G, ElemBF16>(sh, cv.sm, cv.ring, cv.xq, cv.xs, it0, it1, total, grid, cta, scr, emit);
+    }
+  } else {
+    pdl_wait();
+  }
+  if (last_cta<G>(cv.sm, scr, gridDim.x)) {
+    if (warp < p.m) select_row(p.logits, p.e, p.top_k, p.score, warp, p.sel, p.wt);
+  }
+  stream_drain_on_abort<G>(cv.sm);
+}
+
+// ------------------------------------------------------------------------------------
+// Expert groups of one step: the distinct routed experts in order of first appearance,
+// then the shared experts.  Every CTA derives the same table from `sel`.
+struct MoeCommon {
+  int m, h, i_loc, n_experts, top_k, n_shared;
+  const int* sel;
+  const float* wt;
+  const uint8_t* w;          // expert bank
+  const float* w_scale;
+  const uint8_t* shared_w;
+  const float* shared_scale;
+  size_t w_stride, scale_stride;   // bytes / floats between experts
+  int rows_per_expert;
+};
+
+// Returns the number of groups.  `use_wt`: column multipliers are the routing weights
+// (Down) instead of 1 (Gate).  `x_is_pair`: the staged activation row of a column is its
+// pair's row (Down) instead of the token's row (Gate).
+template <class G>
+__device__ int build_groups(StreamSmem<G>* sm, const MoeCommon& mc, bool use_wt, bool x_is_pair,
+                            int* status, int* s_ids /* 64 + kMaxGroups + 1 ints of shared memory */) {
+  const int tid = threadIdx.x;
+  const int pairs = mc.m * mc.top_k;
+  const int slots = mc.top_k + mc.n_shared;
+  if (tid < pairs) {
+    int e = mc.sel[tid];
+    if (e < 0 || e >= mc.n_experts) {
+      set_status(status, IQ_ERR_ROUTE);
+      e = -1;
+    }
+    s_ids[tid] = e;
+  }
+  __syncthreads();
+  int n_groups = 0;
+  if (tid == 0) {
+    for (int p = 0; p < pairs; ++p) {
+      const int e = s_ids[p];
+      if (e < 0) continue;
+      int gi = -1;
+      for (int g = 0; g < n_groups; ++g)
+        if (s_ids[64 + g] == e) { gi = g; break; }
+      if (gi < 0) {
+        gi = n_groups++;
+        s_ids[64 + gi] = e;
+        GroupDesc& gd = sm->groups[gi];
+        gd.w = mc.w + static_cast<size_t>(e) * mc.w_stride;
+        gd.scale = mc.w_scale + static_cast<size_t>(e) * mc.scale_stride;
+        gd.row_base = e * mc.rows_per_expert;
+        gd.map_id = 0;
+        for (int c = 0; c < kMaxCols; ++c) {
+          gd.col_row[c] = -1;
+          gd.col_mul[c] = 0.f;
+          gd.col_out[c] = 0;
+        }
+      }
+      GroupDesc& gd = sm->groups[gi];
+      const int row = p / mc.top_k, slot = p - row * mc.top_k;
+      const int pair_row = row * slots + slot;
+      gd.col_row[row] = static_cast<int16_t>(x_is_pair ? pair_row : row);
+      gd.col_mul[row] = use_wt ? mc.wt[p] : 1.0f;
+      gd.col_out[row] = static_cast<int16_t>(x_is_pair ? row : pair_row);
+    }
+    for (int s = 0; s < mc.n_shared; ++s) {
+      GroupDesc& gd = sm->groups[n_groups++];
+      gd.w = mc.shared_w + static_cast<size_t>(s) * mc.w_stride;
+      gd.scale = mc.shared_scale + static_cast<size_t>(s) * mc.scale_stride;
+      gd.row_base = s * mc.rows_per_expert;
+      gd.map_id = 1;
+      for (int c = 0; c < kMaxCols; ++c) {
+        const bool live = c < mc.m;
+        const int pair_row = c * slots + mc.top_k + s;
+        gd.col_row[c] = static_cast<int16_t>(live ? (x_is_pair ? pair_row : c) : -1);
+        gd.col_mul[c] = live ? 1.0f : 0.f;
+        gd.col_out[c] = static_cast<int16_t>(x_is_pair ? c : pair_row);
+      }
+    }
+    s_ids[64 + kMaxGroups] = n_groups;
+  }
+  __syncthreads();
+  return s_ids[64 + kMaxGroups];
+}
+
+struct GateParams {
+  CUtensorMap map0, map1;   // weight tensor maps (unused for whole-row stages)
+  StreamShape sh;
+  MoeCommon mc;
+  const uint8_t* x_fp8;
+  const float* x_scale;
+  void* act;
+  int act_kind;
+  void* scratch;
+};
+
+template <class G>
+__global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant__ GateParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ int s_ids[64 + kMaxGroups + 1];
+  StreamShape sh = p.sh;
+  const Carve<G> cv = carve<G>(smem, sh);
+  const StreamScratch scr = scratch_of(p.scratch);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  pdl_launch_dependents();
+  stream_init<G>(sh, cv.sm);
+  pdl_wait();                       // the routes come from the predecessor
+  sh.n_groups = build_groups<G>(cv.sm, p.mc, false, false, scr.status, s_ids);
+  const long long total =
+      static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
+  const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
+  const int cta = blockIdx.x;
+  if (cta < grid) {
+    const long long it0 = item_begin(total, grid, cta), it1 = item_begin(total, grid, cta + 1);
+    if (warp == kConsumerWarps) {
+      produce<G>(sh, cv.sm, cv.ring, it0, it1, scr.status, &p.map0, &p.map1);
+    } else {
+      stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
+      named_bar_sync(1, kConsumerThreads);
+      const int i_loc = p.mc.i_loc, m = p.mc.m;
+      const int act_kind = p.act_kind;
+      void* act = p.act;
+      StreamSmem<G>* sm = cv.sm;
+      auto emit = [&](const ItemCoord& c, int r, int col, const float (&val)[G::RT]) {
+        const GroupDesc& gd = sm->groups[c.group];
+        if (col >= m || gd.col_row[col] < 0) return;
+        // sub-tiles [0, RT/2) are gate rows, [RT/2, RT) the matching up rows
+#pragma unroll
+        for (int sub = 0; sub < G::RT / 2; ++sub) {
+          const float gte = val[sub], up = val[sub + G::RT / 2];
+          const float v = gte / (1.0f + expf(-gte)) * up;
+          const size_t o = static_cast<size_t>(gd.col_out[col]) * i_loc +
+                           c.tile_in_group * (G::ROWS / 2) + sub * 16 + r;
+          if (act_kind == IQ_ACT_E4M3)
+            static_cast<uint8_t*>(act)[o] = f32_to_e4m3_sat(v);
+          else
+            static_cast<__nv_bfloat16*>(act)[o] = __float2bfloat16_rn(v);
+        }
+      };
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, it0, it1, total, grid, cta, scr, emit);
+    }
+  }
+  stream_drain_on_abort<G>(cv.sm);
+}
+
+struct DownParams {
+  CUtensorMap map0, map1;   // weight tensor maps (unused for whole-row stages)
+  StreamShape sh;
+  MoeCommon mc;
+  const void* act;
+  int act_kind;
+  __nv_bfloat16* out;
+  void* scratch;
+  int has_tail;
+  iq_tail_args tail;
+};
+
+template <class G>
+__global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant__ DownParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ int s_ids[64 + kMaxGroups + 1];
+  StreamShape sh = p.sh;
+  const Carve<G> cv = carve<G>(smem, sh);
+  const StreamScratch scr = scratch_of(p.scratch);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  pdl_launch_dependents();
+  stream_init<G>(sh, cv.sm);
+  pdl_wait();
+  sh.n_groups = build_groups<G>(cv.sm, p.mc, true, true, scr.status, s_ids);
+  const long long total =
+      static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
+  const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
+  const int cta = blockIdx.x;
+  if (cta < grid) {
+    const long long it0 = item_begin(total, grid, cta), it1 = item_begin(total, grid, cta + 1);
+    if (warp == kConsumerWarps) {
+      produce<G>(sh, cv.sm, cv.ring, it0, it1, scr.status, &p.map0, &p.map1);
+    } else {
+      const int rows = p.mc.m * (p.mc.top_k + p.mc.n_shared);
+      if (p.act_kind == IQ_ACT_E4M3)
+        stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.act), p.mc.i_loc, nullptr,
+                        rows, p.mc.i_loc, tid);
+      else
+        stage_rows_bf16_groupq(cv.xq, cv.xs, sh, static_cast<const __nv_bfloat16*>(p.act),
+                               p.mc.i_loc, rows, p.mc.i_loc, false, tid);
+      named_bar_sync(1, kConsumerThreads);
+      const int m = p.mc.m, h = p.mc.h;
+      __nv_bfloat16* out = p.out;
+      auto emit = [&](const ItemCoord& c, int r, int col, const float (&val)[G::RT]) {
+        if (col >= m) return;
+#pragma unroll
+        for (int sub = 0; sub < G::RT; ++sub)
+          out[static_cast<size_t>(col) * h + c.tile * G::ROWS + sub * 16 + r] =
+              __float2bfloat16_rn(val[sub]);
+      };
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, it0, it1, total, grid, cta, scr, emit);
+    }
+  }
+  if (!p.has_tail) {
+    stream_drain_on_abort<G>(cv.sm);
+    return;
+  }
+  if (last_cta<G>(cv.sm, scr, gridDim.x)) {
+    float* red = reinterpret_cast<float*>(cv.sm->red);
+    run_tail(p.tail, reinterpret_cast<__nv_bfloat16*>(cv.ring), red, &cv.sm->is_last_tile);
+  }
+  stream_drain_on_abort<G>(cv.sm);
+}
+
+// ------------------------------------------------------------------------------------
+// Host side
+static int g_sm_count = 0;
+static int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    g_sm_count = n;
+  }
+  return g_sm_count;
+}
+
+static int ilog2(int v) {
+  int s = 0;
+  while ((1 << s) < v) ++s;
+  return s;
+}
+
+// One opt-in to the full shared memory per (kernel, device).  Callers are serialised per
+// process by the GIL or by their own stream discipline; the table is append-only.
+static bool ensure_smem_optin(const void* fn) {
+  struct Entry { const void* fn; int dev; };
+  static Entry done[256];
+  static int n_done = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  for (int i = 0; i < n_done; ++i)
+    if (done[i].fn == fn && done[i].dev == dev) return true;
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
+      cudaSuccess)
+    return false;
+  if (n_done < 256) done[n_done++] = Entry{fn, dev};
+  return true;
+}
+
+// Tensor maps of weight matrices viewed as [total_rows, k_bytes / 4] u32, box = (kc / 4)
+// x box_rows, no swizzle.  Encoding costs a driver call, so maps are cached by key; a map
+// holds only the address and geometry, never data.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+struct MapKey {
+  const void* ptr;
+  long long rows;
+  int k_bytes, box_rows, kc;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && k_bytes == o.k_bytes && box_rows == o.box_rows &&
+           kc == o.kc;
+  }
+};
+static std::mutex g_map_mutex;
+static std::vector<std::pair<MapKey, CUtensorMap>> g_maps;
+
+static int weight_map(CUtensorMap* out, const void* ptr, long long rows, int k_bytes, int box_rows,
+                      int kc) {
+  static EncodeTiledFn encode = nullptr;
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  const MapKey key{ptr, rows, k_bytes, box_rows, kc};
+  for (const auto& kv : g_maps)
+    if (kv.first == key) { *out = kv.second; return IQ_OK; }
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) !=
+            cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+      return IQ_ERR_CUDA;
+    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(k_bytes / 4), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t gstr[1] = {static_cast<cuuint64_t>(k_bytes)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kc / 4), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), gdim,
+                            gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "iqb200: cuTensorMapEncodeTiled failed (%d)\n", static_cast<int>(r));
+    return IQ_ERR_CUDA;
+  }
+  if (g_maps.size() >= 4096) g_maps.clear();
+  g_maps.emplace_back(key, m);
+  *out = m;
+  return IQ_OK;
+}
+
+// Fills map0 (and map1 for the shared experts) when the geometry streams K-slices.
+template <class G>
+static int fill_maps(CUtensorMap* map0, CUtensorMap* map1, const StreamShape& sh, const void* w,
+                     long long rows, const void* shared_w, long long shared_rows) {
+  if (sh.k_bytes == G::KC) return IQ_OK;      // whole-row stages: untiled copies
+  const int box_rows = sh.pair_half > 0 ? G::ROWS / 2 : G::ROWS;
+  int rc = weight_map(map0, w, rows, sh.k_bytes, box_rows, G::KC);
+  if (rc != IQ_OK) return rc;
+  if (shared_w) rc = weight_map(map1, shared_w, shared_rows, sh.k_bytes, box_rows, G::KC);
+  return rc;
+}
+
+template <class Kernel, class Params>
+static int launch(Kernel kernel, const Params& p, int grid, size_t smem, void* stream, int pdl) {
+  // One opt-in to the full shared memory per kernel and device (this function is
+  // instantiated per kernel, so the flags are per kernel).
+  if (!ensure_smem_optin(reinterpret_cast<const void*>(kernel))) return IQ_ERR_CUDA;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, p);
+  if (err != cudaSuccess) {
+    fprintf(stderr, "iqb200: launch failed: %s\n", cudaGetErrorString(err));
+    return IQ_ERR_CUDA;
+  }
+  return IQ_OK;
+}
+
+// Fills the geometry-dependent part of a shape and returns the dynamic shared memory to
+// request, or 0 when the ring does not fit.
+template <class G>
+static size_t plan_smem(StreamShape& sh, size_t tail_bytes) {
+  const size_t fixed = smem_fixed_bytes<G>(sh.x_rows, sh.x_blocks, sh.x_pitch);
+  if (fixed + 2 * G::STAGE_BYTES > static_cast<size_t>(kSmemLimit)) return 0;
+  // About 96 KB in flight per SM saturates HBM; a deeper ring measured slower.
+  int stages = static_cast<int>((kSmemLimit - fixed) / G::STAGE_BYTES);
+  const int want = (96 * 1024 + G::STAGE_BYTES - 1) / G::STAGE_BYTES;
+  if (stages > want) stages = want;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (const char* e = getenv("IQB_STAGES")) { const int v = atoi(e); if (v >= 2 && v < stages) stages = v; }
+  sh.n_stages = stages;
+  if (const char* e = getenv("IQB_DEBUG")) sh.debug = atoi(e);
+  size_t need = fixed + static_cast<size_t>(stages) * G::STAGE_BYTES;
+  if (need < fixed + tail_bytes) need = fixed + tail_bytes;
+  return need <= static_cast<size_t>(kSmemLimit) ? need : 0;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int check_tail(const iq_tail_args* t) {
+  if (!t) return IQ_OK;
+  if (t->kind != IQ_TAIL_ATTN && t->kind != IQ_TAIL_MLP) return IQ_ERR_ARG;
+  if (t->m < 1 || t->m > 8 || t->h < 128 || t->h % 128) return IQ_ERR_ARG;
+  if (!t->partial || !t->residual || !t->w_norm || !t->h_out || !t->norm_out) return IQ_ERR_ARG;
+  if (t->kind == IQ_TAIL_ATTN && !t->w_first) return IQ_ERR_ARG;
+  if (t->world < 1 || t->rank < 0 || t->rank >= t->world) return IQ_ERR_ARG;
+  if (t->world > 1) {
+    if (!t->arrive || !t->epoch) return IQ_ERR_ARG;
+    if (!t->arrive_mc && !t->peer_arrive) return IQ_ERR_ARG;
+    if (!t->partial_mc && !t->peer_partials) return IQ_ERR_ARG;
+  }
+  if (!aligned16(t->partial) || !aligned16(t->residual) || !aligned16(t->h_out) ||
+      !aligned16(t->norm_out) || !aligned16(t->w_norm))
+    return IQ_ERR_ARG;
+  return IQ_OK;
+}
+
+template <class G>
+static int linear_launch(const iq_linear_args* a, void* stream) {
+  LinearParams p{};
+  StreamShape& sh = p.sh;
+  const bool split2 = a->x_kind == IQ_X_BF16_SPLIT2;
+  sh.mode = kRowsPerGroup;
+  sh.n_groups = 1;
+  sh.rows_per_group = a->n;
+  sh.k_bytes = a->k;
+  sh.rg_shift = ilog2(a->rg);
+  sh.kg_shift = ilog2(a->kg);
+  sh.pair_half = 0;
+  sh.x_rows = split2 ? 2 * a->m : a->m;
+  sh.x_pitch = a->k + 64;
+  sh.x_blocks = (a->k + 127) / 128;
+  const size_t tail_bytes = a->tail ? static_cast<size_t>(a->tail->m) * a->tail->h * 2 : 0;
+  const size_t smem = plan_smem<G>(sh, tail_bytes);
+  if (smem == 0) return IQ_ERR_UNSUPPORTED;
+  const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->n, nullptr, 0);
+  if (mrc != IQ_OK) return mrc;
+  p.x = a->x;
+  p.x_scale = a->x_scale;
+  p.x_kind = a->x_kind;
+  p.m = a->m;
+  p.k = a->k;
+  p.n = a->n;
+  p.w = static_cast<const uint8_t*>(a->w);
+  p.w_scale = a->w_scale;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.scratch = a->scratch;
+  p.has_tail = a->tail != nullptr;
+  if (a->tail) {
+    p.tail = *a->tail;
+    if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
+  }
+  return launch(linear_kernel<G>, p, sm_count(), smem, stream, a->pdl);
+}
+
+}  // namespace iqb
+
+using namespace iqb;
+
+extern "C" size_t iq_scratch_bytes(void) { return kScrBytes; }
+
+extern "C" int iq_sm_count(void) { return sm_count(); }
+
+extern "C" int iq_status_read(void* scratch, int* code, int clear, void* stream) {
+  if (!scratch || !code) return IQ_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(code, scratch, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return IQ_ERR_CUDA;
+  if (clear && cudaMemsetAsync(scratch, 0, sizeof(int), s) != cudaSuccess) return IQ_ERR_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return IQ_ERR_CUDA;
+  return IQ_OK;
+}
+
+extern "C" int iq_tail(const iq_tail_args* a, void* stream, int pdl) {
+  if (!a) return IQ_ERR_ARG;
+  const int rc = check_tail(a);
+  if (rc != IQ_OK) return rc;
+  if (sm_count() == 0) return IQ_ERR_CUDA;
+  TailParams p{};
+  p.a = *a;
+  const size_t smem = 1024 + static_cast<size_t>(a->m) * a->h * 2;
+  if (smem > static_cast<size_t>(kSmemLimit)) return IQ_ERR_UNSUPPORTED;
+  return launch(tail_kernel, p, 1, smem, stream, pdl);
+}
+
+extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
+  if (!a || !a->x || !a->w || !a->w_scale || !a->out || !a->scratch) return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
+  if (a->x_kind < IQ_X_BF16_GROUPQ || a->x_kind > IQ_X_E4M3_UNSCALED) return IQ_ERR_ARG;
+  if (a->x_kind == IQ_X_E4M3_GROUP && !a->x_scale) return IQ_ERR_ARG;
+  const int max_m = a->x_kind == IQ_X_BF16_SPLIT2 ? 4 : 8;
+  if (a->m < 1 || a->m > max_m) return IQ_ERR_ARG;
+  if (a->k < 64 || a->k % 64 || a->n < 16 || a->n % 16) return IQ_ERR_ARG;
+  if (a->x_kind != IQ_X_E4M3_UNSCALED && a->k % 128) return IQ_ERR_ARG;   // 1x128 groups
+  if ((a->rg != 64 && a->rg != 128) || (a->kg != 64 && a->kg != 128)) return IQ_ERR_ARG;
+  if (!aligned16(a->x) || !aligned16(a->w) || !aligned16(a->out)) return IQ_ERR_ARG;
+  if (a->tail) {
+    const int rc = check_tail(a->tail);
+    if (rc != IQ_OK) return rc;
+    if (a->tail->partial != a->out || a->tail->m != a->m || a->tail->h != a->n) return IQ_ERR_ARG;
+  }
+  if (sm_count() == 0) return IQ_ERR_CUDA;
+  const int k = a->k, n = a->n;
+  if (k % 1024 == 0 && n % 16 == 0) return linear_launch<Geo<1, 8, 2>>(a, stream);
+  if (k % 768 == 0 && n % 32 == 0) return linear_launch<Geo<2, 4, 3>>(a, stream);
+  if (k % 512 == 0 && n % 32 == 0) return linear_launch<Geo<2, 4, 2>>(a, stream);
+  if (k % 256 == 0 && n % 64 == 0) return linear_launch<Geo<4, 2, 2>>(a, stream);
+  if (k % 192 == 0 && n % 128 == 0) return linear_launch<Geo<8, 1, 3>>(a, stream);
+  if (k % 128 == 0 && n % 128 == 0) return linear_launch<Geo<8, 1, 2>>(a, stream);
+  if (k % 64 == 0 && n % 128 == 0) return linear_launch<Geo<8, 1, 1>>(a, stream);
+  return IQ_ERR_UNSUPPORTED;
+}
+
+extern "C" int iq_router(const iq_router_args* a, void* stream) {
+  if (!a || !a->x || !a->w || !a->sel || !a->wt || !a->logits || !a->scratch) return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
+  if (a->m < 1 || a->m > 8 || a->h < 512 || a->h % 512) return IQ_ERR_ARG;
+  if (a->e < 16 || a->e % 16 || a->e > 512 || a->top_k < 1 || a->top_k > 32 || a->top_k > a->e)
+    return IQ_ERR_ARG;
+  if (a->score != IQ_ROUTE_SOFTMAX && a->score != IQ_ROUTE_SIGMOID) return IQ_ERR_ARG;
+  if (!aligned16(a->x) || !aligned16(a->w)) return IQ_ERR_ARG;
+  if (sm_count() == 0) return IQ_ERR_CUDA;
+  using G = Geo<1, 8, 2>;
+  RouterParams p{};
+  StreamShape& sh = p.sh;
+  sh.mode = kRowsPerGroup;
+  sh.n_groups = 1;
+  sh.rows_per_group = a->e;
+  sh.k_bytes = a->h * 2;
+  sh.rg_shift = 7;
+  sh.kg_shift = 7;
+  sh.pair_half = 0;
+  sh.x_rows = a->m;
+  sh.x_pitch = a->h * 2 + 64;
+  sh.x_blocks = 1;
+  const size_t smem = plan_smem<G>(sh, 0);
+  if (smem == 0) return IQ_ERR_UNSUPPORTED;
+  const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->e, nullptr, 0);
+  if (mrc != IQ_OK) return mrc;
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.w = static_cast<const uint8_t*>(a->w);
+  p.m = a->m;
+  p.h = a->h;
+  p.e = a->e;
+  p.top_k = a->top_k;
+  p.score = a->score;
+  p.sel = a->sel;
+  p.wt = a->wt;
+  p.logits = a->logits;
+  p.scratch = a->scratch;
+  return launch(router_kernel<G>, p, sm_count(), smem, stream, a->pdl);
+}
+
+static int fill_moe(MoeCommon& mc, int m, int h, int i_loc, int n_experts, int top_k, int n_shared,
+                    const int* sel, const float* wt) {
+  if (m < 1 || m > 8 || top_k < 1 || m * top_k > 64 || n_shared < 0 || n_shared > 4)
+    return IQ_ERR_ARG;
+  if (m * top_k + n_shared > kMaxGroups) return IQ_ERR_ARG;
+  if (n_experts < 1 || !sel) return IQ_ERR_ARG;
+  mc.m = m;
+  mc.h = h;
+  mc.i_loc = i_loc;
+  mc.n_experts = n_experts;
+  mc.top_k = top_k;
+  mc.n_shared = n_shared;
+  mc.sel = sel;
+  mc.wt = wt;
+  return IQ_OK;
+}
+
+extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
+  if (!a || !a->x_fp8 || !a->fc || !a->fc_scale || !a->act || !a->scratch) return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
+  if (a->n_shared > 0 && (!a->shared_fc || !a->shared_fc_scale)) return IQ_ERR_ARG;
+  if (a->act_kind != IQ_ACT_E4M3 && a->act_kind != IQ_ACT_BF16) return IQ_ERR_ARG;
+  if (a->h < 1024 || a->h % 1024 || a->i_loc < 64 || a->i_loc % 64) return IQ_ERR_ARG;
+  if (!aligned16(a->x_fp8) || !aligned16(a->fc)) return IQ_ERR_ARG;
+  using G = Geo<2, 4, 4>;
+  GateParams p{};
+  int rc = fill_moe(p.mc, a->m, a->h, a->i_loc, a->n_experts, a->top_k, a->n_shared, a->sel,
+                    nullptr);
+  if (rc != IQ_OK) return rc;
+  if (sm_count() == 0) return IQ_ERR_CUDA;
+  p.mc.w = static_cast<const uint8_t*>(a->fc);
+  p.mc.w_scale = a->fc_scale;
+  p.mc.shared_w = static_cast<const uint8_t*>(a->shared_fc);
+  p.mc.shared_scale = a->shared_fc_scale;
+  p.mc.w_stride = static_cast<size_t>(2) * a->i_loc * a->h;
+  p.mc.scale_stride = static_cast<size_t>(2 * a->i_loc / 64) * (a->h / 128);
+  p.mc.rows_per_expert = 2 * a->i_loc;
+  StreamShape& sh = p.sh;
+  sh.mode = kRowsPerGroup;
+  sh.n_groups = 1;                 // set in the kernel from the routes
+  sh.rows_per_group = 2 * a->i_loc;
+  sh.k_bytes = a->h;
+  sh.rg_shift = 6;
+  sh.kg_shift = 7;
+  sh.pair_half = a->i_loc;
+  sh.x_rows = a->m;
+  sh.x_pitch = a->h + 64;
+  sh.x_blocks = a->h / 128;
+  const size_t smem = plan_smem<G>(sh, 0);
+  if (smem == 0) return IQ_ERR_UNSUPPORTED;
+  const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->fc,
+                               static_cast<long long>(a->n_experts) * 2 * a->i_loc, a->shared_fc,
+                               static_cast<long long>(a->n_shared) * 2 * a->i_loc);
+  if (mrc != IQ_OK) return mrc;
+  p.x_fp8 = static_cast<const uint8_t*>(a->x_fp8);
+  p.x_scale = a->x_scale;
+  p.act = a->act;
+  p.act_kind = a->act_kind;
+  p.scratch = a->scratch;
+  return launch(gate_kernel<G>, p, sm_count(), smem, stream, a->pdl);
+}
+
+template <class G>
+static int down_launch(const iq_moe_down_args* a, void* stream) {
+  DownParams p{};
+  int rc = fill_moe(p.mc, a->m, a->h, a->i_loc, a->n_experts, a->top_k, a->n_shared, a->sel, a->wt);
+  if (rc != IQ_OK) return rc;
+  p.mc.w = static_cast<const uint8_t*>(a->proj);
+  p.mc.w_scale = a->proj_scale;
+  p.mc.shared_w = static_cast<const uint8_t*>(a->shared_proj);
+  p.mc.shared_scale = a->shared_proj_scale;
+  p.mc.w_stride = static_cast<size_t>(a->h) * a->i_loc;
+  p.mc.scale_stride = static_cast<size_t>(a->h / 128) * (a->i_loc / 64);
+  p.mc.rows_per_expert = a->h;
+  StreamShape& sh = p.sh;
+  sh.mode = kConcatK;
+  sh.n_groups = 1;
+  sh.rows_per_group = a->h;
+  sh.k_bytes = a->i_loc;
+  sh.rg_shift = 7;
+  sh.kg_shift = 6;
+  sh.pair_half = 0;
+  sh.x_rows = a->m * (a->top_k + a->n_shared);
+  sh.x_pitch = a->i_loc + 64;
+  sh.x_blocks = (a->i_loc + 127) / 128;
+  const size_t tail_bytes = a->tail ? static_cast<size_t>(a->tail->m) * a->tail->h * 2 : 0;
+  const size_t smem = plan_smem<G>(sh, tail_bytes);
+  if (smem == 0) return IQ_ERR_UNSUPPORTED;
+  const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->proj,
+                               static_cast<long long>(a->n_experts) * a->h, a->shared_proj,
+                               static_cast<long long>(a->n_shared) * a->h);
+  if (mrc != IQ_OK) return mrc;
+  p.act = a->act;
+  p.act_kind = a->act_kind;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.scratch = a->scratch;
+  p.has_tail = a->tail != nullptr;
+  if (a->tail) {
+    p.tail = *a->tail;
+    if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
+  }
+  return launch(down_kernel<G>, p, sm_count(), smem, stream, a->pdl);
+}
+
+extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
+  if (!a || !a->act || !a->proj || !a->proj_scale || !a->out || !a->wt || !a->scratch)
+    return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
+  if (a->n_shared > 0 && (!a->shared_proj || !a->shared_proj_scale)) return IQ_ERR_ARG;
+  if (a->act_kind != IQ_ACT_E4M3 && a->act_kind != IQ_ACT_BF16) return IQ_ERR_ARG;
+  if (a->h < 128 || a->h % 128 || a->i_loc < 64 || a->i_loc % 64) return IQ_ERR_ARG;
+  if (a->act_kind == IQ_ACT_BF16 && a->i_loc % 128) return IQ_ERR_ARG;
+  if (!aligned16(a->act) || !aligned16(a->proj) || !aligned16(a->out)) return IQ_ERR_ARG;
+  if (a->tail) {
+    const int rc = check_tail(a->tail);
+    if (rc != IQ_OK) return rc;
+    if (a->tail->partial != a->out || a->tail->m != a->m || a->tail->h != a->h) return IQ_ERR_ARG;
+  }
+  if (sm_count() == 0) return IQ_ERR_CUDA;
+  const int k = a->i_loc;
+  if (k % 1024 == 0) return down_launch<Geo<1, 8, 2>>(a, stream);
+  if (k % 512 == 0) return down_launch<Geo<2, 4, 2>>(a, stream);
+  if (k % 256 == 0) return down_launch<Geo<4, 2, 2>>(a, stream);
+  if (k % 192 == 0) return down_launch<Geo<8, 1, 3>>(a, stream);
+  if (k % 128 == 0) return down_launch<Geo<8, 1, 2>>(a, stream);
+  return IQ_ERR_UNSUPPORTED;
+}

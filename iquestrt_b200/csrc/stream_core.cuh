@@ -1,0 +1,512 @@
+// The weight-streaming engine every kernel of the path is built on.
+//
+// One persistent CTA per SM.  A dedicated producer warp streams e4m3 (or bf16) weight tiles
+// from HBM into a shared-memory ring with TMA, ONE copy per ring stage (16-32 KB): a
+// tiled `cp.async.bulk.tensor.2d` box of (rows x 1 KB) when a stage is a K-slice of its
+// rows, an untiled `cp.async.bulk` when the stage's rows are whole and therefore
+// contiguous.  Completion is counted in bytes on an mbarrier per ring slot.  (Measured on
+// B200: one 16 KB copy per stage with six stages in flight streams at 7.0 TB/s; sixteen
+// 1 KB copies per stage reach 3.9 TB/s.)
+// Eight consumer warps read the ring with 16-byte shared loads and feed warp-level MMAs
+// whose B operand carries the (at most eight) activation rows, so a byte of weight costs
+// 1/512 of an MMA and no conversion instruction.  The K index inside an MMA is permuted
+// so that every lane's A and B fragments are plain 16-byte runs (see `consume_stage`).
+//
+// Work is the list of (tile, k-stage) items in tile-major order; CTA i owns the
+// contiguous item range [i*T/G, (i+1)*T/G) ("stream-K"), so every SM streams the same
+// number of bytes to within one stage whatever the shape.  A tile whose stages fall in
+// more than one CTA is finished by whichever contributor arrives last at the tile's
+// counter: it sums the contributors' fp32 partials from scratch in CTA order, so the
+// result does not depend on arrival order.  Nothing waits on another CTA.
+//
+// After its last tile every CTA takes a ticket; the last one runs the kernel's global
+// epilogue (all-reduce tail, or top-k selection) on the completed rows.
+#pragma once
+
+#include "common.cuh"
+
+namespace iqb {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;   // + the producer warp
+constexpr int kMaxStages = 16;
+constexpr int kMaxGroups = 72;                    // 8 rows x 8 routed + shared, with slack
+constexpr int kMaxCols = 8;                       // MMA N
+constexpr int kSmemLimit = 232448;                // 227 KiB per CTA on sm_100
+
+// Ring geometry: a stage is (16*RT) weight rows x (KW*RUNS*64) bytes; warp (rs, kp) of the
+// RT*KW = 8 consumer warps owns row sub-tile rs and the kp-th slice of RUNS 64-byte runs.
+template <int RT_, int KW_, int RUNS_>
+struct Geo {
+  static constexpr int RT = RT_, KW = KW_, RUNS = RUNS_;
+  static_assert(RT * KW == kConsumerWarps, "eight consumer warps");
+  static constexpr int ROWS = 16 * RT;
+  static constexpr int KC = KW * RUNS * 64;
+  // TMA writes a stage densely: row pitch = KC.  When KC is a multiple of 128 the two
+  // rows a quarter-warp reads share banks (a 2-way conflict on 16-byte loads), which
+  // costs nothing at the ~25 B/clk/SM a weight stream needs.
+  static constexpr int PITCH = KC;
+  static constexpr int STAGE_BYTES = ROWS * PITCH;
+};
+
+// One weight matrix instance ("group"): an expert, the shared expert, or the only matrix.
+struct GroupDesc {
+  const uint8_t* w;        // first byte of the group's [rows, k_bytes] matrix
+  const float* scale;      // its scale table (row-major [rows/rg, k/kg]); unused for bf16
+  int row_base;            // the group's first row inside its tensor map
+  int map_id;              // which of the launch's tensor maps covers the group
+  float col_mul[kMaxCols]; // per MMA column multiplier (routing weight; 1 otherwise)
+  int16_t col_row[kMaxCols];  // staged activation row per MMA column, -1 = column unused
+  int16_t col_out[kMaxCols];  // output row per MMA column
+};
+
+enum TileMode : int {
+  kRowsPerGroup = 0,  // tiles = groups x row-tiles; every tile contracts over one group's K
+  kConcatK = 1,       // tiles = row-tiles; every tile contracts over all groups' K in turn
+};
+
+// Uniform description of one launch's streaming work (same on every CTA).
+struct StreamShape {
+  int mode;
+  int n_groups;
+  int rows_per_group;  // weight rows per group
+  int k_bytes;         // bytes per weight row
+  int rg_shift;        // log2(weight rows per scale entry)
+  int kg_shift;        // log2(weight bytes along K per scale entry)
+  int pair_half;       // >0: a tile takes ROWS/2 rows at f and ROWS/2 rows at pair_half + f
+  int x_rows;          // staged activation rows
+  int x_pitch;         // bytes between staged activation rows in shared memory
+  int x_blocks;        // activation scale entries per staged row (k / 128)
+  int n_stages;        // ring depth
+  int debug;           // experiment switch: 1 = consumers skip the math
+};
+
+// Scratch owned by the caller (zero-filled once; every launch leaves it zeroed again).
+struct StreamScratch {
+  float* partials;        // [grid][2][ROWS*8]
+  uint32_t* tile_counter; // [tiles]
+  uint32_t* ticket;       // [1]
+  int* status;            // [1] first error code of any launch using this scratch
+};
+
+__device__ __forceinline__ void set_status(int* status, int code) {
+  if (status) atomicCAS(status, 0, code);
+}
+
+// Item range of CTA `cta` of `grid` over `total` items.
+__host__ __device__ __forceinline__ long long item_begin(long long total, int grid, int cta) {
+  return total * cta / grid;
+}
+// The CTA that owns item q (inverse of item_begin; needs grid <= total).
+__host__ __device__ __forceinline__ int item_owner(long long total, int grid, long long q) {
+  return static_cast<int>(((q + 1) * grid + total - 1) / total - 1);
+}
+
+template <class G>
+struct StreamSmem {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  int abort_flag;
+  int is_last_tile;   // broadcast: this CTA finishes the current split tile
+  int is_last_cta;    // broadcast: this CTA runs the global epilogue
+  int pad;
+  GroupDesc groups[kMaxGroups];
+  float red[2][kConsumerWarps][32][4];
+};
+
+// Weight row `r` of a tile -> row index inside the group.
+__device__ __forceinline__ int tile_row(const StreamShape& sh, int rows, int tile_in_group, int r) {
+  if (sh.pair_half > 0) {
+    const int half = rows / 2;
+    return r < half ? tile_in_group * half + r : sh.pair_half + tile_in_group * half + (r - half);
+  }
+  return tile_in_group * rows + r;
+}
+
+// Position of one (tile, k-stage) item; `advance` steps to the next item in tile-major
+// order without dividing.
+struct ItemCoord {
+  int tile, group, tile_in_group, kstage;   // kstage: stage index inside the group's K
+  int stage;                                // stage index inside the tile
+};
+
+template <class G>
+struct ItemIter {
+  ItemCoord c;
+  int spt, kstages, tiles_per_group, mode;
+  __device__ __forceinline__ void init(const StreamShape& sh, long long item) {
+    mode = sh.mode;
+    kstages = sh.k_bytes / G::KC;
+    tiles_per_group =
+        sh.pair_half > 0 ? sh.pair_half / (G::ROWS / 2) : sh.rows_per_group / G::ROWS;
+    spt = mode == kRowsPerGroup ? kstages : kstages * sh.n_groups;
+    c.tile = static_cast<int>(item / spt);
+    c.stage = static_cast<int>(item - static_cast<long long>(c.tile) * spt);
+    if (mode == kRowsPerGroup) {
+      c.group = c.tile / tiles_per_group;
+      c.tile_in_group = c.tile - c.group * tiles_per_group;
+      c.kstage = c.stage;
+    } else {
+      c.group = c.stage / kstages;
+      c.tile_in_group = c.tile;
+      c.kstage = c.stage - c.group * kstages;
+    }
+  }
+  __device__ __forceinline__ void advance() {
+    ++c.stage;
+    ++c.kstage;
+    if (c.stage == spt) {
+      c.stage = 0;
+      c.kstage = 0;
+      ++c.tile;
+      if (mode == kRowsPerGroup) {
+        if (++c.tile_in_group == tiles_per_group) { c.tile_in_group = 0; ++c.group; }
+      } else {
+        ++c.tile_in_group;
+        c.group = 0;
+      }
+    } else if (mode != kRowsPerGroup && c.kstage == kstages) {
+      c.kstage = 0;
+      ++c.group;
+    }
+  }
+};
+
+template <class G>
+__host__ __device__ __forceinline__ int stream_num_tiles(const StreamShape& sh) {
+  const int tiles_per_group =
+      sh.pair_half > 0 ? sh.pair_half / (G::ROWS / 2) : sh.rows_per_group / G::ROWS;
+  return sh.mode == kRowsPerGroup ? sh.n_groups * tiles_per_group : tiles_per_group;
+}
+template <class G>
+__host__ __device__ __forceinline__ int stream_stages_per_tile(const StreamShape& sh) {
+  const int kstages = sh.k_bytes / G::KC;
+  return sh.mode == kRowsPerGroup ? kstages : kstages * sh.n_groups;
+}
+
+// ------------------------------------------------------------------------------------
+// Producer: one elected lane of one warp, one or two copies per stage.  `maps[i]` are the
+// launch's tensor maps (u32 elements, box = KC bytes x box rows), used when a stage is a
+// K-slice of its rows; whole-row stages are contiguous and use the untiled copy.
+template <class G>
+__device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm,
+                                        uint8_t* ring, long long it0, long long it1,
+                                        int* status, const CUtensorMap* map0,
+                                        const CUtensorMap* map1) {
+  const int lane = threadIdx.x & 31;
+  int slot = 0;
+  uint32_t phase = 0;
+  ItemIter<G> iter;
+  iter.init(sh, it0);
+  const bool whole_rows = sh.k_bytes == G::KC;
+  const int halves = sh.pair_half > 0 ? 2 : 1;
+  constexpr int kHalfRows = G::ROWS / 2;
+  for (long long it = it0; it < it1; ++it, iter.advance()) {
+    if (sm->abort_flag) return;
+    if (!mbar_wait(&sm->empty[slot], phase ^ 1u)) {
+      set_status(status, IQ_ERR_PIPE_TIMEOUT);
+      sm->abort_flag = 1;
+      return;
+    }
+    if (lane == 0) {
+      const ItemCoord c = iter.c;
+      const GroupDesc& gd = sm->groups[c.group];
+      uint64_t* bar = &sm->full[slot];
+      mbar_arrive_expect_tx(bar, G::ROWS * G::KC);
+      uint8_t* dst = ring + static_cast<size_t>(slot) * G::STAGE_BYTES;
+      const int rows = halves == 2 ? kHalfRows : G::ROWS;
+      for (int hf = 0; hf < halves; ++hf) {
+        const int row = tile_row(sh, G::ROWS, c.tile_in_group, hf * kHalfRows);
+        if (whole_rows) {
+          bulk_g2s(dst + hf * kHalfRows * G::PITCH, gd.w + static_cast<size_t>(row) * sh.k_bytes,
+                   rows * G::KC, bar);
+        } else {
+          tma_2d_g2s(dst + hf * kHalfRows * G::PITCH, gd.map_id ? map1 : map0,
+                     c.kstage * (G::KC / 4), gd.row_base + row, bar);
+        }
+      }
+    }
+    __syncwarp();
+    if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
+  }
+}
+
+// The element type of the streamed matrix decides the MMA; everything else is bytes.
+struct ElemE4M3 {
+  static constexpr bool kScaled = true;
+  __device__ static __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+    mma_e4m3(d, a0, a1, a2, a3, b0, b1);
+  }
+};
+struct ElemBF16 {
+  static constexpr bool kScaled = false;
+  __device__ static __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+    mma_bf16(d, a0, a1, a2, a3, b0, b1);
+  }
+};
+
+// One stage on one consumer warp.  Lane = 4g + t reads bytes [16t, 16t+16) of each 64-byte
+// run of rows g and g+8 of its sub-tile, and the same bytes of activation row col_row[g].
+// MMA k-slot 4t+j (resp. 16+4t+j) of the first MMA is byte 16t+j (resp. 16t+4+j) of the
+// run, of the second MMA byte 16t+8+j (resp. 16t+12+j): A and B use the same permutation
+// of K, which a dot product does not see.
+//
+// `StagePrep` is everything that does not depend on the stage's weights having landed
+// (scales, activation fragments), fetched BEFORE the wait on the stage's barrier.
+template <class G>
+struct StagePrep {
+  float s0[G::RUNS], s1[G::RUNS];   // scales of D columns 2t and 2t+1, per run
+  uint4 xv[G::RUNS];                // B fragments
+};
+
+// The weight scales one warp needs for one stage (one per 64-byte run).  They sit in
+// global memory and a miss costs far more than a stage, so `consume` fetches them
+// kScaleAhead stages early.
+template <class G, class E>
+__device__ __forceinline__ void load_scales(const StreamShape& sh, const StreamSmem<G>* sm,
+                                            const ItemCoord& c, int warp, float (&ws)[G::RUNS]) {
+  if (E::kScaled) {
+    const GroupDesc& gd = sm->groups[c.group];
+    const int rs = warp / G::KW, kp = warp - rs * G::KW;
+    const int kbyte0 = c.kstage * G::KC + kp * (G::RUNS * 64);
+    const int row0 = tile_row(sh, G::ROWS, c.tile_in_group, rs * 16);
+    const float* srow =
+        gd.scale + static_cast<size_t>(row0 >> sh.rg_shift) * (sh.k_bytes >> sh.kg_shift);
+#pragma unroll
+    for (int run = 0; run < G::RUNS; ++run) ws[run] = __ldg(srow + ((kbyte0 + run * 64) >> sh.kg_shift));
+  } else {
+#pragma unroll
+    for (int run = 0; run < G::RUNS; ++run) ws[run] = 1.0f;
+  }
+}
+
+template <class G, class E>
+__device__ __forceinline__ void prep_stage(const StreamShape& sh, const GroupDesc& gd,
+                                           const ItemCoord& c, const uint8_t* xq, const float* xs,
+                                           int warp, int lane, const float (&wsc)[G::RUNS],
+                                           StagePrep<G>& pr) {
+  const int g = lane >> 2, t = lane & 3;
+  const int rs = warp / G::KW, kp = warp - rs * G::KW;
+  const int kbyte0 = c.kstage * G::KC + kp * (G::RUNS * 64);   // offset in the weight row
+  const int xrow = gd.col_row[g];
+  const uint8_t* xb = xq + (xrow < 0 ? 0 : xrow) * sh.x_pitch + kbyte0 + t * 16;
+  const int xr0 = gd.col_row[2 * t], xr1 = gd.col_row[2 * t + 1];
+  const float m0 = xr0 < 0 ? 0.f : gd.col_mul[2 * t];
+  const float m1 = xr1 < 0 ? 0.f : gd.col_mul[2 * t + 1];
+#pragma unroll
+  for (int run = 0; run < G::RUNS; ++run) {
+    pr.xv[run] = make_uint4(0u, 0u, 0u, 0u);
+    if (xrow >= 0) pr.xv[run] = *reinterpret_cast<const uint4*>(xb + run * 64);
+    float s0 = m0, s1 = m1;
+    if (E::kScaled) {
+      const int kb = kbyte0 + run * 64;
+      const float ws = wsc[run];
+      const int xblk = kb >> 7;
+      s0 *= ws * (xr0 < 0 ? 0.f : xs[xr0 * sh.x_blocks + xblk]);
+      s1 *= ws * (xr1 < 0 ? 0.f : xs[xr1 * sh.x_blocks + xblk]);
+    }
+    pr.s0[run] = s0;
+    pr.s1[run] = s1;
+  }
+}
+
+template <class G, class E>
+__device__ __forceinline__ void consume_stage(const uint8_t* stage, int warp, int lane,
+                                              const StagePrep<G>& pr, float (&acc)[4]) {
+  const int g = lane >> 2, t = lane & 3;
+  const int rs = warp / G::KW, kp = warp - rs * G::KW;
+  const uint8_t* a_lo = stage + (rs * 16 + g) * G::PITCH + kp * (G::RUNS * 64) + t * 16;
+  const uint8_t* a_hi = a_lo + 8 * G::PITCH;
+  uint4 wa[G::RUNS], wb[G::RUNS];
+#pragma unroll
+  for (int run = 0; run < G::RUNS; ++run) {
+    wa[run] = *reinterpret_cast<const uint4*>(a_lo + run * 64);
+    wb[run] = *reinterpret_cast<const uint4*>(a_hi + run * 64);
+  }
+#pragma unroll
+  for (int run = 0; run < G::RUNS; ++run) {
+    float part[4] = {0.f, 0.f, 0.f, 0.f};
+    E::mma(part, wa[run].x, wb[run].x, wa[run].y, wb[run].y, pr.xv[run].x, pr.xv[run].y);
+    E::mma(part, wa[run].z, wb[run].z, wa[run].w, wb[run].w, pr.xv[run].z, pr.xv[run].w);
+    acc[0] = fmaf(part[0], pr.s0[run], acc[0]);
+    acc[1] = fmaf(part[1], pr.s1[run], acc[1]);
+    acc[2] = fmaf(part[2], pr.s0[run], acc[2]);
+    acc[3] = fmaf(part[3], pr.s1[run], acc[3]);
+  }
+}
+
+// Consumers: eight warps.  `emit(coord, r, col, val)` receives every finished tile exactly
+// once, on consumer threads 0..127 of the CTA that finishes it: thread r*8 + col gets
+// val[sub] = the sum for weight row 16*sub + r of the tile and MMA column col.
+template <class G, class E, class Emit>
+__device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm,
+                                        const uint8_t* ring, const uint8_t* xq, const float* xs,
+                                        long long it0, long long it1, long long total, int grid,
+                                        int cta, const StreamScratch& scr, Emit emit) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int slot = 0;
+  uint32_t phase = 0;
+  int red_buf = 0;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  ItemIter<G> iter;
+  iter.init(sh, it0);
+  const int spt = iter.spt;
+  constexpr int kScaleAhead = 3;
+  float wsp[kScaleAhead][G::RUNS];
+  ItemIter<G> ahead = iter;
+  long long ahead_it = it0;
+#pragma unroll
+  for (int d = 0; d < kScaleAhead; ++d) {
+#pragma unroll
+    for (int run = 0; run < G::RUNS; ++run) wsp[d][run] = 0.f;
+    if (ahead_it < it1) {
+      load_scales<G, E>(sh, sm, ahead.c, warp, wsp[d]);
+      ahead.advance();
+      ++ahead_it;
+    }
+  }
+  for (long long it = it0; it < it1; ++it, iter.advance()) {
+    const ItemCoord c = iter.c;
+    const GroupDesc& gd = sm->groups[c.group];
+    float wsc[G::RUNS];
+#pragma unroll
+    for (int run = 0; run < G::RUNS; ++run) {
+      wsc[run] = wsp[0][run];
+#pragma unroll
+      for (int d = 0; d + 1 < kScaleAhead; ++d) wsp[d][run] = wsp[d + 1][run];
+    }
+    if (ahead_it < it1) {
+      load_scales<G, E>(sh, sm, ahead.c, warp, wsp[kScaleAhead - 1]);
+      ahead.advance();
+      ++ahead_it;
+    }
+    StagePrep<G> pr;
+    prep_stage<G, E>(sh, gd, c, xq, xs, warp, lane, wsc, pr);
+    bool ok = !sm->abort_flag;
+    if (ok && !mbar_wait(&sm->full[slot], phase)) {
+      set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+      sm->abort_flag = 1;
+      ok = false;
+    }
+    if (ok && !(sh.debug & 1))
+      consume_stage<G, E>(ring + static_cast<size_t>(slot) * G::STAGE_BYTES, warp, lane, pr, acc);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm->empty[slot]);
+    if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
+
+    const long long tile_first = it - c.stage;
+    const bool tile_ends = (c.stage + 1 == spt);
+    if (!tile_ends && it + 1 != it1) continue;
+
+    // ---- the CTA's share of tile c.tile is complete: fold the K-split warps.
+    float(*red)[32][4] = sm->red[red_buf];
+    red_buf ^= 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { red[warp][lane][i] = acc[i]; acc[i] = 0.f; }
+    named_bar_sync(1, kConsumerThreads);
+    const bool whole = (it0 <= tile_first) && (it1 >= tile_first + spt);
+    const int r = tid >> 3, col = tid & 7;      // threads 0..127 own (row r, column col)
+    float val[G::RT];
+    if (tid < 128) {
+      const int fl = 4 * (r & 7) + (col >> 1), fi = (r >> 3) * 2 + (col & 1);
+#pragma unroll
+      for (int sub = 0; sub < G::RT; ++sub) {
+        float v = 0.f;
+#pragma unroll
+        for (int kp = 0; kp < G::KW; ++kp) v += red[sub * G::KW + kp][fl][fi];
+        val[sub] = v;
+      }
+    }
+    if (whole) {
+      if (tid < 128) emit(c, r, col, val);
+      continue;
+    }
+    // ---- split tile: publish the partial; the last contributor to arrive sums them all.
+    const int first_tile = static_cast<int>(it0 / spt);
+    const int pslot = (c.tile == first_tile) ? 0 : 1;
+    float* mine = scr.partials + (static_cast<size_t>(cta) * 2 + pslot) * (G::ROWS * 8);
+    if (tid < 128) {
+#pragma unroll
+      for (int sub = 0; sub < G::RT; ++sub) mine[sub * 128 + tid] = val[sub];
+      __threadfence();
+    }
+    named_bar_sync(1, kConsumerThreads);
+    const int c_first = item_owner(total, grid, tile_first);
+    const int c_last = item_owner(total, grid, tile_first + spt - 1);
+    if (tid == 0) {
+      const uint32_t prev = atomicAdd(scr.tile_counter + c.tile, 1u);
+      const int last = (prev == static_cast<uint32_t>(c_last - c_first));
+      if (last) {
+        scr.tile_counter[c.tile] = 0;     // leave the scratch ready for the next launch
+        __threadfence();
+      }
+      sm->is_last_tile = last;
+    }
+    named_bar_sync(1, kConsumerThreads);
+    if (sm->is_last_tile && tid < 128) {
+      float tot[G::RT];
+#pragma unroll
+      for (int sub = 0; sub < G::RT; ++sub) tot[sub] = 0.f;
+      for (int cc = c_first; cc <= c_last; ++cc) {
+        const int ft = static_cast<int>(item_begin(total, grid, cc) / spt);
+        const float* p =
+            scr.partials + (static_cast<size_t>(cc) * 2 + (c.tile == ft ? 0 : 1)) * (G::ROWS * 8);
+#pragma unroll
+        for (int sub = 0; sub < G::RT; ++sub) tot[sub] += __ldcg(p + sub * 128 + tid);
+      }
+      emit(c, r, col, tot);
+    }
+    named_bar_sync(1, kConsumerThreads);
+  }
+}
+
+// After the CTA's last emit: returns true on the one CTA that arrives last, on every one of
+// its threads, with all other CTAs' global writes visible.  Call from all kThreads threads.
+template <class G>
+__device__ __forceinline__ bool last_cta(StreamSmem<G>* sm, const StreamScratch& scr, int grid) {
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(scr.ticket, 1u);
+    const int last = (prev == static_cast<uint32_t>(grid - 1));
+    if (last) {
+      *scr.ticket = 0;
+      __threadfence();
+    }
+    sm->is_last_cta = last;
+  }
+  __syncthreads();
+  return sm->is_last_cta != 0;
+}
+
+// Barrier set-up; call once from all threads before any produce/consume.
+template <class G>
+__device__ __forceinline__ void stream_init(const StreamShape& sh, StreamSmem<G>* sm) {
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < sh.n_stages; ++s) {
+      mbar_init(&sm->full[s], 1);
+      mbar_init(&sm->empty[s], kConsumerWarps);
+    }
+    sm->abort_flag = 0;
+    sm->is_last_tile = 0;
+    sm->is_last_cta = 0;
+    mbar_fence_init();
+  }
+}
+
+// The producer's copies target this CTA's shared memory: before the CTA may exit every
+// issued copy must have landed.  Consumers wait on every full barrier they consume, so on
+// the normal path nothing is in flight here; on the abort path give stragglers a bounded
+// grace period.
+template <class G>
+__device__ __forceinline__ void stream_drain_on_abort(StreamSmem<G>* sm) {
+  if (sm->abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) { }
+  }
+}
+
+}  // namespace iqb

@@ -1,0 +1,149 @@
+"""Seeded synthetic weights and activations of the decode layer, at any TP degree.
+
+There is no checkpoint, so every weight is random-init with the distributions of the
+benchmark configurations: e4m3 weights from N(0,1) clamped to +-448, fp32 scales
+log-uniform in [2^-12, 2^-6] per 128x128 block of the GLOBAL matrix, then sharded the
+way the reference shards its checkpoint (row-parallel o_proj and expert proj on the
+contraction dim, expert fc on its rows, router replicated; rank-local expert scale tables
+at grain 64 -- iquestrt/weights.py:358-439, iquestrt/blockfp8.py:24-36).  Every rank of
+a TP group derives its shard from the same global tensors, so TP=1/2/4/8 see the same
+problem."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+E4M3 = torch.float8_e4m3fn
+BLOCK = 128
+EXPERT_GRAIN = 64
+
+
+@dataclass(frozen=True)
+class LayerShape:
+    hidden: int = 6144
+    q_dim: int = 8192          # o_proj contraction (q heads x head_dim), sharded over TP
+    n_experts: int = 256
+    top_k: int = 8
+    inter: int = 2048          # expert intermediate, sharded over TP
+    n_shared: int = 1
+    eps: float = 1e-6
+
+    def local(self, tp: int):
+        if self.q_dim % (tp * BLOCK) or self.inter % (tp * EXPERT_GRAIN):
+            raise ValueError(f"TP={tp} does not tile q_dim={self.q_dim} / inter={self.inter}")
+        return self.q_dim // tp, self.inter // tp
+
+
+BASELINE = LayerShape()
+# The reference model's own dimensions (iquestrt/engine.py:291-295,
+# iquestrt/kernels/sm100_moe_fp8.py:11): no shared expert.
+REFERENCE_Q1 = LayerShape(hidden=3072, q_dim=6144, n_experts=256, top_k=8, inter=1536,
+                          n_shared=0)
+
+
+def _gen(device, *seed):
+    g = torch.Generator(device=device)
+    s = 0x9E3779B97F4A7C15
+    for v in seed:
+        s = (s * 6364136223846793005 + int(v) + 1442695040888963407) % (1 << 63)
+    g.manual_seed(s)
+    return g
+
+
+def fp8_weight(rows, cols, gen, device):
+    """e4m3 [rows, cols] from N(0,1) clamped to +-448."""
+    w = torch.randn(rows, cols, generator=gen, device=device, dtype=torch.float32)
+    return w.clamp_(-448.0, 448.0).to(E4M3)
+
+
+def block_scales(rows, cols, gen, device):
+    """fp32 [rows/128, cols/128], log-uniform in [2^-12, 2^-6]."""
+    u = torch.rand(rows // BLOCK, cols // BLOCK, generator=gen, device=device,
+                   dtype=torch.float32)
+    return torch.exp2(-12.0 + 6.0 * u)
+
+
+def shard_scale(scale, dim, start, length, grain):
+    """Scale table of a weight slice at `grain` (iquestrt/blockfp8.py:24-36)."""
+    if BLOCK % grain or start % grain or length % grain:
+        raise ValueError(f"grain {grain} does not tile slice [{start}, {start + length})")
+    blocks = (start + torch.arange(0, length, grain, device=scale.device)) // BLOCK
+    return scale.index_select(dim, blocks)
+
+
+def _expert_shard(shape: LayerShape, tp, rank, device, *seed):
+    """One expert's rank-local ([gate;up] fc, fc_scale, proj, proj_scale)."""
+    h, i = shape.hidden, shape.inter
+    il = i // tp
+    g = _gen(device, *seed)
+    gate_up = fp8_weight(2 * i, h, g, device)
+    gu_scale = block_scales(2 * i, h, g, device)
+    down = fp8_weight(h, i, g, device)
+    d_scale = block_scales(h, i, g, device)
+    r0 = rank * il
+    fc = torch.cat([gate_up[r0:r0 + il], gate_up[i + r0:i + r0 + il]], 0).contiguous()
+    fc_scale = torch.cat([shard_scale(gu_scale, 0, r0, il, EXPERT_GRAIN),
+                          shard_scale(gu_scale, 0, i + r0, il, EXPERT_GRAIN)], 0).contiguous()
+    proj = down[:, r0:r0 + il].contiguous()
+    proj_scale = shard_scale(d_scale, 1, r0, il, EXPERT_GRAIN).contiguous()
+    return fc, fc_scale, proj, proj_scale
+
+
+def make_layer(shape: LayerShape, *, tp=1, rank=0, device="cuda", seed=0, layer=0):
+    """Rank-local weights of one decode layer as a dict of tensors on `device`."""
+    h = shape.hidden
+    ql, il = shape.local(tp)
+    out = {}
+    g = _gen(device, seed, layer, 1)
+    o_full = fp8_weight(h, shape.q_dim, g, device)
+    o_scale = block_scales(h, shape.q_dim, g, device)
+    out["o_proj"] = o_full[:, rank * ql:(rank + 1) * ql].contiguous()
+    out["o_scale"] = shard_scale(o_scale, 1, rank * ql, ql, BLOCK).contiguous()
+    del o_full
+    for name in ("attn_out_norm", "feed_forward_norm", "next_attention_norm"):
+        out[name] = 0.5 + torch.rand(h, generator=g, device=device, dtype=torch.float32)
+    router = torch.randn(shape.n_experts, h, generator=g, device=device,
+                         dtype=torch.float32) * 0.02
+    out["router"] = router.to(torch.bfloat16)
+    e = shape.n_experts
+    fc = torch.empty(e, 2 * il, h, dtype=E4M3, device=device)
+    fc_scale = torch.empty(e, 2 * il // EXPERT_GRAIN, h // BLOCK, dtype=torch.float32,
+                           device=device)
+    proj = torch.empty(e, h, il, dtype=E4M3, device=device)
+    proj_scale = torch.empty(e, h // BLOCK, il // EXPERT_GRAIN, dtype=torch.float32,
+                             device=device)
+    for x in range(e):
+        fc[x], fc_scale[x], proj[x], proj_scale[x] = _expert_shard(
+            shape, tp, rank, device, seed, layer, 2, x)
+    out.update(fc=fc, fc_scale=fc_scale, proj=proj, proj_scale=proj_scale)
+    if shape.n_shared:
+        parts = [_expert_shard(shape, tp, rank, device, seed, layer, 3, s)
+                 for s in range(shape.n_shared)]
+        out["shared_fc"] = torch.stack([p[0] for p in parts]).contiguous()
+        out["shared_fc_scale"] = torch.stack([p[1] for p in parts]).contiguous()
+        out["shared_proj"] = torch.stack([p[2] for p in parts]).contiguous()
+        out["shared_proj_scale"] = torch.stack([p[3] for p in parts]).contiguous()
+    return out
+
+
+def make_step_inputs(shape: LayerShape, m, *, tp=1, rank=0, device="cuda", seed=0, step=0):
+    """Activations of one decode step: the attention output `ao [m, q_dim/tp]` (this rank's
+    head slice of a global N(0,1) tensor) and the residual `[m, hidden]`, both bf16."""
+    ql, _ = shape.local(tp)
+    g = _gen(device, seed, 1000 + step)
+    ao = torch.randn(m, shape.q_dim, generator=g, device=device, dtype=torch.float32)
+    res = torch.randn(m, shape.hidden, generator=g, device=device, dtype=torch.float32)
+    return (ao[:, rank * ql:(rank + 1) * ql].to(torch.bfloat16).contiguous(),
+            res.to(torch.bfloat16))
+
+
+def make_linear_case(n, k, m, *, device="cuda", seed=0):
+    """Benchmark configuration 0: bf16 activation ~N(0,1) `[m,k]`, e4m3 weight `[n,k]`,
+    fp32 128x128 block scales."""
+    g = _gen(device, seed, 7)
+    x = torch.randn(m, k, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    w = fp8_weight(n, k, g, device)
+    s = block_scales(n, k, g, device)
+    return x, w, s
