@@ -25,8 +25,7 @@ constexpr size_t kScrCounters = 256;
 constexpr int kMaxTiles = 16384;
 constexpr size_t kScrPartials = kScrCounters + sizeof(uint32_t) * kMaxTiles;
 constexpr int kMaxGrid = 256;
-constexpr size_t kScrDebug = kScrPartials + sizeof(float) * kMaxGrid * 2 * 128 * 8;
-constexpr size_t kScrBytes = kScrDebug + sizeof(uint64_t) * kMaxGrid * 8;   // + timestamps (debug)
+constexpr size_t kScrBytes = kScrPartials + sizeof(float) * kMaxGrid * 2 * 128 * 8;   // + timestamps (debug)
 
 __host__ __device__ inline StreamScratch scratch_of(void* base) {
   StreamScratch s;
@@ -44,15 +43,17 @@ __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a -
 template <class G>
 struct Carve {
   StreamSmem<G>* sm;
+  float* sc;      // gathered weight scales [max_items][SCALES_PER_STAGE]
   float* xs;
   uint8_t* xq;
   uint8_t* ring;
 };
 template <class G>
-__host__ __device__ inline size_t smem_fixed_bytes(int x_rows, int x_blocks, int x_pitch) {
+__host__ __device__ inline size_t smem_fixed_bytes(const StreamShape& sh) {
   size_t off = align_up(sizeof(StreamSmem<G>), 16);
-  off += align_up(sizeof(float) * x_rows * x_blocks, 16);
-  off += static_cast<size_t>(x_rows) * x_pitch;
+  off += align_up(sizeof(float) * sh.max_items * G::SCALES_PER_STAGE, 16);
+  off += align_up(sizeof(float) * sh.x_rows * sh.x_blocks, 16);
+  off += static_cast<size_t>(sh.x_rows) * sh.x_pitch;
   return align_up(off, 128);
 }
 template <class G>
@@ -60,10 +61,12 @@ __device__ inline Carve<G> carve(uint8_t* base, const StreamShape& sh) {
   Carve<G> c;
   c.sm = reinterpret_cast<StreamSmem<G>*>(base);
   size_t off = align_up(sizeof(StreamSmem<G>), 16);
+  c.sc = reinterpret_cast<float*>(base + off);
+  off += align_up(sizeof(float) * sh.max_items * G::SCALES_PER_STAGE, 16);
   c.xs = reinterpret_cast<float*>(base + off);
   off += align_up(sizeof(float) * sh.x_rows * sh.x_blocks, 16);
   c.xq = base + off;
-  c.ring = base + smem_fixed_bytes<G>(sh.x_rows, sh.x_blocks, sh.x_pitch);
+  c.ring = base + smem_fixed_bytes<G>(sh);
   return c;
 }
 
@@ -444,9 +447,6 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
   const int cta = blockIdx.x;
-  uint64_t* dbg = (sh.debug & 4)
-      ? reinterpret_cast<uint64_t*>(static_cast<uint8_t*>(p.scratch) + kScrDebug) + cta * 8 : nullptr;
-  if (dbg && tid == 0) dbg[0] = globaltimer_ns();
   pdl_launch_dependents();
   stream_init<G>(sh, cv.sm);
   if (tid == 0) {
@@ -463,16 +463,14 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
   }
   __syncthreads();
   if (cta < grid) {
-    const long long it0 = item_begin(total, grid, cta), it1 = item_begin(total, grid, cta + 1);
+    const CtaWork wk = cta_work<G>(sh, item_begin(total, grid, cta), item_begin(total, grid, cta + 1));
     if (warp == kConsumerWarps) {
       // Weights never change: start streaming before the predecessor kernel has finished.
-      if (dbg && tid == kConsumerThreads) dbg[4] = globaltimer_ns();
-      produce<G>(sh, cv.sm, cv.ring, it0, it1, scr.status, &p.map0, &p.map1);
-      if (dbg && tid == kConsumerThreads) dbg[5] = globaltimer_ns();
+      produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
       pdl_wait();
     } else {
+      gather_scales<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid);   // weights: before the wait
       pdl_wait();
-      if (dbg && tid == 0) dbg[1] = globaltimer_ns();
       if (p.x_kind == IQ_X_BF16_GROUPQ || p.x_kind == IQ_X_BF16_SPLIT2)
         stage_rows_bf16_groupq(cv.xq, cv.xs, sh, static_cast<const __nv_bfloat16*>(p.x), p.k, p.m,
                                p.k, p.x_kind == IQ_X_BF16_SPLIT2, tid);
@@ -480,14 +478,13 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
         stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.x), p.k,
                         p.x_kind == IQ_X_E4M3_GROUP ? p.x_scale : nullptr, p.m, p.k, tid);
       named_bar_sync(1, kConsumerThreads);
-      if (dbg && tid == 0) dbg[2] = globaltimer_ns();
       const bool split2 = p.x_kind == IQ_X_BF16_SPLIT2;
       const int m = p.m, n = p.n;
       __nv_bfloat16* out = p.out;
-      auto emit = [&](const ItemCoord& c, int r, int col, const float (&val)[G::RT]) {
+      auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
 #pragma unroll
         for (int sub = 0; sub < G::RT; ++sub) {
-          const int row = c.tile_in_group * G::ROWS + sub * 16 + r;
+          const int row = id.tig * G::ROWS + sub * 16 + r;
           if (split2) {
             // columns 2j and 2j+1 are the two terms of row j: fold them on the even lane
             const float other = __shfl_xor_sync(0xffffffffu, val[sub], 1);
@@ -498,8 +495,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
           }
         }
       };
-      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, it0, it1, total, grid, cta, scr, emit);
-      if (dbg && tid == 0) dbg[3] = globaltimer_ns();
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, total, grid, cta, scr, emit);
     }
   } else {
     pdl_wait();
@@ -616,9 +612,9 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
   }
   __syncthreads();
   if (cta < grid) {
-    const long long it0 = item_begin(total, grid, cta), it1 = item_begin(total, grid, cta + 1);
+    const CtaWork wk = cta_work<G>(sh, item_begin(total, grid, cta), item_begin(total, grid, cta + 1));
     if (warp == kConsumerWarps) {
-      produce<G>(sh, cv.sm, cv.ring, it0, it1, scr.status, &p.map0, &p.map1);
+      produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
       pdl_wait();
     } else {
       pdl_wait();
@@ -631,13 +627,13 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
       named_bar_sync(1, kConsumerThreads);
       const int m = p.m, e = p.e;
       float* logits = p.logits;
-      auto emit = [&](const ItemCoord& c, int r, int col, const float (&val)[G::RT]) {
+      auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
 #pragma unroll
         for (int sub = 0; sub < G::RT; ++sub)
           if (col < m)
-            logits[static_cast<size_t>(col) * e + c.tile_in_group * G::ROWS + sub * 16 + r] = val[sub];
+            logits[static_cast<size_t>(col) * e + id.tig * G::ROWS + sub * 16 + r] = val[sub];
       };
-      consume<G, ElemBF16>(sh, cv.sm, cv.ring, cv.xq, cv.xs, it0, it1, total, grid, cta, scr, emit);
+      consume<G, ElemBF16>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, total, grid, cta, scr, emit);
     }
   } else {
     pdl_wait();
@@ -744,7 +740,6 @@ struct GateParams {
 template <class G>
 __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant__ GateParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ int s_ids[64 + kMaxGroups + 1];
   StreamShape sh = p.sh;
   const Carve<G> cv = carve<G>(smem, sh);
   const StreamScratch scr = scratch_of(p.scratch);
@@ -752,24 +747,25 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
   pdl_launch_dependents();
   stream_init<G>(sh, cv.sm);
   pdl_wait();                       // the routes come from the predecessor
-  sh.n_groups = build_groups<G>(cv.sm, p.mc, false, false, scr.status, s_ids);
+  sh.n_groups = build_groups<G>(cv.sm, p.mc, false, false, scr.status, cv.sm->route_ids);
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
   const int cta = blockIdx.x;
   if (cta < grid) {
-    const long long it0 = item_begin(total, grid, cta), it1 = item_begin(total, grid, cta + 1);
+    const CtaWork wk = cta_work<G>(sh, item_begin(total, grid, cta), item_begin(total, grid, cta + 1));
     if (warp == kConsumerWarps) {
-      produce<G>(sh, cv.sm, cv.ring, it0, it1, scr.status, &p.map0, &p.map1);
+      produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
     } else {
+      gather_scales<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid);
       stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
       named_bar_sync(1, kConsumerThreads);
       const int i_loc = p.mc.i_loc, m = p.mc.m;
       const int act_kind = p.act_kind;
       void* act = p.act;
       StreamSmem<G>* sm = cv.sm;
-      auto emit = [&](const ItemCoord& c, int r, int col, const float (&val)[G::RT]) {
-        const GroupDesc& gd = sm->groups[c.group];
+      auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
+        const GroupDesc& gd = sm->groups[id.group];
         if (col >= m || gd.col_row[col] < 0) return;
         // sub-tiles [0, RT/2) are gate rows, [RT/2, RT) the matching up rows
 #pragma unroll
@@ -777,14 +773,14 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
           const float gte = val[sub], up = val[sub + G::RT / 2];
           const float v = gte / (1.0f + expf(-gte)) * up;
           const size_t o = static_cast<size_t>(gd.col_out[col]) * i_loc +
-                           c.tile_in_group * (G::ROWS / 2) + sub * 16 + r;
+                           id.tig * (G::ROWS / 2) + sub * 16 + r;
           if (act_kind == IQ_ACT_E4M3)
             static_cast<uint8_t*>(act)[o] = f32_to_e4m3_sat(v);
           else
             static_cast<__nv_bfloat16*>(act)[o] = __float2bfloat16_rn(v);
         }
       };
-      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, it0, it1, total, grid, cta, scr, emit);
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, total, grid, cta, scr, emit);
     }
   }
   stream_drain_on_abort<G>(cv.sm);
@@ -805,7 +801,6 @@ struct DownParams {
 template <class G>
 __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant__ DownParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ int s_ids[64 + kMaxGroups + 1];
   StreamShape sh = p.sh;
   const Carve<G> cv = carve<G>(smem, sh);
   const StreamScratch scr = scratch_of(p.scratch);
@@ -813,16 +808,17 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
   pdl_launch_dependents();
   stream_init<G>(sh, cv.sm);
   pdl_wait();
-  sh.n_groups = build_groups<G>(cv.sm, p.mc, true, true, scr.status, s_ids);
+  sh.n_groups = build_groups<G>(cv.sm, p.mc, true, true, scr.status, cv.sm->route_ids);
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
   const int cta = blockIdx.x;
   if (cta < grid) {
-    const long long it0 = item_begin(total, grid, cta), it1 = item_begin(total, grid, cta + 1);
+    const CtaWork wk = cta_work<G>(sh, item_begin(total, grid, cta), item_begin(total, grid, cta + 1));
     if (warp == kConsumerWarps) {
-      produce<G>(sh, cv.sm, cv.ring, it0, it1, scr.status, &p.map0, &p.map1);
+      produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
     } else {
+      gather_scales<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid);
       const int rows = p.mc.m * (p.mc.top_k + p.mc.n_shared);
       if (p.act_kind == IQ_ACT_E4M3)
         stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.act), p.mc.i_loc, nullptr,
@@ -833,14 +829,14 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
       named_bar_sync(1, kConsumerThreads);
       const int m = p.mc.m, h = p.mc.h;
       __nv_bfloat16* out = p.out;
-      auto emit = [&](const ItemCoord& c, int r, int col, const float (&val)[G::RT]) {
+      auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
         if (col >= m) return;
 #pragma unroll
         for (int sub = 0; sub < G::RT; ++sub)
-          out[static_cast<size_t>(col) * h + c.tile * G::ROWS + sub * 16 + r] =
+          out[static_cast<size_t>(col) * h + id.tile * G::ROWS + sub * 16 + r] =
               __float2bfloat16_rn(val[sub]);
       };
-      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, it0, it1, total, grid, cta, scr, emit);
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, total, grid, cta, scr, emit);
     }
   }
   if (!p.has_tail) {
@@ -947,11 +943,11 @@ static int weight_map(CUtensorMap* out, const void* ptr, long long rows, int k_b
 template <class G>
 static int fill_maps(CUtensorMap* map0, CUtensorMap* map1, const StreamShape& sh, const void* w,
                      long long rows, const void* shared_w, long long shared_rows) {
-  if (sh.k_bytes == G::KC) return IQ_OK;      // whole-row stages: untiled copies
+  if (sh.k_bytes == G::KC && G::NBOX == 1) return IQ_OK;      // whole-row stages: untiled copies
   const int box_rows = sh.pair_half > 0 ? G::ROWS / 2 : G::ROWS;
-  int rc = weight_map(map0, w, rows, sh.k_bytes, box_rows, G::KC);
+  int rc = weight_map(map0, w, rows, sh.k_bytes, box_rows, G::BOXK);
   if (rc != IQ_OK) return rc;
-  if (shared_w) rc = weight_map(map1, shared_w, shared_rows, sh.k_bytes, box_rows, G::KC);
+  if (shared_w) rc = weight_map(map1, shared_w, shared_rows, sh.k_bytes, box_rows, G::BOXK);
   return rc;
 }
 
@@ -980,9 +976,19 @@ static int launch(Kernel kernel, const Params& p, int grid, size_t smem, void* s
 
 // Fills the geometry-dependent part of a shape and returns the dynamic shared memory to
 // request, or 0 when the ring does not fit.
+// `max_groups` bounds the group count a kernel may derive from the routes.
 template <class G>
-static size_t plan_smem(StreamShape& sh, size_t tail_bytes) {
-  const size_t fixed = smem_fixed_bytes<G>(sh.x_rows, sh.x_blocks, sh.x_pitch);
+static size_t plan_smem(StreamShape& sh, size_t tail_bytes, int max_groups = 1) {
+  {
+    StreamShape worst = sh;
+    worst.n_groups = max_groups;
+    const long long total_max =
+        static_cast<long long>(stream_num_tiles<G>(worst)) * stream_stages_per_tile<G>(worst);
+    if (stream_num_tiles<G>(worst) > kMaxTiles) return 0;
+    const int grid = sm_count() > 0 ? sm_count() : 1;
+    sh.max_items = static_cast<int>((total_max + grid - 1) / grid) + 1;
+  }
+  const size_t fixed = smem_fixed_bytes<G>(sh);
   if (fixed + 2 * G::STAGE_BYTES > static_cast<size_t>(kSmemLimit)) return 0;
   // About 96 KB in flight per SM saturates HBM; a deeper ring measured slower.
   int stages = static_cast<int>((kSmemLimit - fixed) / G::STAGE_BYTES);
@@ -1103,6 +1109,7 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   }
   if (sm_count() == 0) return IQ_ERR_CUDA;
   const int k = a->k, n = a->n;
+  if (k % 2048 == 0 && n % 16 == 0 && !getenv("IQB_SMALLSTAGE")) return linear_launch<Geo<1, 8, 4>>(a, stream);
   if (k % 1024 == 0 && n % 16 == 0) return linear_launch<Geo<1, 8, 2>>(a, stream);
   if (k % 768 == 0 && n % 32 == 0) return linear_launch<Geo<2, 4, 3>>(a, stream);
   if (k % 512 == 0 && n % 32 == 0) return linear_launch<Geo<2, 4, 2>>(a, stream);
@@ -1201,7 +1208,7 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   sh.x_rows = a->m;
   sh.x_pitch = a->h + 64;
   sh.x_blocks = a->h / 128;
-  const size_t smem = plan_smem<G>(sh, 0);
+  const size_t smem = plan_smem<G>(sh, 0, a->m * a->top_k + a->n_shared);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->fc,
                                static_cast<long long>(a->n_experts) * 2 * a->i_loc, a->shared_fc,
@@ -1239,7 +1246,7 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   sh.x_pitch = a->i_loc + 64;
   sh.x_blocks = (a->i_loc + 127) / 128;
   const size_t tail_bytes = a->tail ? static_cast<size_t>(a->tail->m) * a->tail->h * 2 : 0;
-  const size_t smem = plan_smem<G>(sh, tail_bytes);
+  const size_t smem = plan_smem<G>(sh, tail_bytes, a->m * a->top_k + a->n_shared);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->proj,
                                static_cast<long long>(a->n_experts) * a->h, a->shared_proj,
@@ -1273,6 +1280,7 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   }
   if (sm_count() == 0) return IQ_ERR_CUDA;
   const int k = a->i_loc;
+  if (k % 2048 == 0) return down_launch<Geo<1, 8, 4>>(a, stream);
   if (k % 1024 == 0) return down_launch<Geo<1, 8, 2>>(a, stream);
   if (k % 512 == 0) return down_launch<Geo<2, 4, 2>>(a, stream);
   if (k % 256 == 0) return down_launch<Geo<4, 2, 2>>(a, stream);

@@ -19,6 +19,11 @@
 // counter: it sums the contributors' fp32 partials from scratch in CTA order, so the
 // result does not depend on arrival order.  Nothing waits on another CTA.
 //
+// The per-stage consumer path is kept to a few dozen instructions: everything that
+// depends only on the tile or the weight group is hoisted out of the stage loop, and the
+// weight scales of all the CTA's stages are gathered into shared memory once, before the
+// first stage is consumed.
+//
 // After its last tile every CTA takes a ticket; the last one runs the kernel's global
 // epilogue (all-reduce tail, or top-k selection) on the completed rows.
 #pragma once
@@ -43,11 +48,18 @@ struct Geo {
   static_assert(RT * KW == kConsumerWarps, "eight consumer warps");
   static constexpr int ROWS = 16 * RT;
   static constexpr int KC = KW * RUNS * 64;
-  // TMA writes a stage densely: row pitch = KC.  When KC is a multiple of 128 the two
-  // rows a quarter-warp reads share banks (a 2-way conflict on 16-byte loads), which
-  // costs nothing at the ~25 B/clk/SM a weight stream needs.
-  static constexpr int PITCH = KC;
-  static constexpr int STAGE_BYTES = ROWS * PITCH;
+  // A stage lands as NBOX dense boxes of (ROWS x BOXK bytes), one TMA copy each (a tensor
+  // map box is at most 256 four-byte elements wide): row pitch = BOXK.  When BOXK is a
+  // multiple of 128 the two rows a quarter-warp reads share banks (a 2-way conflict on
+  // 16-byte loads), which costs nothing at the ~25 B/clk/SM a weight stream needs.
+  static constexpr int BOXK = KC > 1024 ? 1024 : KC;
+  static constexpr int NBOX = KC / BOXK;
+  static_assert(KC % BOXK == 0 && (RUNS * 64 <= BOXK) && (BOXK % (RUNS * 64) == 0),
+                "a warp's K slice lies inside one box");
+  static constexpr int PITCH = BOXK;
+  static constexpr int STAGE_BYTES = ROWS * KC;
+  // One weight scale per (warp, run) of a stage, gathered into shared memory.
+  static constexpr int SCALES_PER_STAGE = kConsumerWarps * RUNS;
 };
 
 // One weight matrix instance ("group"): an expert, the shared expert, or the only matrix.
@@ -79,6 +91,7 @@ struct StreamShape {
   int x_pitch;         // bytes between staged activation rows in shared memory
   int x_blocks;        // activation scale entries per staged row (k / 128)
   int n_stages;        // ring depth
+  int max_items;       // most stages one CTA can own (sizes the shared scale table)
   int debug;           // experiment switch: 1 = consumers skip the math
 };
 
@@ -112,6 +125,7 @@ struct StreamSmem {
   int is_last_cta;    // broadcast: this CTA runs the global epilogue
   int pad;
   GroupDesc groups[kMaxGroups];
+  int route_ids[64 + kMaxGroups + 1];   // routed expert ids while the group table is built
   float red[2][kConsumerWarps][32][4];
 };
 
@@ -124,60 +138,14 @@ __device__ __forceinline__ int tile_row(const StreamShape& sh, int rows, int til
   return tile_in_group * rows + r;
 }
 
-// Position of one (tile, k-stage) item; `advance` steps to the next item in tile-major
-// order without dividing.
-struct ItemCoord {
-  int tile, group, tile_in_group, kstage;   // kstage: stage index inside the group's K
-  int stage;                                // stage index inside the tile
-};
-
 template <class G>
-struct ItemIter {
-  ItemCoord c;
-  int spt, kstages, tiles_per_group, mode;
-  __device__ __forceinline__ void init(const StreamShape& sh, long long item) {
-    mode = sh.mode;
-    kstages = sh.k_bytes / G::KC;
-    tiles_per_group =
-        sh.pair_half > 0 ? sh.pair_half / (G::ROWS / 2) : sh.rows_per_group / G::ROWS;
-    spt = mode == kRowsPerGroup ? kstages : kstages * sh.n_groups;
-    c.tile = static_cast<int>(item / spt);
-    c.stage = static_cast<int>(item - static_cast<long long>(c.tile) * spt);
-    if (mode == kRowsPerGroup) {
-      c.group = c.tile / tiles_per_group;
-      c.tile_in_group = c.tile - c.group * tiles_per_group;
-      c.kstage = c.stage;
-    } else {
-      c.group = c.stage / kstages;
-      c.tile_in_group = c.tile;
-      c.kstage = c.stage - c.group * kstages;
-    }
-  }
-  __device__ __forceinline__ void advance() {
-    ++c.stage;
-    ++c.kstage;
-    if (c.stage == spt) {
-      c.stage = 0;
-      c.kstage = 0;
-      ++c.tile;
-      if (mode == kRowsPerGroup) {
-        if (++c.tile_in_group == tiles_per_group) { c.tile_in_group = 0; ++c.group; }
-      } else {
-        ++c.tile_in_group;
-        c.group = 0;
-      }
-    } else if (mode != kRowsPerGroup && c.kstage == kstages) {
-      c.kstage = 0;
-      ++c.group;
-    }
-  }
-};
-
+__host__ __device__ __forceinline__ int stream_tiles_per_group(const StreamShape& sh) {
+  return sh.pair_half > 0 ? sh.pair_half / (G::ROWS / 2) : sh.rows_per_group / G::ROWS;
+}
 template <class G>
 __host__ __device__ __forceinline__ int stream_num_tiles(const StreamShape& sh) {
-  const int tiles_per_group =
-      sh.pair_half > 0 ? sh.pair_half / (G::ROWS / 2) : sh.rows_per_group / G::ROWS;
-  return sh.mode == kRowsPerGroup ? sh.n_groups * tiles_per_group : tiles_per_group;
+  const int tpg = stream_tiles_per_group<G>(sh);
+  return sh.mode == kRowsPerGroup ? sh.n_groups * tpg : tpg;
 }
 template <class G>
 __host__ __device__ __forceinline__ int stream_stages_per_tile(const StreamShape& sh) {
@@ -185,50 +153,100 @@ __host__ __device__ __forceinline__ int stream_stages_per_tile(const StreamShape
   return sh.mode == kRowsPerGroup ? kstages : kstages * sh.n_groups;
 }
 
+// The CTA's share of the work, in 32-bit terms.
+struct CtaWork {
+  int tile0;      // first tile
+  int stage0;     // first stage inside it
+  int n_items;    // stages owned
+  int spt;        // stages per tile
+  int kstages;    // stages per group K
+  int tpg;        // tiles per group
+};
+
+template <class G>
+__device__ __forceinline__ CtaWork cta_work(const StreamShape& sh, long long it0, long long it1) {
+  CtaWork w;
+  w.kstages = sh.k_bytes / G::KC;
+  w.tpg = stream_tiles_per_group<G>(sh);
+  w.spt = sh.mode == kRowsPerGroup ? w.kstages : w.kstages * sh.n_groups;
+  w.tile0 = static_cast<int>(it0 / w.spt);
+  w.stage0 = static_cast<int>(it0 - static_cast<long long>(w.tile0) * w.spt);
+  w.n_items = static_cast<int>(it1 - it0);
+  return w;
+}
+
+// (group, tile-in-group, k-stage) of stage `s` of tile `tile`.
+struct StagePos {
+  int group, tig, kstage;
+};
+__device__ __forceinline__ StagePos stage_pos(const StreamShape& sh, const CtaWork& w, int tile,
+                                              int s) {
+  StagePos p;
+  if (sh.mode == kRowsPerGroup) {
+    p.group = tile / w.tpg;
+    p.tig = tile - p.group * w.tpg;
+    p.kstage = s;
+  } else {
+    p.group = s / w.kstages;
+    p.tig = tile;
+    p.kstage = s - p.group * w.kstages;
+  }
+  return p;
+}
+
 // ------------------------------------------------------------------------------------
-// Producer: one elected lane of one warp, one or two copies per stage.  `maps[i]` are the
+// Producer: one elected lane of one warp, one or two copies per stage.  `map0/map1` are the
 // launch's tensor maps (u32 elements, box = KC bytes x box rows), used when a stage is a
 // K-slice of its rows; whole-row stages are contiguous and use the untiled copy.
 template <class G>
-__device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm,
-                                        uint8_t* ring, long long it0, long long it1,
-                                        int* status, const CUtensorMap* map0,
+__device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm, uint8_t* ring,
+                                        const CtaWork& w, int* status, const CUtensorMap* map0,
                                         const CUtensorMap* map1) {
   const int lane = threadIdx.x & 31;
   int slot = 0;
   uint32_t phase = 0;
-  ItemIter<G> iter;
-  iter.init(sh, it0);
-  const bool whole_rows = sh.k_bytes == G::KC;
+  const bool whole_rows = sh.k_bytes == G::KC && G::NBOX == 1;
   const int halves = sh.pair_half > 0 ? 2 : 1;
   constexpr int kHalfRows = G::ROWS / 2;
-  for (long long it = it0; it < it1; ++it, iter.advance()) {
-    if (sm->abort_flag) return;
+  const int copy_rows = halves == 2 ? kHalfRows : G::ROWS;
+  int tile = w.tile0, s = w.stage0;
+  StagePos p = stage_pos(sh, w, tile, s);
+  for (int n = 0; n < w.n_items; ++n) {
     if (!mbar_wait(&sm->empty[slot], phase ^ 1u)) {
       set_status(status, IQ_ERR_PIPE_TIMEOUT);
       sm->abort_flag = 1;
       return;
     }
     if (lane == 0) {
-      const ItemCoord c = iter.c;
-      const GroupDesc& gd = sm->groups[c.group];
+      const GroupDesc& gd = sm->groups[p.group];
       uint64_t* bar = &sm->full[slot];
       mbar_arrive_expect_tx(bar, G::ROWS * G::KC);
-      uint8_t* dst = ring + static_cast<size_t>(slot) * G::STAGE_BYTES;
-      const int rows = halves == 2 ? kHalfRows : G::ROWS;
+      uint8_t* dst = ring + slot * G::STAGE_BYTES;
       for (int hf = 0; hf < halves; ++hf) {
-        const int row = tile_row(sh, G::ROWS, c.tile_in_group, hf * kHalfRows);
+        const int row = tile_row(sh, G::ROWS, p.tig, hf * kHalfRows);
         if (whole_rows) {
           bulk_g2s(dst + hf * kHalfRows * G::PITCH, gd.w + static_cast<size_t>(row) * sh.k_bytes,
-                   rows * G::KC, bar);
+                   copy_rows * G::KC, bar);
         } else {
-          tma_2d_g2s(dst + hf * kHalfRows * G::PITCH, gd.map_id ? map1 : map0,
-                     c.kstage * (G::KC / 4), gd.row_base + row, bar);
+#pragma unroll
+          for (int b = 0; b < G::NBOX; ++b)
+            tma_2d_g2s(dst + b * (G::ROWS * G::BOXK) + hf * kHalfRows * G::PITCH,
+                       gd.map_id ? map1 : map0, p.kstage * (G::KC / 4) + b * (G::BOXK / 4),
+                       gd.row_base + row, bar);
         }
       }
     }
     __syncwarp();
     if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
+    // next item
+    if (++s == w.spt) {
+      s = 0;
+      ++tile;
+      p = stage_pos(sh, w, tile, 0);
+    } else if (++p.kstage == w.kstages) {   // only reachable in kConcatK mode
+      p.kstage = 0;
+      ++p.group;
+    }
   }
 }
 
@@ -248,167 +266,159 @@ struct ElemBF16 {
   }
 };
 
+// Gathers the weight scale of every (stage, warp, run) the CTA will consume into
+// `sc[stage_local * SCALES_PER_STAGE + warp * RUNS + run]`: one global load per entry, all
+// in flight together, issued by the consumer threads before the first stage.
+template <class G, class E>
+__device__ __forceinline__ void gather_scales(const StreamShape& sh, const StreamSmem<G>* sm,
+                                              const CtaWork& w, float* sc, int tid) {
+  if (!E::kScaled) return;
+  const int total = w.n_items * G::SCALES_PER_STAGE;
+  const int krow = sh.k_bytes >> sh.kg_shift;
+  for (int i = tid; i < total; i += kConsumerThreads) {
+    const int st = i / G::SCALES_PER_STAGE, e = i - st * G::SCALES_PER_STAGE;
+    const int warp = e / G::RUNS, run = e - warp * G::RUNS;
+    const int rs = warp / G::KW, kp = warp - rs * G::KW;
+    const int lin = w.stage0 + st;
+    const int tile = w.tile0 + lin / w.spt;
+    const StagePos p = stage_pos(sh, w, tile, lin % w.spt);
+    const int row0 = tile_row(sh, G::ROWS, p.tig, rs * 16);
+    const int kb = p.kstage * G::KC + kp * (G::RUNS * 64) + run * 64;
+    sc[i] = __ldg(sm->groups[p.group].scale + static_cast<size_t>(row0 >> sh.rg_shift) * krow +
+                  (kb >> sh.kg_shift));
+  }
+}
+
+// Per-(tile, group) consumer state: everything the stage loop needs that does not change
+// from stage to stage.
+struct GroupCtx {
+  const uint8_t* xb;   // this lane's B-fragment bytes at k-stage 0 (row col_row[g], or null)
+  const float* xs0;    // activation scale rows of D columns 2t and 2t+1
+  const float* xs1;
+  float m0, m1;        // their multipliers (0 for unused columns)
+};
+
+template <class G>
+__device__ __forceinline__ GroupCtx group_ctx(const StreamShape& sh, const GroupDesc& gd,
+                                              const uint8_t* xq, const float* xs, int warp,
+                                              int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const int kp = warp % G::KW;
+  GroupCtx c;
+  const int xrow = gd.col_row[g];
+  c.xb = xrow < 0 ? nullptr : xq + xrow * sh.x_pitch + kp * (G::RUNS * 64) + t * 16;
+  const int xr0 = gd.col_row[2 * t], xr1 = gd.col_row[2 * t + 1];
+  c.m0 = xr0 < 0 ? 0.f : gd.col_mul[2 * t];
+  c.m1 = xr1 < 0 ? 0.f : gd.col_mul[2 * t + 1];
+  c.xs0 = xs + (xr0 < 0 ? 0 : xr0) * sh.x_blocks;
+  c.xs1 = xs + (xr1 < 0 ? 0 : xr1) * sh.x_blocks;
+  return c;
+}
+
 // One stage on one consumer warp.  Lane = 4g + t reads bytes [16t, 16t+16) of each 64-byte
 // run of rows g and g+8 of its sub-tile, and the same bytes of activation row col_row[g].
 // MMA k-slot 4t+j (resp. 16+4t+j) of the first MMA is byte 16t+j (resp. 16t+4+j) of the
 // run, of the second MMA byte 16t+8+j (resp. 16t+12+j): A and B use the same permutation
 // of K, which a dot product does not see.
-//
-// `StagePrep` is everything that does not depend on the stage's weights having landed
-// (scales, activation fragments), fetched BEFORE the wait on the stage's barrier.
-template <class G>
-struct StagePrep {
-  float s0[G::RUNS], s1[G::RUNS];   // scales of D columns 2t and 2t+1, per run
-  uint4 xv[G::RUNS];                // B fragments
-};
-
-// The weight scales one warp needs for one stage (one per 64-byte run).  They sit in
-// global memory and a miss costs far more than a stage, so `consume` fetches them
-// kScaleAhead stages early.
 template <class G, class E>
-__device__ __forceinline__ void load_scales(const StreamShape& sh, const StreamSmem<G>* sm,
-                                            const ItemCoord& c, int warp, float (&ws)[G::RUNS]) {
-  if (E::kScaled) {
-    const GroupDesc& gd = sm->groups[c.group];
-    const int rs = warp / G::KW, kp = warp - rs * G::KW;
-    const int kbyte0 = c.kstage * G::KC + kp * (G::RUNS * 64);
-    const int row0 = tile_row(sh, G::ROWS, c.tile_in_group, rs * 16);
-    const float* srow =
-        gd.scale + static_cast<size_t>(row0 >> sh.rg_shift) * (sh.k_bytes >> sh.kg_shift);
-#pragma unroll
-    for (int run = 0; run < G::RUNS; ++run) ws[run] = __ldg(srow + ((kbyte0 + run * 64) >> sh.kg_shift));
-  } else {
-#pragma unroll
-    for (int run = 0; run < G::RUNS; ++run) ws[run] = 1.0f;
-  }
-}
-
-template <class G, class E>
-__device__ __forceinline__ void prep_stage(const StreamShape& sh, const GroupDesc& gd,
-                                           const ItemCoord& c, const uint8_t* xq, const float* xs,
-                                           int warp, int lane, const float (&wsc)[G::RUNS],
-                                           StagePrep<G>& pr) {
-  const int g = lane >> 2, t = lane & 3;
-  const int rs = warp / G::KW, kp = warp - rs * G::KW;
-  const int kbyte0 = c.kstage * G::KC + kp * (G::RUNS * 64);   // offset in the weight row
-  const int xrow = gd.col_row[g];
-  const uint8_t* xb = xq + (xrow < 0 ? 0 : xrow) * sh.x_pitch + kbyte0 + t * 16;
-  const int xr0 = gd.col_row[2 * t], xr1 = gd.col_row[2 * t + 1];
-  const float m0 = xr0 < 0 ? 0.f : gd.col_mul[2 * t];
-  const float m1 = xr1 < 0 ? 0.f : gd.col_mul[2 * t + 1];
-#pragma unroll
-  for (int run = 0; run < G::RUNS; ++run) {
-    pr.xv[run] = make_uint4(0u, 0u, 0u, 0u);
-    if (xrow >= 0) pr.xv[run] = *reinterpret_cast<const uint4*>(xb + run * 64);
-    float s0 = m0, s1 = m1;
-    if (E::kScaled) {
-      const int kb = kbyte0 + run * 64;
-      const float ws = wsc[run];
-      const int xblk = kb >> 7;
-      s0 *= ws * (xr0 < 0 ? 0.f : xs[xr0 * sh.x_blocks + xblk]);
-      s1 *= ws * (xr1 < 0 ? 0.f : xs[xr1 * sh.x_blocks + xblk]);
-    }
-    pr.s0[run] = s0;
-    pr.s1[run] = s1;
-  }
-}
-
-template <class G, class E>
-__device__ __forceinline__ void consume_stage(const uint8_t* stage, int warp, int lane,
-                                              const StagePrep<G>& pr, float (&acc)[4]) {
-  const int g = lane >> 2, t = lane & 3;
-  const int rs = warp / G::KW, kp = warp - rs * G::KW;
-  const uint8_t* a_lo = stage + (rs * 16 + g) * G::PITCH + kp * (G::RUNS * 64) + t * 16;
+__device__ __forceinline__ void consume_stage(const uint8_t* a_lo, const GroupCtx& gc, int kbyte0,
+                                              int kwarp0, const float* wsc, float (&acc)[4]) {
   const uint8_t* a_hi = a_lo + 8 * G::PITCH;
-  uint4 wa[G::RUNS], wb[G::RUNS];
+  uint4 wa[G::RUNS], wb[G::RUNS], xv[G::RUNS];
 #pragma unroll
   for (int run = 0; run < G::RUNS; ++run) {
     wa[run] = *reinterpret_cast<const uint4*>(a_lo + run * 64);
     wb[run] = *reinterpret_cast<const uint4*>(a_hi + run * 64);
+    xv[run] = make_uint4(0u, 0u, 0u, 0u);
+    if (gc.xb) xv[run] = *reinterpret_cast<const uint4*>(gc.xb + kbyte0 + run * 64);
   }
 #pragma unroll
   for (int run = 0; run < G::RUNS; ++run) {
     float part[4] = {0.f, 0.f, 0.f, 0.f};
-    E::mma(part, wa[run].x, wb[run].x, wa[run].y, wb[run].y, pr.xv[run].x, pr.xv[run].y);
-    E::mma(part, wa[run].z, wb[run].z, wa[run].w, wb[run].w, pr.xv[run].z, pr.xv[run].w);
-    acc[0] = fmaf(part[0], pr.s0[run], acc[0]);
-    acc[1] = fmaf(part[1], pr.s1[run], acc[1]);
-    acc[2] = fmaf(part[2], pr.s0[run], acc[2]);
-    acc[3] = fmaf(part[3], pr.s1[run], acc[3]);
+    E::mma(part, wa[run].x, wb[run].x, wa[run].y, wb[run].y, xv[run].x, xv[run].y);
+    E::mma(part, wa[run].z, wb[run].z, wa[run].w, wb[run].w, xv[run].z, xv[run].w);
+    float s0 = gc.m0, s1 = gc.m1;
+    if (E::kScaled) {
+      const int xblk = (kbyte0 + kwarp0 + run * 64) >> 7;
+      const float ws = wsc[run];
+      s0 *= ws * gc.xs0[xblk];
+      s1 *= ws * gc.xs1[xblk];
+    }
+    acc[0] = fmaf(part[0], s0, acc[0]);
+    acc[1] = fmaf(part[1], s1, acc[1]);
+    acc[2] = fmaf(part[2], s0, acc[2]);
+    acc[3] = fmaf(part[3], s1, acc[3]);
   }
 }
 
-// Consumers: eight warps.  `emit(coord, r, col, val)` receives every finished tile exactly
+// Identity of a finished tile handed to `emit`.
+struct TileId {
+  int tile, group, tig;
+};
+
+// Consumers: eight warps.  `emit(tile_id, r, col, val)` receives every finished tile exactly
 // once, on consumer threads 0..127 of the CTA that finishes it: thread r*8 + col gets
-// val[sub] = the sum for weight row 16*sub + r of the tile and MMA column col.
+// val[sub] = the sum for weight row 16*sub + r of the tile and MMA column col.  In
+// kConcatK mode `tile_id.group` is 0.
 template <class G, class E, class Emit>
 __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm,
                                         const uint8_t* ring, const uint8_t* xq, const float* xs,
-                                        long long it0, long long it1, long long total, int grid,
-                                        int cta, const StreamScratch& scr, Emit emit) {
+                                        const float* sc, const CtaWork& w, long long total,
+                                        int grid, int cta, const StreamScratch& scr, Emit emit) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int rs = warp / G::KW, kp = warp - rs * G::KW;
+  const int kwarp0 = kp * (G::RUNS * 64);
+  const int a_off = (kwarp0 / G::BOXK) * (G::ROWS * G::BOXK) + (rs * 16 + g) * G::PITCH +
+                    kwarp0 % G::BOXK + t * 16;
   int slot = 0;
   uint32_t phase = 0;
   int red_buf = 0;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  ItemIter<G> iter;
-  iter.init(sh, it0);
-  const int spt = iter.spt;
-  constexpr int kScaleAhead = 3;
-  float wsp[kScaleAhead][G::RUNS];
-  ItemIter<G> ahead = iter;
-  long long ahead_it = it0;
-#pragma unroll
-  for (int d = 0; d < kScaleAhead; ++d) {
-#pragma unroll
-    for (int run = 0; run < G::RUNS; ++run) wsp[d][run] = 0.f;
-    if (ahead_it < it1) {
-      load_scales<G, E>(sh, sm, ahead.c, warp, wsp[d]);
-      ahead.advance();
-      ++ahead_it;
+  const float* wsc = sc + warp * G::RUNS;
+  int tile = w.tile0, s = w.stage0, left = w.n_items;
+  const bool concat = sh.mode != kRowsPerGroup;
+  while (left > 0) {
+    const int s_begin = s;
+    const int s_end = (w.spt - s < left) ? w.spt : s + left;
+    StagePos p = stage_pos(sh, w, tile, s);
+    // ---- stages [s_begin, s_end) of this tile, group by group
+    while (s < s_end) {
+      const GroupCtx gc = group_ctx<G>(sh, sm->groups[p.group], xq, xs, warp, lane);
+      int ks_end = w.kstages;
+      if (s_end - s < ks_end - p.kstage) ks_end = p.kstage + (s_end - s);
+      for (int ks = p.kstage; ks < ks_end; ++ks, ++s) {
+        bool ok = true;
+        if (!mbar_wait(&sm->full[slot], phase)) {   // fails at once after an abort
+          set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+          sm->abort_flag = 1;
+          ok = false;
+        }
+        if (ok && !(sh.debug & 1))
+          consume_stage<G, E>(ring + slot * G::STAGE_BYTES + a_off, gc, ks * G::KC, kwarp0, wsc,
+                              acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->empty[slot]);
+        if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
+        wsc += G::SCALES_PER_STAGE;
+      }
+      p.kstage = 0;
+      ++p.group;        // kConcatK: next group's K; kRowsPerGroup: loop ends here
     }
-  }
-  for (long long it = it0; it < it1; ++it, iter.advance()) {
-    const ItemCoord c = iter.c;
-    const GroupDesc& gd = sm->groups[c.group];
-    float wsc[G::RUNS];
-#pragma unroll
-    for (int run = 0; run < G::RUNS; ++run) {
-      wsc[run] = wsp[0][run];
-#pragma unroll
-      for (int d = 0; d + 1 < kScaleAhead; ++d) wsp[d][run] = wsp[d + 1][run];
-    }
-    if (ahead_it < it1) {
-      load_scales<G, E>(sh, sm, ahead.c, warp, wsp[kScaleAhead - 1]);
-      ahead.advance();
-      ++ahead_it;
-    }
-    StagePrep<G> pr;
-    prep_stage<G, E>(sh, gd, c, xq, xs, warp, lane, wsc, pr);
-    bool ok = !sm->abort_flag;
-    if (ok && !mbar_wait(&sm->full[slot], phase)) {
-      set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
-      sm->abort_flag = 1;
-      ok = false;
-    }
-    if (ok && !(sh.debug & 1))
-      consume_stage<G, E>(ring + static_cast<size_t>(slot) * G::STAGE_BYTES, warp, lane, pr, acc);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&sm->empty[slot]);
-    if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
+    left -= s_end - s_begin;
 
-    const long long tile_first = it - c.stage;
-    const bool tile_ends = (c.stage + 1 == spt);
-    if (!tile_ends && it + 1 != it1) continue;
-
-    // ---- the CTA's share of tile c.tile is complete: fold the K-split warps.
+    // ---- the CTA's share of this tile is complete: fold the K-split warps.
     float(*red)[32][4] = sm->red[red_buf];
     red_buf ^= 1;
 #pragma unroll
     for (int i = 0; i < 4; ++i) { red[warp][lane][i] = acc[i]; acc[i] = 0.f; }
     named_bar_sync(1, kConsumerThreads);
-    const bool whole = (it0 <= tile_first) && (it1 >= tile_first + spt);
+    const bool whole = s_begin == 0 && s_end == w.spt;
     const int r = tid >> 3, col = tid & 7;      // threads 0..127 own (row r, column col)
+    TileId id;
+    id.tile = tile;
+    id.group = concat ? 0 : tile / w.tpg;
+    id.tig = concat ? tile : tile - id.group * w.tpg;
     float val[G::RT];
     if (tid < 128) {
       const int fl = 4 * (r & 7) + (col >> 1), fi = (r >> 3) * 2 + (col & 1);
@@ -416,50 +426,52 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
       for (int sub = 0; sub < G::RT; ++sub) {
         float v = 0.f;
 #pragma unroll
-        for (int kp = 0; kp < G::KW; ++kp) v += red[sub * G::KW + kp][fl][fi];
+        for (int q = 0; q < G::KW; ++q) v += red[sub * G::KW + q][fl][fi];
         val[sub] = v;
       }
     }
     if (whole) {
-      if (tid < 128) emit(c, r, col, val);
-      continue;
-    }
-    // ---- split tile: publish the partial; the last contributor to arrive sums them all.
-    const int first_tile = static_cast<int>(it0 / spt);
-    const int pslot = (c.tile == first_tile) ? 0 : 1;
-    float* mine = scr.partials + (static_cast<size_t>(cta) * 2 + pslot) * (G::ROWS * 8);
-    if (tid < 128) {
+      if (tid < 128) emit(id, r, col, val);
+    } else {
+      // ---- split tile: publish the partial; the last contributor to arrive sums them all.
+      const int pslot = (tile == w.tile0) ? 0 : 1;
+      float* mine = scr.partials + (static_cast<size_t>(cta) * 2 + pslot) * (G::ROWS * 8);
+      if (tid < 128) {
 #pragma unroll
-      for (int sub = 0; sub < G::RT; ++sub) mine[sub * 128 + tid] = val[sub];
-      __threadfence();
-    }
-    named_bar_sync(1, kConsumerThreads);
-    const int c_first = item_owner(total, grid, tile_first);
-    const int c_last = item_owner(total, grid, tile_first + spt - 1);
-    if (tid == 0) {
-      const uint32_t prev = atomicAdd(scr.tile_counter + c.tile, 1u);
-      const int last = (prev == static_cast<uint32_t>(c_last - c_first));
-      if (last) {
-        scr.tile_counter[c.tile] = 0;     // leave the scratch ready for the next launch
+        for (int sub = 0; sub < G::RT; ++sub) mine[sub * 128 + tid] = val[sub];
         __threadfence();
       }
-      sm->is_last_tile = last;
-    }
-    named_bar_sync(1, kConsumerThreads);
-    if (sm->is_last_tile && tid < 128) {
-      float tot[G::RT];
-#pragma unroll
-      for (int sub = 0; sub < G::RT; ++sub) tot[sub] = 0.f;
-      for (int cc = c_first; cc <= c_last; ++cc) {
-        const int ft = static_cast<int>(item_begin(total, grid, cc) / spt);
-        const float* p =
-            scr.partials + (static_cast<size_t>(cc) * 2 + (c.tile == ft ? 0 : 1)) * (G::ROWS * 8);
-#pragma unroll
-        for (int sub = 0; sub < G::RT; ++sub) tot[sub] += __ldcg(p + sub * 128 + tid);
+      named_bar_sync(1, kConsumerThreads);
+      const long long tile_first = static_cast<long long>(tile) * w.spt;
+      const int c_first = item_owner(total, grid, tile_first);
+      const int c_last = item_owner(total, grid, tile_first + w.spt - 1);
+      if (tid == 0) {
+        const uint32_t prev = atomicAdd(scr.tile_counter + tile, 1u);
+        const int last = (prev == static_cast<uint32_t>(c_last - c_first));
+        if (last) {
+          scr.tile_counter[tile] = 0;     // leave the scratch ready for the next launch
+          __threadfence();
+        }
+        sm->is_last_tile = last;
       }
-      emit(c, r, col, tot);
+      named_bar_sync(1, kConsumerThreads);
+      if (sm->is_last_tile && tid < 128) {
+        float tot[G::RT];
+#pragma unroll
+        for (int sub = 0; sub < G::RT; ++sub) tot[sub] = 0.f;
+        for (int cc = c_first; cc <= c_last; ++cc) {
+          const int ft = static_cast<int>(item_begin(total, grid, cc) / w.spt);
+          const float* pp =
+              scr.partials + (static_cast<size_t>(cc) * 2 + (tile == ft ? 0 : 1)) * (G::ROWS * 8);
+#pragma unroll
+          for (int sub = 0; sub < G::RT; ++sub) tot[sub] += __ldcg(pp + sub * 128 + tid);
+        }
+        emit(id, r, col, tot);
+      }
+      named_bar_sync(1, kConsumerThreads);
     }
-    named_bar_sync(1, kConsumerThreads);
+    s = 0;
+    ++tile;
   }
 }
 

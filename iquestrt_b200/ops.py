@@ -132,6 +132,20 @@ class TailSpec:
         return a
 
 
+_SCRATCH: dict[int, Scratch] = {}
+
+
+def default_scratch(device=None) -> Scratch:
+    """The per-device scratch the reference-shaped holders share (their calls are ordered
+    on one stream, as one captured decode step is)."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    if index not in _SCRATCH:
+        _SCRATCH[index] = Scratch(torch.device("cuda", index))
+    return _SCRATCH[index]
+
+
 def tail(spec: TailSpec, scratch: Scratch, *, pdl: bool = False) -> None:
     """The epilogue on its own: one CTA (`iq_tail`)."""
     a = spec.to_c(scratch.ptr)
