@@ -122,6 +122,21 @@ typedef struct iq_linear_args {
 
 int iq_linear(const iq_linear_args* a, void* stream);
 
+/* iq_linear without a caller scratch buffer.  It has no counterpart in the reference: it
+ * exists for callers that cannot allocate device memory where they call the library (a
+ * plugin invoked while the host application captures a stream, a server whose memory
+ * was handed out in full at start-up, a host that only ever receives input and output
+ * pointers).  The work area lives in a device array built into the library, about
+ * 2.1 MB on every GPU that loads it.  a->scratch and a->scratch_bytes are ignored;
+ * a->tail must be NULL; n and k must each be at most 65536, larger shapes are refused
+ * with IQ_ERR_UNSUPPORTED and a message on stderr.  The call allocates and frees no
+ * device memory.  The first call on a device looks the array's address up and should
+ * come before any stream capture.  All calls on a device share the one array: it keeps
+ * the previous call's contents (the part that must start at zero is cleared on the
+ * stream before each launch), and calls that overlap on the GPU race -- order them on
+ * one stream.  Device-side errors are not reported by this variant. */
+int iq_linear_static(const iq_linear_args* a, void* stream);
+
 /* Router: logits = x[m,h] bf16 . w[e,h]^T bf16 (fp32 accumulate), top_k with ties to the
  * lower expert id, weights = softmax over the selected logits (reference) or their
  * sigmoids renormalised, pairs stored in ascending expert id per row.  Replaces

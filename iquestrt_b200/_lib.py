@@ -25,7 +25,7 @@ ROUTE_SOFTMAX, ROUTE_SIGMOID = range(2)
 ACT_E4M3, ACT_BF16 = range(2)
 
 EXPORTS = ("iq_scratch_bytes", "iq_status_read", "iq_sm_count", "iq_tail", "iq_linear",
-           "iq_router", "iq_moe_gate", "iq_moe_down")
+           "iq_linear_static", "iq_router", "iq_moe_gate", "iq_moe_down")
 
 
 class IqError(RuntimeError):
@@ -115,7 +115,8 @@ def load() -> C.CDLL:
         lib.iq_status_read.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_void_p]
         lib.iq_tail.restype = C.c_int
         lib.iq_tail.argtypes = [C.POINTER(TailArgs), C.c_void_p, C.c_int]
-        for name, struct in (("iq_linear", LinearArgs), ("iq_router", RouterArgs),
+        for name, struct in (("iq_linear", LinearArgs), ("iq_linear_static", LinearArgs),
+                             ("iq_router", RouterArgs),
                              ("iq_moe_gate", MoeGateArgs), ("iq_moe_down", MoeDownArgs)):
             fn = getattr(lib, name)
             fn.restype = C.c_int

@@ -1288,3 +1288,60 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   if (k % 128 == 0) return down_launch<Geo<8, 1, 2>>(a, stream);
   return IQ_ERR_UNSUPPORTED;
 }
+
+// ------------------------------------------------------------------------------------
+// iq_linear_static: iq_linear for callers that cannot obtain device memory.
+//
+// Some callers of this library cannot allocate on the device at the point where they
+// call it: a plugin running inside a host application's stream capture (cudaMalloc is
+// illegal there), a serving loop whose memory budget was handed out in full at start-up,
+// or a host that is only given raw pointers to inputs and outputs.  For them the work
+// area of the streaming GEMV (split-tile partial sums, tile counters, the CTA ticket and
+// the status word) lives in this file-scope device array instead of a caller buffer.
+// Every GPU that loads the library holds the array (kScrBytes, about 2.1 MB) until exit.
+//
+// `g_static_scratch` below is a host-side stand-in when named in host code, not a device
+// address; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
+// device with that device current.
+constexpr int kStaticMaxN = 65536;   // largest output width served from the static area
+constexpr int kStaticMaxK = 65536;   // largest contraction length
+static __device__ __align__(256) uint8_t g_static_scratch[kScrBytes];
+static void* g_static_ptr[64] = {};
+
+extern "C" int iq_linear_static(const iq_linear_args* a, void* stream) {
+  if (!a) return IQ_ERR_ARG;
+  if (a->tail) {
+    fprintf(stderr, "iqb200: iq_linear_static does not run a fused tail\n");
+    return IQ_ERR_UNSUPPORTED;
+  }
+  if (a->n > kStaticMaxN || a->k > kStaticMaxK) {
+    fprintf(stderr,
+            "iqb200: iq_linear_static serves n <= %d and k <= %d from its built-in work area; "
+            "got n=%d k=%d (use iq_linear with a caller scratch buffer)\n",
+            kStaticMaxN, kStaticMaxK, a->n, a->k);
+    return IQ_ERR_UNSUPPORTED;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return IQ_ERR_CUDA;
+  if (!g_static_ptr[dev]) {
+    // First call on this device: resolve the array's device address.  Do this before any
+    // stream capture begins.
+    void* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess || !ptr) {
+      fprintf(stderr, "iqb200: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(err));
+      return IQ_ERR_CUDA;
+    }
+    g_static_ptr[dev] = ptr;
+  }
+  // The array keeps whatever the last call left.  The kernel expects the status word,
+  // the ticket and the tile counters at zero; the partial-sum area is written before it
+  // is read and needs no clearing.
+  if (cudaMemsetAsync(g_static_ptr[dev], 0, kScrPartials, static_cast<cudaStream_t>(stream)) !=
+      cudaSuccess)
+    return IQ_ERR_CUDA;
+  iq_linear_args b = *a;
+  b.scratch = g_static_ptr[dev];
+  b.scratch_bytes = kScrBytes;
+  return iq_linear(&b, stream);
+}

@@ -296,3 +296,36 @@ def moe_down(act, sel, wt, proj, proj_scale, out, *, m: int, top_k: int, scratch
     a.pdl = int(pdl)
     _lib.check("iq_moe_down", _lib.load().iq_moe_down(C.byref(a), _stream()))
     return out[:m]
+
+
+def linear_static(x, w, w_scale, out, *, x_kind=None, x_scale=None, block=(128, 128),
+                  pdl: bool = False):
+    """`linear` for callers that cannot allocate device memory where they call it (inside a
+    host application's stream capture, or with a memory budget spent in full at start-up):
+    the kernel's work area is a device array built into the library, so no scratch buffer
+    is passed and `out` must be given.  Limits: n, k <= 65536, no fused tail.  All calls on
+    a device share that array, so order them on one stream; the first call on a device
+    should come before any stream capture."""
+    m, k = x.shape
+    n = w.shape[0]
+    dev = x.device
+    _need("w", w, E4M3, (n, k), dev)
+    rg, kg = block
+    _need("w_scale", w_scale, torch.float32, (n // rg, k // kg), dev)
+    if x_kind is None:
+        if x.dtype == torch.bfloat16:
+            x_kind = X_BF16_GROUPQ
+        else:
+            x_kind = X_E4M3_GROUP if x_scale is not None else X_E4M3_UNSCALED
+    _need("x", x, torch.bfloat16 if x_kind in (X_BF16_GROUPQ, X_BF16_SPLIT2) else E4M3, None, dev)
+    if x_kind == X_E4M3_GROUP:
+        _need("x_scale", x_scale, torch.float32, (m, k // 128), dev)
+    _need("out", out, torch.bfloat16, (m, n), dev)
+    a = _lib.LinearArgs()
+    a.x, a.x_scale, a.x_kind = x.data_ptr(), _ptr(x_scale), x_kind
+    a.m, a.k, a.n = m, k, n
+    a.w, a.w_scale, a.rg, a.kg = w.data_ptr(), w_scale.data_ptr(), rg, kg
+    a.out = out.data_ptr()
+    a.pdl = int(pdl)
+    _lib.check("iq_linear_static", _lib.load().iq_linear_static(C.byref(a), _stream()))
+    return out
