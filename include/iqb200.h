@@ -45,6 +45,14 @@ enum { IQ_TAIL_NONE = 0, IQ_TAIL_ATTN = 1, IQ_TAIL_MLP = 2 };
 enum { IQ_ROUTE_SOFTMAX = 0, IQ_ROUTE_SIGMOID = 1 };
 enum { IQ_ACT_E4M3 = 0, IQ_ACT_BF16 = 1 };
 
+/* The `pdl` field of the argument structs: 0 = plain launch; 1 = launch with the
+ * programmatic-stream-serialization attribute (the kernel streams its weights before
+ * waiting for its predecessor, and lets its own successor start once that wait has
+ * returned); 2 = as 1, and the caller also guarantees that iq_moe_gate's x_fp8/x_scale,
+ * resp. iq_moe_down's sel/wt, were written at least TWO launches earlier on the stream,
+ * so they too are read before the wait (as in the layer: attention tail -> router ->
+ * Gate -> Down, every launch made with pdl >= 1). */
+
 /* Bytes of scratch every streaming entry point needs.  The caller zero-fills it once;
  * each launch leaves it zeroed again (except the status word).  Launches that share a
  * scratch buffer must be ordered on one stream. */

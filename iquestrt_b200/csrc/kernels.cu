@@ -25,7 +25,8 @@ constexpr size_t kScrCounters = 256;
 constexpr int kMaxTiles = 16384;
 constexpr size_t kScrPartials = kScrCounters + sizeof(uint32_t) * kMaxTiles;
 constexpr int kMaxGrid = 256;
-constexpr size_t kScrBytes = kScrPartials + sizeof(float) * kMaxGrid * 2 * 128 * 8;   // + timestamps (debug)
+constexpr size_t kScrDebug = kScrPartials + sizeof(float) * kMaxGrid * 2 * 256 * 8;
+constexpr size_t kScrBytes = kScrDebug + sizeof(long long) * kMaxGrid * 64;   // + experiment counters   // + timestamps (debug)
 
 __host__ __device__ inline StreamScratch scratch_of(void* base) {
   StreamScratch s;
@@ -34,6 +35,7 @@ __host__ __device__ inline StreamScratch scratch_of(void* base) {
   s.ticket = reinterpret_cast<uint32_t*>(b + kScrTicket);
   s.tile_counter = reinterpret_cast<uint32_t*>(b + kScrCounters);
   s.partials = reinterpret_cast<float*>(b + kScrPartials);
+  s.dbg = nullptr;
   return s;
 }
 
@@ -82,6 +84,10 @@ __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape
                                        const uint8_t* src, size_t src_pitch,
                                        const float* src_scale, int rows, int k, int tid) {
   const int vec = k / 16, nvec = rows * vec;
+  // the first activation scale of this thread rides along with the first batch of loads
+  const int nxs = rows * sh.x_blocks;
+  float xs_first = 1.0f;
+  if (src_scale && tid < nxs) xs_first = __ldg(src_scale + tid);
   for (int v0 = 0; v0 < nvec; v0 += kConsumerThreads * kStageBatch) {
     uint4 raw[kStageBatch];
 #pragma unroll
@@ -101,7 +107,8 @@ __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape
       }
     }
   }
-  for (int i = tid; i < rows * sh.x_blocks; i += kConsumerThreads)
+  if (tid < nxs) xs[tid] = xs_first;
+  for (int i = tid + kConsumerThreads; i < nxs; i += kConsumerThreads)
     xs[i] = src_scale ? src_scale[i] : 1.0f;
 }
 
@@ -413,11 +420,23 @@ __device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* rows_s, float* re
 
 __global__ void __launch_bounds__(kThreads, 1) tail_kernel(const TailParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();   // after the wait: see the note on `after_wait` below
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
   run_tail(p.a, reinterpret_cast<__nv_bfloat16*>(smem + 1024), red, sflag);
+}
+
+// Programmatic dependent launch discipline shared by the kernels: a CTA lets its
+// dependents be scheduled only AFTER its own wait on its predecessor has returned.  The
+// successor kernel therefore starts no earlier than the completion of this kernel's
+// predecessor, so before ITS wait it may already read anything written two or more
+// launches back (pdl level 2: the Down reads the router's routes, the Gate reads the
+// attention tail's activations) as well as weights, and only has to wait for what its
+// immediate predecessor writes.
+__device__ __forceinline__ void after_wait() {
+  pdl_wait();
+  pdl_launch_dependents();
 }
 
 // ------------------------------------------------------------------------------------
@@ -445,9 +464,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
   const int tid = threadIdx.x, warp = tid >> 5;
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
-  const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
+  int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   const int cta = blockIdx.x;
-  pdl_launch_dependents();
   stream_init<G>(sh, cv.sm);
   if (tid == 0) {
     GroupDesc& g = cv.sm->groups[0];
@@ -462,22 +480,27 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
     }
   }
   __syncthreads();
-  if (cta < grid) {
-    const CtaWork wk = cta_work<G>(sh, item_begin(total, grid, cta), item_begin(total, grid, cta + 1));
-    if (warp == kConsumerWarps) {
+  {
+    const CtaWork wk = cta_share<G>(sh, static_cast<int>(gridDim.x), cta, grid);
+    if (warp == kProducerWarp) {
       // Weights never change: start streaming before the predecessor kernel has finished.
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
       pdl_wait();
-    } else {
-      gather_scales<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid);   // weights: before the wait
-      pdl_wait();
+    } else if (warp < kConsumerWarps) {
+      float held[kGatherHeld];
+      gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);   // weights: before the wait
+      after_wait();
       if (p.x_kind == IQ_X_BF16_GROUPQ || p.x_kind == IQ_X_BF16_SPLIT2)
         stage_rows_bf16_groupq(cv.xq, cv.xs, sh, static_cast<const __nv_bfloat16*>(p.x), p.k, p.m,
                                p.k, p.x_kind == IQ_X_BF16_SPLIT2, tid);
       else
         stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.x), p.k,
                         p.x_kind == IQ_X_E4M3_GROUP ? p.x_scale : nullptr, p.m, p.k, tid);
+      gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
       named_bar_sync(1, kConsumerThreads);
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
+    } else {
+      pdl_wait();
       const bool split2 = p.x_kind == IQ_X_BF16_SPLIT2;
       const int m = p.m, n = p.n;
       __nv_bfloat16* out = p.out;
@@ -495,10 +518,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
           }
         }
       };
-      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, total, grid, cta, scr, emit);
+      epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, emit);
     }
-  } else {
-    pdl_wait();
   }
   if (!p.has_tail) {
     stream_drain_on_abort<G>(cv.sm);
@@ -594,9 +615,8 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
   const int tid = threadIdx.x, warp = tid >> 5;
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
-  const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
+  int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   const int cta = blockIdx.x;
-  pdl_launch_dependents();
   stream_init<G>(sh, cv.sm);
   if (tid == 0) {
     GroupDesc& g = cv.sm->groups[0];
@@ -611,13 +631,13 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
     }
   }
   __syncthreads();
-  if (cta < grid) {
-    const CtaWork wk = cta_work<G>(sh, item_begin(total, grid, cta), item_begin(total, grid, cta + 1));
-    if (warp == kConsumerWarps) {
+  {
+    const CtaWork wk = cta_share<G>(sh, static_cast<int>(gridDim.x), cta, grid);
+    if (warp == kProducerWarp) {
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
       pdl_wait();
-    } else {
-      pdl_wait();
+    } else if (warp < kConsumerWarps) {
+      after_wait();
       const int vec = p.h / 8;   // 16-byte vectors per bf16 row
       for (int i = tid; i < p.m * vec; i += kConsumerThreads) {
         const int r = i / vec, v = i - r * vec;
@@ -625,6 +645,9 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
             *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(r) * p.h + v * 8);
       }
       named_bar_sync(1, kConsumerThreads);
+      consume<G, ElemBF16>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
+    } else {
+      pdl_wait();
       const int m = p.m, e = p.e;
       float* logits = p.logits;
       auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
@@ -633,10 +656,8 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
           if (col < m)
             logits[static_cast<size_t>(col) * e + id.tig * G::ROWS + sub * 16 + r] = val[sub];
       };
-      consume<G, ElemBF16>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, total, grid, cta, scr, emit);
+      epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, emit);
     }
-  } else {
-    pdl_wait();
   }
   if (last_cta<G>(cv.sm, scr, gridDim.x)) {
     if (warp < p.m) select_row(p.logits, p.e, p.top_k, p.score, warp, p.sel, p.wt);
@@ -661,15 +682,19 @@ struct MoeCommon {
 
 // Returns the number of groups.  `use_wt`: column multipliers are the routing weights
 // (Down) instead of 1 (Gate).  `x_is_pair`: the staged activation row of a column is its
-// pair's row (Down) instead of the token's row (Gate).
+// pair's row (Down) instead of the token's row (Gate).  One thread per routed pair: the
+// table is ready four block barriers after the routes arrive.
 template <class G>
 __device__ int build_groups(StreamSmem<G>* sm, const MoeCommon& mc, bool use_wt, bool x_is_pair,
                             int* status, int* s_ids /* 64 + kMaxGroups + 1 ints of shared memory */) {
   const int tid = threadIdx.x;
   const int pairs = mc.m * mc.top_k;
   const int slots = mc.top_k + mc.n_shared;
+  int e = -1;
+  float wt = 1.0f;
   if (tid < pairs) {
-    int e = mc.sel[tid];
+    e = mc.sel[tid];
+    if (use_wt) wt = mc.wt[tid];
     if (e < 0 || e >= mc.n_experts) {
       set_status(status, IQ_ERR_ROUTE);
       e = -1;
@@ -677,53 +702,63 @@ __device__ int build_groups(StreamSmem<G>* sm, const MoeCommon& mc, bool use_wt,
     s_ids[tid] = e;
   }
   __syncthreads();
-  int n_groups = 0;
-  if (tid == 0) {
-    for (int p = 0; p < pairs; ++p) {
-      const int e = s_ids[p];
-      if (e < 0) continue;
-      int gi = -1;
-      for (int g = 0; g < n_groups; ++g)
-        if (s_ids[64 + g] == e) { gi = g; break; }
-      if (gi < 0) {
-        gi = n_groups++;
-        s_ids[64 + gi] = e;
-        GroupDesc& gd = sm->groups[gi];
-        gd.w = mc.w + static_cast<size_t>(e) * mc.w_stride;
-        gd.scale = mc.w_scale + static_cast<size_t>(e) * mc.scale_stride;
-        gd.row_base = e * mc.rows_per_expert;
-        gd.map_id = 0;
-        for (int c = 0; c < kMaxCols; ++c) {
-          gd.col_row[c] = -1;
-          gd.col_mul[c] = 0.f;
-          gd.col_out[c] = 0;
-        }
-      }
-      GroupDesc& gd = sm->groups[gi];
-      const int row = p / mc.top_k, slot = p - row * mc.top_k;
-      const int pair_row = row * slots + slot;
-      gd.col_row[row] = static_cast<int16_t>(x_is_pair ? pair_row : row);
-      gd.col_mul[row] = use_wt ? mc.wt[p] : 1.0f;
-      gd.col_out[row] = static_cast<int16_t>(x_is_pair ? row : pair_row);
-    }
-    for (int s = 0; s < mc.n_shared; ++s) {
-      GroupDesc& gd = sm->groups[n_groups++];
-      gd.w = mc.shared_w + static_cast<size_t>(s) * mc.w_stride;
-      gd.scale = mc.shared_scale + static_cast<size_t>(s) * mc.scale_stride;
-      gd.row_base = s * mc.rows_per_expert;
-      gd.map_id = 1;
-      for (int c = 0; c < kMaxCols; ++c) {
-        const bool live = c < mc.m;
-        const int pair_row = c * slots + mc.top_k + s;
-        gd.col_row[c] = static_cast<int16_t>(live ? (x_is_pair ? pair_row : c) : -1);
-        gd.col_mul[c] = live ? 1.0f : 0.f;
-        gd.col_out[c] = static_cast<int16_t>(x_is_pair ? c : pair_row);
-      }
-    }
-    s_ids[64 + kMaxGroups] = n_groups;
+  // is pair q the first with its expert?
+  if (tid < pairs) {
+    bool is_first = e >= 0;
+    for (int r = 0; r < tid && is_first; ++r) is_first = s_ids[r] != e;
+    s_ids[64 + tid] = is_first ? 1 : 0;
   }
   __syncthreads();
-  return s_ids[64 + kMaxGroups];
+  // group index = number of distinct experts before the first occurrence of mine
+  int first = tid, gi = 0, n_routed = 0;
+  if (tid < pairs) {
+    for (int q = 0; q < tid; ++q)
+      if (s_ids[q] == e) { first = q; break; }
+    for (int q = 0; q < pairs; ++q) {
+      const int f = s_ids[64 + q];
+      n_routed += f;
+      gi += q < first ? f : 0;
+    }
+    if (tid == 0) s_ids[64 + kMaxGroups] = n_routed + mc.n_shared;
+    if (e >= 0 && first == tid) {
+      GroupDesc& gd = sm->groups[gi];
+      gd.w = mc.w + static_cast<size_t>(e) * mc.w_stride;
+      gd.scale = mc.w_scale + static_cast<size_t>(e) * mc.scale_stride;
+      gd.row_base = e * mc.rows_per_expert;
+      gd.map_id = 0;
+      for (int c = 0; c < kMaxCols; ++c) {
+        gd.col_row[c] = -1;
+        gd.col_mul[c] = 0.f;
+        gd.col_out[c] = 0;
+      }
+    }
+  }
+  __syncthreads();
+  const int n_groups = s_ids[64 + kMaxGroups];
+  if (tid < pairs && e >= 0) {
+    GroupDesc& gd = sm->groups[gi];
+    const int row = tid / mc.top_k, slot = tid - row * mc.top_k;
+    const int pair_row = row * slots + slot;
+    gd.col_row[row] = static_cast<int16_t>(x_is_pair ? pair_row : row);
+    gd.col_mul[row] = wt;
+    gd.col_out[row] = static_cast<int16_t>(x_is_pair ? row : pair_row);
+  } else if (tid >= 64 && tid < 64 + mc.n_shared) {
+    const int sidx = tid - 64;
+    GroupDesc& gd = sm->groups[n_groups - mc.n_shared + sidx];
+    gd.w = mc.shared_w + static_cast<size_t>(sidx) * mc.w_stride;
+    gd.scale = mc.shared_scale + static_cast<size_t>(sidx) * mc.scale_stride;
+    gd.row_base = sidx * mc.rows_per_expert;
+    gd.map_id = 1;
+    for (int c = 0; c < kMaxCols; ++c) {
+      const bool live = c < mc.m;
+      const int pair_row = c * slots + mc.top_k + sidx;
+      gd.col_row[c] = static_cast<int16_t>(live ? (x_is_pair ? pair_row : c) : -1);
+      gd.col_mul[c] = live ? 1.0f : 0.f;
+      gd.col_out[c] = static_cast<int16_t>(x_is_pair ? c : pair_row);
+    }
+  }
+  __syncthreads();
+  return n_groups;
 }
 
 struct GateParams {
@@ -735,6 +770,7 @@ struct GateParams {
   void* act;
   int act_kind;
   void* scratch;
+  int pdl_level;
 };
 
 template <class G>
@@ -742,24 +778,40 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
   extern __shared__ __align__(128) uint8_t smem[];
   StreamShape sh = p.sh;
   const Carve<G> cv = carve<G>(smem, sh);
-  const StreamScratch scr = scratch_of(p.scratch);
+  StreamScratch scr = scratch_of(p.scratch);
+  if (sh.debug & 4)
+    scr.dbg = reinterpret_cast<long long*>(static_cast<uint8_t*>(p.scratch) + kScrDebug) + blockIdx.x * 64;
   const int tid = threadIdx.x, warp = tid >> 5;
-  pdl_launch_dependents();
+  if (scr.dbg && tid == 0) scr.dbg[40] = globaltimer_ns();
   stream_init<G>(sh, cv.sm);
-  pdl_wait();                       // the routes come from the predecessor
+  // Level 2: the activations were written two launches back (by the attention tail) and
+  // can be staged while the router, the immediate predecessor, is still finishing.
+  const bool early_x = p.pdl_level >= 2;
+  if (early_x && warp < kConsumerWarps)
+    stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
+  after_wait();                     // the routes come from the predecessor
+  if (scr.dbg && tid == 0) scr.dbg[41] = globaltimer_ns();
   sh.n_groups = build_groups<G>(cv.sm, p.mc, false, false, scr.status, cv.sm->route_ids);
+  if (scr.dbg && tid == 0) scr.dbg[42] = globaltimer_ns();
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
-  const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
+  int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   const int cta = blockIdx.x;
-  if (cta < grid) {
-    const CtaWork wk = cta_work<G>(sh, item_begin(total, grid, cta), item_begin(total, grid, cta + 1));
-    if (warp == kConsumerWarps) {
-      produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
-    } else {
-      gather_scales<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid);
-      stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
+  {
+    const CtaWork wk = cta_share<G>(sh, static_cast<int>(gridDim.x), cta, grid);
+    if (warp == kProducerWarp) {
+      produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1, scr.dbg);
+    } else if (warp < kConsumerWarps) {
+      float held[kGatherHeld];
+      gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);
+      if (!early_x)
+        stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
+      gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
       named_bar_sync(1, kConsumerThreads);
+      if (scr.dbg && tid == 0) scr.dbg[43] = globaltimer_ns();
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
+      if (scr.dbg && tid == 0) scr.dbg[44] = globaltimer_ns();
+    } else {
       const int i_loc = p.mc.i_loc, m = p.mc.m;
       const int act_kind = p.act_kind;
       void* act = p.act;
@@ -780,7 +832,8 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
             static_cast<__nv_bfloat16*>(act)[o] = __float2bfloat16_rn(v);
         }
       };
-      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, total, grid, cta, scr, emit);
+      epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, emit);
+      if (scr.dbg && (tid & 31) == 0) scr.dbg[45] = globaltimer_ns();
     }
   }
   stream_drain_on_abort<G>(cv.sm);
@@ -795,6 +848,7 @@ struct DownParams {
   __nv_bfloat16* out;
   void* scratch;
   int has_tail;
+  int pdl_level;
   iq_tail_args tail;
 };
 
@@ -805,20 +859,25 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
   const Carve<G> cv = carve<G>(smem, sh);
   const StreamScratch scr = scratch_of(p.scratch);
   const int tid = threadIdx.x, warp = tid >> 5;
-  pdl_launch_dependents();
   stream_init<G>(sh, cv.sm);
-  pdl_wait();
+  // Level 2: the routes were written two launches back (by the router), so the group
+  // table, the weight stream and the scale gather all start while the Gate, the immediate
+  // predecessor, is still finishing; only the Gate's activations are waited for.
+  const bool early = p.pdl_level >= 2;
+  if (!early) after_wait();
   sh.n_groups = build_groups<G>(cv.sm, p.mc, true, true, scr.status, cv.sm->route_ids);
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
-  const int grid = static_cast<int>(total < gridDim.x ? total : gridDim.x);
+  int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   const int cta = blockIdx.x;
-  if (cta < grid) {
-    const CtaWork wk = cta_work<G>(sh, item_begin(total, grid, cta), item_begin(total, grid, cta + 1));
-    if (warp == kConsumerWarps) {
+  {
+    const CtaWork wk = cta_share<G>(sh, static_cast<int>(gridDim.x), cta, grid);
+    if (warp == kProducerWarp) {
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
-    } else {
-      gather_scales<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid);
+    } else if (warp < kConsumerWarps) {
+      float held[kGatherHeld];
+      gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);
+      if (early) after_wait();
       const int rows = p.mc.m * (p.mc.top_k + p.mc.n_shared);
       if (p.act_kind == IQ_ACT_E4M3)
         stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.act), p.mc.i_loc, nullptr,
@@ -826,7 +885,11 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
       else
         stage_rows_bf16_groupq(cv.xq, cv.xs, sh, static_cast<const __nv_bfloat16*>(p.act),
                                p.mc.i_loc, rows, p.mc.i_loc, false, tid);
+      gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
       named_bar_sync(1, kConsumerThreads);
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
+    } else {
+      if (early) pdl_wait();
       const int m = p.mc.m, h = p.mc.h;
       __nv_bfloat16* out = p.out;
       auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
@@ -836,7 +899,7 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
           out[static_cast<size_t>(col) * h + id.tile * G::ROWS + sub * 16 + r] =
               __float2bfloat16_rn(val[sub]);
       };
-      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, total, grid, cta, scr, emit);
+      epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, emit);
     }
   }
   if (!p.has_tail) {
@@ -1109,27 +1172,19 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   }
   if (sm_count() == 0) return IQ_ERR_CUDA;
   const int k = a->k, n = a->n;
-  if (k % 2048 == 0 && n % 16 == 0 && !getenv("IQB_SMALLSTAGE")) return linear_launch<Geo<1, 8, 4>>(a, stream);
-  if (k % 1024 == 0 && n % 16 == 0) return linear_launch<Geo<1, 8, 2>>(a, stream);
-  if (k % 768 == 0 && n % 32 == 0) return linear_launch<Geo<2, 4, 3>>(a, stream);
-  if (k % 512 == 0 && n % 32 == 0) return linear_launch<Geo<2, 4, 2>>(a, stream);
-  if (k % 256 == 0 && n % 64 == 0) return linear_launch<Geo<4, 2, 2>>(a, stream);
-  if (k % 192 == 0 && n % 128 == 0) return linear_launch<Geo<8, 1, 3>>(a, stream);
-  if (k % 128 == 0 && n % 128 == 0) return linear_launch<Geo<8, 1, 2>>(a, stream);
-  if (k % 64 == 0 && n % 128 == 0) return linear_launch<Geo<8, 1, 1>>(a, stream);
+  if (k % 2048 == 0 && n % 16 == 0) return linear_launch<Geo<1, 16, 2>>(a, stream);
+  if (k % 1024 == 0 && n % 16 == 0) return linear_launch<Geo<1, 16, 1>>(a, stream);
+  if (k % 768 == 0 && n % 64 == 0) return linear_launch<Geo<4, 4, 3>>(a, stream);
+  if (k % 512 == 0 && n % 32 == 0) return linear_launch<Geo<2, 8, 1>>(a, stream);
+  if (k % 256 == 0 && n % 64 == 0) return linear_launch<Geo<4, 4, 1>>(a, stream);
+  if (k % 192 == 0 && n % 256 == 0) return linear_launch<Geo<16, 1, 3>>(a, stream);
+  if (k % 128 == 0 && n % 128 == 0) return linear_launch<Geo<8, 2, 1>>(a, stream);
+  if (k % 64 == 0 && n % 256 == 0) return linear_launch<Geo<16, 1, 1>>(a, stream);
   return IQ_ERR_UNSUPPORTED;
 }
 
-extern "C" int iq_router(const iq_router_args* a, void* stream) {
-  if (!a || !a->x || !a->w || !a->sel || !a->wt || !a->logits || !a->scratch) return IQ_ERR_ARG;
-  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
-  if (a->m < 1 || a->m > 8 || a->h < 512 || a->h % 512) return IQ_ERR_ARG;
-  if (a->e < 16 || a->e % 16 || a->e > 512 || a->top_k < 1 || a->top_k > 32 || a->top_k > a->e)
-    return IQ_ERR_ARG;
-  if (a->score != IQ_ROUTE_SOFTMAX && a->score != IQ_ROUTE_SIGMOID) return IQ_ERR_ARG;
-  if (!aligned16(a->x) || !aligned16(a->w)) return IQ_ERR_ARG;
-  if (sm_count() == 0) return IQ_ERR_CUDA;
-  using G = Geo<1, 8, 2>;
+template <class G>
+static int router_launch(const iq_router_args* a, void* stream) {
   RouterParams p{};
   StreamShape& sh = p.sh;
   sh.mode = kRowsPerGroup;
@@ -1160,6 +1215,19 @@ extern "C" int iq_router(const iq_router_args* a, void* stream) {
   return launch(router_kernel<G>, p, sm_count(), smem, stream, a->pdl);
 }
 
+extern "C" int iq_router(const iq_router_args* a, void* stream) {
+  if (!a || !a->x || !a->w || !a->sel || !a->wt || !a->logits || !a->scratch) return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
+  if (a->m < 1 || a->m > 8 || a->h < 512 || a->h % 512) return IQ_ERR_ARG;
+  if (a->e < 16 || a->e % 16 || a->e > 512 || a->top_k < 1 || a->top_k > 32 || a->top_k > a->e)
+    return IQ_ERR_ARG;
+  if (a->score != IQ_ROUTE_SOFTMAX && a->score != IQ_ROUTE_SIGMOID) return IQ_ERR_ARG;
+  if (!aligned16(a->x) || !aligned16(a->w)) return IQ_ERR_ARG;
+  if (sm_count() == 0) return IQ_ERR_CUDA;
+  if ((a->h * 2) % 2048 == 0) return router_launch<Geo<1, 16, 2>>(a, stream);
+  return router_launch<Geo<1, 16, 1>>(a, stream);
+}
+
 static int fill_moe(MoeCommon& mc, int m, int h, int i_loc, int n_experts, int top_k, int n_shared,
                     const int* sel, const float* wt) {
   if (m < 1 || m > 8 || top_k < 1 || m * top_k > 64 || n_shared < 0 || n_shared > 4)
@@ -1184,7 +1252,7 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   if (a->act_kind != IQ_ACT_E4M3 && a->act_kind != IQ_ACT_BF16) return IQ_ERR_ARG;
   if (a->h < 1024 || a->h % 1024 || a->i_loc < 64 || a->i_loc % 64) return IQ_ERR_ARG;
   if (!aligned16(a->x_fp8) || !aligned16(a->fc)) return IQ_ERR_ARG;
-  using G = Geo<2, 4, 4>;
+  using G = Geo<2, 8, 2>;
   GateParams p{};
   int rc = fill_moe(p.mc, a->m, a->h, a->i_loc, a->n_experts, a->top_k, a->n_shared, a->sel,
                     nullptr);
@@ -1219,6 +1287,7 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   p.act = a->act;
   p.act_kind = a->act_kind;
   p.scratch = a->scratch;
+  p.pdl_level = a->pdl;
   return launch(gate_kernel<G>, p, sm_count(), smem, stream, a->pdl);
 }
 
@@ -1257,6 +1326,7 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   p.out = static_cast<__nv_bfloat16*>(a->out);
   p.scratch = a->scratch;
   p.has_tail = a->tail != nullptr;
+  p.pdl_level = a->pdl;
   if (a->tail) {
     p.tail = *a->tail;
     if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
@@ -1280,12 +1350,12 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   }
   if (sm_count() == 0) return IQ_ERR_CUDA;
   const int k = a->i_loc;
-  if (k % 2048 == 0) return down_launch<Geo<1, 8, 4>>(a, stream);
-  if (k % 1024 == 0) return down_launch<Geo<1, 8, 2>>(a, stream);
-  if (k % 512 == 0) return down_launch<Geo<2, 4, 2>>(a, stream);
-  if (k % 256 == 0) return down_launch<Geo<4, 2, 2>>(a, stream);
-  if (k % 192 == 0) return down_launch<Geo<8, 1, 3>>(a, stream);
-  if (k % 128 == 0) return down_launch<Geo<8, 1, 2>>(a, stream);
+  if (k % 2048 == 0) return down_launch<Geo<1, 16, 2>>(a, stream);
+  if (k % 1024 == 0) return down_launch<Geo<1, 16, 1>>(a, stream);
+  if (k % 512 == 0 && a->h % 32 == 0) return down_launch<Geo<2, 8, 1>>(a, stream);
+  if (k % 256 == 0 && a->h % 64 == 0) return down_launch<Geo<4, 4, 1>>(a, stream);
+  if (k % 192 == 0 && a->h % 256 == 0) return down_launch<Geo<16, 1, 3>>(a, stream);
+  if (k % 128 == 0 && a->h % 128 == 0) return down_launch<Geo<8, 2, 1>>(a, stream);
   return IQ_ERR_UNSUPPORTED;
 }
 

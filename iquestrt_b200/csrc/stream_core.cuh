@@ -7,7 +7,7 @@
 // contiguous.  Completion is counted in bytes on an mbarrier per ring slot.  (Measured on
 // B200: one 16 KB copy per stage with six stages in flight streams at 7.0 TB/s; sixteen
 // 1 KB copies per stage reach 3.9 TB/s.)
-// Eight consumer warps read the ring with 16-byte shared loads and feed warp-level MMAs
+// Sixteen consumer warps read the ring with 16-byte shared loads and feed warp-level MMAs
 // whose B operand carries the (at most eight) activation rows, so a byte of weight costs
 // 1/512 of an MMA and no conversion instruction.  The K index inside an MMA is permuted
 // so that every lane's A and B fragments are plain 16-byte runs (see `consume_stage`).
@@ -32,20 +32,22 @@
 
 namespace iqb {
 
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = 16;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;   // + the producer warp
+constexpr int kThreads = kConsumerThreads + 64;   // + the producer warp + the epilogue warp
+constexpr int kProducerWarp = kConsumerWarps;
+constexpr int kEpilogueWarp = kConsumerWarps + 1;
 constexpr int kMaxStages = 16;
 constexpr int kMaxGroups = 72;                    // 8 rows x 8 routed + shared, with slack
 constexpr int kMaxCols = 8;                       // MMA N
 constexpr int kSmemLimit = 232448;                // 227 KiB per CTA on sm_100
 
 // Ring geometry: a stage is (16*RT) weight rows x (KW*RUNS*64) bytes; warp (rs, kp) of the
-// RT*KW = 8 consumer warps owns row sub-tile rs and the kp-th slice of RUNS 64-byte runs.
+// RT*KW = 16 consumer warps owns row sub-tile rs and the kp-th slice of RUNS 64-byte runs.
 template <int RT_, int KW_, int RUNS_>
 struct Geo {
   static constexpr int RT = RT_, KW = KW_, RUNS = RUNS_;
-  static_assert(RT * KW == kConsumerWarps, "eight consumer warps");
+  static_assert(RT * KW == kConsumerWarps, "sixteen consumer warps");
   static constexpr int ROWS = 16 * RT;
   static constexpr int KC = KW * RUNS * 64;
   // A stage lands as NBOX dense boxes of (ROWS x BOXK bytes), one TMA copy each (a tensor
@@ -101,6 +103,7 @@ struct StreamScratch {
   uint32_t* tile_counter; // [tiles]
   uint32_t* ticket;       // [1]
   int* status;            // [1] first error code of any launch using this scratch
+  long long* dbg;         // experiments only: per-CTA cycle counters (null otherwise)
 };
 
 __device__ __forceinline__ void set_status(int* status, int code) {
@@ -120,6 +123,8 @@ template <class G>
 struct StreamSmem {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
+  uint64_t red_full[2];   // the consumers' per-tile partials are in red[i]
+  uint64_t red_empty[2];  // the epilogue warp has read red[i]
   int abort_flag;
   int is_last_tile;   // broadcast: this CTA finishes the current split tile
   int is_last_cta;    // broadcast: this CTA runs the global epilogue
@@ -175,6 +180,40 @@ __device__ __forceinline__ CtaWork cta_work(const StreamShape& sh, long long it0
   return w;
 }
 
+// How the items are cut between CTAs.  Splitting a tile between two CTAs costs three or
+// four serial global-memory round trips at the end of each CTA (publish the partial,
+// fence, count, sum), about as much as streaming four stages.  So when there are at
+// least as many tiles as CTAs and whole tiles balance to within an eighth, every CTA
+// takes whole tiles; otherwise the item range is cut evenly (stream-K).
+__host__ __device__ __forceinline__ bool tile_aligned_split(int n_tiles, int grid) {
+  const int g = n_tiles < grid ? n_tiles : grid;        // CTAs that get work
+  if (g * 10 < grid * 9) return false;                  // would idle over a tenth of the SMs
+  const int per = (n_tiles + g - 1) / g;                // most tiles any CTA takes
+  return static_cast<long long>(per) * grid * 8 <= static_cast<long long>(n_tiles) * 9;
+}
+
+// The CTA's share; `grid` is the number of CTAs launched.  CTAs beyond the work get
+// n_items == 0.  `split_grid` receives the CTA count the stream-K owner arithmetic uses.
+template <class G>
+__device__ __forceinline__ CtaWork cta_share(const StreamShape& sh, int grid, int cta,
+                                             int& split_grid) {
+  const int n_tiles = stream_num_tiles<G>(sh);
+  const int spt = stream_stages_per_tile<G>(sh);
+  const long long total = static_cast<long long>(n_tiles) * spt;
+  if (tile_aligned_split(n_tiles, grid)) {
+    const int g = n_tiles < grid ? n_tiles : grid;
+    split_grid = g;
+    if (cta >= g) return cta_work<G>(sh, 0, 0);
+    const long long t0 = static_cast<long long>(n_tiles) * cta / g;
+    const long long t1 = static_cast<long long>(n_tiles) * (cta + 1) / g;
+    return cta_work<G>(sh, t0 * spt, t1 * spt);
+  }
+  const int g = total < grid ? static_cast<int>(total) : grid;
+  split_grid = g;
+  if (cta >= g) return cta_work<G>(sh, 0, 0);
+  return cta_work<G>(sh, item_begin(total, g, cta), item_begin(total, g, cta + 1));
+}
+
 // (group, tile-in-group, k-stage) of stage `s` of tile `tile`.
 struct StagePos {
   int group, tig, kstage;
@@ -201,7 +240,7 @@ __device__ __forceinline__ StagePos stage_pos(const StreamShape& sh, const CtaWo
 template <class G>
 __device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm, uint8_t* ring,
                                         const CtaWork& w, int* status, const CUtensorMap* map0,
-                                        const CUtensorMap* map1) {
+                                        const CUtensorMap* map1, long long* dbg = nullptr) {
   const int lane = threadIdx.x & 31;
   int slot = 0;
   uint32_t phase = 0;
@@ -211,12 +250,16 @@ __device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm
   const int copy_rows = halves == 2 ? kHalfRows : G::ROWS;
   int tile = w.tile0, s = w.stage0;
   StagePos p = stage_pos(sh, w, tile, s);
+  long long dbg_wait = 0;
+  const long long dbg_t0 = dbg ? clock64() : 0;
   for (int n = 0; n < w.n_items; ++n) {
+    const long long c0 = dbg ? clock64() : 0;
     if (!mbar_wait(&sm->empty[slot], phase ^ 1u)) {
       set_status(status, IQ_ERR_PIPE_TIMEOUT);
       sm->abort_flag = 1;
       return;
     }
+    if (dbg) dbg_wait += clock64() - c0;
     if (lane == 0) {
       const GroupDesc& gd = sm->groups[p.group];
       uint64_t* bar = &sm->full[slot];
@@ -248,6 +291,11 @@ __device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm
       ++p.group;
     }
   }
+  if (dbg && lane == 0) {
+    dbg[0] = dbg_wait;
+    dbg[1] = clock64() - dbg_t0;
+    dbg[2] = w.n_items;
+  }
 }
 
 // The element type of the streamed matrix decides the MMA; everything else is bytes.
@@ -267,51 +315,78 @@ struct ElemBF16 {
 };
 
 // Gathers the weight scale of every (stage, warp, run) the CTA will consume into
-// `sc[stage_local * SCALES_PER_STAGE + warp * RUNS + run]`: one global load per entry, all
-// in flight together, issued by the consumer threads before the first stage.
+// `sc[stage_local * SCALES_PER_STAGE + warp * RUNS + run]`: one global load per entry,
+// issued by the consumer threads before the first stage.  Split in two so that the
+// caller can put other loads (the activations) in flight between issue and use:
+// `gather_scales_load` fills `held` with the thread's first kGatherHeld entries, and
+// `gather_scales_store` writes them out and handles any entries beyond those.
+constexpr int kGatherHeld = 4;
+
+template <class G>
+__device__ __forceinline__ float gather_one(const StreamShape& sh, const StreamSmem<G>* sm,
+                                            const CtaWork& w, int i) {
+  const int krow = sh.k_bytes >> sh.kg_shift;
+  const int st = i / G::SCALES_PER_STAGE, e = i - st * G::SCALES_PER_STAGE;
+  const int warp = e / G::RUNS, run = e - warp * G::RUNS;
+  const int rs = warp / G::KW, kp = warp - rs * G::KW;
+  const int lin = w.stage0 + st;
+  const int tq = lin / w.spt;
+  const StagePos p = stage_pos(sh, w, w.tile0 + tq, lin - tq * w.spt);
+  const int row0 = tile_row(sh, G::ROWS, p.tig, rs * 16);
+  const int kb = p.kstage * G::KC + kp * (G::RUNS * 64) + run * 64;
+  return __ldg(sm->groups[p.group].scale + static_cast<size_t>(row0 >> sh.rg_shift) * krow +
+               (kb >> sh.kg_shift));
+}
+
 template <class G, class E>
-__device__ __forceinline__ void gather_scales(const StreamShape& sh, const StreamSmem<G>* sm,
-                                              const CtaWork& w, float* sc, int tid) {
+__device__ __forceinline__ void gather_scales_load(const StreamShape& sh, const StreamSmem<G>* sm,
+                                                   const CtaWork& w, int tid,
+                                                   float (&held)[kGatherHeld]) {
   if (!E::kScaled) return;
   const int total = w.n_items * G::SCALES_PER_STAGE;
-  const int krow = sh.k_bytes >> sh.kg_shift;
-  for (int i = tid; i < total; i += kConsumerThreads) {
-    const int st = i / G::SCALES_PER_STAGE, e = i - st * G::SCALES_PER_STAGE;
-    const int warp = e / G::RUNS, run = e - warp * G::RUNS;
-    const int rs = warp / G::KW, kp = warp - rs * G::KW;
-    const int lin = w.stage0 + st;
-    const int tile = w.tile0 + lin / w.spt;
-    const StagePos p = stage_pos(sh, w, tile, lin % w.spt);
-    const int row0 = tile_row(sh, G::ROWS, p.tig, rs * 16);
-    const int kb = p.kstage * G::KC + kp * (G::RUNS * 64) + run * 64;
-    sc[i] = __ldg(sm->groups[p.group].scale + static_cast<size_t>(row0 >> sh.rg_shift) * krow +
-                  (kb >> sh.kg_shift));
+#pragma unroll
+  for (int j = 0; j < kGatherHeld; ++j) {
+    const int i = tid + j * kConsumerThreads;
+    held[j] = i < total ? gather_one<G>(sh, sm, w, i) : 0.f;
   }
 }
 
+template <class G, class E>
+__device__ __forceinline__ void gather_scales_store(const StreamShape& sh, const StreamSmem<G>* sm,
+                                                    const CtaWork& w, float* sc, int tid,
+                                                    const float (&held)[kGatherHeld]) {
+  if (!E::kScaled) return;
+  const int total = w.n_items * G::SCALES_PER_STAGE;
+#pragma unroll
+  for (int j = 0; j < kGatherHeld; ++j) {
+    const int i = tid + j * kConsumerThreads;
+    if (i < total) sc[i] = held[j];
+  }
+  for (int i = tid + kGatherHeld * kConsumerThreads; i < total; i += kConsumerThreads)
+    sc[i] = gather_one<G>(sh, sm, w, i);
+}
+
 // Per-(tile, group) consumer state: everything the stage loop needs that does not change
-// from stage to stage.
+// from stage to stage.  Addresses are 32-bit shared-space addresses.
 struct GroupCtx {
-  const uint8_t* xb;   // this lane's B-fragment bytes at k-stage 0 (row col_row[g], or null)
-  const float* xs0;    // activation scale rows of D columns 2t and 2t+1
-  const float* xs1;
+  uint32_t xb;         // this lane's B-fragment bytes at k-stage 0 (row col_row[g]); 0 = none
+  uint32_t xs0, xs1;   // activation scale rows of D columns 2t and 2t+1
   float m0, m1;        // their multipliers (0 for unused columns)
 };
 
 template <class G>
 __device__ __forceinline__ GroupCtx group_ctx(const StreamShape& sh, const GroupDesc& gd,
-                                              const uint8_t* xq, const float* xs, int warp,
-                                              int lane) {
+                                              uint32_t xq, uint32_t xs, int warp, int lane) {
   const int g = lane >> 2, t = lane & 3;
   const int kp = warp % G::KW;
   GroupCtx c;
   const int xrow = gd.col_row[g];
-  c.xb = xrow < 0 ? nullptr : xq + xrow * sh.x_pitch + kp * (G::RUNS * 64) + t * 16;
+  c.xb = xrow < 0 ? 0u : xq + xrow * sh.x_pitch + kp * (G::RUNS * 64) + t * 16;
   const int xr0 = gd.col_row[2 * t], xr1 = gd.col_row[2 * t + 1];
   c.m0 = xr0 < 0 ? 0.f : gd.col_mul[2 * t];
   c.m1 = xr1 < 0 ? 0.f : gd.col_mul[2 * t + 1];
-  c.xs0 = xs + (xr0 < 0 ? 0 : xr0) * sh.x_blocks;
-  c.xs1 = xs + (xr1 < 0 ? 0 : xr1) * sh.x_blocks;
+  c.xs0 = xs + (xr0 < 0 ? 0 : xr0) * sh.x_blocks * 4;
+  c.xs1 = xs + (xr1 < 0 ? 0 : xr1) * sh.x_blocks * 4;
   return c;
 }
 
@@ -321,33 +396,40 @@ __device__ __forceinline__ GroupCtx group_ctx(const StreamShape& sh, const Group
 // run, of the second MMA byte 16t+8+j (resp. 16t+12+j): A and B use the same permutation
 // of K, which a dot product does not see.
 template <class G, class E>
-__device__ __forceinline__ void consume_stage(const uint8_t* a_lo, const GroupCtx& gc, int kbyte0,
-                                              int kwarp0, const float* wsc, float (&acc)[4]) {
-  const uint8_t* a_hi = a_lo + 8 * G::PITCH;
+__device__ __forceinline__ void consume_stage(uint32_t a_lo, const GroupCtx& gc, int kbyte0,
+                                              int kwarp0, uint32_t wsc, float (&acc)[4]) {
+  const uint32_t a_hi = a_lo + 8 * G::PITCH;
   uint4 wa[G::RUNS], wb[G::RUNS], xv[G::RUNS];
 #pragma unroll
   for (int run = 0; run < G::RUNS; ++run) {
-    wa[run] = *reinterpret_cast<const uint4*>(a_lo + run * 64);
-    wb[run] = *reinterpret_cast<const uint4*>(a_hi + run * 64);
+    wa[run] = lds128(a_lo + run * 64);
+    wb[run] = lds128(a_hi + run * 64);
     xv[run] = make_uint4(0u, 0u, 0u, 0u);
-    if (gc.xb) xv[run] = *reinterpret_cast<const uint4*>(gc.xb + kbyte0 + run * 64);
+    if (gc.xb) xv[run] = lds128(gc.xb + kbyte0 + run * 64);
+  }
+  // Every MMA of the stage gets its own accumulator: the tensor pipe's latency is paid
+  // once per stage, not once per dependent MMA.
+  float pa[G::RUNS][4], pb[G::RUNS][4];
+#pragma unroll
+  for (int run = 0; run < G::RUNS; ++run) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { pa[run][i] = 0.f; pb[run][i] = 0.f; }
+    E::mma(pa[run], wa[run].x, wb[run].x, wa[run].y, wb[run].y, xv[run].x, xv[run].y);
+    E::mma(pb[run], wa[run].z, wb[run].z, wa[run].w, wb[run].w, xv[run].z, xv[run].w);
   }
 #pragma unroll
   for (int run = 0; run < G::RUNS; ++run) {
-    float part[4] = {0.f, 0.f, 0.f, 0.f};
-    E::mma(part, wa[run].x, wb[run].x, wa[run].y, wb[run].y, xv[run].x, xv[run].y);
-    E::mma(part, wa[run].z, wb[run].z, wa[run].w, wb[run].w, xv[run].z, xv[run].w);
     float s0 = gc.m0, s1 = gc.m1;
     if (E::kScaled) {
       const int xblk = (kbyte0 + kwarp0 + run * 64) >> 7;
-      const float ws = wsc[run];
-      s0 *= ws * gc.xs0[xblk];
-      s1 *= ws * gc.xs1[xblk];
+      const float ws = lds_f32(wsc + run * 4);
+      s0 *= ws * lds_f32(gc.xs0 + xblk * 4);
+      s1 *= ws * lds_f32(gc.xs1 + xblk * 4);
     }
-    acc[0] = fmaf(part[0], s0, acc[0]);
-    acc[1] = fmaf(part[1], s1, acc[1]);
-    acc[2] = fmaf(part[2], s0, acc[2]);
-    acc[3] = fmaf(part[3], s1, acc[3]);
+    acc[0] = fmaf(pa[run][0] + pb[run][0], s0, acc[0]);
+    acc[1] = fmaf(pa[run][1] + pb[run][1], s1, acc[1]);
+    acc[2] = fmaf(pa[run][2] + pb[run][2], s0, acc[2]);
+    acc[3] = fmaf(pa[run][3] + pb[run][3], s1, acc[3]);
   }
 }
 
@@ -356,15 +438,15 @@ struct TileId {
   int tile, group, tig;
 };
 
-// Consumers: eight warps.  `emit(tile_id, r, col, val)` receives every finished tile exactly
-// once, on consumer threads 0..127 of the CTA that finishes it: thread r*8 + col gets
-// val[sub] = the sum for weight row 16*sub + r of the tile and MMA column col.  In
-// kConcatK mode `tile_id.group` is 0.
-template <class G, class E, class Emit>
+// Consumers: sixteen warps (four per scheduler: the per-stage path is a latency chain, so
+// thread-level parallelism is what keeps the SM ahead of the stream).  At the end of a
+// tile each warp drops its fragment into `red[i]` and moves on; the epilogue warp folds
+// the fragments.
+template <class G, class E>
 __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm,
                                         const uint8_t* ring, const uint8_t* xq, const float* xs,
-                                        const float* sc, const CtaWork& w, long long total,
-                                        int grid, int cta, const StreamScratch& scr, Emit emit) {
+                                        const float* sc, const CtaWork& w,
+                                        const StreamScratch& scr) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int rs = warp / G::KW, kp = warp - rs * G::KW;
@@ -374,101 +456,159 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
   int slot = 0;
   uint32_t phase = 0;
   int red_buf = 0;
+  uint32_t red_phase = 0;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  const float* wsc = sc + warp * G::RUNS;
+  uint32_t wsc = smem_u32(sc) + warp * G::RUNS * 4;
+  const uint32_t ring_s = smem_u32(ring), xq_s = smem_u32(xq), xs_s = smem_u32(xs);
+  long long dbg_wait = 0, dbg_tile = 0;
+  const long long dbg_t0 = scr.dbg ? clock64() : 0;
   int tile = w.tile0, s = w.stage0, left = w.n_items;
-  const bool concat = sh.mode != kRowsPerGroup;
   while (left > 0) {
     const int s_begin = s;
     const int s_end = (w.spt - s < left) ? w.spt : s + left;
     StagePos p = stage_pos(sh, w, tile, s);
     // ---- stages [s_begin, s_end) of this tile, group by group
     while (s < s_end) {
-      const GroupCtx gc = group_ctx<G>(sh, sm->groups[p.group], xq, xs, warp, lane);
+      const GroupCtx gc = group_ctx<G>(sh, sm->groups[p.group], xq_s, xs_s, warp, lane);
       int ks_end = w.kstages;
       if (s_end - s < ks_end - p.kstage) ks_end = p.kstage + (s_end - s);
       for (int ks = p.kstage; ks < ks_end; ++ks, ++s) {
         bool ok = true;
-        if (!mbar_wait(&sm->full[slot], phase)) {   // fails at once after an abort
+        const long long c0 = scr.dbg ? clock64() : 0;
+        const bool waited = mbar_wait(&sm->full[slot], phase);
+        if (scr.dbg) dbg_wait += clock64() - c0;
+        if (scr.dbg && tid == 0 && s == w.stage0 && tile == w.tile0) scr.dbg[46] = globaltimer_ns();
+        if (!waited) {   // fails at once after an abort
           set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
           sm->abort_flag = 1;
           ok = false;
         }
         if (ok && !(sh.debug & 1))
-          consume_stage<G, E>(ring + slot * G::STAGE_BYTES + a_off, gc, ks * G::KC, kwarp0, wsc,
+          consume_stage<G, E>(ring_s + slot * G::STAGE_BYTES + a_off, gc, ks * G::KC, kwarp0, wsc,
                               acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm->empty[slot]);
         if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
-        wsc += G::SCALES_PER_STAGE;
+        wsc += G::SCALES_PER_STAGE * 4;
       }
       p.kstage = 0;
       ++p.group;        // kConcatK: next group's K; kRowsPerGroup: loop ends here
     }
     left -= s_end - s_begin;
+    const long long dbg_c1 = scr.dbg ? clock64() : 0;
 
-    // ---- the CTA's share of this tile is complete: fold the K-split warps.
+    // ---- the CTA's share of this tile is complete: hand the warp's partial to the
+    // epilogue warp and go straight on to the next tile.
+    if (!mbar_wait(&sm->red_empty[red_buf], red_phase ^ 1u)) {
+      set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+      sm->abort_flag = 1;
+    }
     float(*red)[32][4] = sm->red[red_buf];
-    red_buf ^= 1;
 #pragma unroll
     for (int i = 0; i < 4; ++i) { red[warp][lane][i] = acc[i]; acc[i] = 0.f; }
-    named_bar_sync(1, kConsumerThreads);
-    const bool whole = s_begin == 0 && s_end == w.spt;
-    const int r = tid >> 3, col = tid & 7;      // threads 0..127 own (row r, column col)
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm->red_full[red_buf]);
+    if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
+    s = 0;
+    ++tile;
+    if (scr.dbg) dbg_tile += clock64() - dbg_c1;
+  }
+  if (scr.dbg && (tid & 31) == 0 && warp < 8) {
+    scr.dbg[4 + warp * 3 + 0] = dbg_wait;
+    scr.dbg[4 + warp * 3 + 1] = dbg_tile;
+    scr.dbg[4 + warp * 3 + 2] = clock64() - dbg_t0;
+  }
+}
+
+// The epilogue warp: for every tile of the CTA, in order, folds the consumers' fragments
+// and hands the finished values to `emit(tile_id, r, col, val)`: lane l is called four
+// times per tile, with (r, col) = ((l + 32 j) >> 3, (l + 32 j) & 7), val[sub] = the sum for
+// weight row 16*sub + r of the tile and MMA column col.  A tile whose stages are split
+// between CTAs goes through the scratch: every contributor publishes its fp32 partial,
+// and the last one to arrive at the tile's counter sums them in CTA order and emits.  In
+// kConcatK mode `tile_id.group` is 0.
+template <class G, class Emit>
+__device__ __forceinline__ void epilogue(const StreamShape& sh, StreamSmem<G>* sm,
+                                         const CtaWork& w, long long total, int grid, int cta,
+                                         const StreamScratch& scr, Emit emit) {
+  const int lane = threadIdx.x & 31;
+  const bool concat = sh.mode != kRowsPerGroup;
+  int red_buf = 0;
+  uint32_t red_phase = 0;
+  int tile = w.tile0, s = w.stage0, left = w.n_items;
+  while (left > 0) {
+    const int s_end = (w.spt - s < left) ? w.spt : s + left;
+    const bool whole = s == 0 && s_end == w.spt;
+    left -= s_end - s;
     TileId id;
     id.tile = tile;
     id.group = concat ? 0 : tile / w.tpg;
     id.tig = concat ? tile : tile - id.group * w.tpg;
-    float val[G::RT];
-    if (tid < 128) {
+    if (!mbar_wait(&sm->red_full[red_buf], red_phase)) {
+      set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+      sm->abort_flag = 1;
+      return;
+    }
+    const float(*red)[32][4] = sm->red[red_buf];
+    float val[4][G::RT];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = lane + 32 * j, r = idx >> 3, col = idx & 7;
       const int fl = 4 * (r & 7) + (col >> 1), fi = (r >> 3) * 2 + (col & 1);
 #pragma unroll
       for (int sub = 0; sub < G::RT; ++sub) {
         float v = 0.f;
 #pragma unroll
         for (int q = 0; q < G::KW; ++q) v += red[sub * G::KW + q][fl][fi];
-        val[sub] = v;
+        val[j][sub] = v;
       }
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm->red_empty[red_buf]);   // the consumers may reuse red[i]
+    if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
     if (whole) {
-      if (tid < 128) emit(id, r, col, val);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) emit(id, (lane + 32 * j) >> 3, (lane + 32 * j) & 7, val[j]);
     } else {
-      // ---- split tile: publish the partial; the last contributor to arrive sums them all.
       const int pslot = (tile == w.tile0) ? 0 : 1;
       float* mine = scr.partials + (static_cast<size_t>(cta) * 2 + pslot) * (G::ROWS * 8);
-      if (tid < 128) {
 #pragma unroll
-        for (int sub = 0; sub < G::RT; ++sub) mine[sub * 128 + tid] = val[sub];
-        __threadfence();
-      }
-      named_bar_sync(1, kConsumerThreads);
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int sub = 0; sub < G::RT; ++sub) mine[sub * 128 + lane + 32 * j] = val[j][sub];
+      __threadfence();
+      __syncwarp();
       const long long tile_first = static_cast<long long>(tile) * w.spt;
       const int c_first = item_owner(total, grid, tile_first);
       const int c_last = item_owner(total, grid, tile_first + w.spt - 1);
-      if (tid == 0) {
+      int last = 0;
+      if (lane == 0) {
         const uint32_t prev = atomicAdd(scr.tile_counter + tile, 1u);
-        const int last = (prev == static_cast<uint32_t>(c_last - c_first));
+        last = (prev == static_cast<uint32_t>(c_last - c_first));
         if (last) {
           scr.tile_counter[tile] = 0;     // leave the scratch ready for the next launch
           __threadfence();
         }
-        sm->is_last_tile = last;
       }
-      named_bar_sync(1, kConsumerThreads);
-      if (sm->is_last_tile && tid < 128) {
-        float tot[G::RT];
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {
 #pragma unroll
-        for (int sub = 0; sub < G::RT; ++sub) tot[sub] = 0.f;
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int sub = 0; sub < G::RT; ++sub) val[j][sub] = 0.f;
         for (int cc = c_first; cc <= c_last; ++cc) {
           const int ft = static_cast<int>(item_begin(total, grid, cc) / w.spt);
           const float* pp =
               scr.partials + (static_cast<size_t>(cc) * 2 + (tile == ft ? 0 : 1)) * (G::ROWS * 8);
 #pragma unroll
-          for (int sub = 0; sub < G::RT; ++sub) tot[sub] += __ldcg(pp + sub * 128 + tid);
+          for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int sub = 0; sub < G::RT; ++sub)
+              val[j][sub] += __ldcg(pp + sub * 128 + lane + 32 * j);
         }
-        emit(id, r, col, tot);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) emit(id, (lane + 32 * j) >> 3, (lane + 32 * j) & 7, val[j]);
       }
-      named_bar_sync(1, kConsumerThreads);
     }
     s = 0;
     ++tile;
@@ -501,6 +641,10 @@ __device__ __forceinline__ void stream_init(const StreamShape& sh, StreamSmem<G>
     for (int s = 0; s < sh.n_stages; ++s) {
       mbar_init(&sm->full[s], 1);
       mbar_init(&sm->empty[s], kConsumerWarps);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm->red_full[i], kConsumerWarps);
+      mbar_init(&sm->red_empty[i], 1);
     }
     sm->abort_flag = 0;
     sm->is_last_tile = 0;

@@ -91,12 +91,16 @@ class DecodeLayer:
                       lw["shared_proj_scale"])
         out_buf = moe.outputs[moe._out_index]
         mspec = self.mlp_tail.spec(out_buf[:q], h, self.f_scale, lw["next_attention_norm"])
+        # Level 2: the Gate's activations (written by the attention tail) and the Down's
+        # routes (written by the router) are each two launches old when those kernels
+        # start, so they may be read before the kernels' dependency wait.
+        level = 2 if pdl else 0
         if fused:
             moe(sel, wt, lw["fc"], lw["fc_scale"], lw["proj"], lw["proj_scale"], x_scale=x_scale,
-                shared=shared, tail=mspec, pdl=pdl)
+                shared=shared, tail=mspec, pdl=level)
         else:
             moe(sel, wt, lw["fc"], lw["fc_scale"], lw["proj"], lw["proj_scale"], x_scale=x_scale,
-                shared=shared, pdl=pdl)
+                shared=shared, pdl=level)
             ops.tail(mspec, self.scratch, pdl=pdl)
         return mspec.h_out, mspec.norm_out
 
