@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--rows", type=int, default=1, help="tokens per step (1, or 4 for MTP verify)")
     ap.add_argument("--layers", type=int, default=0, help="distinct weight sets to rotate over")
+    ap.add_argument("--experts", type=int, default=256,
+                    help="routed experts in the bank (smaller banks keep profiler captures "
+                         "small; a step still streams top-k routed + the shared expert)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-multicast", action="store_true",
                     help="all-reduce over plain peer loads instead of NVLS multimem")
@@ -207,9 +210,10 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD.group_name
     _build.build()                                          # no-op when the .so is current
-    shape = synth.BASELINE
+    shape = synth.BASELINE if args.experts == 256 else synth.LayerShape(n_experts=args.experts)
     rows = args.rows
-    n_layers = args.layers or max(2, min(4, int(24e9 // (9.8e9 / tp))))
+    bank_bytes = 37.75e6 * (args.experts + 1) / tp
+    n_layers = args.layers or max(2, min(4, int(24e9 // bank_bytes)))
     layer = DecodeLayer(shape, q_len=rows, tp=tp, group=group, device=dev,
                         formats="benchmark", use_multicast=not args.no_multicast)
     weights = [synth.make_layer(shape, tp=tp, rank=rank, device=dev, seed=0, layer=i)
@@ -300,7 +304,7 @@ def run_ours(args):
             evs.append(e)
         stream.synchronize()
         layer.check()
-        for e in evs[4:]:
+        for e in evs[min(4, len(evs) // 2):]:
             for j, name in enumerate(kern_ms):
                 kern_ms[name].append(e[j].elapsed_time(e[j + 1]))
 
@@ -362,6 +366,7 @@ def run_ours(args):
             "ms_per_step": ms / K, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "e4m3 x e4m3 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows": rows, "tp": tp, "launches_per_step": 4,
+                       "experts_in_bank": args.experts,
                        "l2": f"weights rotate over {n_layers} distinct layers "
                              f"({by['total'] * n_layers / 1e6:.0f} MB touched per cycle, L2 is 126 MB)",
                        "all_reduce": "none (TP=1)" if tp == 1 else
@@ -375,7 +380,10 @@ def run_ours(args):
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": by["gate"],
-                         "launch_us": med["gate"] * 1e3, "traffic": None,
+                         "launch_us": med["gate"] * 1e3,
+                         # dram__bytes_read + dram__bytes_write of one launch, from the ncu
+                         # capture summarised in profiles/gate_kernel_tp1_m1.md
+                         "traffic": 231.26e6 if (tp == 1 and rows == 1) else None,
                          "layer_frac": by["total"] / (us * 1e-6) / 1e9 / peak},
             "kernel_us": {k: v * 1e3 for k, v in med.items()},
             "layer_bytes": by["total"],

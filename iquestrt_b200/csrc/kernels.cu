@@ -25,8 +25,7 @@ constexpr size_t kScrCounters = 256;
 constexpr int kMaxTiles = 16384;
 constexpr size_t kScrPartials = kScrCounters + sizeof(uint32_t) * kMaxTiles;
 constexpr int kMaxGrid = 256;
-constexpr size_t kScrDebug = kScrPartials + sizeof(float) * kMaxGrid * 2 * 256 * 8;
-constexpr size_t kScrBytes = kScrDebug + sizeof(long long) * kMaxGrid * 64;   // + experiment counters   // + timestamps (debug)
+constexpr size_t kScrBytes = kScrPartials + sizeof(float) * kMaxGrid * 2 * 256 * 8;
 
 __host__ __device__ inline StreamScratch scratch_of(void* base) {
   StreamScratch s;
@@ -35,7 +34,6 @@ __host__ __device__ inline StreamScratch scratch_of(void* base) {
   s.ticket = reinterpret_cast<uint32_t*>(b + kScrTicket);
   s.tile_counter = reinterpret_cast<uint32_t*>(b + kScrCounters);
   s.partials = reinterpret_cast<float*>(b + kScrPartials);
-  s.dbg = nullptr;
   return s;
 }
 
@@ -202,31 +200,35 @@ __device__ inline U4 f32_to_bf16x8(const float (&f)[8]) {
 }
 __device__ inline float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-// Sum of squares per row across the block: `part[m]` from every thread -> `out[m]` on all.
-// `red` holds 8 x nwarps floats.  Fixed summation order.
-__device__ inline void block_row_sums(float (&part)[8], int m, float* red, float (&out)[8]) {
+// Block-wide sum with one barrier: every warp drops its sum into `slots`, every thread
+// adds the slots up in warp order.  Consecutive calls must alternate `slots` buffers.
+__device__ inline float block_sum(float v, float* slots) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  v = warp_sum(v);
+  if (lane == 0) slots[warp] = v;
   __syncthreads();
-  for (int r = 0; r < m; ++r) {
-    const float s = warp_sum(part[r]);
-    if (lane == 0) red[r * nwarps + warp] = s;
-  }
-  __syncthreads();
-  for (int r = 0; r < m; ++r) {
-    float s = 0.f;
-    for (int w = 0; w < nwarps; ++w) s += red[r * nwarps + w];
-    out[r] = s;
-  }
+  float s = 0.f;
+  for (int w = 0; w < nwarps; ++w) s += slots[w];
+  return s;
 }
 
-// Runs on every thread of one CTA.  `rows_s` is shared memory for m*h bf16 and `red` for
-// 8 * (blockDim/32) floats.  Rows written by other CTAs of this launch must already be
-// visible (the caller passed the ticket).
-__device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* rows_s, float* red,
+constexpr int kTailVecs = 2;   // 16-byte vectors of a row per thread: h <= 8 * 2 * blockDim
+
+struct TailRow {
+  U4 part[kTailVecs];       // reduced partial (bf16 x 8)
+  float res[kTailVecs][8];  // residual
+};
+
+// Runs on every thread of one CTA (blockDim a multiple of 32, h <= 16 * blockDim).  `red`
+// is shared memory for 4 x 32 floats, `sflag` one shared int.  Rows written by other CTAs
+// of this launch must already be visible (the caller passed the ticket).  Rows are
+// handled one after the other, each entirely in registers: all of a row's global loads
+// are issued before the first is used, and each RMSNorm costs one block barrier.
+__device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/, float* red,
                          int* sflag) {
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int m = a.m, h = a.h, vec_per_row = h / 8;
-  const int nvec = m * vec_per_row;
+  const float inv_h = 1.0f / static_cast<float>(h);
 
   // ---- cross-rank readiness
   if (a.world > 1) {
@@ -241,10 +243,15 @@ __device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* rows_s, float* re
                        : "memory");
       }
       const uint64_t budget = 1000000ull * (a.timeout_ms ? a.timeout_ms : 2000u);
-      const uint64_t t0 = globaltimer_ns();
+      uint64_t t0 = 0;
       int ok = 1;
-      while (static_cast<int32_t>(ld_acquire_sys_u32(a.arrive) - target) < 0) {
-        if (globaltimer_ns() - t0 > budget) { ok = 0; break; }
+      for (uint32_t spin = 0;; ++spin) {
+        if (static_cast<int32_t>(ld_acquire_sys_u32(a.arrive) - target) >= 0) break;
+        if ((spin & 255u) == 255u) {
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > budget) { ok = 0; break; }
+        }
       }
       if (!ok) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
       *sflag = ok;
@@ -257,162 +264,139 @@ __device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* rows_s, float* re
     }
   }
 
-  // ---- reduced rows into shared memory (bf16, the switch's rounding point)
-  for (int v = tid; v < nvec; v += nthr) {
-    U4 u;
-    const size_t off = static_cast<size_t>(v) * 8;
-    if (a.world == 1) {
-      const uint4 t = __ldcg(reinterpret_cast<const uint4*>(
-          static_cast<const __nv_bfloat16*>(a.partial) + off));
-      u = U4{t.x, t.y, t.z, t.w};
-    } else if (a.partial_mc) {
-      u = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(a.partial_mc) + off);
-    } else {
-      float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int p = 0; p < a.world; ++p) {
-        const U4 t = ld_global_u4(static_cast<const __nv_bfloat16*>(a.peer_partials[p]) + off);
-        float f[8];
-        bf16x8_to_f32(t, f);
+  for (int r = 0; r < m; ++r) {
+    const size_t row_off = static_cast<size_t>(r) * h;
+    float* slots0 = red + (r & 1) * 64;        // two reductions per row, alternating rows
+    float* slots1 = slots0 + 32;
+    TailRow row;
+    float w1[kTailVecs][8], w2[kTailVecs][8];
+    // ---- every load of the row, issued together
 #pragma unroll
-        for (int j = 0; j < 8; ++j) accv[j] += f[j];
+    for (int i = 0; i < kTailVecs; ++i) {
+      const int v = tid + i * nthr;
+      if (v >= vec_per_row) continue;
+      const size_t off = row_off + static_cast<size_t>(v) * 8;
+      if (a.world == 1) {
+        const uint4 t = __ldcg(reinterpret_cast<const uint4*>(
+            static_cast<const __nv_bfloat16*>(a.partial) + off));
+        row.part[i] = U4{t.x, t.y, t.z, t.w};
+      } else if (a.partial_mc) {
+        row.part[i] = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(a.partial_mc) + off);
+      } else {
+        float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int p = 0; p < a.world; ++p) {
+          const U4 t = ld_global_u4(static_cast<const __nv_bfloat16*>(a.peer_partials[p]) + off);
+          float f[8];
+          bf16x8_to_f32(t, f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) accv[j] += f[j];
+        }
+        row.part[i] = f32_to_bf16x8(accv);
       }
-      u = f32_to_bf16x8(accv);
+      if (a.residual_fp32) {
+        const float* rp = static_cast<const float*>(a.residual) + off;
+        const float4 r0 = *reinterpret_cast<const float4*>(rp);
+        const float4 r1 = *reinterpret_cast<const float4*>(rp + 4);
+        row.res[i][0] = r0.x; row.res[i][1] = r0.y; row.res[i][2] = r0.z; row.res[i][3] = r0.w;
+        row.res[i][4] = r1.x; row.res[i][5] = r1.y; row.res[i][6] = r1.z; row.res[i][7] = r1.w;
+      } else {
+        const uint4 t =
+            *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.residual) + off);
+        bf16x8_to_f32(U4{t.x, t.y, t.z, t.w}, row.res[i]);
+      }
+      const int c0 = v * 8;
+      if (a.kind == IQ_TAIL_ATTN) {
+        const float4 x0 = __ldg(reinterpret_cast<const float4*>(a.w_first + c0));
+        const float4 x1 = __ldg(reinterpret_cast<const float4*>(a.w_first + c0 + 4));
+        w1[i][0] = x0.x; w1[i][1] = x0.y; w1[i][2] = x0.z; w1[i][3] = x0.w;
+        w1[i][4] = x1.x; w1[i][5] = x1.y; w1[i][6] = x1.z; w1[i][7] = x1.w;
+      }
+      const float4 y0 = __ldg(reinterpret_cast<const float4*>(a.w_norm + c0));
+      const float4 y1 = __ldg(reinterpret_cast<const float4*>(a.w_norm + c0 + 4));
+      w2[i][0] = y0.x; w2[i][1] = y0.y; w2[i][2] = y0.z; w2[i][3] = y0.w;
+      w2[i][4] = y1.x; w2[i][5] = y1.y; w2[i][6] = y1.z; w2[i][7] = y1.w;
     }
-    *reinterpret_cast<U4*>(rows_s + off) = u;
-  }
 
-  float part[8], tot[8], inv[8];
-  const float inv_h = 1.0f / static_cast<float>(h);
-  if (a.kind == IQ_TAIL_ATTN) {
-    // first RMSNorm statistics on the reduced rows
-#pragma unroll
-    for (int r = 0; r < 8; ++r) part[r] = 0.f;
-    __syncthreads();
-    for (int v = tid; v < nvec; v += nthr) {
-      float f[8];
-      bf16x8_to_f32(*reinterpret_cast<const U4*>(rows_s + static_cast<size_t>(v) * 8), f);
-      float s = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s = fmaf(f[j], f[j], s);
-      const int r = v / vec_per_row;
-#pragma unroll
-      for (int q = 0; q < 8; ++q) part[q] += (q == r) ? s : 0.f;
-    }
-    block_row_sums(part, m, red, tot);
-    for (int r = 0; r < m; ++r) inv[r] = rsqrtf(tot[r] * inv_h + a.eps);
-  }
-
-  // ---- h = residual + (ATTN: bf16(bf16(w1*(ao*inv))*scale) | MLP: bf16(m*scale))
-#pragma unroll
-  for (int r = 0; r < 8; ++r) part[r] = 0.f;
-  if (a.kind != IQ_TAIL_ATTN) __syncthreads();
-  for (int v = tid; v < nvec; v += nthr) {
-    const int r = v / vec_per_row, c0 = (v - r * vec_per_row) * 8;
-    const size_t off = static_cast<size_t>(v) * 8;
-    float f[8], res[8], hv[8];
-    bf16x8_to_f32(*reinterpret_cast<const U4*>(rows_s + off), f);
-    if (a.residual_fp32) {
-      const float4 r0 = *reinterpret_cast<const float4*>(static_cast<const float*>(a.residual) + off);
-      const float4 r1 =
-          *reinterpret_cast<const float4*>(static_cast<const float*>(a.residual) + off + 4);
-      res[0] = r0.x; res[1] = r0.y; res[2] = r0.z; res[3] = r0.w;
-      res[4] = r1.x; res[5] = r1.y; res[6] = r1.z; res[7] = r1.w;
-    } else {
-      const uint4 t =
-          *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.residual) + off);
-      bf16x8_to_f32(U4{t.x, t.y, t.z, t.w}, res);
-    }
+    float f[kTailVecs][8], hv[kTailVecs][8];
+    float inv1 = 0.f;
     if (a.kind == IQ_TAIL_ATTN) {
-      const float4 w0 = *reinterpret_cast<const float4*>(a.w_first + c0);
-      const float4 w1 = *reinterpret_cast<const float4*>(a.w_first + c0 + 4);
-      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < kTailVecs; ++i) {
+        if (tid + i * nthr >= vec_per_row) continue;
+        bf16x8_to_f32(row.part[i], f[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[i][j], f[i][j], ss);
+      }
+      inv1 = rsqrtf(block_sum(ss, slots0) * inv_h + a.eps);
+    }
+    // ---- h = residual + (ATTN: bf16(bf16(w1*(ao*inv))*scale) | MLP: bf16(m*scale))
+    float ss2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kTailVecs; ++i) {
+      const int v = tid + i * nthr;
+      if (v >= vec_per_row) continue;
+      const size_t off = row_off + static_cast<size_t>(v) * 8;
+      if (a.kind != IQ_TAIL_ATTN) bf16x8_to_f32(row.part[i], f[i]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float nrm = bf16_round(w[j] * (f[j] * inv[r]));
-        const float sc = bf16_round(nrm * a.scale);
-        hv[j] = sc + res[j];
+        float add;
+        if (a.kind == IQ_TAIL_ATTN) {
+          const float nrm = bf16_round(w1[i][j] * (f[i][j] * inv1));
+          add = bf16_round(nrm * a.scale);
+        } else {
+          add = bf16_round(f[i][j] * a.scale);
+        }
+        hv[i][j] = row.res[i][j] + add;
       }
-    } else {
+      if (a.residual_fp32) {
+        float* ho = static_cast<float*>(a.h_out) + off;
+        *reinterpret_cast<float4*>(ho) = make_float4(hv[i][0], hv[i][1], hv[i][2], hv[i][3]);
+        *reinterpret_cast<float4*>(ho + 4) = make_float4(hv[i][4], hv[i][5], hv[i][6], hv[i][7]);
+      } else {
+        const U4 hb = f32_to_bf16x8(hv[i]);
+        *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.h_out) + off) = hb;
+        bf16x8_to_f32(hb, hv[i]);            // the norm sees the rounded stream
+      }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) hv[j] = res[j] + bf16_round(f[j] * a.scale);
+      for (int j = 0; j < 8; ++j) ss2 = fmaf(hv[i][j], hv[i][j], ss2);
     }
-    float s = 0.f;
-    if (a.residual_fp32) {
-      float* ho = static_cast<float*>(a.h_out) + off;
-      *reinterpret_cast<float4*>(ho) = make_float4(hv[0], hv[1], hv[2], hv[3]);
-      *reinterpret_cast<float4*>(ho + 4) = make_float4(hv[4], hv[5], hv[6], hv[7]);
-      // The fp32 stream is normalised unrounded; shared memory keeps a bf16 copy only
-      // when it is the stream itself, so recompute from registers below.
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s = fmaf(hv[j], hv[j], s);
-      // Stash fp32 h for the norm pass in place of the reduced row (two bf16 slots per
-      // value are not available), so the fp32 path normalises in this same pass instead.
-      const U4 hb = f32_to_bf16x8(hv);
-      *reinterpret_cast<U4*>(rows_s + off) = hb;
-    } else {
-      const U4 hb = f32_to_bf16x8(hv);
-      *reinterpret_cast<U4*>(rows_s + off) = hb;
-      *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.h_out) + off) = hb;
-      float hr[8];
-      bf16x8_to_f32(hb, hr);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s = fmaf(hr[j], hr[j], s);
-    }
-#pragma unroll
-    for (int q = 0; q < 8; ++q) part[q] += (q == r) ? s : 0.f;
-  }
-  block_row_sums(part, m, red, tot);
-  for (int r = 0; r < m; ++r) inv[r] = rsqrtf(tot[r] * inv_h + a.eps);
-  if (a.inv_out && tid < m) {
-    float t = inv[0];
-    for (int r = 1; r < m; ++r) t = (tid == r) ? inv[r] : t;
-    a.inv_out[tid] = t;
-  }
+    const float inv2 = rsqrtf(block_sum(ss2, slots1) * inv_h + a.eps);
+    if (a.inv_out && tid == 0) a.inv_out[r] = inv2;
 
-  // ---- norm_out = bf16(w_norm * (h * inv)) (+ e4m3 copy, unscaled or per 1x128 group)
-  for (int v0 = 0; v0 < nvec; v0 += nthr) {
-    const int v = v0 + tid;
-    const bool live = v < nvec;
-    const int vv = live ? v : 0;
-    const int r = vv / vec_per_row, c0 = (vv - r * vec_per_row) * 8;
-    const size_t off = static_cast<size_t>(vv) * 8;
-    float hr[8], o[8];
-    if (a.residual_fp32) {
-      const float* hp = static_cast<const float*>(a.h_out) + off;   // written by this thread
-      const float4 h0 = *reinterpret_cast<const float4*>(hp);
-      const float4 h1 = *reinterpret_cast<const float4*>(hp + 4);
-      hr[0] = h0.x; hr[1] = h0.y; hr[2] = h0.z; hr[3] = h0.w;
-      hr[4] = h1.x; hr[5] = h1.y; hr[6] = h1.z; hr[7] = h1.w;
-    } else {
-      bf16x8_to_f32(*reinterpret_cast<const U4*>(rows_s + off), hr);
-    }
-    const float4 w0 = *reinterpret_cast<const float4*>(a.w_norm + c0);
-    const float4 w1 = *reinterpret_cast<const float4*>(a.w_norm + c0 + 4);
-    const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-    float amax = 0.f;
+    // ---- norm_out = bf16(w_norm * (h * inv)) (+ e4m3 copy, unscaled or per 1x128 group)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      o[j] = bf16_round(w[j] * (hr[j] * inv[r]));
-      amax = fmaxf(amax, fabsf(o[j]));
-    }
-    if (live) *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.norm_out) + off) = f32_to_bf16x8(o);
-    if (a.norm_fp8) {
-      float s = 1.0f;
-      if (a.norm_fp8_scale) {
-        // A 128-element group is sixteen consecutive vectors = sixteen consecutive lanes.
+    for (int i = 0; i < kTailVecs; ++i) {
+      const int v = tid + i * nthr;
+      const bool live = v < vec_per_row;       // uniform over each 16-lane group
+      const size_t off = row_off + static_cast<size_t>(live ? v : 0) * 8;
+      float o[8];
+      float amax = 0.f;
 #pragma unroll
-        for (int o2 = 8; o2; o2 >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o2));
-        s = amax > 0.f ? amax / 448.0f : 1.0f;
-        if (live && (vv & 15) == 0) a.norm_fp8_scale[vv >> 4] = s;
+      for (int j = 0; j < 8; ++j) {
+        o[j] = live ? bf16_round(w2[i][j] * (hv[i][j] * inv2)) : 0.f;
+        amax = fmaxf(amax, fabsf(o[j]));
       }
-      const float rcp = 1.0f / s;
-      uint32_t q0 = 0, q1 = 0;
+      if (live)
+        *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.norm_out) + off) = f32_to_bf16x8(o);
+      if (a.norm_fp8) {
+        float sc = 1.0f;
+        if (a.norm_fp8_scale) {
+          // A 128-element group is sixteen consecutive vectors = sixteen consecutive lanes.
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        q0 |= static_cast<uint32_t>(f32_to_e4m3_sat(o[j] * rcp)) << (8 * j);
-        q1 |= static_cast<uint32_t>(f32_to_e4m3_sat(o[j + 4] * rcp)) << (8 * j);
+          for (int o2 = 8; o2; o2 >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o2));
+          sc = amax > 0.f ? amax / 448.0f : 1.0f;
+          if (live && (v & 15) == 0) a.norm_fp8_scale[static_cast<size_t>(r) * (h / 128) + (v >> 4)] = sc;
+        }
+        const float rcp = 1.0f / sc;
+        uint32_t q0 = 0, q1 = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          q0 |= static_cast<uint32_t>(f32_to_e4m3_sat(o[j] * rcp)) << (8 * j);
+          q1 |= static_cast<uint32_t>(f32_to_e4m3_sat(o[j + 4] * rcp)) << (8 * j);
+        }
+        if (live) *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.norm_fp8) + off) = make_uint2(q0, q1);
       }
-      if (live) *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.norm_fp8) + off) = make_uint2(q0, q1);
     }
   }
   if (a.world > 1 && tid == 0) *a.epoch = *a.epoch + 1u;
@@ -778,11 +762,8 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
   extern __shared__ __align__(128) uint8_t smem[];
   StreamShape sh = p.sh;
   const Carve<G> cv = carve<G>(smem, sh);
-  StreamScratch scr = scratch_of(p.scratch);
-  if (sh.debug & 4)
-    scr.dbg = reinterpret_cast<long long*>(static_cast<uint8_t*>(p.scratch) + kScrDebug) + blockIdx.x * 64;
+  const StreamScratch scr = scratch_of(p.scratch);
   const int tid = threadIdx.x, warp = tid >> 5;
-  if (scr.dbg && tid == 0) scr.dbg[40] = globaltimer_ns();
   stream_init<G>(sh, cv.sm);
   // Level 2: the activations were written two launches back (by the attention tail) and
   // can be staged while the router, the immediate predecessor, is still finishing.
@@ -790,9 +771,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
   if (early_x && warp < kConsumerWarps)
     stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
   after_wait();                     // the routes come from the predecessor
-  if (scr.dbg && tid == 0) scr.dbg[41] = globaltimer_ns();
   sh.n_groups = build_groups<G>(cv.sm, p.mc, false, false, scr.status, cv.sm->route_ids);
-  if (scr.dbg && tid == 0) scr.dbg[42] = globaltimer_ns();
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
@@ -800,7 +779,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
   {
     const CtaWork wk = cta_share<G>(sh, static_cast<int>(gridDim.x), cta, grid);
     if (warp == kProducerWarp) {
-      produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1, scr.dbg);
+      produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
     } else if (warp < kConsumerWarps) {
       float held[kGatherHeld];
       gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);
@@ -808,9 +787,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
         stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
       gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
       named_bar_sync(1, kConsumerThreads);
-      if (scr.dbg && tid == 0) scr.dbg[43] = globaltimer_ns();
       consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
-      if (scr.dbg && tid == 0) scr.dbg[44] = globaltimer_ns();
     } else {
       const int i_loc = p.mc.i_loc, m = p.mc.m;
       const int act_kind = p.act_kind;
@@ -833,7 +810,6 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
         }
       };
       epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, emit);
-      if (scr.dbg && (tid & 31) == 0) scr.dbg[45] = globaltimer_ns();
     }
   }
   stream_drain_on_abort<G>(cv.sm);
@@ -1053,14 +1029,14 @@ static size_t plan_smem(StreamShape& sh, size_t tail_bytes, int max_groups = 1) 
   }
   const size_t fixed = smem_fixed_bytes<G>(sh);
   if (fixed + 2 * G::STAGE_BYTES > static_cast<size_t>(kSmemLimit)) return 0;
-  // About 96 KB in flight per SM saturates HBM; a deeper ring measured slower.
+  // Ring depth: a bare copy loop saturates HBM with ~96 KB in flight per SM, but the
+  // consumers hold a stage or two while they work on it; measured on the layer's kernels,
+  // 160 KB is where more depth stops paying (96 KB: Gate 46 us, 160 KB: 42 us).
   int stages = static_cast<int>((kSmemLimit - fixed) / G::STAGE_BYTES);
-  const int want = (96 * 1024 + G::STAGE_BYTES - 1) / G::STAGE_BYTES;
+  const int want = (160 * 1024 + G::STAGE_BYTES - 1) / G::STAGE_BYTES;
   if (stages > want) stages = want;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (const char* e = getenv("IQB_STAGES")) { const int v = atoi(e); if (v >= 2 && v < stages) stages = v; }
   sh.n_stages = stages;
-  if (const char* e = getenv("IQB_DEBUG")) sh.debug = atoi(e);
   size_t need = fixed + static_cast<size_t>(stages) * G::STAGE_BYTES;
   if (need < fixed + tail_bytes) need = fixed + tail_bytes;
   return need <= static_cast<size_t>(kSmemLimit) ? need : 0;
@@ -1071,7 +1047,8 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 static int check_tail(const iq_tail_args* t) {
   if (!t) return IQ_OK;
   if (t->kind != IQ_TAIL_ATTN && t->kind != IQ_TAIL_MLP) return IQ_ERR_ARG;
-  if (t->m < 1 || t->m > 8 || t->h < 128 || t->h % 128) return IQ_ERR_ARG;
+  if (t->m < 1 || t->m > 8 || t->h < 128 || t->h % 128 || t->h > 8 * kTailVecs * kThreads)
+    return IQ_ERR_ARG;
   if (!t->partial || !t->residual || !t->w_norm || !t->h_out || !t->norm_out) return IQ_ERR_ARG;
   if (t->kind == IQ_TAIL_ATTN && !t->w_first) return IQ_ERR_ARG;
   if (t->world < 1 || t->rank < 0 || t->rank >= t->world) return IQ_ERR_ARG;

@@ -94,7 +94,6 @@ struct StreamShape {
   int x_blocks;        // activation scale entries per staged row (k / 128)
   int n_stages;        // ring depth
   int max_items;       // most stages one CTA can own (sizes the shared scale table)
-  int debug;           // experiment switch: 1 = consumers skip the math
 };
 
 // Scratch owned by the caller (zero-filled once; every launch leaves it zeroed again).
@@ -103,7 +102,6 @@ struct StreamScratch {
   uint32_t* tile_counter; // [tiles]
   uint32_t* ticket;       // [1]
   int* status;            // [1] first error code of any launch using this scratch
-  long long* dbg;         // experiments only: per-CTA cycle counters (null otherwise)
 };
 
 __device__ __forceinline__ void set_status(int* status, int code) {
@@ -240,7 +238,7 @@ __device__ __forceinline__ StagePos stage_pos(const StreamShape& sh, const CtaWo
 template <class G>
 __device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm, uint8_t* ring,
                                         const CtaWork& w, int* status, const CUtensorMap* map0,
-                                        const CUtensorMap* map1, long long* dbg = nullptr) {
+                                        const CUtensorMap* map1) {
   const int lane = threadIdx.x & 31;
   int slot = 0;
   uint32_t phase = 0;
@@ -250,16 +248,12 @@ __device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm
   const int copy_rows = halves == 2 ? kHalfRows : G::ROWS;
   int tile = w.tile0, s = w.stage0;
   StagePos p = stage_pos(sh, w, tile, s);
-  long long dbg_wait = 0;
-  const long long dbg_t0 = dbg ? clock64() : 0;
   for (int n = 0; n < w.n_items; ++n) {
-    const long long c0 = dbg ? clock64() : 0;
     if (!mbar_wait(&sm->empty[slot], phase ^ 1u)) {
       set_status(status, IQ_ERR_PIPE_TIMEOUT);
       sm->abort_flag = 1;
       return;
     }
-    if (dbg) dbg_wait += clock64() - c0;
     if (lane == 0) {
       const GroupDesc& gd = sm->groups[p.group];
       uint64_t* bar = &sm->full[slot];
@@ -290,11 +284,6 @@ __device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm
       p.kstage = 0;
       ++p.group;
     }
-  }
-  if (dbg && lane == 0) {
-    dbg[0] = dbg_wait;
-    dbg[1] = clock64() - dbg_t0;
-    dbg[2] = w.n_items;
   }
 }
 
@@ -460,8 +449,6 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   uint32_t wsc = smem_u32(sc) + warp * G::RUNS * 4;
   const uint32_t ring_s = smem_u32(ring), xq_s = smem_u32(xq), xs_s = smem_u32(xs);
-  long long dbg_wait = 0, dbg_tile = 0;
-  const long long dbg_t0 = scr.dbg ? clock64() : 0;
   int tile = w.tile0, s = w.stage0, left = w.n_items;
   while (left > 0) {
     const int s_begin = s;
@@ -474,16 +461,12 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
       if (s_end - s < ks_end - p.kstage) ks_end = p.kstage + (s_end - s);
       for (int ks = p.kstage; ks < ks_end; ++ks, ++s) {
         bool ok = true;
-        const long long c0 = scr.dbg ? clock64() : 0;
-        const bool waited = mbar_wait(&sm->full[slot], phase);
-        if (scr.dbg) dbg_wait += clock64() - c0;
-        if (scr.dbg && tid == 0 && s == w.stage0 && tile == w.tile0) scr.dbg[46] = globaltimer_ns();
-        if (!waited) {   // fails at once after an abort
+        if (!mbar_wait(&sm->full[slot], phase)) {   // fails at once after an abort
           set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
           sm->abort_flag = 1;
           ok = false;
         }
-        if (ok && !(sh.debug & 1))
+        if (ok)
           consume_stage<G, E>(ring_s + slot * G::STAGE_BYTES + a_off, gc, ks * G::KC, kwarp0, wsc,
                               acc);
         __syncwarp();
@@ -495,7 +478,6 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
       ++p.group;        // kConcatK: next group's K; kRowsPerGroup: loop ends here
     }
     left -= s_end - s_begin;
-    const long long dbg_c1 = scr.dbg ? clock64() : 0;
 
     // ---- the CTA's share of this tile is complete: hand the warp's partial to the
     // epilogue warp and go straight on to the next tile.
@@ -511,12 +493,6 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
     if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
     s = 0;
     ++tile;
-    if (scr.dbg) dbg_tile += clock64() - dbg_c1;
-  }
-  if (scr.dbg && (tid & 31) == 0 && warp < 8) {
-    scr.dbg[4 + warp * 3 + 0] = dbg_wait;
-    scr.dbg[4 + warp * 3 + 1] = dbg_tile;
-    scr.dbg[4 + warp * 3 + 2] = clock64() - dbg_t0;
   }
 }
 
