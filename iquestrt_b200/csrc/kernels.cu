@@ -230,69 +230,18 @@ __device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/, float
   const int m = a.m, h = a.h, vec_per_row = h / 8;
   const float inv_h = 1.0f / static_cast<float>(h);
 
-  // ---- cross-rank readiness
-  if (a.world > 1) {
-    if (tid == 0) {
-      const uint32_t target = (*a.epoch + 1u) * static_cast<uint32_t>(a.world);
-      __threadfence_system();
-      if (a.arrive_mc) {
-        multimem_red_add_release_u32(a.arrive_mc, 1u);
-      } else {
-        for (int p = 0; p < a.world; ++p)
-          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_arrive[p]), "r"(1u)
-                       : "memory");
-      }
-      const uint64_t budget = 1000000ull * (a.timeout_ms ? a.timeout_ms : 2000u);
-      uint64_t t0 = 0;
-      int ok = 1;
-      for (uint32_t spin = 0;; ++spin) {
-        if (static_cast<int32_t>(ld_acquire_sys_u32(a.arrive) - target) >= 0) break;
-        if ((spin & 255u) == 255u) {
-          const uint64_t now = globaltimer_ns();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > budget) { ok = 0; break; }
-        }
-      }
-      if (!ok) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
-      *sflag = ok;
-    }
-    __syncthreads();
-    if (!*sflag) {
-      // Peers are missing: leave the outputs untouched and let the host read the status.
-      if (tid == 0) *a.epoch = *a.epoch + 1u;
-      return;
-    }
-  }
-
   for (int r = 0; r < m; ++r) {
     const size_t row_off = static_cast<size_t>(r) * h;
     float* slots0 = red + (r & 1) * 64;        // two reductions per row, alternating rows
     float* slots1 = slots0 + 32;
     TailRow row;
     float w1[kTailVecs][8], w2[kTailVecs][8];
-    // ---- every load of the row, issued together
+    // ---- the row's local loads (residual, norm weights), issued together
 #pragma unroll
     for (int i = 0; i < kTailVecs; ++i) {
       const int v = tid + i * nthr;
       if (v >= vec_per_row) continue;
       const size_t off = row_off + static_cast<size_t>(v) * 8;
-      if (a.world == 1) {
-        const uint4 t = __ldcg(reinterpret_cast<const uint4*>(
-            static_cast<const __nv_bfloat16*>(a.partial) + off));
-        row.part[i] = U4{t.x, t.y, t.z, t.w};
-      } else if (a.partial_mc) {
-        row.part[i] = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(a.partial_mc) + off);
-      } else {
-        float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int p = 0; p < a.world; ++p) {
-          const U4 t = ld_global_u4(static_cast<const __nv_bfloat16*>(a.peer_partials[p]) + off);
-          float f[8];
-          bf16x8_to_f32(t, f);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) accv[j] += f[j];
-        }
-        row.part[i] = f32_to_bf16x8(accv);
-      }
       if (a.residual_fp32) {
         const float* rp = static_cast<const float*>(a.residual) + off;
         const float4 r0 = *reinterpret_cast<const float4*>(rp);
@@ -315,6 +264,69 @@ __device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/, float
       const float4 y1 = __ldg(reinterpret_cast<const float4*>(a.w_norm + c0 + 4));
       w2[i][0] = y0.x; w2[i][1] = y0.y; w2[i][2] = y0.z; w2[i][3] = y0.w;
       w2[i][4] = y1.x; w2[i][5] = y1.y; w2[i][6] = y1.z; w2[i][7] = y1.w;
+    }
+    // ---- cross-rank readiness: signal, then wait while this row's local loads are in flight
+    if (r == 0 && a.world > 1) {
+      if (tid == 0) {
+        const uint32_t target = (*a.epoch + 1u) * static_cast<uint32_t>(a.world);
+        if (a.arrive_mc) {
+          multimem_red_add_release_u32(a.arrive_mc, 1u);
+        } else {
+          for (int p = 0; p < a.world; ++p)
+            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_arrive[p]), "r"(1u)
+                         : "memory");
+        }
+        const uint64_t budget = 1000000ull * (a.timeout_ms ? a.timeout_ms : 2000u);
+        uint64_t t0 = 0;
+        int ok = 1;
+        for (uint32_t spin = 0;; ++spin) {
+          if (static_cast<int32_t>(ld_acquire_sys_u32(a.arrive) - target) >= 0) break;
+          if ((spin & 255u) == 255u) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > budget) { ok = 0; break; }
+          }
+        }
+        if (!ok) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
+        *sflag = ok;
+      }
+      __syncthreads();
+      if (!*sflag) {
+        // Peers are missing: leave the outputs untouched and let the host read the status.
+        if (tid == 0) *a.epoch = *a.epoch + 1u;
+        return;
+      }
+    }
+    // ---- the reduced partial
+#pragma unroll
+    for (int i = 0; i < kTailVecs; ++i) {
+      const int v = tid + i * nthr;
+      if (v >= vec_per_row) continue;
+      const size_t off = row_off + static_cast<size_t>(v) * 8;
+      if (a.world == 1) {
+        const uint4 t = __ldcg(reinterpret_cast<const uint4*>(
+            static_cast<const __nv_bfloat16*>(a.partial) + off));
+        row.part[i] = U4{t.x, t.y, t.z, t.w};
+      } else if (a.partial_mc) {
+        row.part[i] = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(a.partial_mc) + off);
+      } else {
+        // all peers' vectors in flight together, then summed in rank order
+        U4 pv[8];
+#pragma unroll
+        for (int p = 0; p < 8; ++p)
+          if (p < a.world)
+            pv[p] = ld_global_u4(static_cast<const __nv_bfloat16*>(a.peer_partials[p]) + off);
+        float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          if (p >= a.world) continue;
+          float f[8];
+          bf16x8_to_f32(pv[p], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) accv[j] += f[j];
+        }
+        row.part[i] = f32_to_bf16x8(accv);
+      }
     }
 
     float f[kTailVecs][8], hv[kTailVecs][8];
@@ -1051,7 +1063,7 @@ static int check_tail(const iq_tail_args* t) {
     return IQ_ERR_ARG;
   if (!t->partial || !t->residual || !t->w_norm || !t->h_out || !t->norm_out) return IQ_ERR_ARG;
   if (t->kind == IQ_TAIL_ATTN && !t->w_first) return IQ_ERR_ARG;
-  if (t->world < 1 || t->rank < 0 || t->rank >= t->world) return IQ_ERR_ARG;
+  if (t->world < 1 || t->world > 8 || t->rank < 0 || t->rank >= t->world) return IQ_ERR_ARG;
   if (t->world > 1) {
     if (!t->arrive || !t->epoch) return IQ_ERR_ARG;
     if (!t->arrive_mc && !t->peer_arrive) return IQ_ERR_ARG;

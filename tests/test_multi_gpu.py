@@ -34,7 +34,7 @@ def _run(nproc, *args, env=None, timeout=600):
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=full_env)
     sys.stdout.write(proc.stdout[-4000:])
     if proc.returncode != 0:
-        sys.stderr.write(proc.stderr[-6000:])
+        sys.stdout.write("---- worker stderr ----\n" + proc.stderr[-8000:])
     return proc.returncode
 
 
