@@ -231,6 +231,42 @@ __device__ __forceinline__ StagePos stage_pos(const StreamShape& sh, const CtaWo
   return p;
 }
 
+// The order in which a CTA visits the tiles of its item range.  A tile the CTA shares with
+// its neighbour costs serial global round trips to finish (publish, count, sum), so the
+// shared tile at the END of the range is visited FIRST: by the time the CTA reaches its
+// last tiles, which are whole and are emitted directly, every shared tile has long been
+// settled by both of its owners.  The producer, the consumers and the epilogue warp all
+// walk the same sequence.
+struct TileVisit {
+  int tile;      // tile index
+  int s_begin;   // stage range [s_begin, s_end) of the tile owned by this CTA
+  int s_end;
+  int local0;    // position of stage s_begin in the CTA's natural stage order
+};
+
+struct TileWalk {
+  int n_tiles;       // tiles touched
+  int n_first;       // stages owned in the first touched tile
+  bool last_first;   // visit the last touched tile before the others
+  __device__ __forceinline__ void init(const CtaWork& w) {
+    if (w.n_items <= 0) { n_tiles = 0; n_first = 0; last_first = false; return; }
+    n_first = w.spt - w.stage0 < w.n_items ? w.spt - w.stage0 : w.n_items;
+    const int rest = w.n_items - n_first;
+    n_tiles = 1 + (rest + w.spt - 1) / w.spt;
+    last_first = n_tiles >= 2 && (rest % w.spt) != 0;
+  }
+  __device__ __forceinline__ TileVisit visit(const CtaWork& w, int k) const {
+    const int i = last_first ? (k == 0 ? n_tiles - 1 : k - 1) : k;   // natural index
+    TileVisit v;
+    v.tile = w.tile0 + i;
+    v.s_begin = i == 0 ? w.stage0 : 0;
+    v.local0 = i == 0 ? 0 : n_first + (i - 1) * w.spt;
+    const int avail = w.n_items - v.local0;
+    v.s_end = w.spt - v.s_begin < avail ? w.spt : v.s_begin + avail;
+    return v;
+  }
+};
+
 // ------------------------------------------------------------------------------------
 // Producer: one elected lane of one warp, one or two copies per stage.  `map0/map1` are the
 // launch's tensor maps (u32 elements, box = KC bytes x box rows), used when a stage is a
@@ -246,43 +282,42 @@ __device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm
   const int halves = sh.pair_half > 0 ? 2 : 1;
   constexpr int kHalfRows = G::ROWS / 2;
   const int copy_rows = halves == 2 ? kHalfRows : G::ROWS;
-  int tile = w.tile0, s = w.stage0;
-  StagePos p = stage_pos(sh, w, tile, s);
-  for (int n = 0; n < w.n_items; ++n) {
-    if (!mbar_wait(&sm->empty[slot], phase ^ 1u)) {
-      set_status(status, IQ_ERR_PIPE_TIMEOUT);
-      sm->abort_flag = 1;
-      return;
-    }
-    if (lane == 0) {
-      const GroupDesc& gd = sm->groups[p.group];
-      uint64_t* bar = &sm->full[slot];
-      mbar_arrive_expect_tx(bar, G::ROWS * G::KC);
-      uint8_t* dst = ring + slot * G::STAGE_BYTES;
-      for (int hf = 0; hf < halves; ++hf) {
-        const int row = tile_row(sh, G::ROWS, p.tig, hf * kHalfRows);
-        if (whole_rows) {
-          bulk_g2s(dst + hf * kHalfRows * G::PITCH, gd.w + static_cast<size_t>(row) * sh.k_bytes,
-                   copy_rows * G::KC, bar);
-        } else {
+  TileWalk walk;
+  walk.init(w);
+  for (int k = 0; k < walk.n_tiles; ++k) {
+    const TileVisit tv = walk.visit(w, k);
+    StagePos p = stage_pos(sh, w, tv.tile, tv.s_begin);
+    for (int s = tv.s_begin; s < tv.s_end; ++s) {
+      if (!mbar_wait(&sm->empty[slot], phase ^ 1u)) {
+        set_status(status, IQ_ERR_PIPE_TIMEOUT);
+        sm->abort_flag = 1;
+        return;
+      }
+      if (lane == 0) {
+        const GroupDesc& gd = sm->groups[p.group];
+        uint64_t* bar = &sm->full[slot];
+        mbar_arrive_expect_tx(bar, G::ROWS * G::KC);
+        uint8_t* dst = ring + slot * G::STAGE_BYTES;
+        for (int hf = 0; hf < halves; ++hf) {
+          const int row = tile_row(sh, G::ROWS, p.tig, hf * kHalfRows);
+          if (whole_rows) {
+            bulk_g2s(dst + hf * kHalfRows * G::PITCH,
+                     gd.w + static_cast<size_t>(row) * sh.k_bytes, copy_rows * G::KC, bar);
+          } else {
 #pragma unroll
-          for (int b = 0; b < G::NBOX; ++b)
-            tma_2d_g2s(dst + b * (G::ROWS * G::BOXK) + hf * kHalfRows * G::PITCH,
-                       gd.map_id ? map1 : map0, p.kstage * (G::KC / 4) + b * (G::BOXK / 4),
-                       gd.row_base + row, bar);
+            for (int b = 0; b < G::NBOX; ++b)
+              tma_2d_g2s(dst + b * (G::ROWS * G::BOXK) + hf * kHalfRows * G::PITCH,
+                         gd.map_id ? map1 : map0, p.kstage * (G::KC / 4) + b * (G::BOXK / 4),
+                         gd.row_base + row, bar);
+          }
         }
       }
-    }
-    __syncwarp();
-    if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
-    // next item
-    if (++s == w.spt) {
-      s = 0;
-      ++tile;
-      p = stage_pos(sh, w, tile, 0);
-    } else if (++p.kstage == w.kstages) {   // only reachable in kConcatK mode
-      p.kstage = 0;
-      ++p.group;
+      __syncwarp();
+      if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
+      if (++p.kstage == w.kstages) {   // kConcatK: on to the next group's K
+        p.kstage = 0;
+        ++p.group;
+      }
     }
   }
 }
@@ -447,13 +482,16 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
   int red_buf = 0;
   uint32_t red_phase = 0;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  uint32_t wsc = smem_u32(sc) + warp * G::RUNS * 4;
+  const uint32_t sc_s = smem_u32(sc) + warp * G::RUNS * 4;
   const uint32_t ring_s = smem_u32(ring), xq_s = smem_u32(xq), xs_s = smem_u32(xs);
-  int tile = w.tile0, s = w.stage0, left = w.n_items;
-  while (left > 0) {
-    const int s_begin = s;
-    const int s_end = (w.spt - s < left) ? w.spt : s + left;
-    StagePos p = stage_pos(sh, w, tile, s);
+  TileWalk walk;
+  walk.init(w);
+  for (int k = 0; k < walk.n_tiles; ++k) {
+    const TileVisit tv = walk.visit(w, k);
+    uint32_t wsc = sc_s + tv.local0 * (G::SCALES_PER_STAGE * 4);
+    int s = tv.s_begin;
+    const int s_end = tv.s_end;
+    StagePos p = stage_pos(sh, w, tv.tile, s);
     // ---- stages [s_begin, s_end) of this tile, group by group
     while (s < s_end) {
       const GroupCtx gc = group_ctx<G>(sh, sm->groups[p.group], xq_s, xs_s, warp, lane);
@@ -477,7 +515,6 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
       p.kstage = 0;
       ++p.group;        // kConcatK: next group's K; kRowsPerGroup: loop ends here
     }
-    left -= s_end - s_begin;
 
     // ---- the CTA's share of this tile is complete: hand the warp's partial to the
     // epilogue warp and go straight on to the next tile.
@@ -491,8 +528,6 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
     __syncwarp();
     if (lane == 0) mbar_arrive(&sm->red_full[red_buf]);
     if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
-    s = 0;
-    ++tile;
   }
 }
 
@@ -511,11 +546,12 @@ __device__ __forceinline__ void epilogue(const StreamShape& sh, StreamSmem<G>* s
   const bool concat = sh.mode != kRowsPerGroup;
   int red_buf = 0;
   uint32_t red_phase = 0;
-  int tile = w.tile0, s = w.stage0, left = w.n_items;
-  while (left > 0) {
-    const int s_end = (w.spt - s < left) ? w.spt : s + left;
-    const bool whole = s == 0 && s_end == w.spt;
-    left -= s_end - s;
+  TileWalk walk;
+  walk.init(w);
+  for (int k = 0; k < walk.n_tiles; ++k) {
+    const TileVisit tv = walk.visit(w, k);
+    const int tile = tv.tile;
+    const bool whole = tv.s_begin == 0 && tv.s_end == w.spt;
     TileId id;
     id.tile = tile;
     id.group = concat ? 0 : tile / w.tpg;
@@ -586,8 +622,6 @@ __device__ __forceinline__ void epilogue(const StreamShape& sh, StreamSmem<G>* s
         for (int j = 0; j < 4; ++j) emit(id, (lane + 32 * j) >> 3, (lane + 32 * j) & 7, val[j]);
       }
     }
-    s = 0;
-    ++tile;
   }
 }
 
