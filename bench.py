@@ -49,6 +49,9 @@ def parse_args():
     ap.add_argument("--experts", type=int, default=256,
                     help="routed experts in the bank (smaller banks keep profiler captures "
                          "small; a step still streams top-k routed + the shared expert)")
+    ap.add_argument("--launches", type=int, default=4, choices=(1, 4),
+                    help="kernel launches per layer: the four fused kernels, or the one-launch "
+                         "cooperative layer (same results bit for bit)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-multicast", action="store_true",
                     help="all-reduce over plain peer loads instead of NVLS multimem")
@@ -223,9 +226,11 @@ def run_ours(args):
               for i in range(n_inputs)]
     K, W = max(1, args.steps), max(3, args.warmup)
 
+    one_launch = args.launches == 1
+
     def call(i, **kw):
         ao, res = inputs[i % n_inputs]
-        return layer.step(ao, res, weights[i % n_layers], **kw)
+        return layer.step(ao, res, weights[i % n_layers], one_launch=one_launch, **kw)
 
     def barrier():
         if tp > 1:
@@ -322,7 +327,7 @@ def run_ours(args):
             ao, res = h_in[i % n_inputs]
             d_ao.copy_(ao, non_blocking=True)
             d_res.copy_(res, non_blocking=True)
-            out, _ = layer.step(d_ao, d_res, weights[i % n_layers])
+            out, _ = layer.step(d_ao, d_res, weights[i % n_layers], one_launch=one_launch)
             h_out.copy_(out, non_blocking=True)
             stream.synchronize()
 
@@ -365,7 +370,7 @@ def run_ours(args):
             "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": tp, "steps": K, "warmup": W,
             "ms_per_step": ms / K, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "e4m3 x e4m3 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "rows": rows, "tp": tp, "launches_per_step": 4,
+            "config": {"workload": WORKLOAD, "rows": rows, "tp": tp, "launches_per_step": args.launches,
                        "experts_in_bank": args.experts,
                        "l2": f"weights rotate over {n_layers} distinct layers "
                              f"({by['total'] * n_layers / 1e6:.0f} MB touched per cycle, L2 is 126 MB)",
@@ -375,7 +380,7 @@ def run_ours(args):
             "e2e": {"value": e2e_ms * 1e3 / n_e2e, "unit": UNIT, "steps": n_e2e,
                     "h2d_bytes_per_step": int(d_ao.numel() * 2 + d_res.numel() * 2),
                     "d2h_bytes_per_step": int(h_out.numel() * 2)},
-            "gpu_launches": 4 * K,
+            "gpu_launches": args.launches * K,
             "roofline": {"bound": "hbm", "kernel": "gate_kernel (expert Gate/Up + SiLU)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind,

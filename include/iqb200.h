@@ -214,6 +214,34 @@ typedef struct iq_moe_down_args {
 
 int iq_moe_down(const iq_moe_down_args* a, void* stream);
 
+/* The whole layer of the path in ONE launch: exactly the work of
+ *   iq_linear(oproj, with its attention tail) -> iq_router -> iq_moe_gate ->
+ *   iq_moe_down(with its MLP tail)
+ * on the same arguments, with bit-identical results, but the four weight streams run
+ * back to back through one shared-memory ring and the steps between them (all-reduce
+ * tails, top-k) cost a grid-wide hand-off instead of a kernel boundary.  Replaces the
+ * chain of ten programmatically dependent launches Engine._layer issues per MoE layer
+ * (iquestrt/engine.py:387-450).
+ *
+ * Both tails are required (oproj->tail of kind IQ_TAIL_ATTN, down->tail of kind
+ * IQ_TAIL_MLP, timeout_ms <= 3000).  The four structs must agree on m, h, i_loc, top_k,
+ * n_experts, n_shared, act_kind and scratch, and each part must read what the part before
+ * it writes (router.x == oproj.tail->norm_out, gate.x_fp8 / x_scale == oproj.tail->norm_fp8 /
+ * norm_fp8_scale, gate.sel == down.sel == router.sel, down.wt == router.wt, down.act ==
+ * gate.act); the `pdl` fields inside them are ignored and `pdl` here applies to the one
+ * launch.  Shapes: oproj k % 1024 == 0, h % 1024 == 0,
+ * i_loc % 256 == 0.  The CTAs of this launch wait on one another, so it is launched
+ * cooperatively; it returns IQ_ERR_UNSUPPORTED when one CTA per SM cannot be resident.
+ * After a device-side error (status word != 0) zero the scratch before the next call. */
+typedef struct iq_decode_layer_args {
+  iq_linear_args oproj;
+  iq_router_args router;
+  iq_moe_gate_args gate;
+  iq_moe_down_args down;
+} iq_decode_layer_args;
+
+int iq_decode_layer(const iq_decode_layer_args* a, void* stream, int pdl);
+
 #ifdef __cplusplus
 }
 #endif

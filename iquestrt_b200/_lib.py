@@ -25,7 +25,7 @@ ROUTE_SOFTMAX, ROUTE_SIGMOID = range(2)
 ACT_E4M3, ACT_BF16 = range(2)
 
 EXPORTS = ("iq_scratch_bytes", "iq_status_read", "iq_sm_count", "iq_tail", "iq_linear",
-           "iq_linear_static", "iq_router", "iq_moe_gate", "iq_moe_down")
+           "iq_linear_static", "iq_router", "iq_moe_gate", "iq_moe_down", "iq_decode_layer")
 
 
 class IqError(RuntimeError):
@@ -90,6 +90,11 @@ class MoeDownArgs(C.Structure):
     ]
 
 
+class DecodeLayerArgs(C.Structure):
+    _fields_ = [("oproj", LinearArgs), ("router", RouterArgs), ("gate", MoeGateArgs),
+                ("down", MoeDownArgs)]
+
+
 _LIB = None
 
 
@@ -121,6 +126,8 @@ def load() -> C.CDLL:
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(struct), C.c_void_p]
+        lib.iq_decode_layer.restype = C.c_int
+        lib.iq_decode_layer.argtypes = [C.POINTER(DecodeLayerArgs), C.c_void_p, C.c_int]
         _LIB = lib
     return _LIB
 

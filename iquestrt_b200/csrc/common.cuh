@@ -66,18 +66,22 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: returns false when the phase has not completed about one second after
-// the wait began.  The timer is read only once per 1024 failed tests: a %globaltimer
+// Bounded wait: returns false when the phase has not completed within kPipeBudgetNs of the
+// start of the wait, or as soon as `*abort` is seen non-zero (another role of the CTA gave
+// up).  The timer and the flag are read only once per 1024 failed tests: a %globaltimer
 // read costs far more than a test, and the common case succeeds within a few tests.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+constexpr uint64_t kPipeBudgetNs = 4000000000ull;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          const volatile int* abort = nullptr) {
   uint64_t t0 = 0;
 #pragma unroll 1
   for (uint32_t spin = 0;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 1023u) == 1023u) {
+      if (abort && *abort) return false;
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > 1000000000ull) return false;
+      else if (now - t0 > kPipeBudgetNs) return false;
     }
   }
 }
@@ -110,6 +114,14 @@ __device__ __forceinline__ void bulk_g2s_evict_first(void* dst, const void* src,
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
       "[%0], [%1], %2, [%3], %4;"
       ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_2d_g2s_evict_first(void* dst, const CUtensorMap* map, int x,
+                                                       int y, uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ uint64_t policy_evict_first() {
@@ -152,6 +164,11 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Counts the calling warp in on the barrier without waiting for it.
+__device__ __forceinline__ void named_bar_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // ---------------------------------------------------------------- NVLS / system scope
 struct U4 {
   uint32_t x, y, z, w;
@@ -187,6 +204,26 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+// Self-validating words: a payload and the tag of the launch that wrote it travel in one
+// naturally aligned scalar store, so a reader that sees the tag has the payload, with no
+// fence on the writer's side and no separate flag.
+__device__ __forceinline__ void st_relaxed_gpu_u64(uint64_t* p, uint64_t v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_gpu_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_relaxed_gpu_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void ld_relaxed_gpu_u32x4(const uint32_t* p, uint32_t (&v)[4]) {
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+               : "l"(p)
+               : "memory");
 }
 __device__ __forceinline__ U4 ld_global_u4(const void* p) {
   U4 v;

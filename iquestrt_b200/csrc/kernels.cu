@@ -25,7 +25,12 @@ constexpr size_t kScrCounters = 256;
 constexpr int kMaxTiles = 16384;
 constexpr size_t kScrPartials = kScrCounters + sizeof(uint32_t) * kMaxTiles;
 constexpr int kMaxGrid = 256;
-constexpr size_t kScrBytes = kScrPartials + sizeof(float) * kMaxGrid * 2 * 256 * 8;
+constexpr size_t kScrBasicBytes = kScrPartials + sizeof(float) * kMaxGrid * 2 * 256 * 8;
+// The one-launch layer keeps its tagged hand-off words in an area of their own behind the
+// basic scratch: the other kernels never write there, so a word can only carry a tag that
+// a one-launch layer gave it.
+constexpr size_t kScrLayerBytes = 3 * 1024 * 1024 + 256 * 1024;
+constexpr size_t kScrBytes = kScrBasicBytes + kScrLayerBytes;
 
 __host__ __device__ inline StreamScratch scratch_of(void* base) {
   StreamScratch s;
@@ -74,7 +79,9 @@ __device__ inline Carve<G> carve(uint8_t* base, const StreamShape& sh) {
 // Activation staging (consumer threads only, tid in [0, 256)).
 
 // Both routines issue a batch of independent 16-byte global loads before touching any of
-// them, so a row set costs about one memory latency instead of one per group.
+// them, so a row set costs about one memory latency instead of one per group.  The loads
+// bypass L1 (ld.global.cg): in the one-launch layer the rows were written by another CTA
+// of the same launch.
 constexpr int kStageBatch = 8;
 
 // Raw e4m3 rows (16-byte vectors) + their scales (or 1).
@@ -85,19 +92,21 @@ __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape
   // the first activation scale of this thread rides along with the first batch of loads
   const int nxs = rows * sh.x_blocks;
   float xs_first = 1.0f;
-  if (src_scale && tid < nxs) xs_first = __ldg(src_scale + tid);
+  if (src_scale && tid < nxs) xs_first = __ldcg(src_scale + tid);
   for (int v0 = 0; v0 < nvec; v0 += kConsumerThreads * kStageBatch) {
     uint4 raw[kStageBatch];
 #pragma unroll
     for (int j = 0; j < kStageBatch; ++j) {
+      if (v0 + j * kConsumerThreads >= nvec) break;   // same for every thread
       const int i = v0 + j * kConsumerThreads + tid;
       if (i < nvec) {
         const int r = i / vec, v = i - r * vec;
-        raw[j] = __ldg(reinterpret_cast<const uint4*>(src + r * src_pitch + v * 16));
+        raw[j] = __ldcg(reinterpret_cast<const uint4*>(src + r * src_pitch + v * 16));
       }
     }
 #pragma unroll
     for (int j = 0; j < kStageBatch; ++j) {
+      if (v0 + j * kConsumerThreads >= nvec) break;
       const int i = v0 + j * kConsumerThreads + tid;
       if (i < nvec) {
         const int r = i / vec, v = i - r * vec;
@@ -107,7 +116,7 @@ __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape
   }
   if (tid < nxs) xs[tid] = xs_first;
   for (int i = tid + kConsumerThreads; i < nxs; i += kConsumerThreads)
-    xs[i] = src_scale ? src_scale[i] : 1.0f;
+    xs[i] = src_scale ? __ldcg(src_scale + i) : 1.0f;
 }
 
 // bf16 rows quantised per 1x128 group: scale = amax/448 (1 for an all-zero group), value
@@ -122,15 +131,17 @@ __device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const Stre
     uint4 raw[kStageBatch];
 #pragma unroll
     for (int j = 0; j < kStageBatch; ++j) {
+      if (v0 + j * kConsumerThreads >= nvec) break;   // same for every thread
       const int i = v0 + j * kConsumerThreads + tid;
       raw[j] = make_uint4(0u, 0u, 0u, 0u);
       if (i < nvec) {
         const int r = i / vec, v = i - r * vec;
-        raw[j] = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * src_pitch + v * 8));
+        raw[j] = __ldcg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * src_pitch + v * 8));
       }
     }
 #pragma unroll
     for (int j = 0; j < kStageBatch; ++j) {
+      if (v0 + j * kConsumerThreads >= nvec) break;    // whole batch dead: nothing to do
       const int i = v0 + j * kConsumerThreads + tid;   // uniform trip count: shuffles below
       const bool live = i < nvec;
       const int ii = live ? i : 0;
@@ -200,43 +211,59 @@ __device__ inline U4 f32_to_bf16x8(const float (&f)[8]) {
 }
 __device__ inline float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// The threads that run a block-wide helper together: the whole CTA (n == 0), or threads
+// [0, n) of it meeting on named barrier `id` while the CTA's other warps do something else.
+struct BlockBar {
+  int id = 0, n = 0;
+  __device__ __forceinline__ void sync() const {
+    if (n == 0) __syncthreads();
+    else named_bar_sync(id, n);
+  }
+  __device__ __forceinline__ int threads() const { return n == 0 ? static_cast<int>(blockDim.x) : n; }
+};
+
 // Block-wide sum with one barrier: every warp drops its sum into `slots`, every thread
 // adds the slots up in warp order.  Consecutive calls must alternate `slots` buffers.
-__device__ inline float block_sum(float v, float* slots) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+__device__ inline float block_sum(float v, float* slots, const BlockBar& bar) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = bar.threads() >> 5;
   v = warp_sum(v);
   if (lane == 0) slots[warp] = v;
-  __syncthreads();
+  bar.sync();
   float s = 0.f;
   for (int w = 0; w < nwarps; ++w) s += slots[w];
   return s;
 }
 
-constexpr int kTailVecs = 2;   // 16-byte vectors of a row per thread: h <= 8 * 2 * blockDim
+constexpr int kTailVecs = 2;   // 16-byte vectors of a row per thread: h <= 8 * 2 * threads
 
-struct TailRow {
-  U4 part[kTailVecs];       // reduced partial (bf16 x 8)
-  float res[kTailVecs][8];  // residual
-};
+__device__ __forceinline__ void ldg_f32x8(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(p + 4));
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
 
-// Runs on every thread of one CTA (blockDim a multiple of 32, h <= 16 * blockDim).  `red`
-// is shared memory for 4 x 32 floats, `sflag` one shared int.  Rows written by other CTAs
-// of this launch must already be visible (the caller passed the ticket).  Rows are
-// handled one after the other, each entirely in registers: all of a row's global loads
-// are issued before the first is used, and each RMSNorm costs one block barrier.
-__device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/, float* red,
-                         int* sflag) {
-  const int tid = threadIdx.x, nthr = blockDim.x;
+// Runs on the threads of `bar` (a multiple of 32; h <= 16 * threads).  `red` is shared
+// memory for 4 x 32 floats, `sflag` one shared int.  Rows written by other CTAs of this
+// launch must already be visible (the caller passed the ticket).  Rows are handled one
+// after the other, each entirely in registers, and each RMSNorm costs one block barrier.
+// The kernels this runs in keep almost all of the SM's L1 as shared memory, so a spilled
+// register would cost an L2 round trip: the loads are ordered to keep few values live
+// (the residual stays packed until it is used; each norm weight is fetched just before
+// the barrier of the reduction that precedes its use, which hides its latency).
+__device__ __forceinline__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/,
+                                         float* red, int* sflag, const BlockBar bar = BlockBar{}) {
+  const int tid = threadIdx.x, nthr = bar.threads();
   const int m = a.m, h = a.h, vec_per_row = h / 8;
   const float inv_h = 1.0f / static_cast<float>(h);
+  const bool attn = a.kind == IQ_TAIL_ATTN;
 
   for (int r = 0; r < m; ++r) {
     const size_t row_off = static_cast<size_t>(r) * h;
     float* slots0 = red + (r & 1) * 64;        // two reductions per row, alternating rows
     float* slots1 = slots0 + 32;
-    TailRow row;
-    float w1[kTailVecs][8], w2[kTailVecs][8];
-    // ---- the row's local loads (residual, norm weights), issued together
+    // ---- the row's residual, issued before the cross-rank wait and kept packed
+    uint4 res_raw[kTailVecs][2];
 #pragma unroll
     for (int i = 0; i < kTailVecs; ++i) {
       const int v = tid + i * nthr;
@@ -244,28 +271,14 @@ __device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/, float
       const size_t off = row_off + static_cast<size_t>(v) * 8;
       if (a.residual_fp32) {
         const float* rp = static_cast<const float*>(a.residual) + off;
-        const float4 r0 = *reinterpret_cast<const float4*>(rp);
-        const float4 r1 = *reinterpret_cast<const float4*>(rp + 4);
-        row.res[i][0] = r0.x; row.res[i][1] = r0.y; row.res[i][2] = r0.z; row.res[i][3] = r0.w;
-        row.res[i][4] = r1.x; row.res[i][5] = r1.y; row.res[i][6] = r1.z; row.res[i][7] = r1.w;
+        res_raw[i][0] = __ldcg(reinterpret_cast<const uint4*>(rp));
+        res_raw[i][1] = __ldcg(reinterpret_cast<const uint4*>(rp + 4));
       } else {
-        const uint4 t =
-            *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.residual) + off);
-        bf16x8_to_f32(U4{t.x, t.y, t.z, t.w}, row.res[i]);
+        res_raw[i][0] = __ldcg(
+            reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.residual) + off));
       }
-      const int c0 = v * 8;
-      if (a.kind == IQ_TAIL_ATTN) {
-        const float4 x0 = __ldg(reinterpret_cast<const float4*>(a.w_first + c0));
-        const float4 x1 = __ldg(reinterpret_cast<const float4*>(a.w_first + c0 + 4));
-        w1[i][0] = x0.x; w1[i][1] = x0.y; w1[i][2] = x0.z; w1[i][3] = x0.w;
-        w1[i][4] = x1.x; w1[i][5] = x1.y; w1[i][6] = x1.z; w1[i][7] = x1.w;
-      }
-      const float4 y0 = __ldg(reinterpret_cast<const float4*>(a.w_norm + c0));
-      const float4 y1 = __ldg(reinterpret_cast<const float4*>(a.w_norm + c0 + 4));
-      w2[i][0] = y0.x; w2[i][1] = y0.y; w2[i][2] = y0.z; w2[i][3] = y0.w;
-      w2[i][4] = y1.x; w2[i][5] = y1.y; w2[i][6] = y1.z; w2[i][7] = y1.w;
     }
-    // ---- cross-rank readiness: signal, then wait while this row's local loads are in flight
+    // ---- cross-rank readiness: signal, then wait while the residual loads are in flight
     if (r == 0 && a.world > 1) {
       if (tid == 0) {
         const uint32_t target = (*a.epoch + 1u) * static_cast<uint32_t>(a.world);
@@ -290,7 +303,7 @@ __device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/, float
         if (!ok) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
         *sflag = ok;
       }
-      __syncthreads();
+      bar.sync();
       if (!*sflag) {
         // Peers are missing: leave the outputs untouched and let the host read the status.
         if (tid == 0) *a.epoch = *a.epoch + 1u;
@@ -298,49 +311,57 @@ __device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/, float
       }
     }
     // ---- the reduced partial
+    float f[kTailVecs][8];
 #pragma unroll
     for (int i = 0; i < kTailVecs; ++i) {
       const int v = tid + i * nthr;
       if (v >= vec_per_row) continue;
       const size_t off = row_off + static_cast<size_t>(v) * 8;
+      U4 part;
       if (a.world == 1) {
         const uint4 t = __ldcg(reinterpret_cast<const uint4*>(
             static_cast<const __nv_bfloat16*>(a.partial) + off));
-        row.part[i] = U4{t.x, t.y, t.z, t.w};
+        part = U4{t.x, t.y, t.z, t.w};
       } else if (a.partial_mc) {
-        row.part[i] = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(a.partial_mc) + off);
+        part = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(a.partial_mc) + off);
       } else {
-        // all peers' vectors in flight together, then summed in rank order
-        U4 pv[8];
-#pragma unroll
-        for (int p = 0; p < 8; ++p)
-          if (p < a.world)
-            pv[p] = ld_global_u4(static_cast<const __nv_bfloat16*>(a.peer_partials[p]) + off);
+        // four peers' vectors in flight at a time, summed in rank order
         float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int p = 0; p < 8; ++p) {
-          if (p >= a.world) continue;
-          float f[8];
-          bf16x8_to_f32(pv[p], f);
+        for (int p0 = 0; p0 < 8; p0 += 4) {
+          if (p0 >= a.world) break;
+          U4 pv[4];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) accv[j] += f[j];
+          for (int p = 0; p < 4; ++p)
+            if (p0 + p < a.world)
+              pv[p] = ld_global_u4(static_cast<const __nv_bfloat16*>(a.peer_partials[p0 + p]) + off);
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            if (p0 + p >= a.world) continue;
+            float t[8];
+            bf16x8_to_f32(pv[p], t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) accv[j] += t[j];
+          }
         }
-        row.part[i] = f32_to_bf16x8(accv);
+        part = f32_to_bf16x8(accv);
       }
+      bf16x8_to_f32(part, f[i]);
     }
 
-    float f[kTailVecs][8], hv[kTailVecs][8];
+    float wv[kTailVecs][8];    // w_first, later w_norm
     float inv1 = 0.f;
-    if (a.kind == IQ_TAIL_ATTN) {
+    if (attn) {
       float ss = 0.f;
 #pragma unroll
       for (int i = 0; i < kTailVecs; ++i) {
-        if (tid + i * nthr >= vec_per_row) continue;
-        bf16x8_to_f32(row.part[i], f[i]);
+        const int v = tid + i * nthr;
+        if (v >= vec_per_row) continue;
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss = fmaf(f[i][j], f[i][j], ss);
+        ldg_f32x8(a.w_first + v * 8, wv[i]);      // lands while the reduction's barrier is waited
       }
-      inv1 = rsqrtf(block_sum(ss, slots0) * inv_h + a.eps);
+      inv1 = rsqrtf(block_sum(ss, slots0, bar) * inv_h + a.eps);
     }
     // ---- h = residual + (ATTN: bf16(bf16(w1*(ao*inv))*scale) | MLP: bf16(m*scale))
     float ss2 = 0.f;
@@ -349,31 +370,40 @@ __device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/, float
       const int v = tid + i * nthr;
       if (v >= vec_per_row) continue;
       const size_t off = row_off + static_cast<size_t>(v) * 8;
-      if (a.kind != IQ_TAIL_ATTN) bf16x8_to_f32(row.part[i], f[i]);
+      float res[8];
+      if (a.residual_fp32) {
+        const float* r0 = reinterpret_cast<const float*>(&res_raw[i][0]);
+        const float* r1 = reinterpret_cast<const float*>(&res_raw[i][1]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { res[j] = r0[j]; res[4 + j] = r1[j]; }
+      } else {
+        bf16x8_to_f32(U4{res_raw[i][0].x, res_raw[i][0].y, res_raw[i][0].z, res_raw[i][0].w}, res);
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float add;
-        if (a.kind == IQ_TAIL_ATTN) {
-          const float nrm = bf16_round(w1[i][j] * (f[i][j] * inv1));
+        if (attn) {
+          const float nrm = bf16_round(wv[i][j] * (f[i][j] * inv1));
           add = bf16_round(nrm * a.scale);
         } else {
           add = bf16_round(f[i][j] * a.scale);
         }
-        hv[i][j] = row.res[i][j] + add;
+        f[i][j] = res[j] + add;                 // f now holds h
       }
       if (a.residual_fp32) {
         float* ho = static_cast<float*>(a.h_out) + off;
-        *reinterpret_cast<float4*>(ho) = make_float4(hv[i][0], hv[i][1], hv[i][2], hv[i][3]);
-        *reinterpret_cast<float4*>(ho + 4) = make_float4(hv[i][4], hv[i][5], hv[i][6], hv[i][7]);
+        *reinterpret_cast<float4*>(ho) = make_float4(f[i][0], f[i][1], f[i][2], f[i][3]);
+        *reinterpret_cast<float4*>(ho + 4) = make_float4(f[i][4], f[i][5], f[i][6], f[i][7]);
       } else {
-        const U4 hb = f32_to_bf16x8(hv[i]);
+        const U4 hb = f32_to_bf16x8(f[i]);
         *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.h_out) + off) = hb;
-        bf16x8_to_f32(hb, hv[i]);            // the norm sees the rounded stream
+        bf16x8_to_f32(hb, f[i]);            // the norm sees the rounded stream
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss2 = fmaf(hv[i][j], hv[i][j], ss2);
+      for (int j = 0; j < 8; ++j) ss2 = fmaf(f[i][j], f[i][j], ss2);
+      ldg_f32x8(a.w_norm + v * 8, wv[i]);
     }
-    const float inv2 = rsqrtf(block_sum(ss2, slots1) * inv_h + a.eps);
+    const float inv2 = rsqrtf(block_sum(ss2, slots1, bar) * inv_h + a.eps);
     if (a.inv_out && tid == 0) a.inv_out[r] = inv2;
 
     // ---- norm_out = bf16(w_norm * (h * inv)) (+ e4m3 copy, unscaled or per 1x128 group)
@@ -386,7 +416,7 @@ __device__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/, float
       float amax = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        o[j] = live ? bf16_round(w2[i][j] * (hv[i][j] * inv2)) : 0.f;
+        o[j] = live ? bf16_round(wv[i][j] * (f[i][j] * inv2)) : 0.f;
         amax = fmaxf(amax, fabsf(o[j]));
       }
       if (live)
@@ -420,7 +450,10 @@ __global__ void __launch_bounds__(kThreads, 1) tail_kernel(const TailParams p) {
   pdl_launch_dependents();   // after the wait: see the note on `after_wait` below
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
-  run_tail(p.a, reinterpret_cast<__nv_bfloat16*>(smem + 1024), red, sflag);
+  // Sixteen warps everywhere the tail runs, so that its block-wide sums add in one order.
+  if (threadIdx.x < kConsumerThreads)
+    run_tail(p.a, reinterpret_cast<__nv_bfloat16*>(smem + 1024), red, sflag,
+             BlockBar{2, kConsumerThreads});
 }
 
 // Programmatic dependent launch discipline shared by the kernels: a CTA lets its
@@ -524,7 +557,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
   if (last_cta<G>(cv.sm, scr, gridDim.x)) {
     // The ring is idle now: its first bytes hold the reduced rows.
     float* red = reinterpret_cast<float*>(cv.sm->red);
-    run_tail(p.tail, reinterpret_cast<__nv_bfloat16*>(cv.ring), red, &cv.sm->is_last_tile);
+    if (threadIdx.x < kConsumerThreads)
+      run_tail(p.tail, reinterpret_cast<__nv_bfloat16*>(cv.ring), red, &cv.sm->is_last_tile,
+               BlockBar{2, kConsumerThreads});
   }
   stream_drain_on_abort<G>(cv.sm);
 }
@@ -553,7 +588,7 @@ __device__ inline uint32_t ordered_key(float v) {
 // One warp selects row `row`: top_k rounds of (largest key, then smallest id), softmax
 // or renormalised sigmoid summed in descending-value order, pairs stored by ascending id.
 __device__ void select_row(const float* logits, int e, int top_k, int score, int row, int* sel,
-                           float* wt) {
+                           float* wt, bool logits_in_smem = false) {
   const int lane = threadIdx.x & 31;
   constexpr int kMaxPerLane = 16;            // e <= 512
   uint32_t key[kMaxPerLane];
@@ -561,7 +596,11 @@ __device__ void select_row(const float* logits, int e, int top_k, int score, int
 #pragma unroll
   for (int j = 0; j < kMaxPerLane; ++j) {
     const int id = lane + 32 * j;
-    key[j] = (j < per && id < e) ? ordered_key(__ldcg(logits + static_cast<size_t>(row) * e + id)) : 0u;
+    float lv = 0.f;
+    if (j < per && id < e)
+      lv = logits_in_smem ? logits[static_cast<size_t>(row) * e + id]
+                          : __ldcg(logits + static_cast<size_t>(row) * e + id);
+    key[j] = (j < per && id < e) ? ordered_key(lv) : 0u;
   }
   int my_id = 0x7fffffff;
   float my_val = 0.f, top_val = 0.f, sum = 0.f, my_p = 0.f;
@@ -680,31 +719,50 @@ struct MoeCommon {
 // (Down) instead of 1 (Gate).  `x_is_pair`: the staged activation row of a column is its
 // pair's row (Down) instead of the token's row (Gate).  One thread per routed pair: the
 // table is ready four block barriers after the routes arrive.
-template <class G>
-__device__ int build_groups(StreamSmem<G>* sm, const MoeCommon& mc, bool use_wt, bool x_is_pair,
-                            int* status, int* s_ids /* 64 + kMaxGroups + 1 ints of shared memory */) {
+__device__ __noinline__ int build_groups(GroupDesc* groups, const MoeCommon& mc, bool use_wt,
+                                         bool x_is_pair, int* status,
+                                         int* s_ids /* 64 + kMaxGroups + 1 ints of shared memory */,
+                                         const BlockBar bar = BlockBar{},
+                                         const int* smem_sel = nullptr,
+                                         const float* smem_wt = nullptr,
+                                         GroupDesc* down_groups = nullptr,
+                                         const MoeCommon* down_mc = nullptr) {
+  // With `down_groups` the same pass also fills the Down's table (routing weights as
+  // multipliers, pair rows as activations) for the Gate's table in `groups`.
   const int tid = threadIdx.x;
   const int pairs = mc.m * mc.top_k;
   const int slots = mc.top_k + mc.n_shared;
   int e = -1;
   float wt = 1.0f;
   if (tid < pairs) {
-    e = mc.sel[tid];
-    if (use_wt) wt = mc.wt[tid];
+    // the routes come from global memory, or from the CTA's own copy in shared memory
+    e = smem_sel ? smem_sel[tid] : __ldcg(mc.sel + tid);
+    if (use_wt || down_groups) wt = smem_wt ? smem_wt[tid] : __ldcg(mc.wt + tid);
     if (e < 0 || e >= mc.n_experts) {
       set_status(status, IQ_ERR_ROUTE);
       e = -1;
     }
     s_ids[tid] = e;
   }
-  __syncthreads();
+  bar.sync();
   // is pair q the first with its expert?
   if (tid < pairs) {
     bool is_first = e >= 0;
     for (int r = 0; r < tid && is_first; ++r) is_first = s_ids[r] != e;
     s_ids[64 + tid] = is_first ? 1 : 0;
   }
-  __syncthreads();
+  bar.sync();
+  auto open_group = [](GroupDesc& gd, const MoeCommon& c, int expert) {
+    gd.w = c.w + static_cast<size_t>(expert) * c.w_stride;
+    gd.scale = c.w_scale + static_cast<size_t>(expert) * c.scale_stride;
+    gd.row_base = expert * c.rows_per_expert;
+    gd.map_id = 0;
+    for (int col = 0; col < kMaxCols; ++col) {
+      gd.col_row[col] = -1;
+      gd.col_mul[col] = 0.f;
+      gd.col_out[col] = 0;
+    }
+  };
   // group index = number of distinct experts before the first occurrence of mine
   int first = tid, gi = 0, n_routed = 0;
   if (tid < pairs) {
@@ -717,43 +775,44 @@ __device__ int build_groups(StreamSmem<G>* sm, const MoeCommon& mc, bool use_wt,
     }
     if (tid == 0) s_ids[64 + kMaxGroups] = n_routed + mc.n_shared;
     if (e >= 0 && first == tid) {
-      GroupDesc& gd = sm->groups[gi];
-      gd.w = mc.w + static_cast<size_t>(e) * mc.w_stride;
-      gd.scale = mc.w_scale + static_cast<size_t>(e) * mc.scale_stride;
-      gd.row_base = e * mc.rows_per_expert;
-      gd.map_id = 0;
-      for (int c = 0; c < kMaxCols; ++c) {
-        gd.col_row[c] = -1;
-        gd.col_mul[c] = 0.f;
-        gd.col_out[c] = 0;
-      }
+      open_group(groups[gi], mc, e);
+      if (down_groups) open_group(down_groups[gi], *down_mc, e);
     }
   }
-  __syncthreads();
+  bar.sync();
   const int n_groups = s_ids[64 + kMaxGroups];
+  auto shared_group = [&](GroupDesc& gd, const MoeCommon& c, int sidx, bool pair_rows) {
+    gd.w = c.shared_w + static_cast<size_t>(sidx) * c.w_stride;
+    gd.scale = c.shared_scale + static_cast<size_t>(sidx) * c.scale_stride;
+    gd.row_base = sidx * c.rows_per_expert;
+    gd.map_id = 1;
+    for (int col = 0; col < kMaxCols; ++col) {
+      const bool live = col < c.m;
+      const int pair_row = col * slots + c.top_k + sidx;
+      gd.col_row[col] = static_cast<int16_t>(live ? (pair_rows ? pair_row : col) : -1);
+      gd.col_mul[col] = live ? 1.0f : 0.f;
+      gd.col_out[col] = static_cast<int16_t>(pair_rows ? col : pair_row);
+    }
+  };
   if (tid < pairs && e >= 0) {
-    GroupDesc& gd = sm->groups[gi];
     const int row = tid / mc.top_k, slot = tid - row * mc.top_k;
     const int pair_row = row * slots + slot;
+    GroupDesc& gd = groups[gi];
     gd.col_row[row] = static_cast<int16_t>(x_is_pair ? pair_row : row);
-    gd.col_mul[row] = wt;
+    gd.col_mul[row] = use_wt ? wt : 1.0f;
     gd.col_out[row] = static_cast<int16_t>(x_is_pair ? row : pair_row);
+    if (down_groups) {
+      GroupDesc& dd = down_groups[gi];
+      dd.col_row[row] = static_cast<int16_t>(pair_row);
+      dd.col_mul[row] = wt;
+      dd.col_out[row] = static_cast<int16_t>(row);
+    }
   } else if (tid >= 64 && tid < 64 + mc.n_shared) {
     const int sidx = tid - 64;
-    GroupDesc& gd = sm->groups[n_groups - mc.n_shared + sidx];
-    gd.w = mc.shared_w + static_cast<size_t>(sidx) * mc.w_stride;
-    gd.scale = mc.shared_scale + static_cast<size_t>(sidx) * mc.scale_stride;
-    gd.row_base = sidx * mc.rows_per_expert;
-    gd.map_id = 1;
-    for (int c = 0; c < kMaxCols; ++c) {
-      const bool live = c < mc.m;
-      const int pair_row = c * slots + mc.top_k + sidx;
-      gd.col_row[c] = static_cast<int16_t>(live ? (x_is_pair ? pair_row : c) : -1);
-      gd.col_mul[c] = live ? 1.0f : 0.f;
-      gd.col_out[c] = static_cast<int16_t>(x_is_pair ? c : pair_row);
-    }
+    shared_group(groups[n_groups - mc.n_shared + sidx], mc, sidx, x_is_pair);
+    if (down_groups) shared_group(down_groups[n_groups - mc.n_shared + sidx], *down_mc, sidx, true);
   }
-  __syncthreads();
+  bar.sync();
   return n_groups;
 }
 
@@ -783,7 +842,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
   if (early_x && warp < kConsumerWarps)
     stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
   after_wait();                     // the routes come from the predecessor
-  sh.n_groups = build_groups<G>(cv.sm, p.mc, false, false, scr.status, cv.sm->route_ids);
+  sh.n_groups = build_groups(cv.sm->groups, p.mc, false, false, scr.status, cv.sm->route_ids);
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
@@ -853,7 +912,7 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
   // predecessor, is still finishing; only the Gate's activations are waited for.
   const bool early = p.pdl_level >= 2;
   if (!early) after_wait();
-  sh.n_groups = build_groups<G>(cv.sm, p.mc, true, true, scr.status, cv.sm->route_ids);
+  sh.n_groups = build_groups(cv.sm->groups, p.mc, true, true, scr.status, cv.sm->route_ids);
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
@@ -896,10 +955,18 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
   }
   if (last_cta<G>(cv.sm, scr, gridDim.x)) {
     float* red = reinterpret_cast<float*>(cv.sm->red);
-    run_tail(p.tail, reinterpret_cast<__nv_bfloat16*>(cv.ring), red, &cv.sm->is_last_tile);
+    if (threadIdx.x < kConsumerThreads)
+      run_tail(p.tail, reinterpret_cast<__nv_bfloat16*>(cv.ring), red, &cv.sm->is_last_tile,
+               BlockBar{2, kConsumerThreads});
   }
   stream_drain_on_abort<G>(cv.sm);
 }
+
+}  // namespace iqb
+
+#include "layer_fused.cuh"
+
+namespace iqb {
 
 // ------------------------------------------------------------------------------------
 // Host side
@@ -1003,7 +1070,8 @@ static int fill_maps(CUtensorMap* map0, CUtensorMap* map1, const StreamShape& sh
 }
 
 template <class Kernel, class Params>
-static int launch(Kernel kernel, const Params& p, int grid, size_t smem, void* stream, int pdl) {
+static int launch(Kernel kernel, const Params& p, int grid, size_t smem, void* stream, int pdl,
+                  bool cooperative = false) {
   // One opt-in to the full shared memory per kernel and device (this function is
   // instantiated per kernel, so the flags are per kernel).
   if (!ensure_smem_optin(reinterpret_cast<const void*>(kernel))) return IQ_ERR_CUDA;
@@ -1012,11 +1080,20 @@ static int launch(Kernel kernel, const Params& p, int grid, size_t smem, void* s
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr{};
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cudaLaunchAttribute attr[2] = {};
+  int n_attr = 0;
+  if (cooperative) {
+    attr[n_attr].id = cudaLaunchAttributeCooperative;
+    attr[n_attr].val.cooperative = 1;
+    ++n_attr;
+  }
+  if (pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
   const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, p);
   if (err != cudaSuccess) {
     fprintf(stderr, "iqb200: launch failed: %s\n", cudaGetErrorString(err));
@@ -1059,7 +1136,7 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 static int check_tail(const iq_tail_args* t) {
   if (!t) return IQ_OK;
   if (t->kind != IQ_TAIL_ATTN && t->kind != IQ_TAIL_MLP) return IQ_ERR_ARG;
-  if (t->m < 1 || t->m > 8 || t->h < 128 || t->h % 128 || t->h > 8 * kTailVecs * kThreads)
+  if (t->m < 1 || t->m > 8 || t->h < 128 || t->h % 128 || t->h > 8 * kTailVecs * kConsumerThreads)
     return IQ_ERR_ARG;
   if (!t->partial || !t->residual || !t->w_norm || !t->h_out || !t->norm_out) return IQ_ERR_ARG;
   if (t->kind == IQ_TAIL_ATTN && !t->w_first) return IQ_ERR_ARG;
@@ -1145,7 +1222,7 @@ extern "C" int iq_tail(const iq_tail_args* a, void* stream, int pdl) {
 
 extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   if (!a || !a->x || !a->w || !a->w_scale || !a->out || !a->scratch) return IQ_ERR_ARG;
-  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBasicBytes) return IQ_ERR_ARG;
   if (a->x_kind < IQ_X_BF16_GROUPQ || a->x_kind > IQ_X_E4M3_UNSCALED) return IQ_ERR_ARG;
   if (a->x_kind == IQ_X_E4M3_GROUP && !a->x_scale) return IQ_ERR_ARG;
   const int max_m = a->x_kind == IQ_X_BF16_SPLIT2 ? 4 : 8;
@@ -1206,7 +1283,7 @@ static int router_launch(const iq_router_args* a, void* stream) {
 
 extern "C" int iq_router(const iq_router_args* a, void* stream) {
   if (!a || !a->x || !a->w || !a->sel || !a->wt || !a->logits || !a->scratch) return IQ_ERR_ARG;
-  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBasicBytes) return IQ_ERR_ARG;
   if (a->m < 1 || a->m > 8 || a->h < 512 || a->h % 512) return IQ_ERR_ARG;
   if (a->e < 16 || a->e % 16 || a->e > 512 || a->top_k < 1 || a->top_k > 32 || a->top_k > a->e)
     return IQ_ERR_ARG;
@@ -1236,7 +1313,7 @@ static int fill_moe(MoeCommon& mc, int m, int h, int i_loc, int n_experts, int t
 
 extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   if (!a || !a->x_fp8 || !a->fc || !a->fc_scale || !a->act || !a->scratch) return IQ_ERR_ARG;
-  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBasicBytes) return IQ_ERR_ARG;
   if (a->n_shared > 0 && (!a->shared_fc || !a->shared_fc_scale)) return IQ_ERR_ARG;
   if (a->act_kind != IQ_ACT_E4M3 && a->act_kind != IQ_ACT_BF16) return IQ_ERR_ARG;
   if (a->h < 1024 || a->h % 1024 || a->i_loc < 64 || a->i_loc % 64) return IQ_ERR_ARG;
@@ -1326,7 +1403,7 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
 extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   if (!a || !a->act || !a->proj || !a->proj_scale || !a->out || !a->wt || !a->scratch)
     return IQ_ERR_ARG;
-  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBasicBytes) return IQ_ERR_ARG;
   if (a->n_shared > 0 && (!a->shared_proj || !a->shared_proj_scale)) return IQ_ERR_ARG;
   if (a->act_kind != IQ_ACT_E4M3 && a->act_kind != IQ_ACT_BF16) return IQ_ERR_ARG;
   if (a->h < 128 || a->h % 128 || a->i_loc < 64 || a->i_loc % 64) return IQ_ERR_ARG;
@@ -1348,6 +1425,281 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   return IQ_ERR_UNSUPPORTED;
 }
 
+namespace iqb {
+
+// ------------------------------------------------------------------------------------
+// iq_decode_layer: the four streams in one cooperative launch.
+static void shape_linear(StreamShape& sh, const iq_linear_args* a) {
+  const bool split2 = a->x_kind == IQ_X_BF16_SPLIT2;
+  sh.mode = kRowsPerGroup;
+  sh.n_groups = 1;
+  sh.rows_per_group = a->n;
+  sh.k_bytes = a->k;
+  sh.rg_shift = ilog2(a->rg);
+  sh.kg_shift = ilog2(a->kg);
+  sh.pair_half = 0;
+  sh.x_rows = split2 ? 2 * a->m : a->m;
+  sh.x_pitch = a->k + 64;
+  sh.x_blocks = (a->k + 127) / 128;
+}
+static void shape_router(StreamShape& sh, const iq_router_args* a) {
+  sh.mode = kRowsPerGroup;
+  sh.n_groups = 1;
+  sh.rows_per_group = a->e;
+  sh.k_bytes = a->h * 2;
+  sh.rg_shift = 7;
+  sh.kg_shift = 7;
+  sh.pair_half = 0;
+  sh.x_rows = a->m;
+  sh.x_pitch = a->h * 2 + 64;
+  sh.x_blocks = 1;
+}
+static void shape_gate(StreamShape& sh, const iq_moe_gate_args* a) {
+  sh.mode = kRowsPerGroup;
+  sh.n_groups = 1;
+  sh.rows_per_group = 2 * a->i_loc;
+  sh.k_bytes = a->h;
+  sh.rg_shift = 6;
+  sh.kg_shift = 7;
+  sh.pair_half = a->i_loc;
+  sh.x_rows = a->m;
+  sh.x_pitch = a->h + 64;
+  sh.x_blocks = a->h / 128;
+}
+static void shape_down(StreamShape& sh, const iq_moe_down_args* a) {
+  sh.mode = kConcatK;
+  sh.n_groups = 1;
+  sh.rows_per_group = a->h;
+  sh.k_bytes = a->i_loc;
+  sh.rg_shift = 7;
+  sh.kg_shift = 6;
+  sh.pair_half = 0;
+  sh.x_rows = a->m * (a->top_k + a->n_shared);
+  sh.x_pitch = a->i_loc + 64;
+  sh.x_blocks = (a->i_loc + 127) / 128;
+}
+
+// Most stages one CTA can own when the stream has up to `max_groups` groups; 0 when the
+// stream has more tiles than the scratch has counters.
+template <class G>
+static int max_items_of(const StreamShape& sh, int max_groups) {
+  StreamShape worst = sh;
+  worst.n_groups = max_groups;
+  if (stream_num_tiles<G>(worst) > kMaxTiles) return 0;
+  const long long total =
+      static_cast<long long>(stream_num_tiles<G>(worst)) * stream_stages_per_tile<G>(worst);
+  const int grid = sm_count() > 0 ? sm_count() : 1;
+  return static_cast<int>((total + grid - 1) / grid) + 1;
+}
+
+static void fill_moe_gate(MoeCommon& mc, const iq_moe_gate_args* a) {
+  mc.w = static_cast<const uint8_t*>(a->fc);
+  mc.w_scale = a->fc_scale;
+  mc.shared_w = static_cast<const uint8_t*>(a->shared_fc);
+  mc.shared_scale = a->shared_fc_scale;
+  mc.w_stride = static_cast<size_t>(2) * a->i_loc * a->h;
+  mc.scale_stride = static_cast<size_t>(2 * a->i_loc / 64) * (a->h / 128);
+  mc.rows_per_expert = 2 * a->i_loc;
+}
+static void fill_moe_down(MoeCommon& mc, const iq_moe_down_args* a) {
+  mc.w = static_cast<const uint8_t*>(a->proj);
+  mc.w_scale = a->proj_scale;
+  mc.shared_w = static_cast<const uint8_t*>(a->shared_proj);
+  mc.shared_scale = a->shared_proj_scale;
+  mc.w_stride = static_cast<size_t>(a->h) * a->i_loc;
+  mc.scale_stride = static_cast<size_t>(a->h / 128) * (a->i_loc / 64);
+  mc.rows_per_expert = a->h;
+}
+
+template <class GO, class GD>
+static int layer_launch(const iq_decode_layer_args* a, void* stream, int pdl) {
+  using GR = Geo<1, 16, 2>;
+  using GG = Geo<2, 8, 2>;
+  const iq_linear_args& o = a->oproj;
+  const iq_router_args& r = a->router;
+  const iq_moe_gate_args& g = a->gate;
+  const iq_moe_down_args& d = a->down;
+  LayerParams p{};
+  shape_linear(p.sh_o, &o);
+  shape_router(p.sh_r, &r);
+  shape_gate(p.sh_g, &g);
+  shape_down(p.sh_d, &d);
+  const int max_groups = g.m * g.top_k + g.n_shared;
+  p.sh_o.max_items = max_items_of<GO>(p.sh_o, 1);
+  p.sh_r.max_items = max_items_of<GR>(p.sh_r, 1);
+  p.sh_g.max_items = max_items_of<GG>(p.sh_g, max_groups);
+  p.sh_d.max_items = max_items_of<GD>(p.sh_d, max_groups);
+  if (!p.sh_o.max_items || !p.sh_r.max_items || !p.sh_g.max_items || !p.sh_d.max_items)
+    return IQ_ERR_UNSUPPORTED;
+  // Shared memory: the fixed structures, then one scale table, one activation-scale table
+  // and one activation area, each sized for the stream that needs most, then the ring.
+  auto maxz = [](size_t x, size_t y) { return x > y ? x : y; };
+  size_t sc = static_cast<size_t>(p.sh_o.max_items) * GO::SCALES_PER_STAGE;
+  sc = maxz(sc, static_cast<size_t>(p.sh_g.max_items) * GG::SCALES_PER_STAGE);
+  sc = maxz(sc, static_cast<size_t>(p.sh_d.max_items) * GD::SCALES_PER_STAGE);
+  // Activation rows: o_proj's, then the router's with the Gate's beside them (both are
+  // written by the attention tail), then the Down's; each set overlays the one before.
+  const size_t xq_router = align_up(static_cast<size_t>(p.sh_r.x_rows) * p.sh_r.x_pitch, 16);
+  size_t xs = 0, xq = xq_router + static_cast<size_t>(p.sh_g.x_rows) * p.sh_g.x_pitch;
+  for (const StreamShape* sh : {&p.sh_o, &p.sh_g, &p.sh_d}) {
+    xs = maxz(xs, static_cast<size_t>(sh->x_rows) * sh->x_blocks);
+    xq = maxz(xq, static_cast<size_t>(sh->x_rows) * sh->x_pitch);
+  }
+  size_t off = align_up(sizeof(StreamSmem<GO>), 16);
+  p.off_extra = static_cast<uint32_t>(off);
+  off += align_up(sizeof(LayerSmemExtra), 16);
+  p.off_sc = static_cast<uint32_t>(off);
+  off += align_up(sizeof(float) * sc, 16);
+  p.off_xs = static_cast<uint32_t>(off);
+  off += align_up(sizeof(float) * xs, 16);
+  p.off_xq = static_cast<uint32_t>(off);
+  p.off_xq_gate = static_cast<uint32_t>(off + xq_router);
+  off += align_up(xq, 16);
+  off = align_up(off, 128);
+  p.off_ring = static_cast<uint32_t>(off);
+  int slot_bytes = GO::STAGE_BYTES;
+  for (int b : {GR::STAGE_BYTES, GG::STAGE_BYTES, GD::STAGE_BYTES})
+    if (b > slot_bytes) slot_bytes = b;
+  p.slot_bytes = slot_bytes;
+  int slots = static_cast<int>((static_cast<size_t>(kSmemLimit) - off) / slot_bytes);
+  if (off + 2 * static_cast<size_t>(slot_bytes) > static_cast<size_t>(kSmemLimit)) return IQ_ERR_UNSUPPORTED;
+  const int want = (160 * 1024 + slot_bytes - 1) / slot_bytes;
+  if (slots > want) slots = want;
+  if (slots > kMaxStages) slots = kMaxStages;
+  p.sh_o.n_stages = p.sh_r.n_stages = p.sh_g.n_stages = p.sh_d.n_stages = slots;
+  const size_t smem = off + static_cast<size_t>(slots) * slot_bytes;
+
+  CUtensorMap unused;
+  int rc = fill_maps<GO>(&p.map_o, &unused, p.sh_o, o.w, o.n, nullptr, 0);
+  if (rc == IQ_OK) rc = fill_maps<GR>(&p.map_r, &unused, p.sh_r, r.w, r.e, nullptr, 0);
+  if (rc == IQ_OK)
+    rc = fill_maps<GG>(&p.map_g0, &p.map_g1, p.sh_g, g.fc,
+                       static_cast<long long>(g.n_experts) * 2 * g.i_loc, g.shared_fc,
+                       static_cast<long long>(g.n_shared) * 2 * g.i_loc);
+  if (rc == IQ_OK)
+    rc = fill_maps<GD>(&p.map_d0, &p.map_d1, p.sh_d, d.proj,
+                       static_cast<long long>(d.n_experts) * d.h, d.shared_proj,
+                       static_cast<long long>(d.n_shared) * d.h);
+  if (rc != IQ_OK) return rc;
+
+  p.x = o.x;
+  p.x_scale = o.x_scale;
+  p.x_kind = o.x_kind;
+  p.m = o.m;
+  p.k_o = o.k;
+  p.h = o.n;
+  p.w_o = static_cast<const uint8_t*>(o.w);
+  p.w_o_scale = o.w_scale;
+  p.out_o = static_cast<__nv_bfloat16*>(o.out);
+  p.tail_a = *o.tail;
+  p.w_r = static_cast<const uint8_t*>(r.w);
+  p.e = r.e;
+  p.top_k = r.top_k;
+  p.score = r.score;
+  p.sel = r.sel;
+  p.wt = r.wt;
+  p.logits = r.logits;
+  rc = fill_moe(p.mc_g, g.m, g.h, g.i_loc, g.n_experts, g.top_k, g.n_shared, g.sel, nullptr);
+  if (rc == IQ_OK)
+    rc = fill_moe(p.mc_d, d.m, d.h, d.i_loc, d.n_experts, d.top_k, d.n_shared, d.sel, d.wt);
+  if (rc != IQ_OK) return rc;
+  fill_moe_gate(p.mc_g, &g);
+  fill_moe_down(p.mc_d, &d);
+  p.act = g.act;
+  p.act_kind = g.act_kind;
+  p.out_d = static_cast<__nv_bfloat16*>(d.out);
+  p.tail_m = *d.tail;
+  p.scratch = o.scratch;
+  int* status = scratch_of(o.scratch).status;
+  if (!p.tail_a.status) p.tail_a.status = status;
+  if (!p.tail_m.status) p.tail_m.status = status;
+  unsigned peer_ms = p.tail_a.timeout_ms ? p.tail_a.timeout_ms : 2000u;
+  const unsigned peer_ms_m = p.tail_m.timeout_ms ? p.tail_m.timeout_ms : 2000u;
+  if (peer_ms_m > peer_ms) peer_ms = peer_ms_m;
+  p.wait_ms = peer_ms + 500u;
+
+  auto kernel = layer_kernel<GO, GD>;
+  if (!ensure_smem_optin(reinterpret_cast<const void*>(kernel))) return IQ_ERR_CUDA;
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) != cudaSuccess ||
+      per_sm < 1) {
+    fprintf(stderr, "iqb200: iq_decode_layer needs one resident CTA per SM (%zu B shared)\n", smem);
+    return IQ_ERR_UNSUPPORTED;
+  }
+  return launch(kernel, p, sm_count(), smem, stream, pdl, true);
+}
+
+}  // namespace iqb
+
+using namespace iqb;
+
+extern "C" int iq_decode_layer(const iq_decode_layer_args* a, void* stream, int pdl) {
+  if (!a) return IQ_ERR_ARG;
+  const iq_linear_args& o = a->oproj;
+  const iq_router_args& r = a->router;
+  const iq_moe_gate_args& g = a->gate;
+  const iq_moe_down_args& d = a->down;
+  // ---- each part as its own entry point would check it
+  if (!o.x || !o.w || !o.w_scale || !o.out || !o.scratch || !o.tail || !d.tail) return IQ_ERR_ARG;
+  if (o.scratch_bytes < kScrBytes) return IQ_ERR_ARG;
+  if (r.scratch != o.scratch || g.scratch != o.scratch || d.scratch != o.scratch) return IQ_ERR_ARG;
+  if (o.x_kind < IQ_X_BF16_GROUPQ || o.x_kind > IQ_X_E4M3_UNSCALED) return IQ_ERR_ARG;
+  if (o.x_kind == IQ_X_E4M3_GROUP && !o.x_scale) return IQ_ERR_ARG;
+  const int max_m = o.x_kind == IQ_X_BF16_SPLIT2 ? 4 : 8;
+  if (o.m < 1 || o.m > max_m) return IQ_ERR_ARG;
+  if ((o.rg != 64 && o.rg != 128) || (o.kg != 64 && o.kg != 128)) return IQ_ERR_ARG;
+  if (o.k < 1024 || o.k % 1024 || o.n < 1024 || o.n % 1024) return IQ_ERR_UNSUPPORTED;
+  if (!aligned16(o.x) || !aligned16(o.w) || !aligned16(o.out)) return IQ_ERR_ARG;
+  if (!r.x || !r.w || !r.sel || !r.wt || !r.logits) return IQ_ERR_ARG;
+  if (r.e < 16 || r.e % 16 || r.e > 512 || r.top_k < 1 || r.top_k > 32 || r.top_k > r.e)
+    return IQ_ERR_ARG;
+  if (r.score != IQ_ROUTE_SOFTMAX && r.score != IQ_ROUTE_SIGMOID) return IQ_ERR_ARG;
+  if (!aligned16(r.x) || !aligned16(r.w)) return IQ_ERR_ARG;
+  if (!g.x_fp8 || !g.fc || !g.fc_scale || !g.act || !g.sel) return IQ_ERR_ARG;
+  if (g.n_shared > 0 && (!g.shared_fc || !g.shared_fc_scale)) return IQ_ERR_ARG;
+  if (g.act_kind != IQ_ACT_E4M3 && g.act_kind != IQ_ACT_BF16) return IQ_ERR_ARG;
+  if (!aligned16(g.x_fp8) || !aligned16(g.fc)) return IQ_ERR_ARG;
+  if (!d.act || !d.proj || !d.proj_scale || !d.out || !d.wt || !d.sel) return IQ_ERR_ARG;
+  if (d.n_shared > 0 && (!d.shared_proj || !d.shared_proj_scale)) return IQ_ERR_ARG;
+  if (!aligned16(d.act) || !aligned16(d.proj) || !aligned16(d.out)) return IQ_ERR_ARG;
+  // ---- the four parts describe one layer
+  const int m = o.m, h = o.n;
+  if (r.m != m || g.m != m || d.m != m) return IQ_ERR_ARG;
+  if (r.h != h || g.h != h || d.h != h) return IQ_ERR_ARG;
+  if (g.i_loc != d.i_loc || g.top_k != d.top_k || g.n_shared != d.n_shared ||
+      g.n_experts != d.n_experts || g.act_kind != d.act_kind)
+    return IQ_ERR_ARG;
+  if (r.top_k != g.top_k || r.e != g.n_experts) return IQ_ERR_ARG;
+  // ---- what one part writes is what the next one reads
+  if (r.x != o.tail->norm_out || g.x_fp8 != o.tail->norm_fp8 || g.x_scale != o.tail->norm_fp8_scale)
+    return IQ_ERR_ARG;
+  if (g.sel != r.sel || d.sel != r.sel || d.wt != r.wt || d.act != g.act) return IQ_ERR_ARG;
+  if (g.i_loc < 256 || g.i_loc % 256) return IQ_ERR_UNSUPPORTED;
+  int rc = check_tail(o.tail);
+  if (rc == IQ_OK) rc = check_tail(d.tail);
+  if (rc != IQ_OK) return rc;
+  if (o.tail->kind != IQ_TAIL_ATTN || d.tail->kind != IQ_TAIL_MLP) return IQ_ERR_ARG;
+  if (o.tail->partial != o.out || o.tail->m != m || o.tail->h != h) return IQ_ERR_ARG;
+  if (d.tail->partial != d.out || d.tail->m != m || d.tail->h != h) return IQ_ERR_ARG;
+  if (h > kLayerMaxH) return IQ_ERR_UNSUPPORTED;
+  if (o.tail->timeout_ms > 3000u || d.tail->timeout_ms > 3000u) return IQ_ERR_ARG;
+  if (sm_count() == 0) return IQ_ERR_CUDA;
+  const bool o2 = o.k % 2048 == 0;
+  const int i = g.i_loc;
+  using Geo2048 = Geo<1, 16, 2>;
+  using Geo1024 = Geo<1, 16, 1>;
+  using Geo512 = Geo<2, 8, 1>;
+  using Geo256 = Geo<4, 4, 1>;
+#define IQ_LAYER_DISPATCH(GD)                                                   \
+  return o2 ? layer_launch<Geo<1, 16, 2>, GD>(a, stream, pdl)                   \
+            : layer_launch<Geo<1, 16, 1>, GD>(a, stream, pdl)
+  if (i % 2048 == 0) { IQ_LAYER_DISPATCH(Geo2048); }
+  if (i % 1024 == 0) { IQ_LAYER_DISPATCH(Geo1024); }
+  if (i % 512 == 0) { IQ_LAYER_DISPATCH(Geo512); }
+  IQ_LAYER_DISPATCH(Geo256);
+#undef IQ_LAYER_DISPATCH
+}
+
 // ------------------------------------------------------------------------------------
 // iq_linear_static: iq_linear for callers that cannot obtain device memory.
 //
@@ -1357,14 +1709,14 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
 // or a host that is only given raw pointers to inputs and outputs.  For them the work
 // area of the streaming GEMV (split-tile partial sums, tile counters, the CTA ticket and
 // the status word) lives in this file-scope device array instead of a caller buffer.
-// Every GPU that loads the library holds the array (kScrBytes, about 2.1 MB) until exit.
+// Every GPU that loads the library holds the array (kScrBasicBytes, about 4.3 MB) until exit.
 //
 // `g_static_scratch` below is a host-side stand-in when named in host code, not a device
 // address; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
 // device with that device current.
 constexpr int kStaticMaxN = 65536;   // largest output width served from the static area
 constexpr int kStaticMaxK = 65536;   // largest contraction length
-static __device__ __align__(256) uint8_t g_static_scratch[kScrBytes];
+static __device__ __align__(256) uint8_t g_static_scratch[kScrBasicBytes];
 static void* g_static_ptr[64] = {};
 
 extern "C" int iq_linear_static(const iq_linear_args* a, void* stream) {
@@ -1401,6 +1753,6 @@ extern "C" int iq_linear_static(const iq_linear_args* a, void* stream) {
     return IQ_ERR_CUDA;
   iq_linear_args b = *a;
   b.scratch = g_static_ptr[dev];
-  b.scratch_bytes = kScrBytes;
+  b.scratch_bytes = kScrBasicBytes;
   return iq_linear(&b, stream);
 }

@@ -123,7 +123,7 @@ struct StreamSmem {
   uint64_t empty[kMaxStages];
   uint64_t red_full[2];   // the consumers' per-tile partials are in red[i]
   uint64_t red_empty[2];  // the epilogue warp has read red[i]
-  int abort_flag;
+  volatile int abort_flag;
   int is_last_tile;   // broadcast: this CTA finishes the current split tile
   int is_last_cta;    // broadcast: this CTA runs the global epilogue
   int pad;
@@ -267,48 +267,67 @@ struct TileWalk {
   }
 };
 
+// Where a role stands in the ring (slot + mbarrier parity) and in the pair of per-tile
+// reduction buffers.  A kernel that runs several streams back to back through one ring
+// carries these from one stream to the next.
+struct RingPos {
+  int slot = 0;
+  uint32_t phase = 0;
+};
+struct RedPos {
+  int buf = 0;
+  uint32_t phase = 0;
+};
+
 // ------------------------------------------------------------------------------------
 // Producer: one elected lane of one warp, one or two copies per stage.  `map0/map1` are the
 // launch's tensor maps (u32 elements, box = KC bytes x box rows), used when a stage is a
 // K-slice of its rows; whole-row stages are contiguous and use the untiled copy.
-template <class G>
-__device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm, uint8_t* ring,
-                                        const CtaWork& w, int* status, const CUtensorMap* map0,
-                                        const CUtensorMap* map1) {
+template <class G, class S>
+__device__ __forceinline__ void produce(const StreamShape& sh, S* sm, const GroupDesc* groups,
+                                        uint8_t* ring, int slot_bytes, const CtaWork& w,
+                                        int* status, const CUtensorMap* map0,
+                                        const CUtensorMap* map1, RingPos& pos) {
   const int lane = threadIdx.x & 31;
-  int slot = 0;
-  uint32_t phase = 0;
+  int slot = pos.slot;
+  uint32_t phase = pos.phase;
   const bool whole_rows = sh.k_bytes == G::KC && G::NBOX == 1;
   const int halves = sh.pair_half > 0 ? 2 : 1;
   constexpr int kHalfRows = G::ROWS / 2;
   const int copy_rows = halves == 2 ? kHalfRows : G::ROWS;
+  // Weights pass through once: marked evict-first they do not push the lines that are
+  // reused from launch to launch (activations, scale tables, the kernels' instructions)
+  // out of L2.
+  const uint64_t policy = policy_evict_first();
   TileWalk walk;
   walk.init(w);
   for (int k = 0; k < walk.n_tiles; ++k) {
     const TileVisit tv = walk.visit(w, k);
     StagePos p = stage_pos(sh, w, tv.tile, tv.s_begin);
     for (int s = tv.s_begin; s < tv.s_end; ++s) {
-      if (!mbar_wait(&sm->empty[slot], phase ^ 1u)) {
-        set_status(status, IQ_ERR_PIPE_TIMEOUT);
+      if (!mbar_wait(&sm->empty[slot], phase ^ 1u, &sm->abort_flag)) {
+        if (!sm->abort_flag) set_status(status, IQ_ERR_PIPE_TIMEOUT);
         sm->abort_flag = 1;
         return;
       }
       if (lane == 0) {
-        const GroupDesc& gd = sm->groups[p.group];
+        const GroupDesc& gd = groups[p.group];
         uint64_t* bar = &sm->full[slot];
         mbar_arrive_expect_tx(bar, G::ROWS * G::KC);
-        uint8_t* dst = ring + slot * G::STAGE_BYTES;
+        uint8_t* dst = ring + slot * slot_bytes;
         for (int hf = 0; hf < halves; ++hf) {
           const int row = tile_row(sh, G::ROWS, p.tig, hf * kHalfRows);
           if (whole_rows) {
-            bulk_g2s(dst + hf * kHalfRows * G::PITCH,
-                     gd.w + static_cast<size_t>(row) * sh.k_bytes, copy_rows * G::KC, bar);
+            bulk_g2s_evict_first(dst + hf * kHalfRows * G::PITCH,
+                                 gd.w + static_cast<size_t>(row) * sh.k_bytes,
+                                 copy_rows * G::KC, bar, policy);
           } else {
 #pragma unroll
             for (int b = 0; b < G::NBOX; ++b)
-              tma_2d_g2s(dst + b * (G::ROWS * G::BOXK) + hf * kHalfRows * G::PITCH,
-                         gd.map_id ? map1 : map0, p.kstage * (G::KC / 4) + b * (G::BOXK / 4),
-                         gd.row_base + row, bar);
+              tma_2d_g2s_evict_first(dst + b * (G::ROWS * G::BOXK) + hf * kHalfRows * G::PITCH,
+                                     gd.map_id ? map1 : map0,
+                                     p.kstage * (G::KC / 4) + b * (G::BOXK / 4),
+                                     gd.row_base + row, bar, policy);
           }
         }
       }
@@ -320,6 +339,15 @@ __device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm
       }
     }
   }
+  pos.slot = slot;
+  pos.phase = phase;
+}
+template <class G>
+__device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm, uint8_t* ring,
+                                        const CtaWork& w, int* status, const CUtensorMap* map0,
+                                        const CUtensorMap* map1) {
+  RingPos pos;
+  produce<G>(sh, sm, sm->groups, ring, G::STAGE_BYTES, w, status, map0, map1, pos);
 }
 
 // The element type of the streamed matrix decides the MMA; everything else is bytes.
@@ -347,7 +375,7 @@ struct ElemBF16 {
 constexpr int kGatherHeld = 4;
 
 template <class G>
-__device__ __forceinline__ float gather_one(const StreamShape& sh, const StreamSmem<G>* sm,
+__device__ __forceinline__ float gather_one(const StreamShape& sh, const GroupDesc* groups,
                                             const CtaWork& w, int i) {
   const int krow = sh.k_bytes >> sh.kg_shift;
   const int st = i / G::SCALES_PER_STAGE, e = i - st * G::SCALES_PER_STAGE;
@@ -358,12 +386,12 @@ __device__ __forceinline__ float gather_one(const StreamShape& sh, const StreamS
   const StagePos p = stage_pos(sh, w, w.tile0 + tq, lin - tq * w.spt);
   const int row0 = tile_row(sh, G::ROWS, p.tig, rs * 16);
   const int kb = p.kstage * G::KC + kp * (G::RUNS * 64) + run * 64;
-  return __ldg(sm->groups[p.group].scale + static_cast<size_t>(row0 >> sh.rg_shift) * krow +
+  return __ldg(groups[p.group].scale + static_cast<size_t>(row0 >> sh.rg_shift) * krow +
                (kb >> sh.kg_shift));
 }
 
 template <class G, class E>
-__device__ __forceinline__ void gather_scales_load(const StreamShape& sh, const StreamSmem<G>* sm,
+__device__ __forceinline__ void gather_scales_load(const StreamShape& sh, const GroupDesc* groups,
                                                    const CtaWork& w, int tid,
                                                    float (&held)[kGatherHeld]) {
   if (!E::kScaled) return;
@@ -371,12 +399,12 @@ __device__ __forceinline__ void gather_scales_load(const StreamShape& sh, const 
 #pragma unroll
   for (int j = 0; j < kGatherHeld; ++j) {
     const int i = tid + j * kConsumerThreads;
-    held[j] = i < total ? gather_one<G>(sh, sm, w, i) : 0.f;
+    held[j] = i < total ? gather_one<G>(sh, groups, w, i) : 0.f;
   }
 }
 
 template <class G, class E>
-__device__ __forceinline__ void gather_scales_store(const StreamShape& sh, const StreamSmem<G>* sm,
+__device__ __forceinline__ void gather_scales_store(const StreamShape& sh, const GroupDesc* groups,
                                                     const CtaWork& w, float* sc, int tid,
                                                     const float (&held)[kGatherHeld]) {
   if (!E::kScaled) return;
@@ -387,7 +415,20 @@ __device__ __forceinline__ void gather_scales_store(const StreamShape& sh, const
     if (i < total) sc[i] = held[j];
   }
   for (int i = tid + kGatherHeld * kConsumerThreads; i < total; i += kConsumerThreads)
-    sc[i] = gather_one<G>(sh, sm, w, i);
+    sc[i] = gather_one<G>(sh, groups, w, i);
+}
+
+template <class G, class E>
+__device__ __forceinline__ void gather_scales_load(const StreamShape& sh, const StreamSmem<G>* sm,
+                                                   const CtaWork& w, int tid,
+                                                   float (&held)[kGatherHeld]) {
+  gather_scales_load<G, E>(sh, sm->groups, w, tid, held);
+}
+template <class G, class E>
+__device__ __forceinline__ void gather_scales_store(const StreamShape& sh, const StreamSmem<G>* sm,
+                                                    const CtaWork& w, float* sc, int tid,
+                                                    const float (&held)[kGatherHeld]) {
+  gather_scales_store<G, E>(sh, sm->groups, w, sc, tid, held);
 }
 
 // Per-(tile, group) consumer state: everything the stage loop needs that does not change
@@ -466,21 +507,21 @@ struct TileId {
 // thread-level parallelism is what keeps the SM ahead of the stream).  At the end of a
 // tile each warp drops its fragment into `red[i]` and moves on; the epilogue warp folds
 // the fragments.
-template <class G, class E>
-__device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm,
-                                        const uint8_t* ring, const uint8_t* xq, const float* xs,
-                                        const float* sc, const CtaWork& w,
-                                        const StreamScratch& scr) {
+template <class G, class E, class S>
+__device__ __forceinline__ void consume(const StreamShape& sh, S* sm, const GroupDesc* groups,
+                                        const uint8_t* ring, int slot_bytes, const uint8_t* xq,
+                                        const float* xs, const float* sc, const CtaWork& w,
+                                        const StreamScratch& scr, RingPos& pos, RedPos& rpos) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int rs = warp / G::KW, kp = warp - rs * G::KW;
   const int kwarp0 = kp * (G::RUNS * 64);
   const int a_off = (kwarp0 / G::BOXK) * (G::ROWS * G::BOXK) + (rs * 16 + g) * G::PITCH +
                     kwarp0 % G::BOXK + t * 16;
-  int slot = 0;
-  uint32_t phase = 0;
-  int red_buf = 0;
-  uint32_t red_phase = 0;
+  int slot = pos.slot;
+  uint32_t phase = pos.phase;
+  int red_buf = rpos.buf;
+  uint32_t red_phase = rpos.phase;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   const uint32_t sc_s = smem_u32(sc) + warp * G::RUNS * 4;
   const uint32_t ring_s = smem_u32(ring), xq_s = smem_u32(xq), xs_s = smem_u32(xs);
@@ -494,19 +535,16 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
     StagePos p = stage_pos(sh, w, tv.tile, s);
     // ---- stages [s_begin, s_end) of this tile, group by group
     while (s < s_end) {
-      const GroupCtx gc = group_ctx<G>(sh, sm->groups[p.group], xq_s, xs_s, warp, lane);
+      const GroupCtx gc = group_ctx<G>(sh, groups[p.group], xq_s, xs_s, warp, lane);
       int ks_end = w.kstages;
       if (s_end - s < ks_end - p.kstage) ks_end = p.kstage + (s_end - s);
       for (int ks = p.kstage; ks < ks_end; ++ks, ++s) {
-        bool ok = true;
-        if (!mbar_wait(&sm->full[slot], phase)) {   // fails at once after an abort
-          set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+        if (!mbar_wait(&sm->full[slot], phase, &sm->abort_flag)) {
+          if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
           sm->abort_flag = 1;
-          ok = false;
+          return;
         }
-        if (ok)
-          consume_stage<G, E>(ring_s + slot * G::STAGE_BYTES + a_off, gc, ks * G::KC, kwarp0, wsc,
-                              acc);
+        consume_stage<G, E>(ring_s + slot * slot_bytes + a_off, gc, ks * G::KC, kwarp0, wsc, acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm->empty[slot]);
         if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
@@ -518,9 +556,10 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
 
     // ---- the CTA's share of this tile is complete: hand the warp's partial to the
     // epilogue warp and go straight on to the next tile.
-    if (!mbar_wait(&sm->red_empty[red_buf], red_phase ^ 1u)) {
-      set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+    if (!mbar_wait(&sm->red_empty[red_buf], red_phase ^ 1u, &sm->abort_flag)) {
+      if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
       sm->abort_flag = 1;
+      return;
     }
     float(*red)[32][4] = sm->red[red_buf];
 #pragma unroll
@@ -529,6 +568,19 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
     if (lane == 0) mbar_arrive(&sm->red_full[red_buf]);
     if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
   }
+  pos.slot = slot;
+  pos.phase = phase;
+  rpos.buf = red_buf;
+  rpos.phase = red_phase;
+}
+template <class G, class E>
+__device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm,
+                                        const uint8_t* ring, const uint8_t* xq, const float* xs,
+                                        const float* sc, const CtaWork& w,
+                                        const StreamScratch& scr) {
+  RingPos pos;
+  RedPos rpos;
+  consume<G, E>(sh, sm, sm->groups, ring, G::STAGE_BYTES, xq, xs, sc, w, scr, pos, rpos);
 }
 
 // The epilogue warp: for every tile of the CTA, in order, folds the consumers' fragments
@@ -538,14 +590,14 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
 // between CTAs goes through the scratch: every contributor publishes its fp32 partial,
 // and the last one to arrive at the tile's counter sums them in CTA order and emits.  In
 // kConcatK mode `tile_id.group` is 0.
-template <class G, class Emit>
-__device__ __forceinline__ void epilogue(const StreamShape& sh, StreamSmem<G>* sm,
-                                         const CtaWork& w, long long total, int grid, int cta,
-                                         const StreamScratch& scr, Emit emit) {
+template <class G, class S, class Emit>
+__device__ __forceinline__ void epilogue(const StreamShape& sh, S* sm, const CtaWork& w,
+                                         long long total, int grid, int cta,
+                                         const StreamScratch& scr, RedPos& rpos, Emit emit) {
   const int lane = threadIdx.x & 31;
   const bool concat = sh.mode != kRowsPerGroup;
-  int red_buf = 0;
-  uint32_t red_phase = 0;
+  int red_buf = rpos.buf;
+  uint32_t red_phase = rpos.phase;
   TileWalk walk;
   walk.init(w);
   for (int k = 0; k < walk.n_tiles; ++k) {
@@ -556,8 +608,8 @@ __device__ __forceinline__ void epilogue(const StreamShape& sh, StreamSmem<G>* s
     id.tile = tile;
     id.group = concat ? 0 : tile / w.tpg;
     id.tig = concat ? tile : tile - id.group * w.tpg;
-    if (!mbar_wait(&sm->red_full[red_buf], red_phase)) {
-      set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+    if (!mbar_wait(&sm->red_full[red_buf], red_phase, &sm->abort_flag)) {
+      if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
       sm->abort_flag = 1;
       return;
     }
@@ -623,6 +675,128 @@ __device__ __forceinline__ void epilogue(const StreamShape& sh, StreamSmem<G>* s
       }
     }
   }
+  rpos.buf = red_buf;
+  rpos.phase = red_phase;
+}
+template <class G, class Emit>
+__device__ __forceinline__ void epilogue(const StreamShape& sh, StreamSmem<G>* sm,
+                                         const CtaWork& w, long long total, int grid, int cta,
+                                         const StreamScratch& scr, Emit emit) {
+  RedPos rpos;
+  epilogue<G>(sh, sm, w, total, grid, cta, scr, rpos, emit);
+}
+
+// The epilogue warp of a launch whose CTAs are all resident together (a cooperative launch).
+// Same results as `epilogue`, summed in the same order, but a tile split between CTAs is
+// settled with no fence and no atomic: the CTAs that own its earlier stages store their
+// fp32 partials as tagged 64-bit words (value, tag of this launch) and move on; the CTA
+// that owns its LAST stage reads those words, retrying until each carries this launch's
+// tag, adds its own partial and emits.  The earlier owners visit the tile first and
+// publish without ever waiting, so the reads normally succeed at once.  `parts` holds
+// [grid][2][ROWS*8] such words; a word is valid when its upper half equals `tag`.
+template <class G, class S, class Emit>
+__device__ __forceinline__ void epilogue_resident(const StreamShape& sh, S* sm, const CtaWork& w,
+                                                  long long total, int grid, int cta,
+                                                  const StreamScratch& scr, uint64_t* parts,
+                                                  uint32_t tag, RedPos& rpos, Emit emit) {
+  const int lane = threadIdx.x & 31;
+  const bool concat = sh.mode != kRowsPerGroup;
+  int red_buf = rpos.buf;
+  uint32_t red_phase = rpos.phase;
+  TileWalk walk;
+  walk.init(w);
+  for (int k = 0; k < walk.n_tiles; ++k) {
+    const TileVisit tv = walk.visit(w, k);
+    const int tile = tv.tile;
+    const bool whole = tv.s_begin == 0 && tv.s_end == w.spt;
+    TileId id;
+    id.tile = tile;
+    id.group = concat ? 0 : tile / w.tpg;
+    id.tig = concat ? tile : tile - id.group * w.tpg;
+    if (!mbar_wait(&sm->red_full[red_buf], red_phase, &sm->abort_flag)) {
+      if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+      sm->abort_flag = 1;
+      return;
+    }
+    const float(*red)[32][4] = sm->red[red_buf];
+    float val[4][G::RT];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = lane + 32 * j, r = idx >> 3, col = idx & 7;
+      const int fl = 4 * (r & 7) + (col >> 1), fi = (r >> 3) * 2 + (col & 1);
+#pragma unroll
+      for (int sub = 0; sub < G::RT; ++sub) {
+        float v = 0.f;
+#pragma unroll
+        for (int q = 0; q < G::KW; ++q) v += red[sub * G::KW + q][fl][fi];
+        val[j][sub] = v;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm->red_empty[red_buf]);   // the consumers may reuse red[i]
+    if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
+    if (!whole) {
+      const long long tile_first = static_cast<long long>(tile) * w.spt;
+      const int c_first = item_owner(total, grid, tile_first);
+      const int c_last = item_owner(total, grid, tile_first + w.spt - 1);
+      if (cta != c_last) {
+        const int pslot = (tile == w.tile0) ? 0 : 1;
+        uint64_t* mine = parts + (static_cast<size_t>(cta) * 2 + pslot) * (G::ROWS * 8);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int sub = 0; sub < G::RT; ++sub)
+            st_relaxed_gpu_u64(mine + sub * 128 + lane + 32 * j,
+                               (static_cast<uint64_t>(tag) << 32) | __float_as_uint(val[j][sub]));
+        continue;
+      }
+      float own[4][G::RT];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int sub = 0; sub < G::RT; ++sub) { own[j][sub] = val[j][sub]; val[j][sub] = 0.f; }
+      for (int cc = c_first; cc < c_last; ++cc) {
+        const int ft = static_cast<int>(item_begin(total, grid, cc) / w.spt);
+        const uint64_t* pp =
+            parts + (static_cast<size_t>(cc) * 2 + (tile == ft ? 0 : 1)) * (G::ROWS * 8);
+        uint64_t got[4][G::RT];
+        uint64_t t0 = 0;
+        for (uint32_t spin = 0;; ++spin) {
+          bool ok = true;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int sub = 0; sub < G::RT; ++sub) {
+              got[j][sub] = ld_relaxed_gpu_u64(pp + sub * 128 + lane + 32 * j);
+              ok = ok && static_cast<uint32_t>(got[j][sub] >> 32) == tag;
+            }
+          if (__all_sync(0xffffffffu, ok)) break;
+          if ((spin & 63u) == 63u) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (sm->abort_flag || now - t0 > kPipeBudgetNs) {
+              if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+              sm->abort_flag = 1;
+              return;
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int sub = 0; sub < G::RT; ++sub)
+            val[j][sub] += __uint_as_float(static_cast<uint32_t>(got[j][sub]));
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int sub = 0; sub < G::RT; ++sub) val[j][sub] += own[j][sub];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) emit(id, (lane + 32 * j) >> 3, (lane + 32 * j) & 7, val[j]);
+  }
+  rpos.buf = red_buf;
+  rpos.phase = red_phase;
 }
 
 // After the CTA's last emit: returns true on the one CTA that arrives last, on every one of

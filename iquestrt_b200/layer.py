@@ -62,14 +62,21 @@ class DecodeLayer:
                                         timeout_ms=timeout_ms)
         ws.freeze()
 
-    def step(self, ao, residual, lw, *, fused: bool = True, pdl: bool = True):
+    def step(self, ao, residual, lw, *, fused: bool = True, pdl: bool = True,
+             one_launch: bool = False):
         """One layer for the first `q_len` rows.
 
         `ao [q, q_dim/tp]` bf16 is this rank's attention output, `residual [q, hidden]`
         bf16 the residual base, `lw` the rank-local weights (`synth.make_layer`).  Returns
         `(out, norm_out)`: the layer output (next residual) and its RMSNorm under the next
         layer's attention norm.  `fused=False` runs the two all-reduce tails as their own
-        launches (the reference's kernel boundaries)."""
+        launches (the reference's kernel boundaries).  `one_launch=True` runs the four
+        fused launches as a single cooperative launch (`iq_decode_layer`), same results."""
+        if one_launch:
+            if not fused:
+                raise ValueError("one_launch needs the fused tails")
+            with ops.one_launch(pdl=pdl):
+                return self.step(ao, residual, lw, fused=True, pdl=pdl)
         q = self.q_len
         moe = self.moe
         bench = self.formats == "benchmark"

@@ -18,7 +18,7 @@ from ._lib import (ACT_BF16, ACT_E4M3, ROUTE_SIGMOID, ROUTE_SOFTMAX, TAIL_ATTN, 
 
 E4M3 = torch.float8_e4m3fn
 
-__all__ = ["Scratch", "TailSpec", "linear", "router", "moe_gate", "moe_down", "tail",
+__all__ = ["Scratch", "TailSpec", "linear", "router", "moe_gate", "moe_down", "tail", "one_launch",
            "X_BF16_GROUPQ", "X_BF16_SPLIT2", "X_E4M3_GROUP", "X_E4M3_UNSCALED",
            "TAIL_ATTN", "TAIL_MLP", "ROUTE_SOFTMAX", "ROUTE_SIGMOID", "ACT_E4M3", "ACT_BF16"]
 
@@ -57,10 +57,14 @@ class Scratch:
         self.ptr = self.buf.data_ptr()
 
     def status(self, clear: bool = True) -> int:
-        """Synchronises the current stream and returns the device status code."""
+        """Synchronises the current stream and returns the device status code.  After an
+        error the whole work area is zeroed (with `clear`): a launch that gave up may have
+        left counters and hand-off words behind."""
         code = C.c_int(0)
         _lib.check("iq_status_read",
                    _lib.load().iq_status_read(self.ptr, C.byref(code), int(clear), _stream()))
+        if code.value and clear:
+            self.buf.zero_()
         return code.value
 
     def raise_on_error(self, where: str = "device status") -> None:
@@ -132,6 +136,56 @@ class TailSpec:
         return a
 
 
+class one_launch:
+    """Context in which `linear` (with its attention tail), `router`, `moe_gate` and
+    `moe_down` (with its MLP tail) do not launch but record their arguments; on exit the
+    four recorded calls run as ONE cooperative launch (`iq_decode_layer`) with results
+    bit-identical to the four separate launches.  Exactly those four calls, once each,
+    must be made inside the context."""
+
+    _active: "one_launch | None" = None
+
+    def __init__(self, *, pdl: bool = False):
+        self.pdl = pdl
+        self.parts: dict[str, object] = {}
+        self._keep: list = []
+
+    def __enter__(self):
+        if one_launch._active is not None:
+            raise RuntimeError("one_launch contexts do not nest")
+        one_launch._active = self
+        return self
+
+    def record(self, name: str, args, *keep) -> None:
+        if name in self.parts:
+            raise RuntimeError(f"{name} was called twice inside one_launch")
+        self.parts[name] = args
+        self._keep.extend(keep)
+
+    def __exit__(self, exc_type, exc, tb):
+        one_launch._active = None
+        if exc_type is not None:
+            return False
+        missing = [n for n in ("oproj", "router", "gate", "down") if n not in self.parts]
+        if missing:
+            raise RuntimeError(f"one_launch: no call recorded for {missing}")
+        a = _lib.DecodeLayerArgs()
+        a.oproj, a.router = self.parts["oproj"], self.parts["router"]
+        a.gate, a.down = self.parts["gate"], self.parts["down"]
+        _lib.check("iq_decode_layer",
+                   _lib.load().iq_decode_layer(C.byref(a), _stream(), int(self.pdl)))
+        return False
+
+
+def _launch(name: str, part: str, args, *keep) -> None:
+    """Launches `name` now, or records the call when a `one_launch` context is open."""
+    ctx = one_launch._active
+    if ctx is not None:
+        ctx.record(part, args, *keep)
+        return
+    _lib.check(name, getattr(_lib.load(), name)(C.byref(args), _stream()))
+
+
 _SCRATCH: dict[int, Scratch] = {}
 
 
@@ -187,7 +241,7 @@ def linear(x, w, w_scale, *, scratch: Scratch, out=None, x_kind=None, x_scale=No
         t = tail.to_c(scratch.ptr)
         a.tail = C.pointer(t)
     a.pdl = int(pdl)
-    _lib.check("iq_linear", _lib.load().iq_linear(C.byref(a), _stream()))
+    _launch("iq_linear", "oproj", a, t)
     return out
 
 
@@ -216,7 +270,7 @@ def router(x, weight, *, top_k: int, scratch: Scratch, score: int = ROUTE_SOFTMA
     a.m, a.h, a.e, a.top_k, a.score = m, h, e, top_k, score
     a.sel, a.wt, a.logits = sel.data_ptr(), wt.data_ptr(), logits.data_ptr()
     a.scratch, a.scratch_bytes, a.pdl = scratch.ptr, scratch.bytes, int(pdl)
-    _lib.check("iq_router", _lib.load().iq_router(C.byref(a), _stream()))
+    _launch("iq_router", "router", a)
     return sel, wt, logits
 
 
@@ -255,7 +309,7 @@ def moe_gate(x_fp8, sel, fc, fc_scale, act, *, m: int, top_k: int, scratch: Scra
     a.shared_fc, a.shared_fc_scale = _ptr(shared_fc), _ptr(shared_fc_scale)
     a.act, a.act_kind = act.data_ptr(), ACT_E4M3 if act.dtype == E4M3 else ACT_BF16
     a.scratch, a.scratch_bytes, a.pdl = scratch.ptr, scratch.bytes, int(pdl)
-    _lib.check("iq_moe_gate", _lib.load().iq_moe_gate(C.byref(a), _stream()))
+    _launch("iq_moe_gate", "gate", a)
     return act
 
 
@@ -294,7 +348,7 @@ def moe_down(act, sel, wt, proj, proj_scale, out, *, m: int, top_k: int, scratch
         t = tail.to_c(scratch.ptr)
         a.tail = C.pointer(t)
     a.pdl = int(pdl)
-    _lib.check("iq_moe_down", _lib.load().iq_moe_down(C.byref(a), _stream()))
+    _launch("iq_moe_down", "down", a, t)
     return out[:m]
 
 

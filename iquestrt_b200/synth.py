@@ -93,6 +93,8 @@ def _expert_shard(shape: LayerShape, tp, rank, device, *seed):
 
 def make_layer(shape: LayerShape, *, tp=1, rank=0, device="cuda", seed=0, layer=0):
     """Rank-local weights of one decode layer as a dict of tensors on `device`."""
+    if not 0 <= rank < tp:
+        raise ValueError(f"rank {rank} outside a tensor-parallel group of {tp}")
     h = shape.hidden
     ql, il = shape.local(tp)
     out = {}

@@ -2,9 +2,10 @@
 
     torchrun --nproc-per-node N tests/mp_worker.py --mode parity|timeout [--no-multicast]
 
-parity : the four-launch decode layer at TP = N against the CPU oracle computed from all
-         ranks' shards; identical outputs on every rank; the fused all-reduce against
-         NCCL's all_reduce of the same bf16 partials (untimed cross-check).
+parity : the decode layer at TP = N, as four launches and as one cooperative launch
+         (bit-identical), against the CPU oracle computed from all ranks' shards;
+         identical outputs on every rank; the fused all-reduce against NCCL's all_reduce
+         of the same bf16 partials (untimed cross-check).
 timeout: a rank that does not launch its all-reduce (host-side fault): the peers' wait
          runs out, they return IQ_ERR_PEER_TIMEOUT with the context still usable, the
          late rank catches up and the next call is correct again."""
@@ -76,7 +77,14 @@ def run_parity(rank, world, dev, group, multicast):
         for rep in range(3):                      # both alternating slots, repeated epochs
             out, norm_out = layer.step(ao, res, lws[rank])
         layer.check()
+        four = (out.clone(), norm_out.clone())
+        # the same layer as ONE cooperative launch: bit-identical, all-reduce included
+        for rep in range(3):
+            out, norm_out = layer.step(ao, res, lws[rank], one_launch=True)
+        layer.check()
         out, norm_out = out.clone(), norm_out.clone()
+        assert torch.equal(out.view(torch.int16), four[0].view(torch.int16)), "one launch: out"
+        assert torch.equal(norm_out.view(torch.int16), four[1].view(torch.int16)), "one launch: norm"
         # identical on every rank
         gathered = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(gathered, out)

@@ -160,3 +160,86 @@ def test_captured_layer_steps_replay_identically():
     out, norm = cap.results[-1]
     assert torch.equal(out.view(torch.int16), eager_out.view(torch.int16))
     assert torch.equal(norm.view(torch.int16), eager_norm.view(torch.int16))
+
+
+def _bits(t):
+    t = t.contiguous()
+    return t.view({1: torch.uint8, 2: torch.int16, 4: torch.int32}[t.element_size()])
+
+
+@pytest.mark.parametrize("m,tp,formats", [
+    (1, 8, "benchmark"),     # configuration 2's rank shard
+    (4, 8, "benchmark"),
+    (1, 1, "benchmark"),     # full-width shapes: other tile geometries, tensor-map stages
+    (2, 4, "benchmark"),
+    (2, 8, "reference"),     # unscaled e4m3 activations, W8A16 o_proj, softmax routes
+])
+def test_one_launch_layer_is_bit_identical(m, tp, formats):
+    """`iq_decode_layer` (one cooperative launch) against the four-launch layer it fuses:
+    every intermediate and both outputs bit for bit, three calls in a row (the hand-off
+    words carry a new tag each launch), and the scratch's counters back at zero."""
+    from iquestrt_b200 import synth
+    if formats == "benchmark":
+        shape = synth.LayerShape(n_experts=32)
+    else:
+        # the reference model's hidden size and formats, with widths the one-launch layer
+        # covers at TP=8 (o_proj K a multiple of 1024, expert width a multiple of 256)
+        shape = synth.LayerShape(hidden=3072, q_dim=8192, n_experts=32, top_k=8, inter=2048,
+                                 n_shared=0)
+    layer = _single_rank_layer(shape, m, tp, formats, 0.9, 1.1)
+    rank = min(1, tp - 1)
+    lws = [synth.make_layer(shape, tp=tp, rank=rank, device="cuda", seed=11, layer=i)
+           for i in range(2)]
+
+    def snapshot(out, norm):
+        keep = (out, norm, layer.tail.h, layer.moe.x_pad, layer.moe.x_pad_fp8, layer.router.sel,
+                layer.router.wt, layer.moe.act)
+        return [_bits(t).clone() for t in keep]
+
+    for call in range(3):
+        ao, res = synth.make_step_inputs(shape, m, tp=tp, rank=rank, device="cuda",
+                                         seed=20 + call)
+        lw = lws[call % 2]
+        want = snapshot(*layer.step(ao, res, lw))
+        layer.check()
+        got = snapshot(*layer.step(ao, res, lw, one_launch=True))
+        layer.check()
+        for name, a, b in zip(("out", "norm_out", "h", "x_pad", "x_pad_fp8", "sel", "wt", "act"),
+                              want, got):
+            assert torch.equal(a, b), f"call {call}: {name} differs"
+        control = layer.scratch.buf[:256].clone()
+        control[96:100] = 0                      # the launch counter of the one-launch layer
+        assert int(control.to(torch.int32).abs().sum()) == 0
+
+
+def test_one_launch_layer_rejects_inconsistent_parts():
+    """The four argument structs must describe one layer: a router that reads something
+    other than the attention tail's normalised rows is refused before anything launches."""
+    from iquestrt_b200 import _lib, synth
+    shape = synth.LayerShape(n_experts=16)
+    layer = _single_rank_layer(shape, 1, 8, "benchmark", 1.0, 1.0)
+    lw, ao, res = _layer_case(shape, 8, 0, 1, seed=3)
+    other = torch.zeros_like(layer.moe.x_pad)
+    real = layer.moe.x_pad
+    try:
+        layer.router_input_override = other
+        with pytest.raises(_lib.IqError):
+            from iquestrt_b200 import ops
+            with ops.one_launch(pdl=False):
+                spec = layer.ar_tail.spec(
+                    layer.oproj.outputs[layer.oproj._next_output][:1], res, lw["attn_out_norm"],
+                    lw["feed_forward_norm"], 1.0, 1.0, norm_out=real,
+                    norm_fp8=layer.moe.x_pad_fp8, norm_fp8_scale=layer.moe.x_pad_scale,
+                    inv_out=layer.ar_tail.inv)
+                layer.oproj(ao, lw["o_proj"], lw["o_scale"], tail=spec)
+                sel, wt = layer.router(other, lw["router"])
+                mspec = layer.mlp_tail.spec(layer.moe.outputs[layer.moe._out_index][:1],
+                                            spec.h_out, 1.0, lw["next_attention_norm"])
+                layer.moe(sel, wt, lw["fc"], lw["fc_scale"], lw["proj"], lw["proj_scale"],
+                          x_scale=layer.moe.x_pad_scale,
+                          shared=(lw["shared_fc"], lw["shared_fc_scale"], lw["shared_proj"],
+                                  lw["shared_proj_scale"]), tail=mspec)
+    finally:
+        del layer.router_input_override
+    torch.cuda.synchronize()
+    layer.check()
