@@ -1115,6 +1115,8 @@ static size_t plan_smem(StreamShape& sh, size_t tail_bytes, int max_groups = 1) 
     if (stream_num_tiles<G>(worst) > kMaxTiles) return 0;
     const int grid = sm_count() > 0 ? sm_count() : 1;
     sh.max_items = static_cast<int>((total_max + grid - 1) / grid) + 1;
+    if (sh.whole_tiles && stream_num_tiles<G>(worst) <= grid)     // one whole tile per CTA
+      sh.max_items = stream_stages_per_tile<G>(worst) + 1;
   }
   const size_t fixed = smem_fixed_bytes<G>(sh);
   if (fixed + 2 * G::STAGE_BYTES > static_cast<size_t>(kSmemLimit)) return 0;
@@ -1253,6 +1255,7 @@ template <class G>
 static int router_launch(const iq_router_args* a, void* stream) {
   RouterParams p{};
   StreamShape& sh = p.sh;
+  sh.whole_tiles = 1;
   sh.mode = kRowsPerGroup;
   sh.n_groups = 1;
   sh.rows_per_group = a->e;
@@ -1443,6 +1446,7 @@ static void shape_linear(StreamShape& sh, const iq_linear_args* a) {
   sh.x_blocks = (a->k + 127) / 128;
 }
 static void shape_router(StreamShape& sh, const iq_router_args* a) {
+  sh.whole_tiles = 1;
   sh.mode = kRowsPerGroup;
   sh.n_groups = 1;
   sh.rows_per_group = a->e;
@@ -1489,6 +1493,8 @@ static int max_items_of(const StreamShape& sh, int max_groups) {
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(worst)) * stream_stages_per_tile<G>(worst);
   const int grid = sm_count() > 0 ? sm_count() : 1;
+  if (sh.whole_tiles && stream_num_tiles<G>(worst) <= grid)       // one whole tile per CTA
+    return stream_stages_per_tile<G>(worst) + 1;
   return static_cast<int>((total + grid - 1) / grid) + 1;
 }
 

@@ -94,6 +94,7 @@ struct StreamShape {
   int x_blocks;        // activation scale entries per staged row (k / 128)
   int n_stages;        // ring depth
   int max_items;       // most stages one CTA can own (sizes the shared scale table)
+  int whole_tiles;     // 1: never split a tile between CTAs, even if most SMs stay idle
 };
 
 // Scratch owned by the caller (zero-filled once; every launch leaves it zeroed again).
@@ -198,7 +199,9 @@ __device__ __forceinline__ CtaWork cta_share(const StreamShape& sh, int grid, in
   const int n_tiles = stream_num_tiles<G>(sh);
   const int spt = stream_stages_per_tile<G>(sh);
   const long long total = static_cast<long long>(n_tiles) * spt;
-  if (tile_aligned_split(n_tiles, grid)) {
+  // A stream of a few megabytes is bound by latency, not bandwidth: settling a split tile
+  // costs more than streaming all of its stages through one SM.
+  if (tile_aligned_split(n_tiles, grid) || (sh.whole_tiles && n_tiles <= grid)) {
     const int g = n_tiles < grid ? n_tiles : grid;
     split_grid = g;
     if (cta >= g) return cta_work<G>(sh, 0, 0);
