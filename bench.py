@@ -274,44 +274,68 @@ def run_ours(args):
         ms = t0.elapsed_time(t1)
         layer.check()
 
-        # ---- per-kernel pass: the same calls, eager, queued behind a delay so the launches
-        # are back to back; events bracket each of the four kernels.
-        kern_ms = {"oproj_tail": [], "router": [], "gate": [], "down_tail": []}
-        n_probe = min(K, 64)
-        evs = []
-        torch.cuda._sleep(int(2e9 * 0.02))                  # ~20 ms head start for the host
+        # ---- per-kernel pass: each of the four kernels on its own, `n_probe` launches of
+        # it captured in one graph (same arguments as in the layer, weights rotating over the
+        # layers so that every launch streams from HBM, PDL on) and replayed; the kernel's
+        # time is the replay's device time / n_probe.  Events inside the layer's own graph
+        # would break the launch overlap being measured.
         q = rows
         moe = layer.moe
-        for i in range(n_probe):
+        n_probe = 32
+        sel, wt = layer.router.sel, layer.router.wt
+
+        def k_oproj(i):
             ao, res = inputs[i % n_inputs]
             lw = weights[i % n_layers]
-            e = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
-            spec = layer.ar_tail.spec(
-                layer.oproj.outputs[layer.oproj._next_output][:q], res, lw["attn_out_norm"],
-                lw["feed_forward_norm"], 1.0, 1.0, norm_out=moe.x_pad, norm_fp8=moe.x_pad_fp8,
-                norm_fp8_scale=moe.x_pad_scale, inv_out=layer.ar_tail.inv)
-            e[0].record(stream)
-            layer.oproj(ao, lw["o_proj"], lw["o_scale"], tail=spec)
-            e[1].record(stream)
-            sel, wt = layer.router(moe.x_pad, lw["router"])
-            e[2].record(stream)
+            out = layer.oproj.outputs[i % 2]
+            spec = layer.ar_tail.spec(out[:q], res, lw["attn_out_norm"], lw["feed_forward_norm"],
+                                      1.0, 1.0, norm_out=moe.x_pad, norm_fp8=moe.x_pad_fp8,
+                                      norm_fp8_scale=moe.x_pad_scale, inv_out=layer.ar_tail.inv)
+            ops.linear(ao, lw["o_proj"], lw["o_scale"], scratch=layer.scratch, out=out[:q],
+                       tail=spec, pdl=True)
+
+        def k_router(i):
+            layer.router(moe.x_pad, weights[i % n_layers]["router"], pdl=True)
+
+        def k_gate(i):
+            lw = weights[i % n_layers]
             ops.moe_gate(moe.x_pad_fp8, sel, lw["fc"], lw["fc_scale"], moe.act, m=q,
                          top_k=shape.top_k, scratch=layer.scratch, x_scale=moe.x_pad_scale,
-                         shared_fc=lw["shared_fc"], shared_fc_scale=lw["shared_fc_scale"])
-            e[3].record(stream)
-            out_buf = moe.next_out()
-            mspec = layer.mlp_tail.spec(out_buf[:q], spec.h_out, 1.0, lw["next_attention_norm"])
-            ops.moe_down(moe.act, sel, wt, lw["proj"], lw["proj_scale"], out_buf, m=q,
+                         shared_fc=lw["shared_fc"], shared_fc_scale=lw["shared_fc_scale"],
+                         pdl=True)
+
+        def k_down(i):
+            lw = weights[i % n_layers]
+            out = moe.outputs[i % 2]
+            mspec = layer.mlp_tail.spec(out[:q], layer.tail.h[:q], 1.0, lw["next_attention_norm"])
+            ops.moe_down(moe.act, sel, wt, lw["proj"], lw["proj_scale"], out, m=q,
                          top_k=shape.top_k, scratch=layer.scratch,
                          shared_proj=lw["shared_proj"],
-                         shared_proj_scale=lw["shared_proj_scale"], tail=mspec)
-            e[4].record(stream)
-            evs.append(e)
-        stream.synchronize()
-        layer.check()
-        for e in evs[min(4, len(evs) // 2):]:
-            for j, name in enumerate(kern_ms):
-                kern_ms[name].append(e[j].elapsed_time(e[j + 1]))
+                         shared_proj_scale=lw["shared_proj_scale"], tail=mspec, pdl=True)
+
+        kern_ms = {}
+        for name, fn in (("oproj_tail", k_oproj), ("router", k_router), ("gate", k_gate),
+                         ("down_tail", k_down)):
+            for i in range(2):
+                fn(i)
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(n_probe):
+                    fn(i)
+            g.replay()
+            stream.synchronize()
+            barrier()
+            samples = []
+            for _ in range(5):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                g.replay()
+                b.record(stream)
+                stream.synchronize()
+                samples.append(a.elapsed_time(b) / n_probe)
+            kern_ms[name] = samples
+            layer.check()
 
         # distinct routed experts per step (1 row -> top_k)
         distinct = shape.top_k if rows == 1 else len(set(layer.router.sel.cpu().tolist()))

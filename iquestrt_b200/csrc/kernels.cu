@@ -1102,22 +1102,39 @@ static int launch(Kernel kernel, const Params& p, int grid, size_t smem, void* s
   return IQ_OK;
 }
 
+// Most stages one CTA can own, over every group count the routes can produce, under the
+// same rule cta_share applies on the device; 0 when the stream has more tiles than the
+// scratch has counters.
+template <class G>
+static int max_items_any(const StreamShape& sh, int max_groups) {
+  const int grid = sm_count() > 0 ? sm_count() : 1;
+  int most = 0;
+  for (int n = 1; n <= max_groups; ++n) {
+    StreamShape s = sh;
+    s.n_groups = n;
+    const int n_tiles = stream_num_tiles<G>(s);
+    const int spt = stream_stages_per_tile<G>(s);
+    if (n_tiles > kMaxTiles) return 0;
+    int items;
+    if (tile_aligned_split(n_tiles, grid) || (s.whole_tiles && n_tiles <= grid)) {
+      const int g = n_tiles < grid ? n_tiles : grid;
+      items = ((n_tiles + g - 1) / g) * spt;
+    } else {
+      const long long total = static_cast<long long>(n_tiles) * spt;
+      items = static_cast<int>((total + grid - 1) / grid);
+    }
+    if (items > most) most = items;
+  }
+  return most + 1;
+}
+
 // Fills the geometry-dependent part of a shape and returns the dynamic shared memory to
 // request, or 0 when the ring does not fit.
 // `max_groups` bounds the group count a kernel may derive from the routes.
 template <class G>
 static size_t plan_smem(StreamShape& sh, size_t tail_bytes, int max_groups = 1) {
-  {
-    StreamShape worst = sh;
-    worst.n_groups = max_groups;
-    const long long total_max =
-        static_cast<long long>(stream_num_tiles<G>(worst)) * stream_stages_per_tile<G>(worst);
-    if (stream_num_tiles<G>(worst) > kMaxTiles) return 0;
-    const int grid = sm_count() > 0 ? sm_count() : 1;
-    sh.max_items = static_cast<int>((total_max + grid - 1) / grid) + 1;
-    if (sh.whole_tiles && stream_num_tiles<G>(worst) <= grid)     // one whole tile per CTA
-      sh.max_items = stream_stages_per_tile<G>(worst) + 1;
-  }
+  sh.max_items = max_items_any<G>(sh, max_groups);
+  if (sh.max_items == 0) return 0;
   const size_t fixed = smem_fixed_bytes<G>(sh);
   if (fixed + 2 * G::STAGE_BYTES > static_cast<size_t>(kSmemLimit)) return 0;
   // Ring depth: a bare copy loop saturates HBM with ~96 KB in flight per SM, but the
@@ -1483,19 +1500,9 @@ static void shape_down(StreamShape& sh, const iq_moe_down_args* a) {
   sh.x_blocks = (a->i_loc + 127) / 128;
 }
 
-// Most stages one CTA can own when the stream has up to `max_groups` groups; 0 when the
-// stream has more tiles than the scratch has counters.
 template <class G>
 static int max_items_of(const StreamShape& sh, int max_groups) {
-  StreamShape worst = sh;
-  worst.n_groups = max_groups;
-  if (stream_num_tiles<G>(worst) > kMaxTiles) return 0;
-  const long long total =
-      static_cast<long long>(stream_num_tiles<G>(worst)) * stream_stages_per_tile<G>(worst);
-  const int grid = sm_count() > 0 ? sm_count() : 1;
-  if (sh.whole_tiles && stream_num_tiles<G>(worst) <= grid)       // one whole tile per CTA
-    return stream_stages_per_tile<G>(worst) + 1;
-  return static_cast<int>((total + grid - 1) / grid) + 1;
+  return max_items_any<G>(sh, max_groups);
 }
 
 static void fill_moe_gate(MoeCommon& mc, const iq_moe_gate_args* a) {

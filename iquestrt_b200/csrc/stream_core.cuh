@@ -183,9 +183,12 @@ __device__ __forceinline__ CtaWork cta_work(const StreamShape& sh, long long it0
 // four serial global-memory round trips at the end of each CTA (publish the partial,
 // fence, count, sum), about as much as streaming four stages.  So when there are at
 // least as many tiles as CTAs and whole tiles balance to within an eighth, every CTA
-// takes whole tiles; otherwise the item range is cut evenly (stream-K).
+// takes whole tiles; so it does when there are fewer tiles than CTAs but enough of them
+// to keep three fifths of the SMs busy (such streams are short: latency, not bandwidth,
+// decides); otherwise the item range is cut evenly (stream-K).
 __host__ __device__ __forceinline__ bool tile_aligned_split(int n_tiles, int grid) {
   const int g = n_tiles < grid ? n_tiles : grid;        // CTAs that get work
+  if (n_tiles <= grid) return g * 10 >= grid * 6;       // one tile each on most of the SMs
   if (g * 10 < grid * 9) return false;                  // would idle over a tenth of the SMs
   const int per = (n_tiles + g - 1) / g;                // most tiles any CTA takes
   return static_cast<long long>(per) * grid * 8 <= static_cast<long long>(n_tiles) * 9;
