@@ -412,7 +412,7 @@ def run_ours(args):
                          "launch_us": med["gate"] * 1e3,
                          # dram__bytes_read + dram__bytes_write of one launch, from the ncu
                          # capture summarised in profiles/gate_kernel_tp1_m1.md
-                         "traffic": 231.26e6 if (tp == 1 and rows == 1) else None,
+                         "traffic": 230.82e6 if (tp == 1 and rows == 1) else None,
                          "layer_frac": by["total"] / (us * 1e-6) / 1e9 / peak},
             "kernel_us": {k: v * 1e3 for k, v in med.items()},
             "layer_bytes": by["total"],

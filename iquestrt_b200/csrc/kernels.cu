@@ -1116,7 +1116,7 @@ static int max_items_any(const StreamShape& sh, int max_groups) {
     const int spt = stream_stages_per_tile<G>(s);
     if (n_tiles > kMaxTiles) return 0;
     int items;
-    if (tile_aligned_split(n_tiles, grid) || (s.whole_tiles && n_tiles <= grid)) {
+    if (tile_aligned_split<G>(n_tiles, spt, grid, s.whole_tiles)) {
       const int g = n_tiles < grid ? n_tiles : grid;
       items = ((n_tiles + g - 1) / g) * spt;
     } else {
@@ -1436,7 +1436,10 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   }
   if (sm_count() == 0) return IQ_ERR_CUDA;
   const int k = a->i_loc;
+  // k = 1024: 32 rows x 1 KB stages (two 64-byte runs per warp) measured 5 % faster than
+  // 16 rows x 1 KB; at k = 512 the wider tile (64 rows) measured slower and is not used.
   if (k % 2048 == 0) return down_launch<Geo<1, 16, 2>>(a, stream);
+  if (k % 1024 == 0 && a->h % 32 == 0) return down_launch<Geo<2, 8, 2>>(a, stream);
   if (k % 1024 == 0) return down_launch<Geo<1, 16, 1>>(a, stream);
   if (k % 512 == 0 && a->h % 32 == 0) return down_launch<Geo<2, 8, 1>>(a, stream);
   if (k % 256 == 0 && a->h % 64 == 0) return down_launch<Geo<4, 4, 1>>(a, stream);

@@ -179,19 +179,29 @@ __device__ __forceinline__ CtaWork cta_work(const StreamShape& sh, long long it0
   return w;
 }
 
-// How the items are cut between CTAs.  Splitting a tile between two CTAs costs three or
-// four serial global-memory round trips at the end of each CTA (publish the partial,
-// fence, count, sum), about as much as streaming four stages.  So when there are at
-// least as many tiles as CTAs and whole tiles balance to within an eighth, every CTA
-// takes whole tiles; so it does when there are fewer tiles than CTAs but enough of them
-// to keep three fifths of the SMs busy (such streams are short: latency, not bandwidth,
-// decides); otherwise the item range is cut evenly (stream-K).
-__host__ __device__ __forceinline__ bool tile_aligned_split(int n_tiles, int grid) {
+// How the items are cut between CTAs.  Cutting the item range evenly (stream-K) keeps every
+// SM streaming the same number of bytes, but a tile split between two CTAs has to be
+// settled through global memory (publish, fence, count, sum: three or four round trips,
+// about 3 us) and that is hidden only behind tiles long enough to stream meanwhile.  Giving
+// every CTA whole tiles avoids the settlement at the price of imbalance.  The choice is
+// made from a small cost model in nanoseconds: a stage of S bytes passes through one SM in
+// about S/44 ns (148 SMs at 6.5 TB/s).
+template <class G>
+__host__ __device__ __forceinline__ bool tile_aligned_split(int n_tiles, int spt, int grid,
+                                                            int whole_flag) {
   const int g = n_tiles < grid ? n_tiles : grid;        // CTAs that get work
-  if (n_tiles <= grid) return g * 10 >= grid * 6;       // one tile each on most of the SMs
-  if (g * 10 < grid * 9) return false;                  // would idle over a tenth of the SMs
+  if (whole_flag && n_tiles <= grid) return true;
   const int per = (n_tiles + g - 1) / g;                // most tiles any CTA takes
-  return static_cast<long long>(per) * grid * 8 <= static_cast<long long>(n_tiles) * 9;
+  if (n_tiles >= grid && g * 10 >= grid * 9 &&
+      static_cast<long long>(per) * grid * 8 <= static_cast<long long>(n_tiles) * 9)
+    return true;                                        // balanced to within an eighth
+  const long long stage_ns = G::STAGE_BYTES / 44;
+  const long long total = static_cast<long long>(n_tiles) * spt;
+  const long long even_ns = (total + grid - 1) / grid * stage_ns;
+  const long long whole_ns = static_cast<long long>(per) * spt * stage_ns;
+  const long long tile_ns = spt * stage_ns;
+  const long long settle_ns = tile_ns < 4000 ? 3000 : 500;   // exposed unless tiles are long
+  return whole_ns <= even_ns + settle_ns;
 }
 
 // The CTA's share; `grid` is the number of CTAs launched.  CTAs beyond the work get
@@ -204,7 +214,7 @@ __device__ __forceinline__ CtaWork cta_share(const StreamShape& sh, int grid, in
   const long long total = static_cast<long long>(n_tiles) * spt;
   // A stream of a few megabytes is bound by latency, not bandwidth: settling a split tile
   // costs more than streaming all of its stages through one SM.
-  if (tile_aligned_split(n_tiles, grid) || (sh.whole_tiles && n_tiles <= grid)) {
+  if (tile_aligned_split<G>(n_tiles, spt, grid, sh.whole_tiles)) {
     const int g = n_tiles < grid ? n_tiles : grid;
     split_grid = g;
     if (cta >= g) return cta_work<G>(sh, 0, 0);
