@@ -135,7 +135,7 @@ int iq_linear(const iq_linear_args* a, void* stream);
  * plugin invoked while the host application captures a stream, a server whose memory
  * was handed out in full at start-up, a host that only ever receives input and output
  * pointers).  The work area lives in a device array built into the library, about
- * 2.1 MB on every GPU that loads it.  a->scratch and a->scratch_bytes are ignored;
+ * 4.3 MB on every GPU that loads it.  a->scratch and a->scratch_bytes are ignored;
  * a->tail must be NULL; n and k must each be at most 65536, larger shapes are refused
  * with IQ_ERR_UNSUPPORTED and a message on stderr.  The call allocates and frees no
  * device memory.  The first call on a device looks the array's address up and should
