@@ -1,8 +1,8 @@
 """Generates `tests/golden/*.pt` by running the REFERENCE's own Python code on CPU.
 
-Run in a container that has the reference checked out (default /root/reference):
+Run where the reference is checked out, giving the checkout's root:
 
-    python tests/golden/make_golden.py [reference_root]
+    python tests/golden/make_golden.py <reference_root>
 
 The reference has no golden vectors for this path, so these fixtures are outputs of the
 reference itself on small seeded inputs: `iquestrt.blockfp8.dequant / shard_scale`,
@@ -184,4 +184,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <reference_root>")
+    main(sys.argv[1])
