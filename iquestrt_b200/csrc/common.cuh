@@ -106,6 +106,10 @@ __device__ __forceinline__ void tma_2d_g2s(void* dst, const CUtensorMap* map, in
       ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
+// Brings a tensor map into the descriptor cache ahead of its first copy.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 // Weights are read once per launch: keep them from displacing activations in L2.
 __device__ __forceinline__ void bulk_g2s_evict_first(void* dst, const void* src,
                                                      uint32_t bytes, uint64_t* bar,

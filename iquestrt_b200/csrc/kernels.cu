@@ -496,6 +496,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   const int cta = blockIdx.x;
   stream_init<G>(sh, cv.sm);
+  if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1))
+    prefetch_tensormap(&p.map0);   // only a map the host filled (K-sliced stages)
   if (tid == 0) {
     GroupDesc& g = cv.sm->groups[0];
     g.w = p.w;
@@ -653,6 +655,8 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   const int cta = blockIdx.x;
   stream_init<G>(sh, cv.sm);
+  if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1))
+    prefetch_tensormap(&p.map0);   // only a map the host filled (K-sliced stages)
   if (tid == 0) {
     GroupDesc& g = cv.sm->groups[0];
     g.w = p.w;
@@ -717,8 +721,15 @@ struct MoeCommon {
 
 // Returns the number of groups.  `use_wt`: column multipliers are the routing weights
 // (Down) instead of 1 (Gate).  `x_is_pair`: the staged activation row of a column is its
-// pair's row (Down) instead of the token's row (Gate).  One thread per routed pair: the
-// table is ready four block barriers after the routes arrive.
+// pair's row (Down) instead of the token's row (Gate).  Called by all threads of `bar`;
+// the table is worked out by ONE warp (two pairs per lane, warp-level synchronisation
+// only) while the others wait at the single barrier that ends the call: the routes arrive
+// right after the dependency wait, so this sits on every CTA's critical path, and a chain
+// of block-wide barriers costs far more than the few dozen serial steps it saves.
+// With `down_groups` the same pass also fills the Down's table (routing weights as
+// multipliers, pair rows as activations) next to the Gate's table in `groups`.
+// `shared_first` puts the shared experts at the head of `groups` (not of `down_groups`)
+// instead of its tail: their tiles then have indices that do not depend on the routes.
 __device__ __noinline__ int build_groups(GroupDesc* groups, const MoeCommon& mc, bool use_wt,
                                          bool x_is_pair, int* status,
                                          int* s_ids /* 64 + kMaxGroups + 1 ints of shared memory */,
@@ -726,94 +737,134 @@ __device__ __noinline__ int build_groups(GroupDesc* groups, const MoeCommon& mc,
                                          const int* smem_sel = nullptr,
                                          const float* smem_wt = nullptr,
                                          GroupDesc* down_groups = nullptr,
-                                         const MoeCommon* down_mc = nullptr) {
-  // With `down_groups` the same pass also fills the Down's table (routing weights as
-  // multipliers, pair rows as activations) for the Gate's table in `groups`.
+                                         const MoeCommon* down_mc = nullptr,
+                                         bool shared_first = false) {
   const int tid = threadIdx.x;
-  const int pairs = mc.m * mc.top_k;
+  const int pairs = mc.m * mc.top_k;            // <= 64
   const int slots = mc.top_k + mc.n_shared;
-  int e = -1;
-  float wt = 1.0f;
-  if (tid < pairs) {
-    // the routes come from global memory, or from the CTA's own copy in shared memory
-    e = smem_sel ? smem_sel[tid] : __ldcg(mc.sel + tid);
-    if (use_wt || down_groups) wt = smem_wt ? smem_wt[tid] : __ldcg(mc.wt + tid);
-    if (e < 0 || e >= mc.n_experts) {
-      set_status(status, IQ_ERR_ROUTE);
-      e = -1;
+  const int routed_base = shared_first ? mc.n_shared : 0;
+  if (tid < 32) {
+    const int lane = tid;
+    int e[2] = {-1, -1};
+    float wt[2] = {1.0f, 1.0f};
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int q = lane + 32 * hf;
+      if (q < pairs) {
+        // the routes come from global memory, or from the CTA's own copy in shared memory
+        e[hf] = smem_sel ? smem_sel[q] : __ldcg(mc.sel + q);
+        if (use_wt || down_groups) wt[hf] = smem_wt ? smem_wt[q] : __ldcg(mc.wt + q);
+      }
     }
-    s_ids[tid] = e;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int q = lane + 32 * hf;
+      if (q < pairs) {
+        if (e[hf] < 0 || e[hf] >= mc.n_experts) {
+          set_status(status, IQ_ERR_ROUTE);
+          e[hf] = -1;
+        }
+        s_ids[q] = e[hf];
+      }
+    }
+    __syncwarp();
+    // first pair with my expert, and the group index = number of distinct experts that
+    // appear before it
+    int first[2] = {lane, lane + 32};
+    int gi[2] = {0, 0};
+    int n_routed = 0;
+    if (pairs <= 32) {
+      // one pair per lane: the warp's match / ballot do the search (no loops, no branches)
+      const unsigned live = __ballot_sync(0xffffffffu, lane < pairs && e[0] >= 0);
+      const unsigned same = __match_any_sync(0xffffffffu, e[0]) & live;
+      first[0] = same ? __ffs(same) - 1 : lane;
+      const unsigned firsts =
+          __ballot_sync(0xffffffffu, lane < pairs && e[0] >= 0 && first[0] == lane);
+      gi[0] = __popc(firsts & ((1u << first[0]) - 1u));
+      n_routed = __popc(firsts);
+    } else {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int q = lane + 32 * hf;
+        if (q < pairs) {
+          for (int r = 0; r < q; ++r)
+            if (s_ids[r] == e[hf]) { first[hf] = r; break; }
+          s_ids[64 + q] = (e[hf] >= 0 && first[hf] == q) ? 1 : 0;
+        }
+      }
+      __syncwarp();
+      for (int r = 0; r < pairs; ++r) {
+        const int f = s_ids[64 + r];
+        n_routed += f;
+        gi[0] += r < first[0] ? f : 0;
+        gi[1] += r < first[1] ? f : 0;
+      }
+    }
+    const int n_groups = n_routed + mc.n_shared;
+    if (lane == 0) s_ids[64 + kMaxGroups] = n_groups;
+    auto open_group = [](GroupDesc& gd, const MoeCommon& c, int expert) {
+      gd.w = c.w + static_cast<size_t>(expert) * c.w_stride;
+      gd.scale = c.w_scale + static_cast<size_t>(expert) * c.scale_stride;
+      gd.row_base = expert * c.rows_per_expert;
+      gd.map_id = 0;
+      // all columns unused: multipliers 0, rows -1, outputs 0 (8-byte stores)
+      unsigned long long* mul = reinterpret_cast<unsigned long long*>(gd.col_mul);
+      unsigned long long* row = reinterpret_cast<unsigned long long*>(gd.col_row);
+      unsigned long long* out = reinterpret_cast<unsigned long long*>(gd.col_out);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) mul[i] = 0ull;
+      row[0] = row[1] = ~0ull;
+      out[0] = out[1] = 0ull;
+    };
+    auto shared_group = [&](GroupDesc& gd, const MoeCommon& c, int sidx, bool pair_rows) {
+      gd.w = c.shared_w + static_cast<size_t>(sidx) * c.w_stride;
+      gd.scale = c.shared_scale + static_cast<size_t>(sidx) * c.scale_stride;
+      gd.row_base = sidx * c.rows_per_expert;
+      gd.map_id = 1;
+      for (int col = 0; col < kMaxCols; ++col) {
+        const bool live = col < c.m;
+        const int pair_row = col * slots + c.top_k + sidx;
+        gd.col_row[col] = static_cast<int16_t>(live ? (pair_rows ? pair_row : col) : -1);
+        gd.col_mul[col] = live ? 1.0f : 0.f;
+        gd.col_out[col] = static_cast<int16_t>(pair_rows ? col : pair_row);
+      }
+    };
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int q = lane + 32 * hf;
+      if (q < pairs && e[hf] >= 0 && first[hf] == q) {
+        open_group(groups[routed_base + gi[hf]], mc, e[hf]);
+        if (down_groups) open_group(down_groups[gi[hf]], *down_mc, e[hf]);
+      }
+    }
+    if (lane < mc.n_shared) {
+      shared_group(groups[shared_first ? lane : n_groups - mc.n_shared + lane], mc, lane,
+                   x_is_pair);
+      if (down_groups)
+        shared_group(down_groups[n_groups - mc.n_shared + lane], *down_mc, lane, true);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int q = lane + 32 * hf;
+      if (q < pairs && e[hf] >= 0) {
+        const int row = q / mc.top_k, slot = q - row * mc.top_k;
+        const int pair_row = row * slots + slot;
+        GroupDesc& gd = groups[routed_base + gi[hf]];
+        gd.col_row[row] = static_cast<int16_t>(x_is_pair ? pair_row : row);
+        gd.col_mul[row] = use_wt ? wt[hf] : 1.0f;
+        gd.col_out[row] = static_cast<int16_t>(x_is_pair ? row : pair_row);
+        if (down_groups) {
+          GroupDesc& dd = down_groups[gi[hf]];
+          dd.col_row[row] = static_cast<int16_t>(pair_row);
+          dd.col_mul[row] = wt[hf];
+          dd.col_out[row] = static_cast<int16_t>(row);
+        }
+      }
+    }
   }
   bar.sync();
-  // is pair q the first with its expert?
-  if (tid < pairs) {
-    bool is_first = e >= 0;
-    for (int r = 0; r < tid && is_first; ++r) is_first = s_ids[r] != e;
-    s_ids[64 + tid] = is_first ? 1 : 0;
-  }
-  bar.sync();
-  auto open_group = [](GroupDesc& gd, const MoeCommon& c, int expert) {
-    gd.w = c.w + static_cast<size_t>(expert) * c.w_stride;
-    gd.scale = c.w_scale + static_cast<size_t>(expert) * c.scale_stride;
-    gd.row_base = expert * c.rows_per_expert;
-    gd.map_id = 0;
-    for (int col = 0; col < kMaxCols; ++col) {
-      gd.col_row[col] = -1;
-      gd.col_mul[col] = 0.f;
-      gd.col_out[col] = 0;
-    }
-  };
-  // group index = number of distinct experts before the first occurrence of mine
-  int first = tid, gi = 0, n_routed = 0;
-  if (tid < pairs) {
-    for (int q = 0; q < tid; ++q)
-      if (s_ids[q] == e) { first = q; break; }
-    for (int q = 0; q < pairs; ++q) {
-      const int f = s_ids[64 + q];
-      n_routed += f;
-      gi += q < first ? f : 0;
-    }
-    if (tid == 0) s_ids[64 + kMaxGroups] = n_routed + mc.n_shared;
-    if (e >= 0 && first == tid) {
-      open_group(groups[gi], mc, e);
-      if (down_groups) open_group(down_groups[gi], *down_mc, e);
-    }
-  }
-  bar.sync();
-  const int n_groups = s_ids[64 + kMaxGroups];
-  auto shared_group = [&](GroupDesc& gd, const MoeCommon& c, int sidx, bool pair_rows) {
-    gd.w = c.shared_w + static_cast<size_t>(sidx) * c.w_stride;
-    gd.scale = c.shared_scale + static_cast<size_t>(sidx) * c.scale_stride;
-    gd.row_base = sidx * c.rows_per_expert;
-    gd.map_id = 1;
-    for (int col = 0; col < kMaxCols; ++col) {
-      const bool live = col < c.m;
-      const int pair_row = col * slots + c.top_k + sidx;
-      gd.col_row[col] = static_cast<int16_t>(live ? (pair_rows ? pair_row : col) : -1);
-      gd.col_mul[col] = live ? 1.0f : 0.f;
-      gd.col_out[col] = static_cast<int16_t>(pair_rows ? col : pair_row);
-    }
-  };
-  if (tid < pairs && e >= 0) {
-    const int row = tid / mc.top_k, slot = tid - row * mc.top_k;
-    const int pair_row = row * slots + slot;
-    GroupDesc& gd = groups[gi];
-    gd.col_row[row] = static_cast<int16_t>(x_is_pair ? pair_row : row);
-    gd.col_mul[row] = use_wt ? wt : 1.0f;
-    gd.col_out[row] = static_cast<int16_t>(x_is_pair ? row : pair_row);
-    if (down_groups) {
-      GroupDesc& dd = down_groups[gi];
-      dd.col_row[row] = static_cast<int16_t>(pair_row);
-      dd.col_mul[row] = wt;
-      dd.col_out[row] = static_cast<int16_t>(row);
-    }
-  } else if (tid >= 64 && tid < 64 + mc.n_shared) {
-    const int sidx = tid - 64;
-    shared_group(groups[n_groups - mc.n_shared + sidx], mc, sidx, x_is_pair);
-    if (down_groups) shared_group(down_groups[n_groups - mc.n_shared + sidx], *down_mc, sidx, true);
-  }
-  bar.sync();
-  return n_groups;
+  return s_ids[64 + kMaxGroups];
 }
 
 struct GateParams {
@@ -826,7 +877,53 @@ struct GateParams {
   int act_kind;
   void* scratch;
   int pdl_level;
+  int early_shared;   // see gate_kernel
 };
+
+// One stream of the Gate: the tiles of `wk`, every role with its ring / reduction position
+// carried in `pos` / `rpos` (the kernel may run two streams back to back).
+template <class G>
+__device__ __forceinline__ void gate_stream(const GateParams& p, const StreamShape& sh,
+                                            const Carve<G>& cv, const StreamScratch& scr,
+                                            const CtaWork& wk, long long total, int grid, int cta,
+                                            bool stage_x, RingPos& pos, RedPos& rpos) {
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (warp == kProducerWarp) {
+    produce<G>(sh, cv.sm, cv.sm->groups, cv.ring, G::STAGE_BYTES, wk, scr.status, &p.map0, &p.map1,
+               pos);
+  } else if (warp < kConsumerWarps) {
+    float held[kGatherHeld];
+    gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);
+    if (stage_x)
+      stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
+    gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
+    named_bar_sync(1, kConsumerThreads);
+    consume<G, ElemE4M3>(sh, cv.sm, cv.sm->groups, cv.ring, G::STAGE_BYTES, cv.xq, cv.xs, cv.sc, wk,
+                         scr, pos, rpos);
+  } else {
+    const int i_loc = p.mc.i_loc, m = p.mc.m;
+    const int act_kind = p.act_kind;
+    void* act = p.act;
+    StreamSmem<G>* sm = cv.sm;
+    auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
+      const GroupDesc& gd = sm->groups[id.group];
+      if (col >= m || gd.col_row[col] < 0) return;
+      // sub-tiles [0, RT/2) are gate rows, [RT/2, RT) the matching up rows
+#pragma unroll
+      for (int sub = 0; sub < G::RT / 2; ++sub) {
+        const float gte = val[sub], up = val[sub + G::RT / 2];
+        const float v = gte / (1.0f + expf(-gte)) * up;
+        const size_t o = static_cast<size_t>(gd.col_out[col]) * i_loc +
+                         id.tig * (G::ROWS / 2) + sub * 16 + r;
+        if (act_kind == IQ_ACT_E4M3)
+          static_cast<uint8_t*>(act)[o] = f32_to_e4m3_sat(v);
+        else
+          static_cast<__nv_bfloat16*>(act)[o] = __float2bfloat16_rn(v);
+      }
+    };
+    epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, rpos, emit);
+  }
+}
 
 template <class G>
 __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant__ GateParams p) {
@@ -835,54 +932,64 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
   const Carve<G> cv = carve<G>(smem, sh);
   const StreamScratch scr = scratch_of(p.scratch);
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int cta = blockIdx.x, n_cta = static_cast<int>(gridDim.x);
   stream_init<G>(sh, cv.sm);
+  if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
+    prefetch_tensormap(&p.map0);   // only maps the host filled (K-sliced stages)
+    if (p.mc.n_shared > 0) prefetch_tensormap(&p.map1);
+  }
+  RingPos pos;
+  RedPos rpos;
   // Level 2: the activations were written two launches back (by the attention tail) and
   // can be staged while the router, the immediate predecessor, is still finishing.
   const bool early_x = p.pdl_level >= 2;
   if (early_x && warp < kConsumerWarps)
     stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
+  // With `early_shared` (host: level 2, shared experts, whole tiles dealt round robin
+  // whatever the routes) the shared experts are the first groups, CTA c's first tile is
+  // tile c, and if that is a shared expert's tile the CTA streams and finishes it NOW:
+  // nothing in it depends on the routes.  A whole tile needs no scratch, and the
+  // activation buffer's last reader (the previous layer's Down) finished before the
+  // router could start.
+  int done_tiles = 0;
+  if (p.early_shared) {
+    const int tpg = stream_tiles_per_group<G>(sh);
+    if (tid < p.mc.n_shared) {
+      GroupDesc& gd = cv.sm->groups[tid];
+      gd.w = p.mc.shared_w + static_cast<size_t>(tid) * p.mc.w_stride;
+      gd.scale = p.mc.shared_scale + static_cast<size_t>(tid) * p.mc.scale_stride;
+      gd.row_base = tid * p.mc.rows_per_expert;
+      gd.map_id = 1;
+      for (int c = 0; c < kMaxCols; ++c) {
+        const bool live = c < p.mc.m;
+        gd.col_row[c] = static_cast<int16_t>(live ? c : -1);
+        gd.col_mul[c] = live ? 1.0f : 0.f;
+        gd.col_out[c] = static_cast<int16_t>(c * (p.mc.top_k + p.mc.n_shared) + p.mc.top_k + tid);
+      }
+    }
+    __syncthreads();
+    if (cta < p.mc.n_shared * tpg) {
+      StreamShape sa = sh;
+      sa.n_groups = p.mc.n_shared;
+      CtaWork wa = cta_work<G>(sa, static_cast<long long>(cta) * stream_stages_per_tile<G>(sa),
+                               static_cast<long long>(cta + 1) * stream_stages_per_tile<G>(sa));
+      gate_stream<G>(p, sa, cv, scr, wa, 0, n_cta, cta, false, pos, rpos);
+      done_tiles = 1;
+    }
+    __syncthreads();
+  }
   after_wait();                     // the routes come from the predecessor
-  sh.n_groups = build_groups(cv.sm->groups, p.mc, false, false, scr.status, cv.sm->route_ids);
+  sh.n_groups = build_groups(cv.sm->groups, p.mc, false, false, scr.status, cv.sm->route_ids,
+                             BlockBar{}, nullptr, nullptr, nullptr, nullptr, p.early_shared != 0);
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
-  const int cta = blockIdx.x;
-  {
-    const CtaWork wk = cta_share<G>(sh, static_cast<int>(gridDim.x), cta, grid);
-    if (warp == kProducerWarp) {
-      produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
-    } else if (warp < kConsumerWarps) {
-      float held[kGatherHeld];
-      gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);
-      if (!early_x)
-        stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
-      gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
-      named_bar_sync(1, kConsumerThreads);
-      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
-    } else {
-      const int i_loc = p.mc.i_loc, m = p.mc.m;
-      const int act_kind = p.act_kind;
-      void* act = p.act;
-      StreamSmem<G>* sm = cv.sm;
-      auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
-        const GroupDesc& gd = sm->groups[id.group];
-        if (col >= m || gd.col_row[col] < 0) return;
-        // sub-tiles [0, RT/2) are gate rows, [RT/2, RT) the matching up rows
-#pragma unroll
-        for (int sub = 0; sub < G::RT / 2; ++sub) {
-          const float gte = val[sub], up = val[sub + G::RT / 2];
-          const float v = gte / (1.0f + expf(-gte)) * up;
-          const size_t o = static_cast<size_t>(gd.col_out[col]) * i_loc +
-                           id.tig * (G::ROWS / 2) + sub * 16 + r;
-          if (act_kind == IQ_ACT_E4M3)
-            static_cast<uint8_t*>(act)[o] = f32_to_e4m3_sat(v);
-          else
-            static_cast<__nv_bfloat16*>(act)[o] = __float2bfloat16_rn(v);
-        }
-      };
-      epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, emit);
-    }
+  CtaWork wk = cta_share<G>(sh, n_cta, cta, grid);
+  if (done_tiles) {                 // the first tile is finished already
+    wk.tile0 += wk.tile_step;
+    wk.n_items -= wk.spt;
   }
+  gate_stream<G>(p, sh, cv, scr, wk, total, grid, cta, !early_x, pos, rpos);
   stream_drain_on_abort<G>(cv.sm);
 }
 
@@ -907,6 +1014,10 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
   const StreamScratch scr = scratch_of(p.scratch);
   const int tid = threadIdx.x, warp = tid >> 5;
   stream_init<G>(sh, cv.sm);
+  if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
+    prefetch_tensormap(&p.map0);   // only maps the host filled (K-sliced stages)
+    if (p.mc.n_shared > 0) prefetch_tensormap(&p.map1);
+  }
   // Level 2: the routes were written two launches back (by the router), so the group
   // table, the weight stream and the scale gather all start while the Gate, the immediate
   // predecessor, is still finishing; only the Gate's activations are waited for.
@@ -1362,6 +1473,22 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   sh.x_rows = a->m;
   sh.x_pitch = a->h + 64;
   sh.x_blocks = a->h / 128;
+  // Early start on the shared experts (pdl level 2 only): needs whole tiles for every group
+  // count valid routes can produce, so that a CTA's first tile is known before the routes.
+  bool early = a->pdl >= 2 && a->n_shared > 0;
+  if (early) {
+    const int grid = sm_count();
+    for (int n = a->n_shared + a->top_k; n <= a->n_shared + a->m * a->top_k && early; ++n) {
+      StreamShape t = sh;
+      t.n_groups = n;
+      early = tile_aligned_split<G>(stream_num_tiles<G>(t), stream_stages_per_tile<G>(t), grid, 0);
+    }
+  }
+  if (early) {
+    sh.whole_tiles = 2;
+    sh.round_robin = 1;
+  }
+  p.early_shared = early ? 1 : 0;
   const size_t smem = plan_smem<G>(sh, 0, a->m * a->top_k + a->n_shared);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->fc,

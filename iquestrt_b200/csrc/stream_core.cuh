@@ -28,6 +28,8 @@
 // epilogue (all-reduce tail, or top-k selection) on the completed rows.
 #pragma once
 
+#include <cstddef>
+
 #include "common.cuh"
 
 namespace iqb {
@@ -75,6 +77,10 @@ struct GroupDesc {
   int16_t col_out[kMaxCols];  // output row per MMA column
 };
 
+static_assert(offsetof(GroupDesc, col_mul) % 8 == 0 && offsetof(GroupDesc, col_row) % 8 == 0 &&
+                  offsetof(GroupDesc, col_out) % 8 == 0 && sizeof(GroupDesc) % 8 == 0,
+              "the column arrays are cleared with 8-byte stores");
+
 enum TileMode : int {
   kRowsPerGroup = 0,  // tiles = groups x row-tiles; every tile contracts over one group's K
   kConcatK = 1,       // tiles = row-tiles; every tile contracts over all groups' K in turn
@@ -94,7 +100,8 @@ struct StreamShape {
   int x_blocks;        // activation scale entries per staged row (k / 128)
   int n_stages;        // ring depth
   int max_items;       // most stages one CTA can own (sizes the shared scale table)
-  int whole_tiles;     // 1: never split a tile between CTAs, even if most SMs stay idle
+  int whole_tiles;     // 1: never split a tile when there are no more tiles than CTAs; 2: never
+  int round_robin;     // 1: when CTAs take whole tiles, CTA c takes tiles c, c+G, c+2G, ...
 };
 
 // Scratch owned by the caller (zero-filled once; every launch leaves it zeroed again).
@@ -160,6 +167,7 @@ __host__ __device__ __forceinline__ int stream_stages_per_tile(const StreamShape
 // The CTA's share of the work, in 32-bit terms.
 struct CtaWork {
   int tile0;      // first tile
+  int tile_step;  // distance between the CTA's consecutive tiles (1 unless round robin)
   int stage0;     // first stage inside it
   int n_items;    // stages owned
   int spt;        // stages per tile
@@ -174,6 +182,7 @@ __device__ __forceinline__ CtaWork cta_work(const StreamShape& sh, long long it0
   w.tpg = stream_tiles_per_group<G>(sh);
   w.spt = sh.mode == kRowsPerGroup ? w.kstages : w.kstages * sh.n_groups;
   w.tile0 = static_cast<int>(it0 / w.spt);
+  w.tile_step = 1;
   w.stage0 = static_cast<int>(it0 - static_cast<long long>(w.tile0) * w.spt);
   w.n_items = static_cast<int>(it1 - it0);
   return w;
@@ -190,7 +199,7 @@ template <class G>
 __host__ __device__ __forceinline__ bool tile_aligned_split(int n_tiles, int spt, int grid,
                                                             int whole_flag) {
   const int g = n_tiles < grid ? n_tiles : grid;        // CTAs that get work
-  if (whole_flag && n_tiles <= grid) return true;
+  if (whole_flag >= 2 || (whole_flag && n_tiles <= grid)) return true;
   const int per = (n_tiles + g - 1) / g;                // most tiles any CTA takes
   if (n_tiles >= grid && g * 10 >= grid * 9 &&
       static_cast<long long>(per) * grid * 8 <= static_cast<long long>(n_tiles) * 9)
@@ -218,6 +227,15 @@ __device__ __forceinline__ CtaWork cta_share(const StreamShape& sh, int grid, in
     const int g = n_tiles < grid ? n_tiles : grid;
     split_grid = g;
     if (cta >= g) return cta_work<G>(sh, 0, 0);
+    if (sh.round_robin) {
+      // tiles cta, cta + grid, ...: the CTA's first tile does not depend on how many
+      // tiles (groups) there turn out to be
+      const int count = (n_tiles - cta + grid - 1) / grid;
+      CtaWork w = cta_work<G>(sh, static_cast<long long>(cta) * spt,
+                              static_cast<long long>(cta + count) * spt);
+      w.tile_step = grid;
+      return w;
+    }
     const long long t0 = static_cast<long long>(n_tiles) * cta / g;
     const long long t1 = static_cast<long long>(n_tiles) * (cta + 1) / g;
     return cta_work<G>(sh, t0 * spt, t1 * spt);
@@ -274,7 +292,7 @@ struct TileWalk {
   __device__ __forceinline__ TileVisit visit(const CtaWork& w, int k) const {
     const int i = last_first ? (k == 0 ? n_tiles - 1 : k - 1) : k;   // natural index
     TileVisit v;
-    v.tile = w.tile0 + i;
+    v.tile = w.tile0 + i * w.tile_step;
     v.s_begin = i == 0 ? w.stage0 : 0;
     v.local0 = i == 0 ? 0 : n_first + (i - 1) * w.spt;
     const int avail = w.n_items - v.local0;
@@ -399,7 +417,7 @@ __device__ __forceinline__ float gather_one(const StreamShape& sh, const GroupDe
   const int rs = warp / G::KW, kp = warp - rs * G::KW;
   const int lin = w.stage0 + st;
   const int tq = lin / w.spt;
-  const StagePos p = stage_pos(sh, w, w.tile0 + tq, lin - tq * w.spt);
+  const StagePos p = stage_pos(sh, w, w.tile0 + tq * w.tile_step, lin - tq * w.spt);
   const int row0 = tile_row(sh, G::ROWS, p.tig, rs * 16);
   const int kb = p.kstage * G::KC + kp * (G::RUNS * 64) + run * 64;
   return __ldg(groups[p.group].scale + static_cast<size_t>(row0 >> sh.rg_shift) * krow +
