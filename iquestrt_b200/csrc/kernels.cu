@@ -589,10 +589,11 @@ __device__ inline uint32_t ordered_key(float v) {
 
 // One warp selects row `row`: top_k rounds of (largest key, then smallest id), softmax
 // or renormalised sigmoid summed in descending-value order, pairs stored by ascending id.
-__device__ void select_row(const float* logits, int e, int top_k, int score, int row, int* sel,
-                           float* wt, bool logits_in_smem = false) {
+template <int kMaxPerLane>
+__device__ __forceinline__ void select_row_impl(const float* logits, int e, int top_k, int score,
+                                                int row, int* sel, float* wt,
+                                                bool logits_in_smem) {
   const int lane = threadIdx.x & 31;
-  constexpr int kMaxPerLane = 16;            // e <= 512
   uint32_t key[kMaxPerLane];
   const int per = (e + 31) / 32;
 #pragma unroll
@@ -641,6 +642,16 @@ __device__ void select_row(const float* logits, int e, int top_k, int score, int
     sel[row * top_k + rank] = my_id;
     wt[row * top_k + rank] = my_p / sum;
   }
+}
+
+// The selection runs on one warp at the end of the router's critical path, so its length
+// in instructions matters: up to 256 experts take the variant with 8 keys per lane.
+__device__ void select_row(const float* logits, int e, int top_k, int score, int row, int* sel,
+                           float* wt, bool logits_in_smem = false) {
+  if (e <= 256)
+    select_row_impl<8>(logits, e, top_k, score, row, sel, wt, logits_in_smem);
+  else
+    select_row_impl<16>(logits, e, top_k, score, row, sel, wt, logits_in_smem);   // e <= 512
 }
 
 template <class G>
