@@ -139,3 +139,54 @@ class CapturedSteps:
 
     def replay(self):
         self.graph.replay()
+
+
+class HostStep:
+    """One `DecodeLayer.step` from HOST buffers as a single CUDA-graph launch: the graph
+    holds the host-to-device copies of the step's inputs (from this object's pinned
+    buffers), the layer's launches, and the device-to-host copy of the layer output.
+
+        hs = HostStep(layer, lw)
+        out = hs(ao_host, residual_host)        # host bf16 tensors in, pinned host tensor out
+
+    `__call__` copies its arguments into the pinned input buffers, launches the graph and
+    waits for it; `out` is overwritten by the next call."""
+
+    def __init__(self, layer: DecodeLayer, lw, *, one_launch: bool = False, pdl: bool = True):
+        dev = layer.norm_out.device
+        q, shape = layer.q_len, layer.shape
+        self.layer = layer
+        self.stream = torch.cuda.Stream(device=dev)
+        self.ao_pin = torch.empty(q, layer.q_loc, dtype=torch.bfloat16).pin_memory()
+        self.res_pin = torch.empty(q, shape.hidden, dtype=torch.bfloat16).pin_memory()
+        self.out_pin = torch.empty(q, shape.hidden, dtype=torch.bfloat16).pin_memory()
+        self.ao_dev = torch.empty(q, layer.q_loc, dtype=torch.bfloat16, device=dev)
+        self.res_dev = torch.empty(q, shape.hidden, dtype=torch.bfloat16, device=dev)
+        self.ao_pin.zero_()
+        self.res_pin.zero_()
+
+        def body():
+            self.ao_dev.copy_(self.ao_pin, non_blocking=True)
+            self.res_dev.copy_(self.res_pin, non_blocking=True)
+            out, _ = layer.step(self.ao_dev, self.res_dev, lw, one_launch=one_launch, pdl=pdl)
+            self.out_pin.copy_(out, non_blocking=True)
+
+        with torch.cuda.stream(self.stream):
+            for _ in range(2):                    # both output slots warm before the capture
+                body()
+            self.stream.synchronize()
+            layer.check()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self.stream):
+                body()
+        self.stream.synchronize()
+        self.h2d_bytes = 2 * (self.ao_pin.numel() + self.res_pin.numel())
+        self.d2h_bytes = 2 * self.out_pin.numel()
+
+    def __call__(self, ao_host, residual_host):
+        self.ao_pin.copy_(ao_host)
+        self.res_pin.copy_(residual_host)
+        with torch.cuda.stream(self.stream):
+            self.graph.replay()
+        self.stream.synchronize()
+        return self.out_pin

@@ -243,3 +243,22 @@ def test_one_launch_layer_rejects_inconsistent_parts():
         del layer.router_input_override
     torch.cuda.synchronize()
     layer.check()
+
+
+def test_host_step_matches_device_step():
+    """`HostStep` (host buffers in, one graph launch with the copies inside, host buffer
+    out) returns what `DecodeLayer.step` returns on the same inputs, call after call."""
+    from iquestrt_b200 import synth
+    from iquestrt_b200.layer import HostStep
+    shape = synth.LayerShape(n_experts=16)
+    layer = _single_rank_layer(shape, 1, 8, "benchmark", 1.0, 1.0)
+    lw, _, _ = _layer_case(shape, 8, 0, 1, seed=3)
+    hs = HostStep(layer, lw)
+    for call in range(3):
+        ao, res = synth.make_step_inputs(shape, 1, tp=8, rank=0, device="cuda", seed=40 + call)
+        want, _ = layer.step(ao, res, lw)
+        want = want.cpu()
+        got = hs(ao.cpu(), res.cpu())
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    layer.check()
+    assert hs.h2d_bytes == 2 * (ao.numel() + res.numel()) and hs.d2h_bytes == 2 * want.numel()
