@@ -1237,6 +1237,7 @@ static int max_items_any(const StreamShape& sh, int max_groups) {
     const int n_tiles = stream_num_tiles<G>(s);
     const int spt = stream_stages_per_tile<G>(s);
     if (n_tiles > kMaxTiles) return 0;
+    if (spt >= 32768) return 0;        // the gather's multiply-high division needs 16-bit operands
     int items;
     if (tile_aligned_split<G>(n_tiles, spt, grid, s.whole_tiles)) {
       const int g = n_tiles < grid ? n_tiles : grid;
@@ -1245,6 +1246,7 @@ static int max_items_any(const StreamShape& sh, int max_groups) {
       const long long total = static_cast<long long>(n_tiles) * spt;
       items = static_cast<int>((total + grid - 1) / grid);
     }
+    if (items >= 32768) return 0;
     if (items > most) most = items;
   }
   return most + 1;

@@ -164,6 +164,17 @@ __host__ __device__ __forceinline__ int stream_stages_per_tile(const StreamShape
   return sh.mode == kRowsPerGroup ? kstages : kstages * sh.n_groups;
 }
 
+// Exact a / d for 0 <= a < 65536 and 1 <= d < 65536 as one multiply-high: magic(d) =
+// floor(2^32 / d) + 1 (0 stands for d == 1).  The per-entry index arithmetic of the scale
+// gather runs on every CTA's critical path; a runtime integer division costs ~30
+// instructions, this costs one.
+__host__ __device__ __forceinline__ uint32_t div_magic(int d) {
+  return d <= 1 ? 0u : static_cast<uint32_t>(0x100000000ull / static_cast<uint32_t>(d)) + 1u;
+}
+__device__ __forceinline__ int fast_div(int a, uint32_t magic) {
+  return magic ? static_cast<int>(__umulhi(static_cast<uint32_t>(a), magic)) : a;
+}
+
 // The CTA's share of the work, in 32-bit terms.
 struct CtaWork {
   int tile0;      // first tile
@@ -173,6 +184,7 @@ struct CtaWork {
   int spt;        // stages per tile
   int kstages;    // stages per group K
   int tpg;        // tiles per group
+  uint32_t mg_spt, mg_kstages, mg_tpg;   // div_magic of the three
 };
 
 template <class G>
@@ -181,6 +193,9 @@ __device__ __forceinline__ CtaWork cta_work(const StreamShape& sh, long long it0
   w.kstages = sh.k_bytes / G::KC;
   w.tpg = stream_tiles_per_group<G>(sh);
   w.spt = sh.mode == kRowsPerGroup ? w.kstages : w.kstages * sh.n_groups;
+  w.mg_spt = div_magic(w.spt);
+  w.mg_kstages = div_magic(w.kstages);
+  w.mg_tpg = div_magic(w.tpg);
   w.tile0 = static_cast<int>(it0 / w.spt);
   w.tile_step = 1;
   w.stage0 = static_cast<int>(it0 - static_cast<long long>(w.tile0) * w.spt);
@@ -415,9 +430,20 @@ __device__ __forceinline__ float gather_one(const StreamShape& sh, const GroupDe
   const int st = i / G::SCALES_PER_STAGE, e = i - st * G::SCALES_PER_STAGE;
   const int warp = e / G::RUNS, run = e - warp * G::RUNS;
   const int rs = warp / G::KW, kp = warp - rs * G::KW;
+  // (all operands are far below 65536: stages per CTA, tiles <= 16384, stages per tile)
   const int lin = w.stage0 + st;
-  const int tq = lin / w.spt;
-  const StagePos p = stage_pos(sh, w, w.tile0 + tq * w.tile_step, lin - tq * w.spt);
+  const int tq = fast_div(lin, w.mg_spt);
+  const int tile = w.tile0 + tq * w.tile_step, s = lin - tq * w.spt;
+  StagePos p;
+  if (sh.mode == kRowsPerGroup) {
+    p.group = fast_div(tile, w.mg_tpg);
+    p.tig = tile - p.group * w.tpg;
+    p.kstage = s;
+  } else {
+    p.group = fast_div(s, w.mg_kstages);
+    p.tig = tile;
+    p.kstage = s - p.group * w.kstages;
+  }
   const int row0 = tile_row(sh, G::ROWS, p.tig, rs * 16);
   const int kb = p.kstage * G::KC + kp * (G::RUNS * 64) + run * 64;
   return __ldg(groups[p.group].scale + static_cast<size_t>(row0 >> sh.rg_shift) * krow +
