@@ -606,7 +606,7 @@ __device__ __forceinline__ void select_row_impl(const float* logits, int e, int 
     key[j] = (j < per && id < e) ? ordered_key(lv) : 0u;
   }
   int my_id = 0x7fffffff;
-  float my_val = 0.f, top_val = 0.f, sum = 0.f, my_p = 0.f;
+  float top_val = 0.f, sum = 0.f, my_p = 0.f;
   for (int t = 0; t < top_k; ++t) {
     uint32_t best = 0;
     int best_id = 0x7fffffff;
@@ -626,12 +626,11 @@ __device__ __forceinline__ void select_row_impl(const float* logits, int e, int 
     const float p = score == IQ_ROUTE_SOFTMAX ? expf(__fsub_rn(val, top_val))
                                               : 1.0f / (1.0f + expf(-val));
     sum = __fadd_rn(sum, p);
-    if (lane == t) { my_id = win; my_val = val; my_p = p; }
+    if (lane == t) { my_id = win; my_p = p; }
 #pragma unroll
     for (int j = 0; j < kMaxPerLane; ++j)
       if ((win & 31) == lane && (win >> 5) == j) key[j] = 0u;
   }
-  (void)my_val;
   // rank of my id among the selected ids
   int rank = 0;
   for (int t = 0; t < top_k; ++t) {

@@ -113,10 +113,6 @@ struct LayerParams {
   uint32_t wait_ms;        // budget of the grid-wide hand-offs
 };
 
-__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
 // One thread: spins until *word >= target.  False when the budget runs out or the CTA
 // has aborted.
 __device__ inline bool poll_word(const uint32_t* word, uint32_t target, uint32_t budget_ms,
@@ -295,13 +291,6 @@ struct TailSinks {
 // global memory), run by the sixteen consumer warps of EVERY CTA.  Same arithmetic and
 // rounding points as run_tail.  Each CTA stores to global memory only the 16-byte vectors
 // v with v % n_cta == cta; all of the normalised row goes to `sinks`.
-#ifdef IQB_TRACE
-__device__ long long g_clk[4][16];
-#define IQB_CLK(i) do { if (threadIdx.x == 0 && cta < 4) g_clk[cta][(a.kind == IQ_TAIL_ATTN ? 0 : 8) + i] = clock64(); } while (0)
-#else
-#define IQB_CLK(i) do { } while (0)
-#endif
-
 // What a tail needs besides the rows themselves, for one row.  All of it is requested in
 // one go together with the row, so the whole tail pays ONE global round trip (a dependent
 // global load costs about a microsecond here) instead of one per operand.
@@ -341,7 +330,6 @@ __device__ __forceinline__ void tail_everywhere(S* sm, const iq_tail_args& a, co
                                                 const TailSinks& sinks, int cta, int n_cta) {
   TailOperands op;
   const BlockBar bar{kBarHelpers, kConsumerThreads};
-  IQB_CLK(0);
   const int tid = threadIdx.x, nthr = kConsumerThreads;
   const int m = a.m, h = a.h, vec_per_row = h / 8;
   const float inv_h = 1.0f / static_cast<float>(h);
@@ -372,9 +360,7 @@ __device__ __forceinline__ void tail_everywhere(S* sm, const iq_tail_args& a, co
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss = fmaf(f[i][j], f[i][j], ss);
       }
-      IQB_CLK(1);
       inv1 = rsqrtf(block_sum(ss, slots0, bar) * inv_h + a.eps);
-      IQB_CLK(2);
     }
     float ss2 = 0.f;
 #pragma unroll
@@ -418,9 +404,7 @@ __device__ __forceinline__ void tail_everywhere(S* sm, const iq_tail_args& a, co
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss2 = fmaf(f[i][j], f[i][j], ss2);
     }
-    IQB_CLK(3);
     const float inv2 = rsqrtf(block_sum(ss2, slots1, bar) * inv_h + a.eps);
-    IQB_CLK(4);
     if (a.inv_out && tid == 0 && cta == 0) a.inv_out[r] = inv2;
 
 #pragma unroll
@@ -466,7 +450,6 @@ __device__ __forceinline__ void tail_everywhere(S* sm, const iq_tail_args& a, co
       }
     }
   }
-  IQB_CLK(5);
 }
 
 #ifdef IQB_TRACE
@@ -826,9 +809,6 @@ __global__ void __launch_bounds__(kThreads, 1) layer_kernel(const __grid_constan
     }
   }
   __syncthreads();
-#ifdef IQB_TRACE
-  if (tid < 8 && cta < 4) trace[16 + tid] = static_cast<unsigned long long>(g_clk[cta][tid]);
-#endif
   IQB_STAMP(13);
   stream_drain_on_abort<GO>(sm);
 }

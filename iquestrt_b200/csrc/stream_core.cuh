@@ -12,12 +12,15 @@
 // 1/512 of an MMA and no conversion instruction.  The K index inside an MMA is permuted
 // so that every lane's A and B fragments are plain 16-byte runs (see `consume_stage`).
 //
-// Work is the list of (tile, k-stage) items in tile-major order; CTA i owns the
-// contiguous item range [i*T/G, (i+1)*T/G) ("stream-K"), so every SM streams the same
-// number of bytes to within one stage whatever the shape.  A tile whose stages fall in
-// more than one CTA is finished by whichever contributor arrives last at the tile's
-// counter: it sums the contributors' fp32 partials from scratch in CTA order, so the
-// result does not depend on arrival order.  Nothing waits on another CTA.
+// Work is the list of (tile, k-stage) items in tile-major order.  Either every CTA takes
+// whole tiles (contiguous ranges, or round robin), or CTA i owns the contiguous item range
+// [i*T/G, (i+1)*T/G) ("stream-K"), so that every SM streams the same number of bytes to
+// within one stage whatever the shape; `tile_aligned_split` picks by a small cost model.
+// A tile whose stages fall in more than one CTA is finished by whichever contributor
+// arrives last at the tile's counter: it sums the contributors' fp32 partials from scratch
+// in CTA order, so the result does not depend on arrival order, and nothing waits on
+// another CTA.  (`epilogue_resident`, for cooperative launches only, lets the owner of the
+// tile's last stage poll the others' tagged partials instead.)
 //
 // The per-stage consumer path is kept to a few dozen instructions: everything that
 // depends only on the tile or the weight group is hoisted out of the stage loop, and the
