@@ -263,15 +263,19 @@ def run_ours(args):
         graphs[0][0].replay()                               # one untimed replay
         stream.synchronize()
         barrier()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # one event per graph boundary: the total is first-to-last, the per-chunk times give
+        # the spread
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(len(graphs) + 1)]
         with ClockSampler(local_rank) as clocks:
-            t0.record(stream)
-            for g, _ in graphs:
+            marks[0].record(stream)
+            for j, (g, _) in enumerate(graphs):
                 g.replay()
-            t1.record(stream)
+                marks[j + 1].record(stream)
             stream.synchronize()
         barrier()
-        ms = t0.elapsed_time(t1)
+        ms = marks[0].elapsed_time(marks[-1])
+        per_step_us = sorted(marks[j].elapsed_time(marks[j + 1]) * 1e3 / n
+                             for j, (_, n) in enumerate(graphs))
         layer.check()
 
         # ---- per-kernel pass: each of the four kernels on its own, `n_probe` launches of
@@ -406,6 +410,8 @@ def run_ours(args):
             "kernel_us": {k: v * 1e3 for k, v in med.items()},
             "layer_bytes": by["total"],
             "tokens_per_s_per_layer": rows / (us * 1e-6),
+            "spread_us": {"chunks": len(per_step_us), "min": per_step_us[0],
+                          "median": per_step_us[len(per_step_us) // 2], "max": per_step_us[-1]},
             "cpu_baseline": cpu,
         }
         print(json.dumps(line))

@@ -99,7 +99,9 @@ _LIB = None
 
 
 def lib_path() -> str:
-    return _build.LIB
+    """The library to load: `IQB200_LIB` (a prebuilt `libiqb200.so` elsewhere) or the in-tree
+    build."""
+    return os.environ.get("IQB200_LIB") or _build.LIB
 
 
 def load() -> C.CDLL:
