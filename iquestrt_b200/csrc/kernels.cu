@@ -1381,6 +1381,8 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   if (sm_count() == 0) return IQ_ERR_CUDA;
   const int k = a->k, n = a->n;
   if (k % 2048 == 0 && n % 16 == 0) return linear_launch<Geo<1, 16, 2>>(a, stream);
+  // k = 1024: 32-row stages (half as many tile hand-offs) measured 0.25 us faster
+  if (k % 1024 == 0 && n % 32 == 0) return linear_launch<Geo<2, 8, 2>>(a, stream);
   if (k % 1024 == 0 && n % 16 == 0) return linear_launch<Geo<1, 16, 1>>(a, stream);
   if (k % 768 == 0 && n % 64 == 0) return linear_launch<Geo<4, 4, 3>>(a, stream);
   if (k % 512 == 0 && n % 32 == 0) return linear_launch<Geo<2, 8, 1>>(a, stream);
