@@ -104,3 +104,51 @@ def test_abi_library_exports_every_declared_symbol():
     assert lib.iq_linear(None, None) == _lib.IQ_ERR_ARG
     a = _lib.RouterArgs()
     assert lib.iq_router(C.byref(a), None) == _lib.IQ_ERR_ARG
+
+
+def test_one_launch_context_checks_its_calls():
+    """`ops.one_launch` records the four calls of a layer and launches once on exit; on the
+    host it refuses nesting, a call recorded twice, and an exit with a part missing -- all
+    before anything reaches the library."""
+    from iquestrt_b200 import _lib, ops
+    with pytest.raises(RuntimeError, match="do not nest"):
+        with ops.one_launch():
+            with ops.one_launch():
+                pass
+    assert ops.one_launch._active is None
+    with pytest.raises(RuntimeError, match="called twice"):
+        with ops.one_launch() as ctx:
+            ctx.record("router", _lib.RouterArgs())
+            ctx.record("router", _lib.RouterArgs())
+    assert ops.one_launch._active is None
+    with pytest.raises(RuntimeError, match="no call recorded"):
+        with ops.one_launch() as ctx:
+            ctx.record("oproj", _lib.LinearArgs())
+    assert ops.one_launch._active is None
+    # an exception inside the context propagates and leaves no context open
+    with pytest.raises(ValueError):
+        with ops.one_launch():
+            raise ValueError("inside")
+    assert ops.one_launch._active is None
+
+
+def test_abi_rejects_null_arguments_without_a_gpu():
+    """Argument checks come before any CUDA call: every entry point returns IQ_ERR_ARG for a
+    null argument block, and the scratch size covers the one-launch layer's own area."""
+    import ctypes as C
+    from iquestrt_b200 import _lib
+    _lib.load()                                   # raises if the library is not built
+    lib = C.CDLL(_lib.lib_path())                 # a handle of its own: argtypes set here stay here
+    lib.iq_scratch_bytes.restype = C.c_size_t
+    lib.iq_status_read.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    null = C.c_void_p(None)
+    for name in ("iq_linear", "iq_linear_static", "iq_router", "iq_moe_gate", "iq_moe_down"):
+        fn = getattr(lib, name)
+        fn.argtypes = [C.c_void_p, C.c_void_p]
+        assert fn(null, null) == _lib.IQ_ERR_ARG, name
+    lib.iq_tail.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+    assert lib.iq_tail(null, null, 0) == _lib.IQ_ERR_ARG
+    lib.iq_decode_layer.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+    assert lib.iq_decode_layer(null, null, 0) == _lib.IQ_ERR_ARG
+    assert lib.iq_status_read(null, null, 0, null) == _lib.IQ_ERR_ARG
+    assert lib.iq_scratch_bytes() >= 7 * 1024 * 1024
