@@ -3,6 +3,8 @@
 
     python bench.py --gpus N --steps K --warmup W            # this build's CUDA path
     python bench.py --impl reference --gpus N ...            # the reference's CPU algebra
+    python bench.py --impl reference-gpu                     # the reference's own SM100 kernels
+                                                             # beside this build's, one GPU
 
 N is the tensor-parallel degree (one process per GPU; under torchrun for N > 1).  A step
 is one pass of the hot path of ONE decode layer at batch 1 over one synthetic input:
@@ -12,10 +14,13 @@ o_proj K 8192, 256 experts top-8 + 1 shared, expert intermediate 2048, all shard
 N).  Total work is fixed as N grows ("strong" scaling).  Weights rotate over several
 distinct layers so every step streams from HBM, not L2.
 
-Prints ONE JSON line: `value` = microseconds per layer with inputs resident in HBM (K
-steps replayed from CUDA graphs, device-timed, max over ranks); `e2e` = the same through
-the public holder API from pinned HOST buffers (input copy in, result copy out, every
-step); `roofline` = the dominant kernel (expert Gate) against the measured HBM peak;
+Prints ONE JSON line: `value` = microseconds per layer with inputs resident in HBM (a
+pass of exactly K steps replayed from CUDA graphs, device-timed; several passes back to
+back, the first dropped, the median taken, max over ranks); `e2e` = the same through the
+public holder API from pinned HOST buffers (input copy in, result copy out, every step);
+`roofline` = the dominant kernel (expert Gate) against the measured HBM peak,
+`roofline_fused` = the two GEMV + all-reduce launches; `parity` = one untimed step at
+this N checked on rank 0 against the reference's algebra over all ranks' shards;
 `cpu_baseline` = the reference's torch algebra on this box's host cores."""
 
 from __future__ import annotations
@@ -43,15 +48,18 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1024)
     ap.add_argument("--warmup", type=int, default=16)
-    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference", "reference-gpu"))
     ap.add_argument("--rows", type=int, default=1, help="tokens per step (1, or 4 for MTP verify)")
     ap.add_argument("--layers", type=int, default=0, help="distinct weight sets to rotate over")
     ap.add_argument("--experts", type=int, default=256,
                     help="routed experts in the bank (smaller banks keep profiler captures "
                          "small; a step still streams top-k routed + the shared expert)")
-    ap.add_argument("--launches", type=int, default=4, choices=(1, 4),
-                    help="kernel launches per layer: the four fused kernels, or the one-launch "
-                         "cooperative layer (same results bit for bit)")
+    ap.add_argument("--protocol", default="push", choices=("push", "pull"),
+                    help="all-reduce of the two tails: tiles pushed into every rank's landing "
+                         "zone from the GEMV epilogue, or signal / wait / switch read")
+    ap.add_argument("--passes", type=int, default=0,
+                    help="timed passes of K steps (default: 11, more when K steps are short)")
+    ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-multicast", action="store_true",
                     help="all-reduce over plain peer loads instead of NVLS multimem")
@@ -138,15 +146,23 @@ def layer_bytes(shape, tp, rows, distinct_routed):
 
 # ------------------------------------------------------------------------------ CPU arm
 
-def cpu_layer_time(rows, budget_s=20.0, max_steps=8, threads=None):
+def host_threads():
+    """All the host cores for the CPU arm, whatever the launcher put into OMP_NUM_THREADS
+    (torchrun sets it to 1), so that the figure is comparable across N."""
+    import torch
+    n = os.cpu_count() or 1
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
+def cpu_layer_time(rows, budget_s=20.0, max_steps=8):
     """Times the reference's torch algebra for the same layer on the host cores.  The
     expert bank is cut to 16 experts (routing picks 8 of them, plus the shared expert, so
     the work per layer is unchanged) to keep generation short."""
     import torch
     from iquestrt_b200 import synth
     from oracle.cpu_layer import layer_cpu
-    if threads:
-        torch.set_num_threads(threads)
+    cores = host_threads()
     shape = synth.LayerShape(n_experts=16)
     lw = synth.make_layer(shape, tp=1, rank=0, device="cpu", seed=0)
     times = []
@@ -161,17 +177,17 @@ def cpu_layer_time(rows, budget_s=20.0, max_steps=8, threads=None):
             times.append(dt)
         if time.time() - t_all > budget_s and times:
             break
-    return times, torch.get_num_threads()
+    return times, cores
 
 
 def run_reference(args):
     """`--impl reference`: the reference's CPU algebra (oracle port: the reference is
-    Python and is not present on the GPU box), rank 0 only."""
+    Python and is not present on the GPU box), rank 0 only, all host cores."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     steps = max(1, args.steps)
-    # a step is one full layer (~1-2 s on a few cores); bound the run to a few minutes
+    # a step is one full layer (~0.3 s on 16 cores); bound the run to a few minutes
     max_steps = min(steps + args.warmup, 60)
     times, cores = cpu_layer_time(args.rows, budget_s=150.0, max_steps=max_steps)
     timed = times[min(args.warmup, max(0, len(times) - 1)):] or times
@@ -192,13 +208,88 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------------------ parity
+
+def parity_check(args, tp, rank, dev, group):
+    """One untimed layer step per row count at this N, on the benchmark's shapes with the
+    expert bank cut to 16 experts, checked on rank 0 against the reference's algebra over
+    ALL ranks' shards (`oracle.cpu_layer.layer_cpu`); outputs must also be bit-identical on
+    every rank.  Returns the `parity` object of the JSON line (rank 0) or None."""
+    import torch
+    import torch.distributed as dist
+    from iquestrt_b200 import synth
+    from iquestrt_b200.layer import DecodeLayer
+    tol = 2e-2
+    shape = synth.LayerShape(n_experts=16)
+    report = {"tol": tol, "oracle": "reference torch algebra (bf16 activations) over all "
+                                    f"{tp} rank shards, 16-expert bank", "cases": []}
+    ok = True
+    for rows in (1, 4):
+        layer = DecodeLayer(shape, q_len=rows, tp=tp, group=group, device=dev,
+                            formats="benchmark", use_multicast=not args.no_multicast,
+                            protocol=args.protocol)
+        lws = [synth.make_layer(shape, tp=tp, rank=r, device=dev, seed=0) for r in range(tp)]
+        ins = [synth.make_step_inputs(shape, rows, tp=tp, rank=r, device=dev, seed=0)
+               for r in range(tp)]
+        ao, res = ins[rank]
+        for _ in range(2):                                  # both alternating slots
+            out, norm = layer.step(ao, res, lws[rank])
+        layer.check()
+        out, norm = out.clone(), norm.clone()
+        same = True
+        if tp > 1:
+            both = torch.cat([out.view(torch.int16), norm.view(torch.int16)])
+            gathered = [torch.empty_like(both) for _ in range(tp)]
+            dist.all_gather(gathered, both)
+            same = all(torch.equal(g, both) for g in gathered)
+        if rank == 0:
+            from oracle import ref_path as R
+            from oracle.cpu_layer import layer_cpu
+            host_threads()
+            cl = [{k: v.cpu() for k, v in lw.items()} for lw in lws]
+            sel = layer.router.sel.cpu().view(rows, shape.top_k)
+            ref_out, ref_norm, ref_sel, _ = layer_cpu(
+                cl, [i[0].cpu() for i in ins], res.cpu(), top_k=shape.top_k,
+                n_shared=shape.n_shared, eps=shape.eps, score="sigmoid")
+            logits = layer.router.logits[:rows].cpu()
+            top = torch.sort(logits, dim=-1, descending=True).values
+            margin = float((top[:, shape.top_k - 1] - top[:, shape.top_k]).min())
+            routes_equal = bool(torch.equal(sel, ref_sel))
+            e_out = R.rel_fro(out.cpu(), ref_out)
+            e_norm = R.rel_fro(norm.cpu(), ref_norm)
+            good = same and e_out <= tol and e_norm <= tol and (routes_equal or margin <= 1e-3)
+            ok = ok and good
+            report["cases"].append({"rows": rows, "rel_fro_out": e_out, "rel_fro_norm": e_norm,
+                                    "routes_equal": routes_equal, "min_topk_margin": margin,
+                                    "ranks_bit_identical": same, "ok": good})
+        del layer, lws
+    if rank != 0:
+        return None
+    report["rel_fro_out"] = max(c["rel_fro_out"] for c in report["cases"])
+    report["rel_fro_norm"] = max(c["rel_fro_norm"] for c in report["cases"])
+    report["routes_equal"] = all(c["routes_equal"] for c in report["cases"])
+    report["ok"] = ok
+    return report
+
+
 # ------------------------------------------------------------------------------ GPU arm
+
+def dram_traffic(kernel, tp, rows):
+    """DRAM bytes per launch of `kernel` from the committed profiler summary, or None."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            table = json.load(f)
+        return table[kernel][f"tp{tp}_m{rows}"]["dram_bytes_per_launch"]
+    except (OSError, KeyError, ValueError):
+        return None
+
 
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from iquestrt_b200 import _build, ops, synth
-    from iquestrt_b200.layer import DecodeLayer
+    from iquestrt_b200 import _build, synth
+    from iquestrt_b200.layer import DecodeLayer, HostStep
 
     tp = args.gpus
     rank = int(os.environ.get("RANK", "0"))
@@ -213,29 +304,41 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD.group_name
     _build.build()                                          # no-op when the .so is current
+
+    parity = None
+    if not args.no_parity:
+        parity = parity_check(args, tp, rank, dev, group)
+
     shape = synth.BASELINE if args.experts == 256 else synth.LayerShape(n_experts=args.experts)
     rows = args.rows
     bank_bytes = 37.75e6 * (args.experts + 1) / tp
     n_layers = args.layers or max(2, min(4, int(24e9 // bank_bytes)))
     layer = DecodeLayer(shape, q_len=rows, tp=tp, group=group, device=dev,
-                        formats="benchmark", use_multicast=not args.no_multicast)
+                        formats="benchmark", use_multicast=not args.no_multicast,
+                        protocol=args.protocol)
     weights = [synth.make_layer(shape, tp=tp, rank=rank, device=dev, seed=0, layer=i)
                for i in range(n_layers)]
     n_inputs = 8
     inputs = [synth.make_step_inputs(shape, rows, tp=tp, rank=rank, device=dev, seed=0, step=i)
               for i in range(n_inputs)]
     K, W = max(1, args.steps), max(3, args.warmup)
-
-    one_launch = args.launches == 1
+    launches_per_step = 4
 
     def call(i, **kw):
         ao, res = inputs[i % n_inputs]
-        return layer.step(ao, res, weights[i % n_layers], one_launch=one_launch, **kw)
+        return layer.step(ao, res, weights[i % n_layers], **kw)
 
     def barrier():
         if tp > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if tp == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     stream = torch.cuda.Stream(device=dev)
     chunk = 128
@@ -244,9 +347,12 @@ def run_ours(args):
             call(i)
         stream.synchronize()
         layer.check()
-        # Exactly K steps: a graph of `chunk` steps replayed K // chunk times plus a graph of
-        # the remainder.  `chunk` is even, so the alternating output slots keep alternating
-        # across replays.
+
+        # A pass is exactly K steps: a graph of `chunk` steps replayed K // chunk times plus
+        # a graph of the remainder.  The two output slots of each all-reduce alternate from
+        # step to step and a captured graph fixes which slot each of its steps uses, so the
+        # unit that is replayed must hold an even number of steps: for an odd K it is two
+        # passes (2K steps), timed as such.
         def capture(n):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
@@ -254,72 +360,53 @@ def run_ours(args):
                     call(i)
             return g
 
+        unit = K * (2 if K % 2 else 1)                      # steps between two events
         graphs = []
-        if K >= chunk:
+        if unit >= chunk:
             g_chunk = capture(chunk)
-            graphs += [(g_chunk, chunk)] * (K // chunk)
-        if K % chunk:
-            graphs.append((capture(K % chunk), K % chunk))
-        graphs[0][0].replay()                               # one untimed replay
+            graphs += [g_chunk] * (unit // chunk)
+        if unit % chunk:
+            graphs.append(capture(unit % chunk))
+
+        def run_pass():
+            for g in graphs:
+                g.replay()
+
+        # Passes run back to back with one event between them and no host synchronisation:
+        # the ranks start their first pass at different moments (host launch skew after the
+        # barrier), the all-reduces inside it bring them into lock-step, and that pass is
+        # dropped.  The number of passes grows until the timed region is at least ~50 ms.
+        run_pass()
         stream.synchronize()
+        probe = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        probe[0].record(stream)
+        run_pass()
+        probe[1].record(stream)
+        stream.synchronize()
+        est_ms = max(probe[0].elapsed_time(probe[1]), 1e-3)
+        passes = args.passes or int(min(2001, max(11, 50.0 / est_ms + 2)))
+        passes = int(max_over_ranks(float(passes)))         # the same count on every rank
         barrier()
-        # one event per graph boundary: the total is first-to-last, the per-chunk times give
-        # the spread
-        marks = [torch.cuda.Event(enable_timing=True) for _ in range(len(graphs) + 1)]
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(passes + 1)]
         with ClockSampler(local_rank) as clocks:
             marks[0].record(stream)
-            for j, (g, _) in enumerate(graphs):
-                g.replay()
+            for j in range(passes):
+                run_pass()
                 marks[j + 1].record(stream)
             stream.synchronize()
         barrier()
-        ms = marks[0].elapsed_time(marks[-1])
-        per_step_us = sorted(marks[j].elapsed_time(marks[j + 1]) * 1e3 / n
-                             for j, (_, n) in enumerate(graphs))
+        pass_ms = [marks[j].elapsed_time(marks[j + 1]) * K / unit
+                   for j in range(1, passes)]               # first dropped; per K steps
         layer.check()
 
-        # ---- per-kernel pass: each of the four kernels on its own, `n_probe` launches of
-        # it captured in one graph (same arguments as in the layer, weights rotating over the
+        # ---- per-kernel pass: each of the four launches on its own, `n_probe` of them
+        # captured in one graph (same arguments as in the layer, weights rotating over the
         # layers so that every launch streams from HBM, PDL on) and replayed; the kernel's
         # time is the replay's device time / n_probe.  Events inside the layer's own graph
         # would break the launch overlap being measured.
-        q = rows
-        moe = layer.moe
         n_probe = 32
-        sel, wt = layer.router.sel, layer.router.wt
-
-        def k_oproj(i):
-            ao, res = inputs[i % n_inputs]
-            lw = weights[i % n_layers]
-            out = layer.oproj.outputs[i % 2]
-            spec = layer.ar_tail.spec(out[:q], res, lw["attn_out_norm"], lw["feed_forward_norm"],
-                                      1.0, 1.0, norm_out=moe.x_pad, norm_fp8=moe.x_pad_fp8,
-                                      norm_fp8_scale=moe.x_pad_scale, inv_out=layer.ar_tail.inv)
-            ops.linear(ao, lw["o_proj"], lw["o_scale"], scratch=layer.scratch, out=out[:q],
-                       tail=spec, pdl=True)
-
-        def k_router(i):
-            layer.router(moe.x_pad, weights[i % n_layers]["router"], pdl=True)
-
-        def k_gate(i):
-            lw = weights[i % n_layers]
-            ops.moe_gate(moe.x_pad_fp8, sel, lw["fc"], lw["fc_scale"], moe.act, m=q,
-                         top_k=shape.top_k, scratch=layer.scratch, x_scale=moe.x_pad_scale,
-                         shared_fc=lw["shared_fc"], shared_fc_scale=lw["shared_fc_scale"],
-                         pdl=True)
-
-        def k_down(i):
-            lw = weights[i % n_layers]
-            out = moe.outputs[i % 2]
-            mspec = layer.mlp_tail.spec(out[:q], layer.tail.h[:q], 1.0, lw["next_attention_norm"])
-            ops.moe_down(moe.act, sel, wt, lw["proj"], lw["proj_scale"], out, m=q,
-                         top_k=shape.top_k, scratch=layer.scratch,
-                         shared_proj=lw["shared_proj"],
-                         shared_proj_scale=lw["shared_proj_scale"], tail=mspec, pdl=True)
-
         kern_ms = {}
-        for name, fn in (("oproj_tail", k_oproj), ("router", k_router), ("gate", k_gate),
-                         ("down_tail", k_down)):
+        for name, fn in layer.kernel_probes(inputs, weights).items():
             for i in range(2):
                 fn(i)
             stream.synchronize()
@@ -330,15 +417,13 @@ def run_ours(args):
             g.replay()
             stream.synchronize()
             barrier()
-            samples = []
-            for _ in range(5):
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(stream)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
+            ev[0].record(stream)
+            for j in range(6):
                 g.replay()
-                b.record(stream)
-                stream.synchronize()
-                samples.append(a.elapsed_time(b) / n_probe)
-            kern_ms[name] = samples
+                ev[j + 1].record(stream)
+            stream.synchronize()
+            kern_ms[name] = [ev[j].elapsed_time(ev[j + 1]) / n_probe for j in range(1, 6)]
             layer.check()
 
         # distinct routed experts per step (1 row -> top_k)
@@ -347,9 +432,8 @@ def run_ours(args):
         # ---- end to end from HOST buffers: `HostStep` (one graph launch per step holding
         # the H2D copies of the step's inputs, the layer, and the D2H copy of its output),
         # one synchronise per step, weights rotating over the layers as above.
-        from iquestrt_b200.layer import HostStep
         h_in = [(ao.cpu(), res.cpu()) for ao, res in inputs]
-        host_steps = [HostStep(layer, weights[j], one_launch=one_launch) for j in range(n_layers)]
+        host_steps = [HostStep(layer, weights[j]) for j in range(n_layers)]
         n_e2e = min(K, 256)
         for i in range(4):
             host_steps[i % n_layers](*h_in[i % n_inputs])
@@ -361,22 +445,17 @@ def run_ours(args):
         h2d_bytes, d2h_bytes = host_steps[0].h2d_bytes, host_steps[0].d2h_bytes
         layer.check()
 
-    def max_over_ranks(v):
-        if tp == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    ms = max_over_ranks(ms)
+    med_ms = max_over_ranks(statistics.median(pass_ms))
+    min_ms = max_over_ranks(min(pass_ms))
+    max_ms = max_over_ranks(max(pass_ms))
     e2e_ms = max_over_ranks(e2e_ms)
     med = {k: max_over_ranks(statistics.median(v)) for k, v in kern_ms.items()}
+    failed = False
     if rank == 0:
-        us = ms * 1e3 / K
+        us = med_ms * 1e3 / K
         peak, peak_kind = measured_peak()
         by = layer_bytes(shape, tp, rows, distinct)
-        gate_s = med["gate"] * 1e-3
-        achieved = by["gate"] / gate_s / 1e9
+        frac = {k: by[k] / (med[k] * 1e-3) / 1e9 / peak for k in med}
         cpu = None
         if not args.no_cpu_baseline and tp == 1:
             times, cores = cpu_layer_time(rows, budget_s=20.0, max_steps=8)
@@ -386,44 +465,161 @@ def run_ours(args):
                              "(expert bank cut to 16 experts, same work per layer), median"}
         line = {
             "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": tp, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": False, "scaling": "strong",
+            "ms_per_step": med_ms / K, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "e4m3 x e4m3 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "rows": rows, "tp": tp, "launches_per_step": args.launches,
-                       "experts_in_bank": args.experts,
+            "config": {"workload": WORKLOAD, "rows": rows, "tp": tp,
+                       "launches_per_step": launches_per_step, "experts_in_bank": args.experts,
+                       "timing": f"{passes} passes of {K} steps back to back, first dropped, "
+                                 "median pass",
                        "l2": f"weights rotate over {n_layers} distinct layers "
                              f"({by['total'] * n_layers / 1e6:.0f} MB touched per cycle, L2 is 126 MB)",
                        "all_reduce": "none (TP=1)" if tp == 1 else
-                                     ("peer loads" if args.no_multicast else "NVLS multimem")},
+                                     f"{args.protocol}, " +
+                                     ("peer stores/loads" if args.no_multicast else "NVLS multimem")},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_ms * 1e3 / n_e2e, "unit": UNIT, "steps": n_e2e,
                     "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": int(d2h_bytes)},
-            "gpu_launches": args.launches * K,
+            "gpu_launches": launches_per_step * unit * (passes - 1),
+            "passes_timed": passes - 1,
             "roofline": {"bound": "hbm", "kernel": "gate_kernel (expert Gate/Up + SiLU)",
-                         "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_kind": peak_kind,
+                         "achieved": frac["gate"] * peak, "peak": peak, "unit": "GB/s",
+                         "frac": frac["gate"], "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": by["gate"],
                          "launch_us": med["gate"] * 1e3,
-                         # dram__bytes_read + dram__bytes_write of one launch, from the ncu
-                         # capture summarised in profiles/gate_kernel_tp1_m1.md
-                         "traffic": 230.82e6 if (tp == 1 and rows == 1) else None,
+                         "traffic": dram_traffic("gate_kernel", tp, rows),
                          "layer_frac": by["total"] / (us * 1e-6) / 1e9 / peak},
+            "roofline_fused": {"oproj_tail": frac["oproj_tail"], "down_tail": frac["down_tail"],
+                               "router": frac["router"], "unit": "fraction of the HBM peak",
+                               "bytes": {k: by[k] for k in ("oproj_tail", "down_tail", "router")}},
             "kernel_us": {k: v * 1e3 for k, v in med.items()},
             "layer_bytes": by["total"],
             "tokens_per_s_per_layer": rows / (us * 1e-6),
-            "spread_us": {"chunks": len(per_step_us), "min": per_step_us[0],
-                          "median": per_step_us[len(per_step_us) // 2], "max": per_step_us[-1]},
+            "spread_us": {"passes": passes - 1, "min": min_ms * 1e3 / K,
+                          "median": med_ms * 1e3 / K, "max": max_ms * 1e3 / K},
+            "parity": parity,
             "cpu_baseline": cpu,
         }
         print(json.dumps(line))
+        failed = parity is not None and not parity["ok"]
     if tp > 1:
+        flag = torch.tensor([int(failed)], device=dev)
+        dist.broadcast(flag, src=0)
+        failed = bool(flag.item())
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("parity check failed (see the `parity` object of the JSON line)")
+
+
+# ------------------------------------------------------------------------------ reference GPU arm
+
+def run_reference_gpu(args):
+    """`--impl reference-gpu`: the reference's own expert Gate, expert Down and router
+    kernels (its unmodified `load_inline` sources, built into `oracle/_ref/` by
+    `oracle/build_ref.py`) timed beside this build's kernels on ONE GPU, at the reference's
+    shapes (hidden 3072, 256 experts top-8, expert width 192 per rank), same seeded weights
+    and routes, 32 launches per CUDA graph, weights rotating over two layers."""
+    import torch
+    from iquestrt_b200 import _build, ops, synth
+    from oracle import build_ref
+    from oracle import ref_path as R
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    if not build_ref.available():
+        print(json.dumps({"impl": "reference-gpu", "unavailable":
+                          "oracle/_ref modules not built (python -m oracle.build_ref needs the "
+                          "reference checkout)"}))
+        return
+    torch.cuda.set_device(0)
+    _build.build()
+    ext = {n: build_ref.load(n) for n in build_ref.UNITS}
+    H, I_LOC, E, TOPK, Q, BM = 3072, 192, 256, 8, 8, 16
+    shape = synth.REFERENCE_Q1
+    banks = [synth.make_layer(shape, tp=8, rank=0, device="cuda", seed=0, layer=i)
+             for i in range(2)]
+    scratch = ops.Scratch("cuda")
+    stream = torch.cuda.Stream()
+    n_probe = 32
+    out = {"impl": "reference-gpu", "unit": "us per launch", "shapes":
+           {"hidden": H, "i_loc": I_LOC, "experts": E, "top_k": TOPK},
+           "method": f"{n_probe} launches per CUDA graph (PDL on), median of 5 replays, "
+                     "weights rotate over 2 layers (0.9 GB)", "rows": {}}
+    g = torch.Generator().manual_seed(1)
+    x = torch.zeros(BM, H)
+    x[:Q] = torch.randn(Q, H, generator=g)
+    xb = x.bfloat16().cuda()
+    x8 = R.to_e4m3_sat(x.bfloat16()).cuda()
+    sel = torch.stack([torch.sort(torch.randperm(E, generator=g)[:TOPK]).values
+                       for _ in range(Q)]).to(torch.int32).flatten().cuda()
+    wt = torch.softmax(torch.randn(Q, TOPK, generator=g), -1).flatten().contiguous().cuda()
+    act_ref = torch.zeros(Q * TOPK, BM, I_LOC, dtype=torch.float8_e4m3fn, device="cuda")
+    out_ref = torch.zeros(BM, H, dtype=torch.bfloat16, device="cuda")
+    parts = torch.full((12, BM, E), float("nan"), dtype=torch.float32, device="cuda")
+    sel_r = torch.zeros(Q * TOPK, dtype=torch.int32, device="cuda")
+    wt_r = torch.zeros(Q * TOPK, dtype=torch.float32, device="cuda")
+    out_own = torch.zeros(BM, H, dtype=torch.bfloat16, device="cuda")
+    routers = [(torch.randn(E, H, generator=g) * 0.02).bfloat16().cuda() for _ in range(2)]
+
+    def timed(fn):
+        with torch.cuda.stream(stream):
+            for i in range(2):
+                fn(i)
+            stream.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                for i in range(n_probe):
+                    fn(i)
+            gr.replay()
+            stream.synchronize()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+            ev[0].record(stream)
+            for j in range(5):
+                gr.replay()
+                ev[j + 1].record(stream)
+            stream.synchronize()
+        return statistics.median(ev[j].elapsed_time(ev[j + 1]) for j in range(5)) / n_probe * 1e3
+
+    dev_index = torch.cuda.current_device()
+    for rows in (1, 4, 6, 8):
+        act_own = torch.zeros(rows * TOPK, I_LOC, dtype=torch.float8_e4m3fn, device="cuda")
+        r = {}
+        r["gate_reference"] = timed(lambda i: ext["iquestrt_moe_gate"].moe_gate_launch(
+            x8.data_ptr(), banks[i % 2]["fc"].data_ptr(), banks[i % 2]["fc_scale"].data_ptr(),
+            sel.data_ptr(), act_ref.data_ptr(), rows)) if rows < 7 else None
+        r["gate_this_build"] = timed(lambda i: ops.moe_gate(
+            x8[:rows], sel[:rows * TOPK], banks[i % 2]["fc"], banks[i % 2]["fc_scale"], act_own,
+            m=rows, top_k=TOPK, scratch=scratch, pdl=True))
+        r["down_reference"] = timed(lambda i: ext["iquestrt_moe_down"].moe_down_launch(
+            act_ref.data_ptr(), banks[i % 2]["proj"].data_ptr(),
+            banks[i % 2]["proj_scale"].data_ptr(), sel.data_ptr(), wt.data_ptr(),
+            out_ref.data_ptr(), rows))
+        r["down_this_build"] = timed(lambda i: ops.moe_down(
+            act_own, sel[:rows * TOPK], wt[:rows * TOPK], banks[i % 2]["proj"],
+            banks[i % 2]["proj_scale"], out_own, m=rows, top_k=TOPK, scratch=scratch, pdl=True))
+        if rows == 8:
+            r["router_reference"] = timed(lambda i: ext["iquestrt_router_q8_sm100"].router_q8_launch(
+                xb.data_ptr(), routers[i % 2].data_ptr(), parts.data_ptr(), sel_r.data_ptr(),
+                wt_r.data_ptr(), dev_index))
+        r["router_this_build"] = timed(lambda i: ops.router(
+            xb[:rows], routers[i % 2], top_k=TOPK, scratch=scratch, score=ops.ROUTE_SOFTMAX,
+            pdl=True))
+        code = scratch.status()
+        if code:
+            raise SystemExit(f"device status {code}")
+        out["rows"][str(rows)] = r
+    out["note"] = ("the reference's Gate for 7-8 rows is a second build of its source (not "
+                   "built here); its router always computes 8 rows; its o_proj, all-reduce "
+                   "tails and dense MLP are TileLang / 8-rank NVLS kernels: unavailable on "
+                   "this box")
+    print(json.dumps(out))
 
 
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     else:
         run_ours(args)
 

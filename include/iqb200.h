@@ -51,11 +51,14 @@ enum { IQ_ACT_E4M3 = 0, IQ_ACT_BF16 = 1 };
  * returned); 2 = as 1, and the caller also guarantees that iq_moe_gate's x_fp8/x_scale,
  * resp. iq_moe_down's sel/wt, were written at least TWO launches earlier on the stream,
  * so they too are read before the wait (as in the layer: attention tail -> router ->
- * Gate -> Down, every launch made with pdl >= 1). */
+ * Gate -> Down, every launch made with pdl >= 1).  At level 2 iq_moe_gate with shared
+ * experts also WRITES the shared experts' rows of `act` before its wait, so the launch
+ * immediately before it must not read `act` (in the layer that launch is the router). */
 
 /* Bytes of scratch every streaming entry point needs.  The caller zero-fills it once;
- * each launch leaves it zeroed again (except the status word).  Launches that share a
- * scratch buffer must be ordered on one stream. */
+ * each launch leaves its counters zeroed again (the status word and the launch counter
+ * that tags hand-off words persist).  Launches that share a scratch buffer must be
+ * ordered on one stream. */
 size_t iq_scratch_bytes(void);
 
 /* Copies the device status word at the start of `scratch` to *code after synchronising
@@ -76,11 +79,34 @@ int iq_sm_count(void);
  *   MLP:  m = AR(partial);  h = bf16(residual + bf16(m*scale));
  *         norm_out = bf16(w_norm*(h*inv))
  *
- * world == 1 reads `partial` locally.  world > 1: every rank adds one to every rank's
- * `arrive` counter (one multimem.red through `arrive_mc`, else one store per peer through
- * `peer_arrive`), waits (bounded by timeout_ms) until its own counter shows all ranks of
- * this call, then reads the switch-reduced rows with multimem.ld_reduce through
- * `partial_mc` (else sums the peers' rows through `peer_partials` in rank order). */
+ * Two all-reduce protocols exist for world > 1.
+ *
+ * Pull (`push` == NULL): every rank adds one to every rank's `arrive` counter (one
+ * multimem.red through `arrive_mc`, else one store per peer through `peer_arrive`), waits
+ * (bounded by timeout_ms) until its own counter shows all ranks of this call, then reads
+ * the switch-reduced rows with multimem.ld_reduce through `partial_mc` (else sums the
+ * peers' rows through `peer_partials` in rank order).
+ *
+ * Push (`push` != NULL): the producing GEMV stores every finished tile of its rows, as
+ * 32-bit words that carry the bf16 value and a 16-bit tag of the call, straight from its
+ * epilogue into a per-source landing zone on EVERY rank (one multimem.st per 16 bytes
+ * through `recv_mc`, else one store per peer through `peer_recv`).  The tail polls its
+ * own rank's landing zone (local memory only) until every word of a row carries the
+ * call's tag (bounded by timeout_ms), adds the sources in rank order in fp32 and rounds
+ * once to bf16.  There is no flag, counter or fence on the producer's side, and no load
+ * crosses NVLink.  world == 1 uses the same hand-off through a zone inside the scratch.
+ * Rows are independent: each row of a call is finished by its own CTA. */
+typedef struct iq_push_args {
+  int world, rank;
+  int rows;                      /* rows the zone is laid out for (>= m) */
+  int h;
+  uint32_t* recv;                /* this rank's zone: u32 [world][rows][h] */
+  uint32_t* recv_mc;             /* multicast alias of `recv`, or NULL */
+  uint32_t* const* peer_recv;    /* device array [world] of the ranks' zones, or NULL */
+  uint32_t* epoch;               /* local device word: completed calls on this zone */
+  uint32_t* ticket;              /* local device word, zero between calls */
+} iq_push_args;
+
 typedef struct iq_tail_args {
   int kind;
   int world, rank;
@@ -104,15 +130,25 @@ typedef struct iq_tail_args {
   float* inv_out;                    /* optional fp32 [m]: rsqrt of the last norm */
   int* status;                       /* device status word (normally the scratch's) */
   unsigned timeout_ms;               /* peer wait budget; 0 = 2000 */
+  const iq_push_args* push;          /* push protocol (see above), or NULL */
 } iq_tail_args;
 
+/* The tail on its own, one CTA per row (the pull protocol with world > 1: one CTA).  With
+ * `push`, the rows must have been produced by iq_linear / iq_moe_down calls given the
+ * same `push`. */
 int iq_tail(const iq_tail_args* a, void* stream, int pdl);
 
 /* out[m,n] bf16 = x[m,k] . dequant(w[n,k] e4m3, w_scale)^T, optionally followed in the
  * same kernel by the tail.  Replaces reference.linear
  * (iquestrt/model/reference.py:23-27) and OProjGemv.__call__ / build_gemv_block
  * (iquestrt/kernels/oproj.py:83-171).  w_scale is [n/rg, k/kg] fp32 (rg, kg in
- * {64,128}); when `tail` is given, `out` must be tail->partial. */
+ * {64,128}); when `tail` is given, `out` must be tail->partial.
+ *
+ * With a tail that uses the push protocol (or world == 1) the last m CTAs of the launch
+ * take no part in the GEMV: CTA i of them finishes row i (polls the landing zone, adds
+ * the ranks, residual, RMSNorms) while the others are still streaming.  With the pull
+ * protocol the last CTA to finish its tiles runs the tail for all rows.  `push` without
+ * `tail` only sends the rows (for a later iq_tail with the same `push`). */
 typedef struct iq_linear_args {
   const void* x;
   const float* x_scale;
@@ -126,6 +162,7 @@ typedef struct iq_linear_args {
   size_t scratch_bytes;
   const iq_tail_args* tail;
   int pdl;
+  const iq_push_args* push;
 } iq_linear_args;
 
 int iq_linear(const iq_linear_args* a, void* stream);
@@ -142,8 +179,15 @@ int iq_linear(const iq_linear_args* a, void* stream);
  * come before any stream capture.  All calls on a device share the one array: it keeps
  * the previous call's contents (the part that must start at zero is cleared on the
  * stream before each launch), and calls that overlap on the GPU race -- order them on
- * one stream.  Device-side errors are not reported by this variant. */
+ * one stream.  A device-side error (a pipeline wait that ran out) is recorded in the
+ * array's status word until the next iq_linear_static call on the device clears it: read
+ * it with iq_linear_static_status before making that next call. */
 int iq_linear_static(const iq_linear_args* a, void* stream);
+
+/* Copies the status word of iq_linear_static's built-in work area on the current device
+ * to *code after synchronising `stream` (0 when no call has been made yet).  Allocates
+ * nothing.  It has no counterpart in the reference either. */
+int iq_linear_static_status(int* code, void* stream);
 
 /* Router: logits = x[m,h] bf16 . w[e,h]^T bf16 (fp32 accumulate), top_k with ties to the
  * lower expert id, weights = softmax over the selected logits (reference) or their
@@ -170,7 +214,9 @@ int iq_router(const iq_router_args* a, void* stream);
  * silu(gate) * up.  Replaces moe_gate (iquestrt/kernels/sm100_moe_fp8.py:110-188) and
  * the Gate half of DenseMlp (iquestrt/kernels/oproj.py:174-197).  fc is
  * [E, 2*i_loc, h] e4m3 ([gate; up]) with scales [E, 2*i_loc/64, h/128]; the shared
- * expert uses the same shapes without the leading E. */
+ * expert uses the same shapes without the leading E.  The activations come as e4m3
+ * (x_fp8, with x_scale or unscaled) or, when x_bf16 is given, as bf16 rows that the kernel
+ * quantises per 1x128 group itself (x_fp8 / x_scale are then ignored). */
 typedef struct iq_moe_gate_args {
   const void* x_fp8;        /* [m,h] e4m3 */
   const float* x_scale;     /* [m,h/128] or NULL (unscaled) */
@@ -185,6 +231,7 @@ typedef struct iq_moe_gate_args {
   void* scratch;
   size_t scratch_bytes;
   int pdl;
+  const void* x_bf16;       /* optional [m,h] bf16 (see above) */
 } iq_moe_gate_args;
 
 int iq_moe_gate(const iq_moe_gate_args* a, void* stream);
@@ -210,37 +257,10 @@ typedef struct iq_moe_down_args {
   size_t scratch_bytes;
   const iq_tail_args* tail;
   int pdl;
+  const iq_push_args* push; /* as in iq_linear_args */
 } iq_moe_down_args;
 
 int iq_moe_down(const iq_moe_down_args* a, void* stream);
-
-/* The whole layer of the path in ONE launch: exactly the work of
- *   iq_linear(oproj, with its attention tail) -> iq_router -> iq_moe_gate ->
- *   iq_moe_down(with its MLP tail)
- * on the same arguments, with bit-identical results, but the four weight streams run
- * back to back through one shared-memory ring and the steps between them (all-reduce
- * tails, top-k) cost a grid-wide hand-off instead of a kernel boundary.  Replaces the
- * chain of ten programmatically dependent launches Engine._layer issues per MoE layer
- * (iquestrt/engine.py:387-450).
- *
- * Both tails are required (oproj->tail of kind IQ_TAIL_ATTN, down->tail of kind
- * IQ_TAIL_MLP, timeout_ms <= 3000).  The four structs must agree on m, h, i_loc, top_k,
- * n_experts, n_shared, act_kind and scratch, and each part must read what the part before
- * it writes (router.x == oproj.tail->norm_out, gate.x_fp8 / x_scale == oproj.tail->norm_fp8 /
- * norm_fp8_scale, gate.sel == down.sel == router.sel, down.wt == router.wt, down.act ==
- * gate.act); the `pdl` fields inside them are ignored and `pdl` here applies to the one
- * launch.  Shapes: oproj k % 1024 == 0, h % 1024 == 0,
- * i_loc % 256 == 0.  The CTAs of this launch wait on one another, so it is launched
- * cooperatively; it returns IQ_ERR_UNSUPPORTED when one CTA per SM cannot be resident.
- * After a device-side error (status word != 0) zero the scratch before the next call. */
-typedef struct iq_decode_layer_args {
-  iq_linear_args oproj;
-  iq_router_args router;
-  iq_moe_gate_args gate;
-  iq_moe_down_args down;
-} iq_decode_layer_args;
-
-int iq_decode_layer(const iq_decode_layer_args* a, void* stream, int pdl);
 
 #ifdef __cplusplus
 }

@@ -25,13 +25,22 @@ ROUTE_SOFTMAX, ROUTE_SIGMOID = range(2)
 ACT_E4M3, ACT_BF16 = range(2)
 
 EXPORTS = ("iq_scratch_bytes", "iq_status_read", "iq_sm_count", "iq_tail", "iq_linear",
-           "iq_linear_static", "iq_router", "iq_moe_gate", "iq_moe_down", "iq_decode_layer")
+           "iq_linear_static", "iq_linear_static_status", "iq_router", "iq_moe_gate",
+           "iq_moe_down")
 
 
 class IqError(RuntimeError):
     def __init__(self, where: str, code: int):
         super().__init__(f"{where}: {ERR_NAMES.get(code, 'error')} (code {code})")
         self.code = code
+
+
+class PushArgs(C.Structure):
+    _fields_ = [
+        ("world", C.c_int), ("rank", C.c_int), ("rows", C.c_int), ("h", C.c_int),
+        ("recv", C.c_void_p), ("recv_mc", C.c_void_p), ("peer_recv", C.c_void_p),
+        ("epoch", C.c_void_p), ("ticket", C.c_void_p),
+    ]
 
 
 class TailArgs(C.Structure):
@@ -43,7 +52,7 @@ class TailArgs(C.Structure):
         ("w_first", C.c_void_p), ("w_norm", C.c_void_p), ("scale", C.c_float), ("eps", C.c_float),
         ("h_out", C.c_void_p), ("norm_out", C.c_void_p), ("norm_fp8", C.c_void_p),
         ("norm_fp8_scale", C.c_void_p), ("inv_out", C.c_void_p), ("status", C.c_void_p),
-        ("timeout_ms", C.c_uint),
+        ("timeout_ms", C.c_uint), ("push", C.POINTER(PushArgs)),
     ]
 
 
@@ -53,7 +62,7 @@ class LinearArgs(C.Structure):
         ("m", C.c_int), ("k", C.c_int), ("n", C.c_int),
         ("w", C.c_void_p), ("w_scale", C.c_void_p), ("rg", C.c_int), ("kg", C.c_int),
         ("out", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
-        ("tail", C.POINTER(TailArgs)), ("pdl", C.c_int),
+        ("tail", C.POINTER(TailArgs)), ("pdl", C.c_int), ("push", C.POINTER(PushArgs)),
     ]
 
 
@@ -75,6 +84,7 @@ class MoeGateArgs(C.Structure):
         ("shared_fc", C.c_void_p), ("shared_fc_scale", C.c_void_p),
         ("act", C.c_void_p), ("act_kind", C.c_int),
         ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t), ("pdl", C.c_int),
+        ("x_bf16", C.c_void_p),
     ]
 
 
@@ -86,13 +96,8 @@ class MoeDownArgs(C.Structure):
         ("sel", C.c_void_p), ("wt", C.c_void_p), ("proj", C.c_void_p), ("proj_scale", C.c_void_p),
         ("shared_proj", C.c_void_p), ("shared_proj_scale", C.c_void_p),
         ("out", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
-        ("tail", C.POINTER(TailArgs)), ("pdl", C.c_int),
+        ("tail", C.POINTER(TailArgs)), ("pdl", C.c_int), ("push", C.POINTER(PushArgs)),
     ]
-
-
-class DecodeLayerArgs(C.Structure):
-    _fields_ = [("oproj", LinearArgs), ("router", RouterArgs), ("gate", MoeGateArgs),
-                ("down", MoeDownArgs)]
 
 
 _LIB = None
@@ -128,8 +133,8 @@ def load() -> C.CDLL:
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(struct), C.c_void_p]
-        lib.iq_decode_layer.restype = C.c_int
-        lib.iq_decode_layer.argtypes = [C.POINTER(DecodeLayerArgs), C.c_void_p, C.c_int]
+        lib.iq_linear_static_status.restype = C.c_int
+        lib.iq_linear_static_status.argtypes = [C.POINTER(C.c_int), C.c_void_p]
         _LIB = lib
     return _LIB
 

@@ -1,8 +1,9 @@
 """Block-FP8 weights: dequantisation and rank-local scale tables.
 
-Same names, arguments and errors as the reference's `iquestrt/blockfp8.py` (L10-36).
-These run at weight-preparation time on whatever device the tensors live on; the decode
-path itself never dequantises (the kernels apply the scales to fp32 partial sums)."""
+Same names, argument meaning and error type as the reference's `iquestrt/blockfp8.py`
+(`dequant` L10-21, `shard_scale` L24-36).  These run at weight-preparation time on whatever
+device the tensors live on; the decode path itself never dequantises (the kernels apply
+the scales to fp32 partial sums)."""
 
 from __future__ import annotations
 
@@ -13,21 +14,32 @@ BLOCK = 128
 
 def dequant(q: torch.Tensor, scale: torch.Tensor, block: tuple[int, int] = (BLOCK, BLOCK),
             dtype: torch.dtype = torch.float64) -> torch.Tensor:
-    """`q [..., R, C]` e4m3 with `scale [..., R/br, C/bc]` -> `q * scale[block]`."""
+    """`q [..., R, C]` e4m3 times its scale table `[..., R/br, C/bc]`, in `dtype`.
+
+    The weight is viewed as a grid of `br x bc` tiles and every tile is multiplied by its
+    own table entry (a broadcast over two inserted axes; the table is never expanded to
+    the weight's size)."""
     br, bc = block
-    if q.shape[-2] != scale.shape[-2] * br or q.shape[-1] != scale.shape[-1] * bc:
-        raise ValueError(f"scale {tuple(scale.shape)} at block {block} does not tile "
-                         f"weight {tuple(q.shape)}")
-    s = scale.to(dtype).repeat_interleave(br, -2).repeat_interleave(bc, -1)
-    return q.to(dtype) * s
+    *lead, rows, cols = q.shape
+    grid = (*lead, rows // br, cols // bc)
+    if rows % br or cols % bc or tuple(scale.shape) != grid:
+        raise ValueError(f"a {tuple(q.shape)} weight in {br}x{bc} blocks needs a scale table of "
+                         f"shape {grid}, got {tuple(scale.shape)}")
+    tiles = q.to(dtype).reshape(*lead, rows // br, br, cols // bc, bc)
+    return (tiles * scale.to(dtype)[..., :, None, :, None]).reshape(q.shape)
 
 
 def shard_scale(scale: torch.Tensor, dim: int, start: int, length: int,
                 grain: int) -> torch.Tensor:
-    """The scale table of the weight slice `[start, start + length)` along `dim`, one
-    entry per `grain` (which must divide 128 and tile the slice)."""
-    if BLOCK % grain or start % grain or length % grain:
-        raise ValueError(f"grain {grain} does not tile slice [{start}, {start + length}) "
-                         f"inside {BLOCK}-blocks")
-    blocks = (start + torch.arange(0, length, grain, device=scale.device)) // BLOCK
-    return scale.index_select(dim, blocks)
+    """Scale table of the weight slice `[start, start + length)` along `dim`, with one
+    entry per `grain` elements.  `grain` must divide the 128-element block and tile the
+    slice; entry j of the result is the checkpoint entry of the block that holds element
+    `start + j * grain`."""
+    if grain <= 0 or BLOCK % grain or start % grain or length % grain:
+        raise ValueError(f"a grain of {grain} cannot tile [{start}, {start + length}) inside "
+                         f"{BLOCK}-element blocks")
+    per_block = BLOCK // grain
+    first, count = start // grain, length // grain
+    source = torch.arange(first, first + count, device=scale.device).div(per_block,
+                                                                         rounding_mode="floor")
+    return scale.index_select(dim, source)

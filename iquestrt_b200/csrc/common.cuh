@@ -70,7 +70,11 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // start of the wait, or as soon as `*abort` is seen non-zero (another role of the CTA gave
 // up).  The timer and the flag are read only once per 1024 failed tests: a %globaltimer
 // read costs far more than a test, and the common case succeeds within a few tests.
-constexpr uint64_t kPipeBudgetNs = 4000000000ull;
+// The budget covers waits between roles of one CTA that are all past their dependency
+// wait (microseconds when healthy); a role that may be held up by the PREVIOUS kernel
+// (which can itself be waiting for a late peer) first executes griddepcontrol.wait, which
+// is not timed.
+constexpr uint64_t kPipeBudgetNs = 250000000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           const volatile int* abort = nullptr) {
   uint64_t t0 = 0;
@@ -236,6 +240,28 @@ __device__ __forceinline__ U4 ld_global_u4(const void* p) {
                : "l"(p)
                : "memory");
   return v;
+}
+// Four 32-bit words (16-byte aligned) that land in every rank's copy.
+__device__ __forceinline__ void multimem_st_u32x4(void* mc, const uint32_t (&v)[4]) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc),
+               "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
+               : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys_u32x4(void* p, const uint32_t (&v)[4]) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v[0]),
+               "r"(v[1]), "r"(v[2]), "r"(v[3])
+               : "memory");
+}
+__device__ __forceinline__ void st_relaxed_gpu_u32x4(void* p, const uint32_t (&v)[4]) {
+  asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v[0]),
+               "r"(v[1]), "r"(v[2]), "r"(v[3])
+               : "memory");
+}
+__device__ __forceinline__ void ld_relaxed_sys_u32x4(const uint32_t* p, uint32_t (&v)[4]) {
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+               : "l"(p)
+               : "memory");
 }
 // ---------------------------------------------------------------- small numerics
 __device__ __forceinline__ uint8_t f32_to_e4m3_sat(float v) {

@@ -11,26 +11,32 @@
 #include <stdlib.h>
 
 #include <mutex>
+#include <unordered_map>
+#include <unordered_set>
 #include <utility>
-#include <vector>
 
 #include "stream_core.cuh"
 
 namespace iqb {
 
 // ------------------------------------------------------------------------------------
-// Scratch layout (bytes): status @0, ticket @64, tile counters @256, partials after.
+// Scratch layout (bytes): status @0, ticket @64, launch tag @128, tail ticket @132, tile
+// counters @256, partials after; behind this basic part the tagged hand-off words of the
+// router's logits and the landing zone of a tail that has no peers.
 constexpr size_t kScrTicket = 64;
+constexpr size_t kScrLaunchTag = 128;    // u32: launches that handed results off as tagged words
+constexpr size_t kScrTailTicket = 132;   // u32: tail CTAs of the running launch that are done
 constexpr size_t kScrCounters = 256;
 constexpr int kMaxTiles = 16384;
 constexpr size_t kScrPartials = kScrCounters + sizeof(uint32_t) * kMaxTiles;
 constexpr int kMaxGrid = 256;
 constexpr size_t kScrBasicBytes = kScrPartials + sizeof(float) * kMaxGrid * 2 * 256 * 8;
-// The one-launch layer keeps its tagged hand-off words in an area of their own behind the
-// basic scratch: the other kernels never write there, so a word can only carry a tag that
-// a one-launch layer gave it.
-constexpr size_t kScrLayerBytes = 3 * 1024 * 1024 + 256 * 1024;
-constexpr size_t kScrBytes = kScrBasicBytes + kScrLayerBytes;
+constexpr int kMaxRows = 8;
+constexpr int kMaxExperts = 512;
+constexpr int kZoneMaxH = 8192;
+constexpr size_t kScrLogits = kScrBasicBytes;                                    // u64 [8][512]
+constexpr size_t kScrZone = kScrLogits + sizeof(uint64_t) * kMaxRows * kMaxExperts;   // u32 [8][8192]
+constexpr size_t kScrBytes = kScrZone + sizeof(uint32_t) * kMaxRows * kZoneMaxH;
 
 __host__ __device__ inline StreamScratch scratch_of(void* base) {
   StreamScratch s;
@@ -189,8 +195,53 @@ __device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const Stre
 
 // ------------------------------------------------------------------------------------
 // The tail: all-reduce of the ranks' bf16 rows, residual add and RMSNorm(s).
+//
+// Push protocol.  A producing GEMV hands its rows to the tail as 32-bit words, bf16 value
+// in the low half and the 16-bit tag of the call in the high half, stored from its epilogue
+// into the landing zone `recv[source rank][row][feature]` of EVERY rank (one multimem.st
+// per four words; one store per peer without multicast; a local store without peers).  A
+// word that shows the call's tag is complete by itself, so the producer needs no fence, no
+// counter and no flag, and the tail reads local memory only.
+struct PushView {
+  uint32_t* recv;             // this rank's landing zone, u32 [world][rows][h]
+  uint32_t* recv_mc;          // multicast alias, or null
+  uint32_t* const* peer_recv; // device array [world], or null
+  uint32_t* epoch;            // local word: completed calls on the zone (the tag's source)
+  uint32_t* ticket;           // local word: tail CTAs of the running call that are done
+  int world, rank, rows, h;
+};
+
+// Tags run over 1..65535, so a zero-filled zone never looks complete.
+__device__ __forceinline__ uint32_t tag16_of(uint32_t epoch) { return epoch % 65535u + 1u; }
+
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Four consecutive features of `row`, tagged, into every rank's zone.
+__device__ __forceinline__ void push_words(const PushView& pv, int row, int feat,
+                                           const uint32_t (&w)[4]) {
+  const size_t off = (static_cast<size_t>(pv.rank) * pv.rows + row) * pv.h + feat;
+  if (pv.recv_mc) {
+    multimem_st_u32x4(pv.recv_mc + off, w);
+  } else if (pv.world > 1) {
+    for (int p = 0; p < pv.world; ++p) st_relaxed_sys_u32x4(pv.peer_recv[p] + off, w);
+  } else {
+    st_relaxed_gpu_u32x4(pv.recv + off, w);
+  }
+}
+
+__device__ __forceinline__ uint32_t tagged_bf16(float v, uint32_t tag) {
+  return (tag << 16) | static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(v)));
+}
+
 struct TailParams {
   iq_tail_args a;
+  PushView pv;
+  int push;      // 1: rows arrive through the landing zone
+  int n_tail;    // CTAs that share the rows
 };
 
 __device__ inline void bf16x8_to_f32(const U4& u, float (&f)[8]) {
@@ -243,22 +294,108 @@ __device__ __forceinline__ void ldg_f32x8(const float* p, float (&v)[8]) {
   v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
-// Runs on the threads of `bar` (a multiple of 32; h <= 16 * threads).  `red` is shared
-// memory for 4 x 32 floats, `sflag` one shared int.  Rows written by other CTAs of this
-// launch must already be visible (the caller passed the ticket).  Rows are handled one
-// after the other, each entirely in registers, and each RMSNorm costs one block barrier.
-// The kernels this runs in keep almost all of the SM's L1 as shared memory, so a spilled
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// Row `r` of the landing zone, summed over the source ranks in rank order (fp32, one bf16
+// rounding), for this thread's vectors.  Every (vector, source) chunk of 8 words is copied
+// into shared memory `zs` ([world][h] words) with asynchronous 16-byte copies that go to
+// L2, all of them in flight together; a chunk whose words do not all show `tag` yet is
+// copied again.  A thread reads back only what it copied itself.  Returns false when the
+// budget ran out.
+__device__ __forceinline__ bool poll_zone_row(const PushView& pv, uint32_t* zs, int r,
+                                              uint32_t tag, int tid, int nthr, int vec_per_row,
+                                              uint64_t budget_ns, float (&f)[kTailVecs][8]) {
+  const size_t src_stride = static_cast<size_t>(pv.rows) * pv.h;
+  const uint32_t* row0 = pv.recv + static_cast<size_t>(r) * pv.h;
+  const uint32_t zs_s = smem_u32(zs);
+  uint32_t pend = 0;                                      // bit i*8+p: chunk still incomplete
+#pragma unroll
+  for (int i = 0; i < kTailVecs; ++i)
+    if (tid + i * nthr < vec_per_row) pend |= ((1u << pv.world) - 1u) << (8 * i);
+  uint64_t t0 = 0;
+  bool ok = true;
+  while (pend) {
+#pragma unroll
+    for (int i = 0; i < kTailVecs; ++i) {
+      const int v = tid + i * nthr;
+      for (int p = 0; p < pv.world; ++p) {
+        if (!((pend >> (8 * i + p)) & 1u)) continue;
+        const uint32_t* src = row0 + p * src_stride + v * 8;
+        const uint32_t dst = zs_s + (p * pv.h + v * 8) * 4;
+        cp_async16(dst, src);
+        cp_async16(dst + 16, src + 4);
+      }
+    }
+    cp_async_wait_all();
+#pragma unroll
+    for (int i = 0; i < kTailVecs; ++i) {
+      const int v = tid + i * nthr;
+      for (int p = 0; p < pv.world; ++p) {
+        if (!((pend >> (8 * i + p)) & 1u)) continue;
+        const uint4 lo = lds128(zs_s + (p * pv.h + v * 8) * 4);
+        const uint4 hi = lds128(zs_s + (p * pv.h + v * 8) * 4 + 16);
+        const uint32_t all = (lo.x >> 16 == tag) & (lo.y >> 16 == tag) & (lo.z >> 16 == tag) &
+                             (lo.w >> 16 == tag) & (hi.x >> 16 == tag) & (hi.y >> 16 == tag) &
+                             (hi.z >> 16 == tag) & (hi.w >> 16 == tag);
+        if (all) pend &= ~(1u << (8 * i + p));
+      }
+    }
+    if (pend) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) { ok = false; break; }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kTailVecs; ++i) {
+    const int v = tid + i * nthr;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (ok && v < vec_per_row) {
+      for (int p = 0; p < pv.world; ++p) {
+        const uint4 lo = lds128(zs_s + (p * pv.h + v * 8) * 4);
+        const uint4 hi = lds128(zs_s + (p * pv.h + v * 8) * 4 + 16);
+        acc[0] += __uint_as_float(lo.x << 16); acc[1] += __uint_as_float(lo.y << 16);
+        acc[2] += __uint_as_float(lo.z << 16); acc[3] += __uint_as_float(lo.w << 16);
+        acc[4] += __uint_as_float(hi.x << 16); acc[5] += __uint_as_float(hi.y << 16);
+        acc[6] += __uint_as_float(hi.z << 16); acc[7] += __uint_as_float(hi.w << 16);
+      }
+    }
+    bf16x8_to_f32(f32_to_bf16x8(acc), f[i]);
+  }
+  return ok;
+}
+
+// Runs on the threads of `bar` (a multiple of 32; h <= 16 * threads) for rows r_begin,
+// r_begin + r_step, ... of the call.  `red` is shared memory for 4 x 32 floats, `sflag`
+// one shared int, `zs` (push only) shared memory for world x h words.  Without `kPush`,
+// rows written by other CTAs of this launch must already be visible (the caller passed
+// the ticket) and the pull protocol's signal / wait / switch read applies for world > 1.
+// Each row is handled entirely in registers and each RMSNorm costs one block barrier.  The
+// kernels this runs in keep almost all of the SM's L1 as shared memory, so a spilled
 // register would cost an L2 round trip: the loads are ordered to keep few values live
 // (the residual stays packed until it is used; each norm weight is fetched just before
 // the barrier of the reduction that precedes its use, which hides its latency).
-__device__ __forceinline__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /*rows_s*/,
-                                         float* red, int* sflag, const BlockBar bar = BlockBar{}) {
+template <bool kPush>
+__device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& pv, uint32_t* zs,
+                                         float* red, int* sflag, const BlockBar bar = BlockBar{},
+                                         int r_begin = 0, int r_step = 1) {
   const int tid = threadIdx.x, nthr = bar.threads();
   const int m = a.m, h = a.h, vec_per_row = h / 8;
   const float inv_h = 1.0f / static_cast<float>(h);
   const bool attn = a.kind == IQ_TAIL_ATTN;
+  uint32_t tag = 0;
+  if (kPush) {
+    tag = tag16_of(ld_volatile_u32(pv.epoch));
+    if (tid == 0) *sflag = 1;
+    bar.sync();
+  }
 
-  for (int r = 0; r < m; ++r) {
+  for (int r = r_begin; r < m; r += r_step) {
     const size_t row_off = static_cast<size_t>(r) * h;
     float* slots0 = red + (r & 1) * 64;        // two reductions per row, alternating rows
     float* slots1 = slots0 + 32;
@@ -278,75 +415,87 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /
             reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.residual) + off));
       }
     }
-    // ---- cross-rank readiness: signal, then wait while the residual loads are in flight
-    if (r == 0 && a.world > 1) {
-      if (tid == 0) {
-        const uint32_t target = (*a.epoch + 1u) * static_cast<uint32_t>(a.world);
-        if (a.arrive_mc) {
-          multimem_red_add_release_u32(a.arrive_mc, 1u);
-        } else {
-          for (int p = 0; p < a.world; ++p)
-            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_arrive[p]), "r"(1u)
-                         : "memory");
-        }
-        const uint64_t budget = 1000000ull * (a.timeout_ms ? a.timeout_ms : 2000u);
-        uint64_t t0 = 0;
-        int ok = 1;
-        for (uint32_t spin = 0;; ++spin) {
-          if (static_cast<int32_t>(ld_acquire_sys_u32(a.arrive) - target) >= 0) break;
-          if ((spin & 255u) == 255u) {
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > budget) { ok = 0; break; }
-          }
-        }
-        if (!ok) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
-        *sflag = ok;
-      }
+    float f[kTailVecs][8];
+    if (kPush) {
+      // ---- the row arrives in the landing zone: poll it, add the ranks
+      const uint64_t budget = 1000000ull * (a.timeout_ms ? a.timeout_ms : 2000u);
+      if (!poll_zone_row(pv, zs, r, tag, tid, nthr, vec_per_row, budget, f)) *sflag = 0;
       bar.sync();
       if (!*sflag) {
-        // Peers are missing: leave the outputs untouched and let the host read the status.
-        if (tid == 0) *a.epoch = *a.epoch + 1u;
+        // A source is missing: leave the outputs untouched and let the host read the status.
+        if (tid == 0) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
         return;
       }
-    }
-    // ---- the reduced partial
-    float f[kTailVecs][8];
-#pragma unroll
-    for (int i = 0; i < kTailVecs; ++i) {
-      const int v = tid + i * nthr;
-      if (v >= vec_per_row) continue;
-      const size_t off = row_off + static_cast<size_t>(v) * 8;
-      U4 part;
-      if (a.world == 1) {
-        const uint4 t = __ldcg(reinterpret_cast<const uint4*>(
-            static_cast<const __nv_bfloat16*>(a.partial) + off));
-        part = U4{t.x, t.y, t.z, t.w};
-      } else if (a.partial_mc) {
-        part = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(a.partial_mc) + off);
-      } else {
-        // four peers' vectors in flight at a time, summed in rank order
-        float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int p0 = 0; p0 < 8; p0 += 4) {
-          if (p0 >= a.world) break;
-          U4 pv[4];
-#pragma unroll
-          for (int p = 0; p < 4; ++p)
-            if (p0 + p < a.world)
-              pv[p] = ld_global_u4(static_cast<const __nv_bfloat16*>(a.peer_partials[p0 + p]) + off);
-#pragma unroll
-          for (int p = 0; p < 4; ++p) {
-            if (p0 + p >= a.world) continue;
-            float t[8];
-            bf16x8_to_f32(pv[p], t);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) accv[j] += t[j];
+    } else {
+      // ---- cross-rank readiness: signal, then wait while the residual loads are in flight
+      if (r == r_begin && a.world > 1) {
+        if (tid == 0) {
+          const uint32_t target = (*a.epoch + 1u) * static_cast<uint32_t>(a.world);
+          if (a.arrive_mc) {
+            multimem_red_add_release_u32(a.arrive_mc, 1u);
+          } else {
+            for (int p = 0; p < a.world; ++p)
+              asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_arrive[p]), "r"(1u)
+                           : "memory");
           }
+          const uint64_t budget = 1000000ull * (a.timeout_ms ? a.timeout_ms : 2000u);
+          uint64_t t0 = 0;
+          int ok = 1;
+          for (uint32_t spin = 0;; ++spin) {
+            if (static_cast<int32_t>(ld_acquire_sys_u32(a.arrive) - target) >= 0) break;
+            if ((spin & 255u) == 255u) {
+              const uint64_t now = globaltimer_ns();
+              if (t0 == 0) t0 = now;
+              else if (now - t0 > budget) { ok = 0; break; }
+            }
+          }
+          if (!ok) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
+          *sflag = ok;
         }
-        part = f32_to_bf16x8(accv);
+        bar.sync();
+        if (!*sflag) {
+          // Peers are missing: leave the outputs untouched and let the host read the status.
+          if (tid == 0) *a.epoch = *a.epoch + 1u;
+          return;
+        }
       }
-      bf16x8_to_f32(part, f[i]);
+      // ---- the reduced partial
+#pragma unroll
+      for (int i = 0; i < kTailVecs; ++i) {
+        const int v = tid + i * nthr;
+        if (v >= vec_per_row) continue;
+        const size_t off = row_off + static_cast<size_t>(v) * 8;
+        U4 part;
+        if (a.world == 1) {
+          const uint4 t = __ldcg(reinterpret_cast<const uint4*>(
+              static_cast<const __nv_bfloat16*>(a.partial) + off));
+          part = U4{t.x, t.y, t.z, t.w};
+        } else if (a.partial_mc) {
+          part = multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(a.partial_mc) + off);
+        } else {
+          // four peers' vectors in flight at a time, summed in rank order
+          float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int p0 = 0; p0 < 8; p0 += 4) {
+            if (p0 >= a.world) break;
+            U4 pvv[4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p)
+              if (p0 + p < a.world)
+                pvv[p] = ld_global_u4(static_cast<const __nv_bfloat16*>(a.peer_partials[p0 + p]) + off);
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              if (p0 + p >= a.world) continue;
+              float t[8];
+              bf16x8_to_f32(pvv[p], t);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) accv[j] += t[j];
+            }
+          }
+          part = f32_to_bf16x8(accv);
+        }
+        bf16x8_to_f32(part, f[i]);
+      }
     }
 
     float wv[kTailVecs][8];    // w_first, later w_norm
@@ -441,19 +590,49 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, __nv_bfloat16* /
       }
     }
   }
-  if (a.world > 1 && tid == 0) *a.epoch = *a.epoch + 1u;
+  if (!kPush && a.world > 1 && tid == 0) *a.epoch = *a.epoch + 1u;
+}
+
+// A tail CTA of the push protocol: CTA `index` of `n_tail` finishes rows index,
+// index + n_tail, ...  The last tail CTA to finish closes the call (the zone's epoch moves
+// on once every tail CTA has read it).  Sixteen warps run the tail wherever it runs, so
+// its block-wide sums add in one order.
+__device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& pv, int index,
+                                         int n_tail, uint8_t* smem) {
+  float* red = reinterpret_cast<float*>(smem);
+  int* sflag = reinterpret_cast<int*>(smem + 512);
+  uint32_t* zs = reinterpret_cast<uint32_t*>(smem + 1024);
+  if (threadIdx.x < kConsumerThreads)
+    run_tail<true>(a, pv, zs, red, sflag, BlockBar{2, kConsumerThreads}, index, n_tail);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(pv.ticket, 1u);
+    if (prev == static_cast<uint32_t>(n_tail - 1)) {
+      *pv.ticket = 0;
+      *pv.epoch = ld_volatile_u32(pv.epoch) + 1u;
+    }
+  }
+}
+
+// Shared memory a tail CTA of the push protocol needs.
+__host__ __device__ inline size_t tail_cta_smem(int world, int h) {
+  return 1024 + static_cast<size_t>(world) * h * 4;
 }
 
 __global__ void __launch_bounds__(kThreads, 1) tail_kernel(const TailParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_wait();
   pdl_launch_dependents();   // after the wait: see the note on `after_wait` below
+  if (p.push) {
+    tail_cta(p.a, p.pv, static_cast<int>(blockIdx.x), p.n_tail, smem);
+    return;
+  }
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
-  // Sixteen warps everywhere the tail runs, so that its block-wide sums add in one order.
   if (threadIdx.x < kConsumerThreads)
-    run_tail(p.a, reinterpret_cast<__nv_bfloat16*>(smem + 1024), red, sflag,
-             BlockBar{2, kConsumerThreads});
+    run_tail<false>(p.a, p.pv, nullptr, red, sflag, BlockBar{2, kConsumerThreads},
+                    static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
 }
 
 // Programmatic dependent launch discipline shared by the kernels: a CTA lets its
@@ -470,6 +649,12 @@ __device__ __forceinline__ void after_wait() {
 
 // ------------------------------------------------------------------------------------
 // iq_linear
+enum TailRun : int {
+  kTailNone = 0,
+  kTailLastCta = 1,   // pull protocol: the last CTA to finish its tiles runs the tail
+  kTailCtas = 2,      // push protocol: the launch's last `n_tail` CTAs are tail CTAs
+};
+
 struct LinearParams {
   CUtensorMap map0, map1;   // weight tensor maps (unused for whole-row stages)
   StreamShape sh;
@@ -480,21 +665,50 @@ struct LinearParams {
   const float* w_scale;
   __nv_bfloat16* out;
   void* scratch;
-  int has_tail;
+  int tail_run;             // TailRun
+  int n_tail;               // tail CTAs at the end of the grid (kTailCtas)
+  int push;                 // the epilogue also sends the rows to the landing zone
   iq_tail_args tail;
+  PushView pv;
 };
+
+// Four consecutive features of one output row: bf16 into `out`, and (push) tagged into
+// the landing zone.
+__device__ __forceinline__ void store_row4(__nv_bfloat16* out, size_t index, const float (&v)[4],
+                                           bool push, const PushView& pv, uint32_t tag, int row,
+                                           int feat) {
+  const __nv_bfloat162 lo = __float22bfloat162_rn(make_float2(v[0], v[1]));
+  const __nv_bfloat162 hi = __float22bfloat162_rn(make_float2(v[2], v[3]));
+  uint2 packed;
+  packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(out + index) = packed;
+  if (push) {
+    const uint32_t t = tag << 16;
+    const uint32_t w[4] = {t | (packed.x & 0xffffu), t | (packed.x >> 16),
+                           t | (packed.y & 0xffffu), t | (packed.y >> 16)};
+    push_words(pv, row, feat, w);
+  }
+}
 
 template <class G>
 __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_constant__ LinearParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const StreamShape& sh = p.sh;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int cta = blockIdx.x;
+  // CTAs that stream; the rest of the grid (push protocol) finishes the rows.
+  const int stream_ctas = static_cast<int>(gridDim.x) - p.n_tail;
+  if (cta >= stream_ctas) {
+    after_wait();
+    tail_cta(p.tail, p.pv, cta - stream_ctas, p.n_tail, smem);
+    return;
+  }
   const Carve<G> cv = carve<G>(smem, sh);
   const StreamScratch scr = scratch_of(p.scratch);
-  const int tid = threadIdx.x, warp = tid >> 5;
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
-  const int cta = blockIdx.x;
   stream_init<G>(sh, cv.sm);
   if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1))
     prefetch_tensormap(&p.map0);   // only a map the host filled (K-sliced stages)
@@ -512,7 +726,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
   }
   __syncthreads();
   {
-    const CtaWork wk = cta_share<G>(sh, static_cast<int>(gridDim.x), cta, grid);
+    const CtaWork wk = cta_share<G>(sh, stream_ctas, cta, grid);
     if (warp == kProducerWarp) {
       // Weights never change: start streaming before the predecessor kernel has finished.
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
@@ -535,33 +749,35 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
       const bool split2 = p.x_kind == IQ_X_BF16_SPLIT2;
       const int m = p.m, n = p.n;
       __nv_bfloat16* out = p.out;
-      auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
+      const bool push = p.push != 0;
+      const uint32_t tag = push ? tag16_of(ld_volatile_u32(p.pv.epoch)) : 0u;
+      const PushView& pv = p.pv;
+      auto emit = [&](const TileId& id, int r0, int col, const float (&val)[4][G::RT]) {
 #pragma unroll
         for (int sub = 0; sub < G::RT; ++sub) {
-          const int row = id.tig * G::ROWS + sub * 16 + r;
+          const int feat = id.tig * G::ROWS + sub * 16 + r0;
+          float v[4] = {val[0][sub], val[1][sub], val[2][sub], val[3][sub]};
+          int row = col;
+          bool live = col < m;
           if (split2) {
-            // columns 2j and 2j+1 are the two terms of row j: fold them on the even lane
-            const float other = __shfl_xor_sync(0xffffffffu, val[sub], 1);
-            if ((col & 1) == 0 && (col >> 1) < m)
-              out[static_cast<size_t>(col >> 1) * n + row] = __float2bfloat16_rn(val[sub] + other);
-          } else if (col < m) {
-            out[static_cast<size_t>(col) * n + row] = __float2bfloat16_rn(val[sub]);
+            // columns 2j and 2j+1 (four lanes apart) are the two terms of row j: fold them
+            // on the even column's lane
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] += __shfl_xor_sync(0xffffffffu, v[j], 4);
+            row = col >> 1;
+            live = (col & 1) == 0 && row < m;
           }
+          if (live) store_row4(out, static_cast<size_t>(row) * n + feat, v, push, pv, tag, row, feat);
         }
       };
-      epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, emit);
+      epilogue<G, true>(sh, cv.sm, wk, total, grid, cta, scr, emit);
     }
   }
-  if (!p.has_tail) {
-    stream_drain_on_abort<G>(cv.sm);
-    return;
-  }
-  if (last_cta<G>(cv.sm, scr, gridDim.x)) {
-    // The ring is idle now: its first bytes hold the reduced rows.
+  if (p.tail_run == kTailLastCta && last_cta<G>(cv.sm, scr, gridDim.x)) {
     float* red = reinterpret_cast<float*>(cv.sm->red);
     if (threadIdx.x < kConsumerThreads)
-      run_tail(p.tail, reinterpret_cast<__nv_bfloat16*>(cv.ring), red, &cv.sm->is_last_tile,
-               BlockBar{2, kConsumerThreads});
+      run_tail<false>(p.tail, p.pv, nullptr, red, &cv.sm->is_last_tile,
+                      BlockBar{2, kConsumerThreads});
   }
   stream_drain_on_abort<G>(cv.sm);
 }
@@ -653,17 +869,65 @@ __device__ void select_row(const float* logits, int e, int top_k, int score, int
     select_row_impl<16>(logits, e, top_k, score, row, sel, wt, logits_in_smem);   // e <= 512
 }
 
+// The router's hand-off inside one launch: the CTAs that stream the weight rows store
+// each logit as a 64-bit word (fp32 value, 32-bit tag of the launch) with one relaxed
+// store; the launch's LAST CTA streams nothing and polls those words (one warp per row),
+// writes the plain logits and selects.  No fence, ticket or counter on the producers'
+// side.  The tag is the scratch's launch counter, which the selecting CTA advances when
+// it is done.
 template <class G>
 __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_constant__ RouterParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const StreamShape& sh = p.sh;
-  const Carve<G> cv = carve<G>(smem, sh);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cta = blockIdx.x;
+  const int stream_ctas = static_cast<int>(gridDim.x) - 1;
+  uint8_t* scratch = static_cast<uint8_t*>(p.scratch);
+  uint32_t* launch_tag = reinterpret_cast<uint32_t*>(scratch + kScrLaunchTag);
+  uint64_t* tagged = reinterpret_cast<uint64_t*>(scratch + kScrLogits);
   const StreamScratch scr = scratch_of(p.scratch);
-  const int tid = threadIdx.x, warp = tid >> 5;
+  if (cta == stream_ctas) {
+    // ---- the selecting CTA
+    after_wait();
+    const uint32_t tag = ld_volatile_u32(launch_tag) + 1u;
+    float* lg = reinterpret_cast<float*>(smem);          // [m][e]
+    if (warp < p.m) {
+      const int per = (p.e + 31) / 32;                   // <= 16
+      uint32_t pend = (1u << per) - 1u;
+      uint64_t t0 = 0;
+      bool ok = true;
+      while (true) {
+        for (int j = 0; j < per; ++j) {
+          const int id = lane + 32 * j;
+          if (!((pend >> j) & 1u) || id >= p.e) { pend &= ~(1u << j); continue; }
+          const uint64_t wv = ld_relaxed_gpu_u64(tagged + static_cast<size_t>(warp) * p.e + id);
+          if (static_cast<uint32_t>(wv >> 32) == tag) {
+            lg[warp * p.e + id] = __uint_as_float(static_cast<uint32_t>(wv));
+            pend &= ~(1u << j);
+          }
+        }
+        if (__all_sync(0xffffffffu, pend == 0u)) break;
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kPipeBudgetNs) { ok = false; break; }
+      }
+      __syncwarp();
+      if (ok) {
+        for (int id = lane; id < p.e; id += 32)
+          p.logits[static_cast<size_t>(warp) * p.e + id] = lg[warp * p.e + id];
+        select_row(lg, p.e, p.top_k, p.score, warp, p.sel, p.wt, true);
+      } else if (lane == 0) {
+        set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+      }
+    }
+    __syncthreads();
+    if (tid == 0) *launch_tag = tag;
+    return;
+  }
+  const Carve<G> cv = carve<G>(smem, sh);
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
-  const int cta = blockIdx.x;
   stream_init<G>(sh, cv.sm);
   if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1))
     prefetch_tensormap(&p.map0);   // only a map the host filled (K-sliced stages)
@@ -681,35 +945,35 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
   }
   __syncthreads();
   {
-    const CtaWork wk = cta_share<G>(sh, static_cast<int>(gridDim.x), cta, grid);
+    const CtaWork wk = cta_share<G>(sh, stream_ctas, cta, grid);
     if (warp == kProducerWarp) {
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
       pdl_wait();
     } else if (warp < kConsumerWarps) {
       after_wait();
-      const int vec = p.h / 8;   // 16-byte vectors per bf16 row
-      for (int i = tid; i < p.m * vec; i += kConsumerThreads) {
-        const int r = i / vec, v = i - r * vec;
-        *reinterpret_cast<uint4*>(cv.xq + r * sh.x_pitch + v * 16) =
-            *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(r) * p.h + v * 8);
+      if (wk.n_items > 0) {
+        const int vec = p.h / 8;   // 16-byte vectors per bf16 row
+        for (int i = tid; i < p.m * vec; i += kConsumerThreads) {
+          const int r = i / vec, v = i - r * vec;
+          *reinterpret_cast<uint4*>(cv.xq + r * sh.x_pitch + v * 16) =
+              *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(r) * p.h + v * 8);
+        }
       }
       named_bar_sync(1, kConsumerThreads);
       consume<G, ElemBF16>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
     } else {
       pdl_wait();
       const int m = p.m, e = p.e;
-      float* logits = p.logits;
+      const uint64_t tag = static_cast<uint64_t>(ld_volatile_u32(launch_tag) + 1u) << 32;
       auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
 #pragma unroll
         for (int sub = 0; sub < G::RT; ++sub)
           if (col < m)
-            logits[static_cast<size_t>(col) * e + id.tig * G::ROWS + sub * 16 + r] = val[sub];
+            st_relaxed_gpu_u64(tagged + static_cast<size_t>(col) * e + id.tig * G::ROWS + sub * 16 + r,
+                               tag | __float_as_uint(val[sub]));
       };
-      epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, emit);
+      epilogue<G, false>(sh, cv.sm, wk, total, grid, cta, scr, emit);
     }
-  }
-  if (last_cta<G>(cv.sm, scr, gridDim.x)) {
-    if (warp < p.m) select_row(p.logits, p.e, p.top_k, p.score, warp, p.sel, p.wt);
   }
   stream_drain_on_abort<G>(cv.sm);
 }
@@ -883,12 +1147,22 @@ struct GateParams {
   MoeCommon mc;
   const uint8_t* x_fp8;
   const float* x_scale;
+  const __nv_bfloat16* x_bf16;   // instead of x_fp8: quantised per 1x128 group while staging
   void* act;
   int act_kind;
   void* scratch;
   int pdl_level;
   int early_shared;   // see gate_kernel
 };
+
+template <class G>
+__device__ __forceinline__ void gate_stage_x(const GateParams& p, const StreamShape& sh,
+                                             const Carve<G>& cv, int tid) {
+  if (p.x_bf16)
+    stage_rows_bf16_groupq(cv.xq, cv.xs, sh, p.x_bf16, p.mc.h, p.mc.m, p.mc.h, false, tid);
+  else
+    stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
+}
 
 // One stream of the Gate: the tiles of `wk`, every role with its ring / reduction position
 // carried in `pos` / `rpos` (the kernel may run two streams back to back).
@@ -899,13 +1173,14 @@ __device__ __forceinline__ void gate_stream(const GateParams& p, const StreamSha
                                             bool stage_x, RingPos& pos, RedPos& rpos) {
   const int tid = threadIdx.x, warp = tid >> 5;
   if (warp == kProducerWarp) {
+    // (both of the Gate's streams are consumed as they arrive: the first ahead of the
+    // dependency wait by design, the second after every role has passed it)
     produce<G>(sh, cv.sm, cv.sm->groups, cv.ring, G::STAGE_BYTES, wk, scr.status, &p.map0, &p.map1,
-               pos);
+               pos, false);
   } else if (warp < kConsumerWarps) {
     float held[kGatherHeld];
     gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);
-    if (stage_x)
-      stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
+    if (stage_x) gate_stage_x<G>(p, sh, cv, tid);
     gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
     named_bar_sync(1, kConsumerThreads);
     consume<G, ElemE4M3>(sh, cv.sm, cv.sm->groups, cv.ring, G::STAGE_BYTES, cv.xq, cv.xs, cv.sc, wk,
@@ -931,7 +1206,7 @@ __device__ __forceinline__ void gate_stream(const GateParams& p, const StreamSha
           static_cast<__nv_bfloat16*>(act)[o] = __float2bfloat16_rn(v);
       }
     };
-    epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, rpos, emit);
+    epilogue<G, false>(sh, cv.sm, wk, total, grid, cta, scr, rpos, emit);
   }
 }
 
@@ -953,8 +1228,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
   // Level 2: the activations were written two launches back (by the attention tail) and
   // can be staged while the router, the immediate predecessor, is still finishing.
   const bool early_x = p.pdl_level >= 2;
-  if (early_x && warp < kConsumerWarps)
-    stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
+  if (early_x && warp < kConsumerWarps) gate_stage_x<G>(p, sh, cv, tid);
   // With `early_shared` (host: level 2, shared experts, whole tiles dealt round robin
   // whatever the routes) the shared experts are the first groups, CTA c's first tile is
   // tile c, and if that is a shared expert's tile the CTA streams and finishes it NOW:
@@ -1011,18 +1285,28 @@ struct DownParams {
   int act_kind;
   __nv_bfloat16* out;
   void* scratch;
-  int has_tail;
+  int tail_run;             // TailRun
+  int n_tail;
+  int push;
   int pdl_level;
   iq_tail_args tail;
+  PushView pv;
 };
 
 template <class G>
 __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant__ DownParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   StreamShape sh = p.sh;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int cta = blockIdx.x;
+  const int stream_ctas = static_cast<int>(gridDim.x) - p.n_tail;
+  if (cta >= stream_ctas) {
+    after_wait();
+    tail_cta(p.tail, p.pv, cta - stream_ctas, p.n_tail, smem);
+    return;
+  }
   const Carve<G> cv = carve<G>(smem, sh);
   const StreamScratch scr = scratch_of(p.scratch);
-  const int tid = threadIdx.x, warp = tid >> 5;
   stream_init<G>(sh, cv.sm);
   if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
     prefetch_tensormap(&p.map0);   // only maps the host filled (K-sliced stages)
@@ -1037,9 +1321,8 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
-  const int cta = blockIdx.x;
   {
-    const CtaWork wk = cta_share<G>(sh, static_cast<int>(gridDim.x), cta, grid);
+    const CtaWork wk = cta_share<G>(sh, stream_ctas, cta, grid);
     if (warp == kProducerWarp) {
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
     } else if (warp < kConsumerWarps) {
@@ -1060,46 +1343,50 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
       if (early) pdl_wait();
       const int m = p.mc.m, h = p.mc.h;
       __nv_bfloat16* out = p.out;
-      auto emit = [&](const TileId& id, int r, int col, const float (&val)[G::RT]) {
+      const bool push = p.push != 0;
+      const uint32_t tag = push ? tag16_of(ld_volatile_u32(p.pv.epoch)) : 0u;
+      const PushView& pv = p.pv;
+      auto emit = [&](const TileId& id, int r0, int col, const float (&val)[4][G::RT]) {
         if (col >= m) return;
 #pragma unroll
-        for (int sub = 0; sub < G::RT; ++sub)
-          out[static_cast<size_t>(col) * h + id.tile * G::ROWS + sub * 16 + r] =
-              __float2bfloat16_rn(val[sub]);
+        for (int sub = 0; sub < G::RT; ++sub) {
+          const int feat = id.tile * G::ROWS + sub * 16 + r0;
+          const float v[4] = {val[0][sub], val[1][sub], val[2][sub], val[3][sub]};
+          store_row4(out, static_cast<size_t>(col) * h + feat, v, push, pv, tag, col, feat);
+        }
       };
-      epilogue<G>(sh, cv.sm, wk, total, grid, cta, scr, emit);
+      epilogue<G, true>(sh, cv.sm, wk, total, grid, cta, scr, emit);
     }
   }
-  if (!p.has_tail) {
-    stream_drain_on_abort<G>(cv.sm);
-    return;
-  }
-  if (last_cta<G>(cv.sm, scr, gridDim.x)) {
+  if (p.tail_run == kTailLastCta && last_cta<G>(cv.sm, scr, gridDim.x)) {
     float* red = reinterpret_cast<float*>(cv.sm->red);
     if (threadIdx.x < kConsumerThreads)
-      run_tail(p.tail, reinterpret_cast<__nv_bfloat16*>(cv.ring), red, &cv.sm->is_last_tile,
-               BlockBar{2, kConsumerThreads});
+      run_tail<false>(p.tail, p.pv, nullptr, red, &cv.sm->is_last_tile,
+                      BlockBar{2, kConsumerThreads});
   }
   stream_drain_on_abort<G>(cv.sm);
 }
 
 }  // namespace iqb
 
-#include "layer_fused.cuh"
-
 namespace iqb {
 
 // ------------------------------------------------------------------------------------
-// Host side
-static int g_sm_count = 0;
+// Host side.  The library is entered through a C ABI, possibly from several host threads
+// (one per stream): every piece of host state below is guarded by `g_host_mutex`.
+static std::mutex g_host_mutex;
+
 static int sm_count() {
-  if (g_sm_count == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  static int per_device[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
+  if (per_device[dev] == 0) {
+    int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    g_sm_count = n;
+    per_device[dev] = n;
   }
-  return g_sm_count;
+  return per_device[dev];
 }
 
 static int ilog2(int v) {
@@ -1108,26 +1395,24 @@ static int ilog2(int v) {
   return s;
 }
 
-// One opt-in to the full shared memory per (kernel, device).  Callers are serialised per
-// process by the GIL or by their own stream discipline; the table is append-only.
+// One opt-in to the full shared memory per (kernel, device).
 static bool ensure_smem_optin(const void* fn) {
-  struct Entry { const void* fn; int dev; };
-  static Entry done[256];
-  static int n_done = 0;
+  static std::unordered_set<uint64_t> done;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return false;
-  for (int i = 0; i < n_done; ++i)
-    if (done[i].fn == fn && done[i].dev == dev) return true;
+  const uint64_t key = (reinterpret_cast<uint64_t>(fn) << 6) ^ static_cast<uint64_t>(dev);
+  std::lock_guard<std::mutex> lock(g_host_mutex);
+  if (done.count(key)) return true;
   if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
       cudaSuccess)
     return false;
-  if (n_done < 256) done[n_done++] = Entry{fn, dev};
+  done.insert(key);
   return true;
 }
 
 // Tensor maps of weight matrices viewed as [total_rows, k_bytes / 4] u32, box = (kc / 4)
-// x box_rows, no swizzle.  Encoding costs a driver call, so maps are cached by key; a map
-// holds only the address and geometry, never data.
+// x box_rows, no swizzle.  Encoding costs a driver call, so maps are cached in a hash map
+// keyed by address and geometry; a map holds only the address and geometry, never data.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1141,16 +1426,25 @@ struct MapKey {
            kc == o.kc;
   }
 };
-static std::mutex g_map_mutex;
-static std::vector<std::pair<MapKey, CUtensorMap>> g_maps;
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t x = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+    x ^= static_cast<uint64_t>(k.rows) * 0xC2B2AE3D27D4EB4Full;
+    x ^= (static_cast<uint64_t>(k.k_bytes) << 40) ^ (static_cast<uint64_t>(k.box_rows) << 20) ^
+         static_cast<uint64_t>(k.kc);
+    return static_cast<size_t>(x ^ (x >> 29));
+  }
+};
+constexpr size_t kMaxCachedMaps = 1 << 16;   // a deep model has a few maps per layer
 
 static int weight_map(CUtensorMap* out, const void* ptr, long long rows, int k_bytes, int box_rows,
                       int kc) {
   static EncodeTiledFn encode = nullptr;
-  std::lock_guard<std::mutex> lock(g_map_mutex);
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
   const MapKey key{ptr, rows, k_bytes, box_rows, kc};
-  for (const auto& kv : g_maps)
-    if (kv.first == key) { *out = kv.second; return IQ_OK; }
+  const auto hit = maps.find(key);
+  if (hit != maps.end()) { *out = hit->second; return IQ_OK; }
   if (!encode) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -1172,8 +1466,8 @@ static int weight_map(CUtensorMap* out, const void* ptr, long long rows, int k_b
     fprintf(stderr, "iqb200: cuTensorMapEncodeTiled failed (%d)\n", static_cast<int>(r));
     return IQ_ERR_CUDA;
   }
-  if (g_maps.size() >= 4096) g_maps.clear();
-  g_maps.emplace_back(key, m);
+  if (maps.size() >= kMaxCachedMaps) maps.clear();
+  maps.emplace(key, m);
   *out = m;
   return IQ_OK;
 }
@@ -1191,23 +1485,16 @@ static int fill_maps(CUtensorMap* map0, CUtensorMap* map1, const StreamShape& sh
 }
 
 template <class Kernel, class Params>
-static int launch(Kernel kernel, const Params& p, int grid, size_t smem, void* stream, int pdl,
-                  bool cooperative = false) {
-  // One opt-in to the full shared memory per kernel and device (this function is
-  // instantiated per kernel, so the flags are per kernel).
+static int launch(Kernel kernel, const Params& p, int grid, size_t smem, void* stream, int pdl) {
+  // One opt-in to the full shared memory per kernel and device.
   if (!ensure_smem_optin(reinterpret_cast<const void*>(kernel))) return IQ_ERR_CUDA;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr[2] = {};
+  cudaLaunchAttribute attr[1] = {};
   int n_attr = 0;
-  if (cooperative) {
-    attr[n_attr].id = cudaLaunchAttributeCooperative;
-    attr[n_attr].val.cooperative = 1;
-    ++n_attr;
-  }
   if (pdl) {
     attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
@@ -1223,12 +1510,11 @@ static int launch(Kernel kernel, const Params& p, int grid, size_t smem, void* s
   return IQ_OK;
 }
 
-// Most stages one CTA can own, over every group count the routes can produce, under the
-// same rule cta_share applies on the device; 0 when the stream has more tiles than the
-// scratch has counters.
+// Most stages one of `grid` streaming CTAs can own, over every group count the routes can
+// produce, under the same rule cta_share applies on the device; 0 when the stream has more
+// tiles than the scratch has counters.
 template <class G>
-static int max_items_any(const StreamShape& sh, int max_groups) {
-  const int grid = sm_count() > 0 ? sm_count() : 1;
+static int max_items_any(const StreamShape& sh, int max_groups, int grid) {
   int most = 0;
   for (int n = 1; n <= max_groups; ++n) {
     StreamShape s = sh;
@@ -1252,11 +1538,13 @@ static int max_items_any(const StreamShape& sh, int max_groups) {
 }
 
 // Fills the geometry-dependent part of a shape and returns the dynamic shared memory to
-// request, or 0 when the ring does not fit.
-// `max_groups` bounds the group count a kernel may derive from the routes.
+// request, or 0 when the ring does not fit.  `grid` is the number of CTAs that stream,
+// `max_groups` bounds the group count a kernel may derive from the routes, `other_bytes`
+// is what another role of the launch (a tail CTA) needs.
 template <class G>
-static size_t plan_smem(StreamShape& sh, size_t tail_bytes, int max_groups = 1) {
-  sh.max_items = max_items_any<G>(sh, max_groups);
+static size_t plan_smem(StreamShape& sh, int grid, size_t other_bytes, int max_groups = 1) {
+  if (grid < 1) return 0;
+  sh.max_items = max_items_any<G>(sh, max_groups, grid);
   if (sh.max_items == 0) return 0;
   const size_t fixed = smem_fixed_bytes<G>(sh);
   if (fixed + 2 * G::STAGE_BYTES > static_cast<size_t>(kSmemLimit)) return 0;
@@ -1269,11 +1557,20 @@ static size_t plan_smem(StreamShape& sh, size_t tail_bytes, int max_groups = 1) 
   if (stages > kMaxStages) stages = kMaxStages;
   sh.n_stages = stages;
   size_t need = fixed + static_cast<size_t>(stages) * G::STAGE_BYTES;
-  if (need < fixed + tail_bytes) need = fixed + tail_bytes;
+  if (need < other_bytes) need = other_bytes;
   return need <= static_cast<size_t>(kSmemLimit) ? need : 0;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int check_push(const iq_push_args* u, int m, int h) {
+  if (u->world < 1 || u->world > 8 || u->rank < 0 || u->rank >= u->world) return IQ_ERR_ARG;
+  if (u->rows < m || u->rows > 64 || u->h != h) return IQ_ERR_ARG;
+  if (!u->recv || !u->epoch || !u->ticket || !aligned16(u->recv)) return IQ_ERR_ARG;
+  if (u->world > 1 && !u->recv_mc && !u->peer_recv) return IQ_ERR_ARG;
+  if (u->recv_mc && !aligned16(u->recv_mc)) return IQ_ERR_ARG;
+  return IQ_OK;
+}
 
 static int check_tail(const iq_tail_args* t) {
   if (!t) return IQ_OK;
@@ -1283,7 +1580,11 @@ static int check_tail(const iq_tail_args* t) {
   if (!t->partial || !t->residual || !t->w_norm || !t->h_out || !t->norm_out) return IQ_ERR_ARG;
   if (t->kind == IQ_TAIL_ATTN && !t->w_first) return IQ_ERR_ARG;
   if (t->world < 1 || t->world > 8 || t->rank < 0 || t->rank >= t->world) return IQ_ERR_ARG;
-  if (t->world > 1) {
+  if (t->push) {
+    const int rc = check_push(t->push, t->m, t->h);
+    if (rc != IQ_OK) return rc;
+    if (t->push->world != t->world || t->push->rank != t->rank) return IQ_ERR_ARG;
+  } else if (t->world > 1) {
     if (!t->arrive || !t->epoch) return IQ_ERR_ARG;
     if (!t->arrive_mc && !t->peer_arrive) return IQ_ERR_ARG;
     if (!t->partial_mc && !t->peer_partials) return IQ_ERR_ARG;
@@ -1291,6 +1592,63 @@ static int check_tail(const iq_tail_args* t) {
   if (!aligned16(t->partial) || !aligned16(t->residual) || !aligned16(t->h_out) ||
       !aligned16(t->norm_out) || !aligned16(t->w_norm))
     return IQ_ERR_ARG;
+  return IQ_OK;
+}
+
+// The landing zone a launch uses: the caller's, or (no peers) the one inside the scratch.
+static int make_push_view(PushView& pv, const iq_push_args* u, void* scratch, size_t scratch_bytes,
+                          int h) {
+  if (u) {
+    pv.recv = u->recv;
+    pv.recv_mc = u->recv_mc;
+    pv.peer_recv = u->peer_recv;
+    pv.epoch = u->epoch;
+    pv.ticket = u->ticket;
+    pv.world = u->world;
+    pv.rank = u->rank;
+    pv.rows = u->rows;
+    pv.h = u->h;
+    return IQ_OK;
+  }
+  if (!scratch || scratch_bytes < kScrBytes || h > kZoneMaxH) return IQ_ERR_ARG;
+  uint8_t* b = static_cast<uint8_t*>(scratch);
+  pv.recv = reinterpret_cast<uint32_t*>(b + kScrZone);
+  pv.recv_mc = nullptr;
+  pv.peer_recv = nullptr;
+  pv.epoch = reinterpret_cast<uint32_t*>(b + kScrLaunchTag);
+  pv.ticket = reinterpret_cast<uint32_t*>(b + kScrTailTicket);
+  pv.world = 1;
+  pv.rank = 0;
+  pv.rows = kMaxRows;
+  pv.h = h;
+  return IQ_OK;
+}
+
+// How a fused tail runs, and through which zone: push when the tail names a zone or has
+// no peers, pull (last CTA) otherwise.
+struct TailPlan {
+  int tail_run = kTailNone, n_tail = 0, push = 0;
+  size_t smem = 0;      // what a tail CTA needs
+  PushView pv{};
+};
+static int plan_tail(TailPlan& tp, const iq_tail_args* tail, const iq_push_args* push_only,
+                     void* scratch, size_t scratch_bytes, int m, int h) {
+  if (tail && (tail->push || tail->world == 1)) {
+    const int rc = make_push_view(tp.pv, tail->push, scratch, scratch_bytes, h);
+    if (rc != IQ_OK) return rc;
+    tp.tail_run = kTailCtas;
+    tp.n_tail = m;
+    tp.push = 1;
+    tp.smem = tail_cta_smem(tp.pv.world, h);
+    if (tp.smem > static_cast<size_t>(kSmemLimit)) return IQ_ERR_UNSUPPORTED;
+  } else if (tail) {
+    tp.tail_run = kTailLastCta;
+  } else if (push_only) {
+    int rc = check_push(push_only, m, h);
+    if (rc == IQ_OK) rc = make_push_view(tp.pv, push_only, scratch, scratch_bytes, h);
+    if (rc != IQ_OK) return rc;
+    tp.push = 1;
+  }
   return IQ_OK;
 }
 
@@ -1309,11 +1667,14 @@ static int linear_launch(const iq_linear_args* a, void* stream) {
   sh.x_rows = split2 ? 2 * a->m : a->m;
   sh.x_pitch = a->k + 64;
   sh.x_blocks = (a->k + 127) / 128;
-  const size_t tail_bytes = a->tail ? static_cast<size_t>(a->tail->m) * a->tail->h * 2 : 0;
-  const size_t smem = plan_smem<G>(sh, tail_bytes);
+  TailPlan tp;
+  int rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->n);
+  if (rc != IQ_OK) return rc;
+  const int grid = sm_count();
+  const size_t smem = plan_smem<G>(sh, grid - tp.n_tail, tp.smem);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
-  const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->n, nullptr, 0);
-  if (mrc != IQ_OK) return mrc;
+  rc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->n, nullptr, 0);
+  if (rc != IQ_OK) return rc;
   p.x = a->x;
   p.x_scale = a->x_scale;
   p.x_kind = a->x_kind;
@@ -1324,12 +1685,15 @@ static int linear_launch(const iq_linear_args* a, void* stream) {
   p.w_scale = a->w_scale;
   p.out = static_cast<__nv_bfloat16*>(a->out);
   p.scratch = a->scratch;
-  p.has_tail = a->tail != nullptr;
+  p.tail_run = tp.tail_run;
+  p.n_tail = tp.n_tail;
+  p.push = tp.push;
+  p.pv = tp.pv;
   if (a->tail) {
     p.tail = *a->tail;
     if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
   }
-  return launch(linear_kernel<G>, p, sm_count(), smem, stream, a->pdl);
+  return launch(linear_kernel<G>, p, grid, smem, stream, a->pdl);
 }
 
 }  // namespace iqb
@@ -1357,9 +1721,17 @@ extern "C" int iq_tail(const iq_tail_args* a, void* stream, int pdl) {
   if (sm_count() == 0) return IQ_ERR_CUDA;
   TailParams p{};
   p.a = *a;
-  const size_t smem = 1024 + static_cast<size_t>(a->m) * a->h * 2;
-  if (smem > static_cast<size_t>(kSmemLimit)) return IQ_ERR_UNSUPPORTED;
-  return launch(tail_kernel, p, 1, smem, stream, pdl);
+  if (a->push) {
+    // rows pushed by an earlier iq_linear / iq_moe_down: one polling CTA per row
+    if (make_push_view(p.pv, a->push, nullptr, 0, a->h) != IQ_OK) return IQ_ERR_ARG;
+    p.push = 1;
+    p.n_tail = a->m;
+    const size_t smem = tail_cta_smem(p.pv.world, a->h);
+    if (smem > static_cast<size_t>(kSmemLimit)) return IQ_ERR_UNSUPPORTED;
+    return launch(tail_kernel, p, a->m, smem, stream, pdl);
+  }
+  // rows in `partial`: one CTA per row without peers, one CTA (one signal / wait) with
+  return launch(tail_kernel, p, a->world == 1 ? a->m : 1, 1024, stream, pdl);
 }
 
 extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
@@ -1408,7 +1780,9 @@ static int router_launch(const iq_router_args* a, void* stream) {
   sh.x_rows = a->m;
   sh.x_pitch = a->h * 2 + 64;
   sh.x_blocks = 1;
-  const size_t smem = plan_smem<G>(sh, 0);
+  const int grid = sm_count();
+  // the launch's last CTA selects; it keeps the rows' logits in shared memory
+  const size_t smem = plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->e, nullptr, 0);
   if (mrc != IQ_OK) return mrc;
@@ -1423,18 +1797,19 @@ static int router_launch(const iq_router_args* a, void* stream) {
   p.wt = a->wt;
   p.logits = a->logits;
   p.scratch = a->scratch;
-  return launch(router_kernel<G>, p, sm_count(), smem, stream, a->pdl);
+  return launch(router_kernel<G>, p, grid, smem, stream, a->pdl);
 }
 
 extern "C" int iq_router(const iq_router_args* a, void* stream) {
   if (!a || !a->x || !a->w || !a->sel || !a->wt || !a->logits || !a->scratch) return IQ_ERR_ARG;
-  if (a->scratch_bytes < kScrBasicBytes) return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBytes) return IQ_ERR_ARG;
   if (a->m < 1 || a->m > 8 || a->h < 512 || a->h % 512) return IQ_ERR_ARG;
-  if (a->e < 16 || a->e % 16 || a->e > 512 || a->top_k < 1 || a->top_k > 32 || a->top_k > a->e)
+  if (a->e < 16 || a->e % 16 || a->e > kMaxExperts || a->top_k < 1 || a->top_k > 32 ||
+      a->top_k > a->e)
     return IQ_ERR_ARG;
   if (a->score != IQ_ROUTE_SOFTMAX && a->score != IQ_ROUTE_SIGMOID) return IQ_ERR_ARG;
   if (!aligned16(a->x) || !aligned16(a->w)) return IQ_ERR_ARG;
-  if (sm_count() == 0) return IQ_ERR_CUDA;
+  if (sm_count() < 2) return IQ_ERR_CUDA;
   if ((a->h * 2) % 2048 == 0) return router_launch<Geo<1, 16, 2>>(a, stream);
   return router_launch<Geo<1, 16, 1>>(a, stream);
 }
@@ -1457,12 +1832,13 @@ static int fill_moe(MoeCommon& mc, int m, int h, int i_loc, int n_experts, int t
 }
 
 extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
-  if (!a || !a->x_fp8 || !a->fc || !a->fc_scale || !a->act || !a->scratch) return IQ_ERR_ARG;
+  if (!a || (!a->x_fp8 && !a->x_bf16) || !a->fc || !a->fc_scale || !a->act || !a->scratch)
+    return IQ_ERR_ARG;
   if (a->scratch_bytes < kScrBasicBytes) return IQ_ERR_ARG;
   if (a->n_shared > 0 && (!a->shared_fc || !a->shared_fc_scale)) return IQ_ERR_ARG;
   if (a->act_kind != IQ_ACT_E4M3 && a->act_kind != IQ_ACT_BF16) return IQ_ERR_ARG;
   if (a->h < 1024 || a->h % 1024 || a->i_loc < 64 || a->i_loc % 64) return IQ_ERR_ARG;
-  if (!aligned16(a->x_fp8) || !aligned16(a->fc)) return IQ_ERR_ARG;
+  if (!aligned16(a->x_fp8) || !aligned16(a->x_bf16) || !aligned16(a->fc)) return IQ_ERR_ARG;
   using G = Geo<2, 8, 2>;
   GateParams p{};
   int rc = fill_moe(p.mc, a->m, a->h, a->i_loc, a->n_experts, a->top_k, a->n_shared, a->sel,
@@ -1503,7 +1879,7 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
     sh.round_robin = 1;
   }
   p.early_shared = early ? 1 : 0;
-  const size_t smem = plan_smem<G>(sh, 0, a->m * a->top_k + a->n_shared);
+  const size_t smem = plan_smem<G>(sh, sm_count(), 0, a->m * a->top_k + a->n_shared);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->fc,
                                static_cast<long long>(a->n_experts) * 2 * a->i_loc, a->shared_fc,
@@ -1511,6 +1887,7 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   if (mrc != IQ_OK) return mrc;
   p.x_fp8 = static_cast<const uint8_t*>(a->x_fp8);
   p.x_scale = a->x_scale;
+  p.x_bf16 = static_cast<const __nv_bfloat16*>(a->x_bf16);
   p.act = a->act;
   p.act_kind = a->act_kind;
   p.scratch = a->scratch;
@@ -1541,8 +1918,11 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   sh.x_rows = a->m * (a->top_k + a->n_shared);
   sh.x_pitch = a->i_loc + 64;
   sh.x_blocks = (a->i_loc + 127) / 128;
-  const size_t tail_bytes = a->tail ? static_cast<size_t>(a->tail->m) * a->tail->h * 2 : 0;
-  const size_t smem = plan_smem<G>(sh, tail_bytes, a->m * a->top_k + a->n_shared);
+  TailPlan tp;
+  rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->h);
+  if (rc != IQ_OK) return rc;
+  const int grid = sm_count();
+  const size_t smem = plan_smem<G>(sh, grid - tp.n_tail, tp.smem, a->m * a->top_k + a->n_shared);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->proj,
                                static_cast<long long>(a->n_experts) * a->h, a->shared_proj,
@@ -1552,13 +1932,16 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   p.act_kind = a->act_kind;
   p.out = static_cast<__nv_bfloat16*>(a->out);
   p.scratch = a->scratch;
-  p.has_tail = a->tail != nullptr;
+  p.tail_run = tp.tail_run;
+  p.n_tail = tp.n_tail;
+  p.push = tp.push;
+  p.pv = tp.pv;
   p.pdl_level = a->pdl;
   if (a->tail) {
     p.tail = *a->tail;
     if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
   }
-  return launch(down_kernel<G>, p, sm_count(), smem, stream, a->pdl);
+  return launch(down_kernel<G>, p, grid, smem, stream, a->pdl);
 }
 
 extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
@@ -1589,274 +1972,6 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   return IQ_ERR_UNSUPPORTED;
 }
 
-namespace iqb {
-
-// ------------------------------------------------------------------------------------
-// iq_decode_layer: the four streams in one cooperative launch.
-static void shape_linear(StreamShape& sh, const iq_linear_args* a) {
-  const bool split2 = a->x_kind == IQ_X_BF16_SPLIT2;
-  sh.mode = kRowsPerGroup;
-  sh.n_groups = 1;
-  sh.rows_per_group = a->n;
-  sh.k_bytes = a->k;
-  sh.rg_shift = ilog2(a->rg);
-  sh.kg_shift = ilog2(a->kg);
-  sh.pair_half = 0;
-  sh.x_rows = split2 ? 2 * a->m : a->m;
-  sh.x_pitch = a->k + 64;
-  sh.x_blocks = (a->k + 127) / 128;
-}
-static void shape_router(StreamShape& sh, const iq_router_args* a) {
-  sh.whole_tiles = 1;
-  sh.mode = kRowsPerGroup;
-  sh.n_groups = 1;
-  sh.rows_per_group = a->e;
-  sh.k_bytes = a->h * 2;
-  sh.rg_shift = 7;
-  sh.kg_shift = 7;
-  sh.pair_half = 0;
-  sh.x_rows = a->m;
-  sh.x_pitch = a->h * 2 + 64;
-  sh.x_blocks = 1;
-}
-static void shape_gate(StreamShape& sh, const iq_moe_gate_args* a) {
-  sh.mode = kRowsPerGroup;
-  sh.n_groups = 1;
-  sh.rows_per_group = 2 * a->i_loc;
-  sh.k_bytes = a->h;
-  sh.rg_shift = 6;
-  sh.kg_shift = 7;
-  sh.pair_half = a->i_loc;
-  sh.x_rows = a->m;
-  sh.x_pitch = a->h + 64;
-  sh.x_blocks = a->h / 128;
-}
-static void shape_down(StreamShape& sh, const iq_moe_down_args* a) {
-  sh.mode = kConcatK;
-  sh.n_groups = 1;
-  sh.rows_per_group = a->h;
-  sh.k_bytes = a->i_loc;
-  sh.rg_shift = 7;
-  sh.kg_shift = 6;
-  sh.pair_half = 0;
-  sh.x_rows = a->m * (a->top_k + a->n_shared);
-  sh.x_pitch = a->i_loc + 64;
-  sh.x_blocks = (a->i_loc + 127) / 128;
-}
-
-template <class G>
-static int max_items_of(const StreamShape& sh, int max_groups) {
-  return max_items_any<G>(sh, max_groups);
-}
-
-static void fill_moe_gate(MoeCommon& mc, const iq_moe_gate_args* a) {
-  mc.w = static_cast<const uint8_t*>(a->fc);
-  mc.w_scale = a->fc_scale;
-  mc.shared_w = static_cast<const uint8_t*>(a->shared_fc);
-  mc.shared_scale = a->shared_fc_scale;
-  mc.w_stride = static_cast<size_t>(2) * a->i_loc * a->h;
-  mc.scale_stride = static_cast<size_t>(2 * a->i_loc / 64) * (a->h / 128);
-  mc.rows_per_expert = 2 * a->i_loc;
-}
-static void fill_moe_down(MoeCommon& mc, const iq_moe_down_args* a) {
-  mc.w = static_cast<const uint8_t*>(a->proj);
-  mc.w_scale = a->proj_scale;
-  mc.shared_w = static_cast<const uint8_t*>(a->shared_proj);
-  mc.shared_scale = a->shared_proj_scale;
-  mc.w_stride = static_cast<size_t>(a->h) * a->i_loc;
-  mc.scale_stride = static_cast<size_t>(a->h / 128) * (a->i_loc / 64);
-  mc.rows_per_expert = a->h;
-}
-
-template <class GO, class GD>
-static int layer_launch(const iq_decode_layer_args* a, void* stream, int pdl) {
-  using GR = Geo<1, 16, 2>;
-  using GG = Geo<2, 8, 2>;
-  const iq_linear_args& o = a->oproj;
-  const iq_router_args& r = a->router;
-  const iq_moe_gate_args& g = a->gate;
-  const iq_moe_down_args& d = a->down;
-  LayerParams p{};
-  shape_linear(p.sh_o, &o);
-  shape_router(p.sh_r, &r);
-  shape_gate(p.sh_g, &g);
-  shape_down(p.sh_d, &d);
-  const int max_groups = g.m * g.top_k + g.n_shared;
-  p.sh_o.max_items = max_items_of<GO>(p.sh_o, 1);
-  p.sh_r.max_items = max_items_of<GR>(p.sh_r, 1);
-  p.sh_g.max_items = max_items_of<GG>(p.sh_g, max_groups);
-  p.sh_d.max_items = max_items_of<GD>(p.sh_d, max_groups);
-  if (!p.sh_o.max_items || !p.sh_r.max_items || !p.sh_g.max_items || !p.sh_d.max_items)
-    return IQ_ERR_UNSUPPORTED;
-  // Shared memory: the fixed structures, then one scale table, one activation-scale table
-  // and one activation area, each sized for the stream that needs most, then the ring.
-  auto maxz = [](size_t x, size_t y) { return x > y ? x : y; };
-  size_t sc = static_cast<size_t>(p.sh_o.max_items) * GO::SCALES_PER_STAGE;
-  sc = maxz(sc, static_cast<size_t>(p.sh_g.max_items) * GG::SCALES_PER_STAGE);
-  sc = maxz(sc, static_cast<size_t>(p.sh_d.max_items) * GD::SCALES_PER_STAGE);
-  // Activation rows: o_proj's, then the router's with the Gate's beside them (both are
-  // written by the attention tail), then the Down's; each set overlays the one before.
-  const size_t xq_router = align_up(static_cast<size_t>(p.sh_r.x_rows) * p.sh_r.x_pitch, 16);
-  size_t xs = 0, xq = xq_router + static_cast<size_t>(p.sh_g.x_rows) * p.sh_g.x_pitch;
-  for (const StreamShape* sh : {&p.sh_o, &p.sh_g, &p.sh_d}) {
-    xs = maxz(xs, static_cast<size_t>(sh->x_rows) * sh->x_blocks);
-    xq = maxz(xq, static_cast<size_t>(sh->x_rows) * sh->x_pitch);
-  }
-  size_t off = align_up(sizeof(StreamSmem<GO>), 16);
-  p.off_extra = static_cast<uint32_t>(off);
-  off += align_up(sizeof(LayerSmemExtra), 16);
-  p.off_sc = static_cast<uint32_t>(off);
-  off += align_up(sizeof(float) * sc, 16);
-  p.off_xs = static_cast<uint32_t>(off);
-  off += align_up(sizeof(float) * xs, 16);
-  p.off_xq = static_cast<uint32_t>(off);
-  p.off_xq_gate = static_cast<uint32_t>(off + xq_router);
-  off += align_up(xq, 16);
-  off = align_up(off, 128);
-  p.off_ring = static_cast<uint32_t>(off);
-  int slot_bytes = GO::STAGE_BYTES;
-  for (int b : {GR::STAGE_BYTES, GG::STAGE_BYTES, GD::STAGE_BYTES})
-    if (b > slot_bytes) slot_bytes = b;
-  p.slot_bytes = slot_bytes;
-  int slots = static_cast<int>((static_cast<size_t>(kSmemLimit) - off) / slot_bytes);
-  if (off + 2 * static_cast<size_t>(slot_bytes) > static_cast<size_t>(kSmemLimit)) return IQ_ERR_UNSUPPORTED;
-  const int want = (160 * 1024 + slot_bytes - 1) / slot_bytes;
-  if (slots > want) slots = want;
-  if (slots > kMaxStages) slots = kMaxStages;
-  p.sh_o.n_stages = p.sh_r.n_stages = p.sh_g.n_stages = p.sh_d.n_stages = slots;
-  const size_t smem = off + static_cast<size_t>(slots) * slot_bytes;
-
-  CUtensorMap unused;
-  int rc = fill_maps<GO>(&p.map_o, &unused, p.sh_o, o.w, o.n, nullptr, 0);
-  if (rc == IQ_OK) rc = fill_maps<GR>(&p.map_r, &unused, p.sh_r, r.w, r.e, nullptr, 0);
-  if (rc == IQ_OK)
-    rc = fill_maps<GG>(&p.map_g0, &p.map_g1, p.sh_g, g.fc,
-                       static_cast<long long>(g.n_experts) * 2 * g.i_loc, g.shared_fc,
-                       static_cast<long long>(g.n_shared) * 2 * g.i_loc);
-  if (rc == IQ_OK)
-    rc = fill_maps<GD>(&p.map_d0, &p.map_d1, p.sh_d, d.proj,
-                       static_cast<long long>(d.n_experts) * d.h, d.shared_proj,
-                       static_cast<long long>(d.n_shared) * d.h);
-  if (rc != IQ_OK) return rc;
-
-  p.x = o.x;
-  p.x_scale = o.x_scale;
-  p.x_kind = o.x_kind;
-  p.m = o.m;
-  p.k_o = o.k;
-  p.h = o.n;
-  p.w_o = static_cast<const uint8_t*>(o.w);
-  p.w_o_scale = o.w_scale;
-  p.out_o = static_cast<__nv_bfloat16*>(o.out);
-  p.tail_a = *o.tail;
-  p.w_r = static_cast<const uint8_t*>(r.w);
-  p.e = r.e;
-  p.top_k = r.top_k;
-  p.score = r.score;
-  p.sel = r.sel;
-  p.wt = r.wt;
-  p.logits = r.logits;
-  rc = fill_moe(p.mc_g, g.m, g.h, g.i_loc, g.n_experts, g.top_k, g.n_shared, g.sel, nullptr);
-  if (rc == IQ_OK)
-    rc = fill_moe(p.mc_d, d.m, d.h, d.i_loc, d.n_experts, d.top_k, d.n_shared, d.sel, d.wt);
-  if (rc != IQ_OK) return rc;
-  fill_moe_gate(p.mc_g, &g);
-  fill_moe_down(p.mc_d, &d);
-  p.act = g.act;
-  p.act_kind = g.act_kind;
-  p.out_d = static_cast<__nv_bfloat16*>(d.out);
-  p.tail_m = *d.tail;
-  p.scratch = o.scratch;
-  int* status = scratch_of(o.scratch).status;
-  if (!p.tail_a.status) p.tail_a.status = status;
-  if (!p.tail_m.status) p.tail_m.status = status;
-  unsigned peer_ms = p.tail_a.timeout_ms ? p.tail_a.timeout_ms : 2000u;
-  const unsigned peer_ms_m = p.tail_m.timeout_ms ? p.tail_m.timeout_ms : 2000u;
-  if (peer_ms_m > peer_ms) peer_ms = peer_ms_m;
-  p.wait_ms = peer_ms + 500u;
-
-  auto kernel = layer_kernel<GO, GD>;
-  if (!ensure_smem_optin(reinterpret_cast<const void*>(kernel))) return IQ_ERR_CUDA;
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) != cudaSuccess ||
-      per_sm < 1) {
-    fprintf(stderr, "iqb200: iq_decode_layer needs one resident CTA per SM (%zu B shared)\n", smem);
-    return IQ_ERR_UNSUPPORTED;
-  }
-  return launch(kernel, p, sm_count(), smem, stream, pdl, true);
-}
-
-}  // namespace iqb
-
-using namespace iqb;
-
-extern "C" int iq_decode_layer(const iq_decode_layer_args* a, void* stream, int pdl) {
-  if (!a) return IQ_ERR_ARG;
-  const iq_linear_args& o = a->oproj;
-  const iq_router_args& r = a->router;
-  const iq_moe_gate_args& g = a->gate;
-  const iq_moe_down_args& d = a->down;
-  // ---- each part as its own entry point would check it
-  if (!o.x || !o.w || !o.w_scale || !o.out || !o.scratch || !o.tail || !d.tail) return IQ_ERR_ARG;
-  if (o.scratch_bytes < kScrBytes) return IQ_ERR_ARG;
-  if (r.scratch != o.scratch || g.scratch != o.scratch || d.scratch != o.scratch) return IQ_ERR_ARG;
-  if (o.x_kind < IQ_X_BF16_GROUPQ || o.x_kind > IQ_X_E4M3_UNSCALED) return IQ_ERR_ARG;
-  if (o.x_kind == IQ_X_E4M3_GROUP && !o.x_scale) return IQ_ERR_ARG;
-  const int max_m = o.x_kind == IQ_X_BF16_SPLIT2 ? 4 : 8;
-  if (o.m < 1 || o.m > max_m) return IQ_ERR_ARG;
-  if ((o.rg != 64 && o.rg != 128) || (o.kg != 64 && o.kg != 128)) return IQ_ERR_ARG;
-  if (o.k < 1024 || o.k % 1024 || o.n < 1024 || o.n % 1024) return IQ_ERR_UNSUPPORTED;
-  if (!aligned16(o.x) || !aligned16(o.w) || !aligned16(o.out)) return IQ_ERR_ARG;
-  if (!r.x || !r.w || !r.sel || !r.wt || !r.logits) return IQ_ERR_ARG;
-  if (r.e < 16 || r.e % 16 || r.e > 512 || r.top_k < 1 || r.top_k > 32 || r.top_k > r.e)
-    return IQ_ERR_ARG;
-  if (r.score != IQ_ROUTE_SOFTMAX && r.score != IQ_ROUTE_SIGMOID) return IQ_ERR_ARG;
-  if (!aligned16(r.x) || !aligned16(r.w)) return IQ_ERR_ARG;
-  if (!g.x_fp8 || !g.fc || !g.fc_scale || !g.act || !g.sel) return IQ_ERR_ARG;
-  if (g.n_shared > 0 && (!g.shared_fc || !g.shared_fc_scale)) return IQ_ERR_ARG;
-  if (g.act_kind != IQ_ACT_E4M3 && g.act_kind != IQ_ACT_BF16) return IQ_ERR_ARG;
-  if (!aligned16(g.x_fp8) || !aligned16(g.fc)) return IQ_ERR_ARG;
-  if (!d.act || !d.proj || !d.proj_scale || !d.out || !d.wt || !d.sel) return IQ_ERR_ARG;
-  if (d.n_shared > 0 && (!d.shared_proj || !d.shared_proj_scale)) return IQ_ERR_ARG;
-  if (!aligned16(d.act) || !aligned16(d.proj) || !aligned16(d.out)) return IQ_ERR_ARG;
-  // ---- the four parts describe one layer
-  const int m = o.m, h = o.n;
-  if (r.m != m || g.m != m || d.m != m) return IQ_ERR_ARG;
-  if (r.h != h || g.h != h || d.h != h) return IQ_ERR_ARG;
-  if (g.i_loc != d.i_loc || g.top_k != d.top_k || g.n_shared != d.n_shared ||
-      g.n_experts != d.n_experts || g.act_kind != d.act_kind)
-    return IQ_ERR_ARG;
-  if (r.top_k != g.top_k || r.e != g.n_experts) return IQ_ERR_ARG;
-  // ---- what one part writes is what the next one reads
-  if (r.x != o.tail->norm_out || g.x_fp8 != o.tail->norm_fp8 || g.x_scale != o.tail->norm_fp8_scale)
-    return IQ_ERR_ARG;
-  if (g.sel != r.sel || d.sel != r.sel || d.wt != r.wt || d.act != g.act) return IQ_ERR_ARG;
-  if (g.i_loc < 256 || g.i_loc % 256) return IQ_ERR_UNSUPPORTED;
-  int rc = check_tail(o.tail);
-  if (rc == IQ_OK) rc = check_tail(d.tail);
-  if (rc != IQ_OK) return rc;
-  if (o.tail->kind != IQ_TAIL_ATTN || d.tail->kind != IQ_TAIL_MLP) return IQ_ERR_ARG;
-  if (o.tail->partial != o.out || o.tail->m != m || o.tail->h != h) return IQ_ERR_ARG;
-  if (d.tail->partial != d.out || d.tail->m != m || d.tail->h != h) return IQ_ERR_ARG;
-  if (h > kLayerMaxH) return IQ_ERR_UNSUPPORTED;
-  if (o.tail->timeout_ms > 3000u || d.tail->timeout_ms > 3000u) return IQ_ERR_ARG;
-  if (sm_count() == 0) return IQ_ERR_CUDA;
-  const bool o2 = o.k % 2048 == 0;
-  const int i = g.i_loc;
-  using Geo2048 = Geo<1, 16, 2>;
-  using Geo1024 = Geo<1, 16, 1>;
-  using Geo512 = Geo<2, 8, 1>;
-  using Geo256 = Geo<4, 4, 1>;
-#define IQ_LAYER_DISPATCH(GD)                                                   \
-  return o2 ? layer_launch<Geo<1, 16, 2>, GD>(a, stream, pdl)                   \
-            : layer_launch<Geo<1, 16, 1>, GD>(a, stream, pdl)
-  if (i % 2048 == 0) { IQ_LAYER_DISPATCH(Geo2048); }
-  if (i % 1024 == 0) { IQ_LAYER_DISPATCH(Geo1024); }
-  if (i % 512 == 0) { IQ_LAYER_DISPATCH(Geo512); }
-  IQ_LAYER_DISPATCH(Geo256);
-#undef IQ_LAYER_DISPATCH
-}
-
 // ------------------------------------------------------------------------------------
 // iq_linear_static: iq_linear for callers that cannot obtain device memory.
 //
@@ -1874,7 +1989,27 @@ extern "C" int iq_decode_layer(const iq_decode_layer_args* a, void* stream, int 
 constexpr int kStaticMaxN = 65536;   // largest output width served from the static area
 constexpr int kStaticMaxK = 65536;   // largest contraction length
 static __device__ __align__(256) uint8_t g_static_scratch[kScrBasicBytes];
-static void* g_static_ptr[64] = {};
+static void* g_static_ptr[64] = {};   // per device, guarded by g_host_mutex
+
+// The array's device address on the current device; looked up on the first call.
+static int static_scratch_ptr(void** out, bool resolve) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return IQ_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
+  if (!g_static_ptr[dev] && resolve) {
+    // First call on this device: resolve the array's device address.  Do this before any
+    // stream capture begins.
+    void* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess || !ptr) {
+      fprintf(stderr, "iqb200: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(err));
+      return IQ_ERR_CUDA;
+    }
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return IQ_OK;
+}
 
 extern "C" int iq_linear_static(const iq_linear_args* a, void* stream) {
   if (!a) return IQ_ERR_ARG;
@@ -1889,27 +2024,31 @@ extern "C" int iq_linear_static(const iq_linear_args* a, void* stream) {
             kStaticMaxN, kStaticMaxK, a->n, a->k);
     return IQ_ERR_UNSUPPORTED;
   }
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return IQ_ERR_CUDA;
-  if (!g_static_ptr[dev]) {
-    // First call on this device: resolve the array's device address.  Do this before any
-    // stream capture begins.
-    void* ptr = nullptr;
-    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
-    if (err != cudaSuccess || !ptr) {
-      fprintf(stderr, "iqb200: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(err));
-      return IQ_ERR_CUDA;
-    }
-    g_static_ptr[dev] = ptr;
-  }
+  void* base = nullptr;
+  const int prc = static_scratch_ptr(&base, true);
+  if (prc != IQ_OK) return prc;
   // The array keeps whatever the last call left.  The kernel expects the status word,
   // the ticket and the tile counters at zero; the partial-sum area is written before it
   // is read and needs no clearing.
-  if (cudaMemsetAsync(g_static_ptr[dev], 0, kScrPartials, static_cast<cudaStream_t>(stream)) !=
-      cudaSuccess)
+  if (cudaMemsetAsync(base, 0, kScrPartials, static_cast<cudaStream_t>(stream)) != cudaSuccess)
     return IQ_ERR_CUDA;
   iq_linear_args b = *a;
-  b.scratch = g_static_ptr[dev];
+  b.scratch = base;
   b.scratch_bytes = kScrBasicBytes;
+  b.push = nullptr;
   return iq_linear(&b, stream);
+}
+
+extern "C" int iq_linear_static_status(int* code, void* stream) {
+  if (!code) return IQ_ERR_ARG;
+  void* base = nullptr;
+  const int prc = static_scratch_ptr(&base, false);
+  if (prc != IQ_OK) return prc;
+  *code = 0;
+  if (!base) return IQ_OK;              // no call has been made on this device yet
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(code, base, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return IQ_ERR_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return IQ_ERR_CUDA;
+  return IQ_OK;
 }

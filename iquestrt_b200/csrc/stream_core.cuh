@@ -19,8 +19,7 @@
 // A tile whose stages fall in more than one CTA is finished by whichever contributor
 // arrives last at the tile's counter: it sums the contributors' fp32 partials from scratch
 // in CTA order, so the result does not depend on arrival order, and nothing waits on
-// another CTA.  (`epilogue_resident`, for cooperative launches only, lets the owner of the
-// tile's last stage poll the others' tagged partials instead.)
+// another CTA.
 //
 // The per-stage consumer path is kept to a few dozen instructions: everything that
 // depends only on the tile or the weight group is hoisted out of the stage loop, and the
@@ -332,14 +331,17 @@ struct RedPos {
 };
 
 // ------------------------------------------------------------------------------------
-// Producer: one elected lane of one warp, one or two copies per stage.  `map0/map1` are the
+// Producer: one elected lane of one warp, one or two copies per stage.  `dep_wait`: the
+// consumers of this stream do not start before the kernel's dependency wait (pass false
+// for a stream that is consumed ahead of that wait).  `map0/map1` are the
 // launch's tensor maps (u32 elements, box = KC bytes x box rows), used when a stage is a
 // K-slice of its rows; whole-row stages are contiguous and use the untiled copy.
 template <class G, class S>
 __device__ __forceinline__ void produce(const StreamShape& sh, S* sm, const GroupDesc* groups,
                                         uint8_t* ring, int slot_bytes, const CtaWork& w,
                                         int* status, const CUtensorMap* map0,
-                                        const CUtensorMap* map1, RingPos& pos) {
+                                        const CUtensorMap* map1, RingPos& pos,
+                                        bool dep_wait = true) {
   const int lane = threadIdx.x & 31;
   int slot = pos.slot;
   uint32_t phase = pos.phase;
@@ -357,10 +359,15 @@ __device__ __forceinline__ void produce(const StreamShape& sh, S* sm, const Grou
     const TileVisit tv = walk.visit(w, k);
     StagePos p = stage_pos(sh, w, tv.tile, tv.s_begin);
     for (int s = tv.s_begin; s < tv.s_end; ++s) {
-      if (!mbar_wait(&sm->empty[slot], phase ^ 1u, &sm->abort_flag)) {
-        if (!sm->abort_flag) set_status(status, IQ_ERR_PIPE_TIMEOUT);
-        sm->abort_flag = 1;
-        return;
+      if (!mbar_try_wait(&sm->empty[slot], phase ^ 1u)) {
+        // The ring is full.  When the consumers may still be held at their dependency
+        // wait, join that (untimed) wait first: only then does the pipeline budget apply.
+        if (dep_wait) pdl_wait();
+        if (!mbar_wait(&sm->empty[slot], phase ^ 1u, &sm->abort_flag)) {
+          if (!sm->abort_flag) set_status(status, IQ_ERR_PIPE_TIMEOUT);
+          sm->abort_flag = 1;
+          return;
+        }
       }
       if (lane == 0) {
         const GroupDesc& gd = groups[p.group];
@@ -397,9 +404,9 @@ __device__ __forceinline__ void produce(const StreamShape& sh, S* sm, const Grou
 template <class G>
 __device__ __forceinline__ void produce(const StreamShape& sh, StreamSmem<G>* sm, uint8_t* ring,
                                         const CtaWork& w, int* status, const CUtensorMap* map0,
-                                        const CUtensorMap* map1) {
+                                        const CUtensorMap* map1, bool dep_wait = true) {
   RingPos pos;
-  produce<G>(sh, sm, sm->groups, ring, G::STAGE_BYTES, w, status, map0, map1, pos);
+  produce<G>(sh, sm, sm->groups, ring, G::STAGE_BYTES, w, status, map0, map1, pos, dep_wait);
 }
 
 // The element type of the streamed matrix decides the MMA; everything else is bytes.
@@ -647,13 +654,33 @@ __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm
 }
 
 // The epilogue warp: for every tile of the CTA, in order, folds the consumers' fragments
-// and hands the finished values to `emit(tile_id, r, col, val)`: lane l is called four
-// times per tile, with (r, col) = ((l + 32 j) >> 3, (l + 32 j) & 7), val[sub] = the sum for
-// weight row 16*sub + r of the tile and MMA column col.  A tile whose stages are split
-// between CTAs goes through the scratch: every contributor publishes its fp32 partial,
-// and the last one to arrive at the tile's counter sums them in CTA order and emits.  In
-// kConcatK mode `tile_id.group` is 0.
-template <class G, class S, class Emit>
+// and hands the finished values to `emit`.  Two lane layouts:
+//   kVec == false: `emit(tile_id, r, col, val)` is called four times per tile and lane,
+//     with (r, col) = ((l + 32 j) >> 3, (l + 32 j) & 7) and val[sub] = the sum for weight
+//     row 16*sub + r of the tile and MMA column col (a quarter-warp covers one row's eight
+//     columns: the layout for kernels that combine columns or sub-tiles);
+//   kVec == true: `emit(tile_id, r0, col, val)` is called once per tile and lane with
+//     col = l >> 2, r0 = 4 * (l & 3) and val[j][sub] = the sum for weight row
+//     16*sub + r0 + j: four consecutive output features of one activation row per lane,
+//     so a row-major result leaves as 8- or 16-byte stores.
+// A tile whose stages are split between CTAs goes through the scratch: every contributor
+// publishes its fp32 partial, and the last one to arrive at the tile's counter sums them
+// in CTA order and emits.  In kConcatK mode `tile_id.group` is 0.
+template <bool kVec>
+__device__ __forceinline__ int epilogue_index(int lane, int j) {
+  return kVec ? (((lane & 3) * 4 + j) << 3) + (lane >> 2) : lane + 32 * j;   // r * 8 + col
+}
+template <class G, bool kVec, class Emit>
+__device__ __forceinline__ void epilogue_emit(Emit& emit, const TileId& id, int lane,
+                                              const float (&val)[4][G::RT]) {
+  if constexpr (kVec) {
+    emit(id, (lane & 3) * 4, lane >> 2, val);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) emit(id, (lane + 32 * j) >> 3, (lane + 32 * j) & 7, val[j]);
+  }
+}
+template <class G, bool kVec, class S, class Emit>
 __device__ __forceinline__ void epilogue(const StreamShape& sh, S* sm, const CtaWork& w,
                                          long long total, int grid, int cta,
                                          const StreamScratch& scr, RedPos& rpos, Emit emit) {
@@ -680,7 +707,7 @@ __device__ __forceinline__ void epilogue(const StreamShape& sh, S* sm, const Cta
     float val[4][G::RT];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int idx = lane + 32 * j, r = idx >> 3, col = idx & 7;
+      const int idx = epilogue_index<kVec>(lane, j), r = idx >> 3, col = idx & 7;
       const int fl = 4 * (r & 7) + (col >> 1), fi = (r >> 3) * 2 + (col & 1);
 #pragma unroll
       for (int sub = 0; sub < G::RT; ++sub) {
@@ -694,8 +721,7 @@ __device__ __forceinline__ void epilogue(const StreamShape& sh, S* sm, const Cta
     if (lane == 0) mbar_arrive(&sm->red_empty[red_buf]);   // the consumers may reuse red[i]
     if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
     if (whole) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) emit(id, (lane + 32 * j) >> 3, (lane + 32 * j) & 7, val[j]);
+      epilogue_emit<G, kVec>(emit, id, lane, val);
     } else {
       const int pslot = (tile == w.tile0) ? 0 : 1;
       float* mine = scr.partials + (static_cast<size_t>(cta) * 2 + pslot) * (G::ROWS * 8);
@@ -733,133 +759,19 @@ __device__ __forceinline__ void epilogue(const StreamShape& sh, S* sm, const Cta
             for (int sub = 0; sub < G::RT; ++sub)
               val[j][sub] += __ldcg(pp + sub * 128 + lane + 32 * j);
         }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) emit(id, (lane + 32 * j) >> 3, (lane + 32 * j) & 7, val[j]);
+        epilogue_emit<G, kVec>(emit, id, lane, val);
       }
     }
   }
   rpos.buf = red_buf;
   rpos.phase = red_phase;
 }
-template <class G, class Emit>
+template <class G, bool kVec, class Emit>
 __device__ __forceinline__ void epilogue(const StreamShape& sh, StreamSmem<G>* sm,
                                          const CtaWork& w, long long total, int grid, int cta,
                                          const StreamScratch& scr, Emit emit) {
   RedPos rpos;
-  epilogue<G>(sh, sm, w, total, grid, cta, scr, rpos, emit);
-}
-
-// The epilogue warp of a launch whose CTAs are all resident together (a cooperative launch).
-// Same results as `epilogue`, summed in the same order, but a tile split between CTAs is
-// settled with no fence and no atomic: the CTAs that own its earlier stages store their
-// fp32 partials as tagged 64-bit words (value, tag of this launch) and move on; the CTA
-// that owns its LAST stage reads those words, retrying until each carries this launch's
-// tag, adds its own partial and emits.  The earlier owners visit the tile first and
-// publish without ever waiting, so the reads normally succeed at once.  `parts` holds
-// [grid][2][ROWS*8] such words; a word is valid when its upper half equals `tag`.
-template <class G, class S, class Emit>
-__device__ __forceinline__ void epilogue_resident(const StreamShape& sh, S* sm, const CtaWork& w,
-                                                  long long total, int grid, int cta,
-                                                  const StreamScratch& scr, uint64_t* parts,
-                                                  uint32_t tag, RedPos& rpos, Emit emit) {
-  const int lane = threadIdx.x & 31;
-  const bool concat = sh.mode != kRowsPerGroup;
-  int red_buf = rpos.buf;
-  uint32_t red_phase = rpos.phase;
-  TileWalk walk;
-  walk.init(w);
-  for (int k = 0; k < walk.n_tiles; ++k) {
-    const TileVisit tv = walk.visit(w, k);
-    const int tile = tv.tile;
-    const bool whole = tv.s_begin == 0 && tv.s_end == w.spt;
-    TileId id;
-    id.tile = tile;
-    id.group = concat ? 0 : tile / w.tpg;
-    id.tig = concat ? tile : tile - id.group * w.tpg;
-    if (!mbar_wait(&sm->red_full[red_buf], red_phase, &sm->abort_flag)) {
-      if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
-      sm->abort_flag = 1;
-      return;
-    }
-    const float(*red)[32][4] = sm->red[red_buf];
-    float val[4][G::RT];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int idx = lane + 32 * j, r = idx >> 3, col = idx & 7;
-      const int fl = 4 * (r & 7) + (col >> 1), fi = (r >> 3) * 2 + (col & 1);
-#pragma unroll
-      for (int sub = 0; sub < G::RT; ++sub) {
-        float v = 0.f;
-#pragma unroll
-        for (int q = 0; q < G::KW; ++q) v += red[sub * G::KW + q][fl][fi];
-        val[j][sub] = v;
-      }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&sm->red_empty[red_buf]);   // the consumers may reuse red[i]
-    if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
-    if (!whole) {
-      const long long tile_first = static_cast<long long>(tile) * w.spt;
-      const int c_first = item_owner(total, grid, tile_first);
-      const int c_last = item_owner(total, grid, tile_first + w.spt - 1);
-      if (cta != c_last) {
-        const int pslot = (tile == w.tile0) ? 0 : 1;
-        uint64_t* mine = parts + (static_cast<size_t>(cta) * 2 + pslot) * (G::ROWS * 8);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-          for (int sub = 0; sub < G::RT; ++sub)
-            st_relaxed_gpu_u64(mine + sub * 128 + lane + 32 * j,
-                               (static_cast<uint64_t>(tag) << 32) | __float_as_uint(val[j][sub]));
-        continue;
-      }
-      float own[4][G::RT];
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int sub = 0; sub < G::RT; ++sub) { own[j][sub] = val[j][sub]; val[j][sub] = 0.f; }
-      for (int cc = c_first; cc < c_last; ++cc) {
-        const int ft = static_cast<int>(item_begin(total, grid, cc) / w.spt);
-        const uint64_t* pp =
-            parts + (static_cast<size_t>(cc) * 2 + (tile == ft ? 0 : 1)) * (G::ROWS * 8);
-        uint64_t got[4][G::RT];
-        uint64_t t0 = 0;
-        for (uint32_t spin = 0;; ++spin) {
-          bool ok = true;
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-#pragma unroll
-            for (int sub = 0; sub < G::RT; ++sub) {
-              got[j][sub] = ld_relaxed_gpu_u64(pp + sub * 128 + lane + 32 * j);
-              ok = ok && static_cast<uint32_t>(got[j][sub] >> 32) == tag;
-            }
-          if (__all_sync(0xffffffffu, ok)) break;
-          if ((spin & 63u) == 63u) {
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            if (sm->abort_flag || now - t0 > kPipeBudgetNs) {
-              if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
-              sm->abort_flag = 1;
-              return;
-            }
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-          for (int sub = 0; sub < G::RT; ++sub)
-            val[j][sub] += __uint_as_float(static_cast<uint32_t>(got[j][sub]));
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int sub = 0; sub < G::RT; ++sub) val[j][sub] += own[j][sub];
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) emit(id, (lane + 32 * j) >> 3, (lane + 32 * j) & 7, val[j]);
-  }
-  rpos.buf = red_buf;
-  rpos.phase = red_phase;
+  epilogue<G, kVec>(sh, sm, w, total, grid, cta, scr, rpos, emit);
 }
 
 // After the CTA's last emit: returns true on the one CTA that arrives last, on every one of

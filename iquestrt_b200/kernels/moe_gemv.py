@@ -3,7 +3,7 @@ MoeDecodeKernels, iquestrt/kernels/moe_gemv.py:8-61)."""
 
 import torch
 
-from .. import ops
+from .. import ops, parallel
 
 ROW_BM = 16
 
@@ -60,13 +60,14 @@ class MoeDecodeKernels:
         return out
 
     def __call__(self, sel, wt, fc, fc_scale, proj, proj_scale, *, rows=None, x_scale=None,
-                 shared=None, tail=None, out=None, pdl=False):
+                 shared=None, tail=None, push=None, out=None, pdl=False):
         """Routed pairs `sel`/`wt` [Q*topk] -> [rows, H] bf16, unreduced across ranks.
 
         `x_pad_fp8` (and `x_scale`, when the activations carry 1x128 group scales) were
         written by the attention tail; `sel` is int32, ascending by expert id within each
         row.  `shared = (fc, fc_scale, proj, proj_scale)` of the shared experts.  `tail`
-        runs the MLP all-reduce epilogue inside the Down launch."""
+        runs the MLP all-reduce epilogue inside the Down launch; `push` (the output's
+        symmetric slot) only sends the rows, for a tail launched separately."""
         rows = self.q_len if rows is None else rows
         if not 1 <= rows <= self.q_len:
             raise ValueError(f"rows must be in 1..{self.q_len}, got {rows}")
@@ -74,6 +75,8 @@ class MoeDecodeKernels:
             raise ValueError("shared expert weights do not match n_shared")
         if out is None:
             out = self.next_out()
+        if tail is None and push is None:
+            push = parallel.slot_of(out)        # the slot's only reader is its all-reduce tail
         sfc = sfs = spj = sps = None
         if shared is not None:
             sfc, sfs, spj, sps = shared
@@ -82,4 +85,4 @@ class MoeDecodeKernels:
                      shared_fc_scale=sfs, pdl=pdl)
         return ops.moe_down(self.act, sel, wt, proj, proj_scale, out, m=rows, top_k=self.topk,
                             scratch=self.scratch, shared_proj=spj, shared_proj_scale=sps,
-                            tail=tail, pdl=pdl)
+                            tail=tail, push=push, pdl=pdl)

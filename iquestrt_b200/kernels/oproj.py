@@ -2,7 +2,7 @@
 
 import torch
 
-from .. import ops
+from .. import ops, parallel
 
 BM = 16   # rows of the symmetric output slots (the reference pads its MMA M to 16)
 
@@ -46,33 +46,39 @@ class OProjGemv:
         self._next_output = (self._next_output + 1) % len(self.outputs)
         return out
 
-    def __call__(self, ao, w_o, w_scale, *, out=None, tail=None, pdl=False):
+    def __call__(self, ao, w_o, w_scale, *, out=None, tail=None, push=None, pdl=False):
         """ao [Q, q_dim] bf16 contiguous, w_o [hidden, q_dim] e4m3 with its rank-local
-        [hidden/128, q_dim/128] scales -> [Q, hidden] bf16 (unreduced across ranks)."""
+        [hidden/128, q_dim/128] scales -> [Q, hidden] bf16 (unreduced across ranks).
+        `push` (the output's symmetric slot) also sends the rows to every rank's landing
+        zone, for an all-reduce tail launched separately."""
         if out is None:
             out = self.next_out()
+        if tail is None and push is None:
+            push = parallel.slot_of(out)        # the slot's only reader is its all-reduce tail
         view = out[:self.q_len]
         ops.linear(ao.reshape(self.q_len, self.q_dim), w_o, w_scale, scratch=self.scratch,
-                   out=view, x_kind=self.x_kind, tail=tail, pdl=pdl)
+                   out=view, x_kind=self.x_kind, tail=tail, push=push, pdl=pdl)
         return view
 
 
 class DenseMlp:
     """Dense SwiGLU MLP: block-FP8 Gate/Up + SiLU, block-FP8 Down into `out` (the
-    reference's layer-0 MLP; the benchmark configuration's shared expert has the same
-    form).  Runs on the grouped-expert kernels with the dense weights as one group."""
+    reference's layer-0 MLP, iquestrt/kernels/oproj.py:174-197; the benchmark
+    configuration's shared expert has the same form).  Runs on the grouped-expert kernels
+    with the dense weights as one group."""
 
     def __init__(self, hidden: int, inter: int, *, ws, q_len: int, scratch=None):
         if not 1 <= q_len <= 8:
             raise ValueError(f"the dense MLP covers 1..8 rows, got {q_len}")
+        if hidden % 1024 or inter % 128:
+            raise ValueError(f"unsupported dense MLP shape H={hidden}, I={inter}")
         self.q_len, self.inter, self.hidden = q_len, inter, hidden
-        self.x_fp8 = ws.slot(("dense", "x_fp8"), (q_len, hidden), torch.float8_e4m3fn)
-        self.x_scale = ws.slot(("dense", "x_scale"), (q_len, hidden // 128), torch.float32)
         self.act = ws.slot(("dense", "act"), (q_len, inter), torch.bfloat16)
         self.sel = ws.slot(("dense", "sel"), (q_len,), torch.int32)
         self.wt = ws.slot(("dense", "wt"), (q_len,), torch.float32)
         self.wt.fill_(1.0)
         self._scratch = scratch
+        self._tables: dict[tuple[int, int], torch.Tensor] = {}
 
     @property
     def scratch(self):
@@ -80,14 +86,31 @@ class DenseMlp:
             self._scratch = ops.default_scratch(self.act.device)
         return self._scratch
 
-    def __call__(self, x_fp8, x_scale, w_gate_up, gate_up_scale, w_down, down_scale, out, *,
+    def _grain64(self, table: torch.Tensor, dim: int, blocks: int) -> torch.Tensor:
+        """The kernels read expert-style tables (one entry per 64 rows of gate/up, per 64
+        columns of down).  A checkpoint-grain table (one entry per 128) is widened once per
+        weight and kept, so that calls inside a captured graph allocate nothing."""
+        if table.shape[dim] == 2 * blocks:
+            return table
+        if table.shape[dim] != blocks:
+            raise ValueError(f"scale table {tuple(table.shape)} does not tile the dense weight")
+        key = (table.data_ptr(), dim)
+        if key not in self._tables:
+            self._tables[key] = table.repeat_interleave(2, dim).contiguous()
+        return self._tables[key]
+
+    def __call__(self, hn, w_gate_up, gate_up_scale, w_down, down_scale, out, *, x_scale=None,
                  tail=None, pdl=False):
-        """`x_fp8 [Q, hidden]` e4m3 with `x_scale [Q, hidden/128]` (or None) -> out[:Q]
-        bf16, the rank's partial Down output.  Scale tables at grain (64, 128) for
-        gate/up and (128, 64) for down, like the expert banks."""
+        """`hn [Q, hidden]` bf16 (quantised per 1x128 group inside the Gate kernel) -> out[:Q]
+        bf16, the rank's partial Down output.  `w_gate_up [2I, hidden]` and `w_down
+        [hidden, I]` are e4m3 with fp32 scale tables at the checkpoint's 128 grain or at
+        the expert kernels' 64 grain.  An `hn` that is already e4m3 is used as is, with
+        `x_scale [Q, hidden/128]` (or unscaled when that is None)."""
         q = self.q_len
-        ops.moe_gate(x_fp8, self.sel, w_gate_up.unsqueeze(0), gate_up_scale.unsqueeze(0),
-                     self.act, m=q, top_k=1, scratch=self.scratch, x_scale=x_scale, pdl=pdl)
+        gu_scale = self._grain64(gate_up_scale, 0, 2 * self.inter // 128)
+        dn_scale = self._grain64(down_scale, 1, self.inter // 128)
+        ops.moe_gate(hn, self.sel, w_gate_up.unsqueeze(0), gu_scale.unsqueeze(0), self.act, m=q,
+                     top_k=1, scratch=self.scratch, x_scale=x_scale, pdl=pdl)
         return ops.moe_down(self.act, self.sel, self.wt, w_down.unsqueeze(0),
-                            down_scale.unsqueeze(0), out, m=q, top_k=1,
-                            scratch=self.scratch, tail=tail, pdl=pdl)
+                            dn_scale.unsqueeze(0), out, m=q, top_k=1, scratch=self.scratch,
+                            tail=tail, pdl=pdl)

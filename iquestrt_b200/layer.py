@@ -6,14 +6,18 @@
     -> (at the start of the next layer) MLP all-reduce tail + next attention norm
 
 as ten kernels chained by programmatic dependent launch.  Here the same step is FOUR
-launches: o_proj with the attention tail in its epilogue, the router, the expert Gate,
-and the expert Down with the MLP tail in its epilogue.  Attention itself, QKV and the
+launches: o_proj with the attention tail in the same launch, the router, the expert Gate,
+and the expert Down with the MLP tail in the same launch.  Attention itself, QKV and the
 KV cache are outside this path: `step` takes the attention output `ao` as its input.
 
 `formats="benchmark"`: activations carry 1x128 group scales, router scores are
 renormalised sigmoids, one shared expert (the benchmark configurations).
 `formats="reference"`: unscaled e4m3 MoE activations, W8A16 o_proj, softmax-of-top-k
-router weights, no shared expert (the reference model's own numerics)."""
+router weights, no shared expert (the reference model's own numerics).
+
+`protocol` picks the all-reduce of the two tails (see `parallel`): "push" (default: tiles
+stored into every rank's landing zone from the GEMV epilogue, rows finished by dedicated
+CTAs of the same launch) or "pull" (signal, wait, `multimem.ld_reduce` on the last CTA)."""
 
 from __future__ import annotations
 
@@ -31,7 +35,8 @@ class DecodeLayer:
 
     def __init__(self, shape: LayerShape, *, q_len: int = 1, tp: int = 1, group=None,
                  device="cuda", formats: str = "benchmark", a_scale: float = 1.0,
-                 f_scale: float = 1.0, use_multicast: bool = True, timeout_ms: int = 2000):
+                 f_scale: float = 1.0, use_multicast: bool = True, timeout_ms: int = 2000,
+                 protocol: str = "push", oproj_activation: str | None = None):
         if formats not in ("benchmark", "reference"):
             raise ValueError(f"formats must be 'benchmark' or 'reference', got {formats!r}")
         self.shape, self.q_len, self.tp, self.formats = shape, q_len, tp, formats
@@ -41,12 +46,14 @@ class DecodeLayer:
         self.q_loc, self.i_loc = q_loc, i_loc
         h = shape.hidden
         self.ws = Workspace(device=device, symm_group=group if tp > 1 else None,
-                            use_multicast=use_multicast)
+                            use_multicast=use_multicast, protocol=protocol)
         ws = self.ws
         self.scratch = ops.Scratch(device)
         self.tail = TailKernels(h, shape.eps, ws=ws, q_len=q_len)
+        if oproj_activation is None:
+            oproj_activation = "group" if bench or q_len > 4 else "w8a16"
         self.oproj = OProjGemv(q_loc, h, ws=ws, q_len=q_len, scratch=self.scratch,
-                               activation="group" if bench or q_len > 4 else "w8a16")
+                               activation=oproj_activation)
         self.router = RouterSelect(shape.n_experts, shape.top_k, h, device=device, ws=ws,
                                    q_len=q_len, score="sigmoid" if bench else "softmax",
                                    scratch=self.scratch)
@@ -62,54 +69,94 @@ class DecodeLayer:
                                         timeout_ms=timeout_ms)
         ws.freeze()
 
-    def step(self, ao, residual, lw, *, fused: bool = True, pdl: bool = True,
-             one_launch: bool = False):
+    # ------------------------------------------------------------------ the four launches
+    def _attn_spec(self, out_buf, residual, lw):
+        moe = self.moe
+        x_scale = moe.x_pad_scale if self.formats == "benchmark" else None
+        return self.ar_tail.spec(
+            out_buf[:self.q_len], residual, lw["attn_out_norm"], lw["feed_forward_norm"],
+            self.a_scale, self.f_scale, norm_out=moe.x_pad, norm_fp8=moe.x_pad_fp8,
+            norm_fp8_scale=x_scale, inv_out=self.ar_tail.inv)
+
+    def _shared(self, lw):
+        if not self.shape.n_shared:
+            return None
+        return (lw["shared_fc"], lw["shared_fc_scale"], lw["shared_proj"],
+                lw["shared_proj_scale"])
+
+    def step(self, ao, residual, lw, *, fused: bool = True, pdl: bool = True):
         """One layer for the first `q_len` rows.
 
         `ao [q, q_dim/tp]` bf16 is this rank's attention output, `residual [q, hidden]`
         bf16 the residual base, `lw` the rank-local weights (`synth.make_layer`).  Returns
         `(out, norm_out)`: the layer output (next residual) and its RMSNorm under the next
         layer's attention norm.  `fused=False` runs the two all-reduce tails as their own
-        launches (the reference's kernel boundaries).  `one_launch=True` runs the four
-        fused launches as a single cooperative launch (`iq_decode_layer`), same results."""
-        if one_launch:
-            if not fused:
-                raise ValueError("one_launch needs the fused tails")
-            with ops.one_launch(pdl=pdl):
-                return self.step(ao, residual, lw, fused=True, pdl=pdl)
+        launches (the reference's kernel boundaries)."""
         q = self.q_len
         moe = self.moe
-        bench = self.formats == "benchmark"
-        x_scale = moe.x_pad_scale if bench else None
-        spec = self.ar_tail.spec(
-            self.oproj.outputs[self.oproj._next_output][:q], residual, lw["attn_out_norm"],
-            lw["feed_forward_norm"], self.a_scale, self.f_scale, norm_out=moe.x_pad,
-            norm_fp8=moe.x_pad_fp8, norm_fp8_scale=x_scale, inv_out=self.ar_tail.inv)
+        x_scale = moe.x_pad_scale if self.formats == "benchmark" else None
+        out_buf = self.oproj.outputs[self.oproj._next_output]
+        spec = self._attn_spec(out_buf, residual, lw)
         if fused:
             self.oproj(ao, lw["o_proj"], lw["o_scale"], tail=spec, pdl=pdl)
         else:
-            self.oproj(ao, lw["o_proj"], lw["o_scale"], pdl=pdl)
+            self.oproj(ao, lw["o_proj"], lw["o_scale"], push=spec.comm, pdl=pdl)
             ops.tail(spec, self.scratch, pdl=pdl)
         h = spec.h_out
         sel, wt = self.router(moe.x_pad, lw["router"], pdl=pdl)
-        shared = None
-        if self.shape.n_shared:
-            shared = (lw["shared_fc"], lw["shared_fc_scale"], lw["shared_proj"],
-                      lw["shared_proj_scale"])
-        out_buf = moe.outputs[moe._out_index]
-        mspec = self.mlp_tail.spec(out_buf[:q], h, self.f_scale, lw["next_attention_norm"])
+        mlp_buf = moe.outputs[moe._out_index]
+        mspec = self.mlp_tail.spec(mlp_buf[:q], h, self.f_scale, lw["next_attention_norm"])
         # Level 2: the Gate's activations (written by the attention tail) and the Down's
         # routes (written by the router) are each two launches old when those kernels
         # start, so they may be read before the kernels' dependency wait.
         level = 2 if pdl else 0
         if fused:
             moe(sel, wt, lw["fc"], lw["fc_scale"], lw["proj"], lw["proj_scale"], x_scale=x_scale,
-                shared=shared, tail=mspec, pdl=level)
+                shared=self._shared(lw), tail=mspec, pdl=level)
         else:
             moe(sel, wt, lw["fc"], lw["fc_scale"], lw["proj"], lw["proj_scale"], x_scale=x_scale,
-                shared=shared, pdl=level)
+                shared=self._shared(lw), push=mspec.comm, pdl=level)
             ops.tail(mspec, self.scratch, pdl=pdl)
         return mspec.h_out, mspec.norm_out
+
+    def kernel_probes(self, inputs, weights):
+        """`{name: fn(i)}`: each of the layer's four launches on its own, with the layer's
+        arguments (input set `i % len(inputs)`, weight set `i % len(weights)`), for timing
+        one kernel in isolation."""
+        q, moe, shape = self.q_len, self.moe, self.shape
+        sel, wt = self.router.sel, self.router.wt
+        x_scale = moe.x_pad_scale if self.formats == "benchmark" else None
+
+        def oproj_tail(i):
+            ao, res = inputs[i % len(inputs)]
+            lw = weights[i % len(weights)]
+            out = self.oproj.outputs[i % 2]
+            ops.linear(ao, lw["o_proj"], lw["o_scale"], scratch=self.scratch, out=out[:q],
+                       x_kind=self.oproj.x_kind, tail=self._attn_spec(out, res, lw), pdl=True)
+
+        def router(i):
+            self.router(moe.x_pad, weights[i % len(weights)]["router"], pdl=True)
+
+        def gate(i):
+            lw = weights[i % len(weights)]
+            sh = self._shared(lw)
+            ops.moe_gate(moe.x_pad_fp8, sel, lw["fc"], lw["fc_scale"], moe.act, m=q,
+                         top_k=shape.top_k, scratch=self.scratch, x_scale=x_scale,
+                         shared_fc=sh[0] if sh else None, shared_fc_scale=sh[1] if sh else None,
+                         pdl=True)
+
+        def down_tail(i):
+            lw = weights[i % len(weights)]
+            sh = self._shared(lw)
+            out = moe.outputs[i % 2]
+            mspec = self.mlp_tail.spec(out[:q], self.tail.h[:q], self.f_scale,
+                                       lw["next_attention_norm"])
+            ops.moe_down(moe.act, sel, wt, lw["proj"], lw["proj_scale"], out, m=q,
+                         top_k=shape.top_k, scratch=self.scratch,
+                         shared_proj=sh[2] if sh else None,
+                         shared_proj_scale=sh[3] if sh else None, tail=mspec, pdl=True)
+
+        return {"oproj_tail": oproj_tail, "router": router, "gate": gate, "down_tail": down_tail}
 
     def check(self) -> None:
         """Synchronises and raises if any launch recorded a device-side error."""
@@ -152,7 +199,7 @@ class HostStep:
     `__call__` copies its arguments into the pinned input buffers, launches the graph and
     waits for it; `out` is overwritten by the next call."""
 
-    def __init__(self, layer: DecodeLayer, lw, *, one_launch: bool = False, pdl: bool = True):
+    def __init__(self, layer: DecodeLayer, lw, *, pdl: bool = True):
         dev = layer.norm_out.device
         q, shape = layer.q_len, layer.shape
         self.layer = layer
@@ -168,7 +215,7 @@ class HostStep:
         def body():
             self.ao_dev.copy_(self.ao_pin, non_blocking=True)
             self.res_dev.copy_(self.res_pin, non_blocking=True)
-            out, _ = layer.step(self.ao_dev, self.res_dev, lw, one_launch=one_launch, pdl=pdl)
+            out, _ = layer.step(self.ao_dev, self.res_dev, lw, pdl=pdl)
             self.out_pin.copy_(out, non_blocking=True)
 
         with torch.cuda.stream(self.stream):

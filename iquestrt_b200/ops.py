@@ -18,7 +18,8 @@ from ._lib import (ACT_BF16, ACT_E4M3, ROUTE_SIGMOID, ROUTE_SOFTMAX, TAIL_ATTN, 
 
 E4M3 = torch.float8_e4m3fn
 
-__all__ = ["Scratch", "TailSpec", "linear", "router", "moe_gate", "moe_down", "tail", "one_launch",
+__all__ = ["Scratch", "TailSpec", "linear", "linear_static", "linear_static_status", "router",
+           "moe_gate", "moe_down", "tail",
            "X_BF16_GROUPQ", "X_BF16_SPLIT2", "X_E4M3_GROUP", "X_E4M3_UNSCALED",
            "TAIL_ATTN", "TAIL_MLP", "ROUTE_SOFTMAX", "ROUTE_SIGMOID", "ACT_E4M3", "ACT_BF16"]
 
@@ -136,56 +137,6 @@ class TailSpec:
         return a
 
 
-class one_launch:
-    """Context in which `linear` (with its attention tail), `router`, `moe_gate` and
-    `moe_down` (with its MLP tail) do not launch but record their arguments; on exit the
-    four recorded calls run as ONE cooperative launch (`iq_decode_layer`) with results
-    bit-identical to the four separate launches.  Exactly those four calls, once each,
-    must be made inside the context."""
-
-    _active: "one_launch | None" = None
-
-    def __init__(self, *, pdl: bool = False):
-        self.pdl = pdl
-        self.parts: dict[str, object] = {}
-        self._keep: list = []
-
-    def __enter__(self):
-        if one_launch._active is not None:
-            raise RuntimeError("one_launch contexts do not nest")
-        one_launch._active = self
-        return self
-
-    def record(self, name: str, args, *keep) -> None:
-        if name in self.parts:
-            raise RuntimeError(f"{name} was called twice inside one_launch")
-        self.parts[name] = args
-        self._keep.extend(keep)
-
-    def __exit__(self, exc_type, exc, tb):
-        one_launch._active = None
-        if exc_type is not None:
-            return False
-        missing = [n for n in ("oproj", "router", "gate", "down") if n not in self.parts]
-        if missing:
-            raise RuntimeError(f"one_launch: no call recorded for {missing}")
-        a = _lib.DecodeLayerArgs()
-        a.oproj, a.router = self.parts["oproj"], self.parts["router"]
-        a.gate, a.down = self.parts["gate"], self.parts["down"]
-        _lib.check("iq_decode_layer",
-                   _lib.load().iq_decode_layer(C.byref(a), _stream(), int(self.pdl)))
-        return False
-
-
-def _launch(name: str, part: str, args, *keep) -> None:
-    """Launches `name` now, or records the call when a `one_launch` context is open."""
-    ctx = one_launch._active
-    if ctx is not None:
-        ctx.record(part, args, *keep)
-        return
-    _lib.check(name, getattr(_lib.load(), name)(C.byref(args), _stream()))
-
-
 _SCRATCH: dict[int, Scratch] = {}
 
 
@@ -206,13 +157,9 @@ def tail(spec: TailSpec, scratch: Scratch, *, pdl: bool = False) -> None:
     _lib.check("iq_tail", _lib.load().iq_tail(C.byref(a), _stream(), int(pdl)))
 
 
-def linear(x, w, w_scale, *, scratch: Scratch, out=None, x_kind=None, x_scale=None,
-           block=(128, 128), tail: TailSpec | None = None, pdl: bool = False):
-    """`out[m,n] bf16 = x[m,k] @ dequant(w[n,k], w_scale).T` on the streaming GEMV kernel,
-    optionally followed in the same launch by `tail` (whose `partial` must be `out`).
-
-    `x` is bf16 (quantised in the kernel per 1x128 group, or split in two e4m3 terms with
-    `x_kind=X_BF16_SPLIT2`) or e4m3 (with `x_scale [m,k/128]`, or unscaled)."""
+def _linear_args(x, w, w_scale, out, x_kind, x_scale, block):
+    """Checks the operands of the block-FP8 GEMV and fills the part of `iq_linear_args`
+    that `linear` and `linear_static` share."""
     m, k = x.shape
     n = w.shape[0]
     dev = x.device
@@ -227,21 +174,36 @@ def linear(x, w, w_scale, *, scratch: Scratch, out=None, x_kind=None, x_scale=No
     _need("x", x, torch.bfloat16 if x_kind in (X_BF16_GROUPQ, X_BF16_SPLIT2) else E4M3, None, dev)
     if x_kind == X_E4M3_GROUP:
         _need("x_scale", x_scale, torch.float32, (m, k // 128), dev)
-    if out is None:
-        out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
     _need("out", out, torch.bfloat16, (m, n), dev)
     a = _lib.LinearArgs()
     a.x, a.x_scale, a.x_kind = x.data_ptr(), _ptr(x_scale), x_kind
     a.m, a.k, a.n = m, k, n
     a.w, a.w_scale, a.rg, a.kg = w.data_ptr(), w_scale.data_ptr(), rg, kg
     a.out = out.data_ptr()
+    return a
+
+
+def linear(x, w, w_scale, *, scratch: Scratch, out=None, x_kind=None, x_scale=None,
+           block=(128, 128), tail: TailSpec | None = None, push=None, pdl: bool = False):
+    """`out[m,n] bf16 = x[m,k] @ dequant(w[n,k], w_scale).T` on the streaming GEMV kernel,
+    optionally followed in the same launch by `tail` (whose `partial` must be `out`).
+
+    `x` is bf16 (quantised in the kernel per 1x128 group, or split in two e4m3 terms with
+    `x_kind=X_BF16_SPLIT2`) or e4m3 (with `x_scale [m,k/128]`, or unscaled).  `push` (a
+    `parallel.SymmSlot`) sends the rows to that slot's landing zone on every rank without
+    running a tail, for a later `tail(...)` on the same slot."""
+    if out is None:
+        out = torch.empty(x.shape[0], w.shape[0], dtype=torch.bfloat16, device=x.device)
+    a = _linear_args(x, w, w_scale, out, x_kind, x_scale, block)
     a.scratch, a.scratch_bytes = scratch.ptr, scratch.bytes
     t = None
     if tail is not None:
         t = tail.to_c(scratch.ptr)
         a.tail = C.pointer(t)
+    elif push is not None and push.world > 1 and push.protocol == "push":
+        a.push = C.pointer(push.push_args())
     a.pdl = int(pdl)
-    _launch("iq_linear", "oproj", a, t)
+    _lib.check("iq_linear", _lib.load().iq_linear(C.byref(a), _stream()))
     return out
 
 
@@ -270,22 +232,24 @@ def router(x, weight, *, top_k: int, scratch: Scratch, score: int = ROUTE_SOFTMA
     a.m, a.h, a.e, a.top_k, a.score = m, h, e, top_k, score
     a.sel, a.wt, a.logits = sel.data_ptr(), wt.data_ptr(), logits.data_ptr()
     a.scratch, a.scratch_bytes, a.pdl = scratch.ptr, scratch.bytes, int(pdl)
-    _launch("iq_router", "router", a)
+    _lib.check("iq_router", _lib.load().iq_router(C.byref(a), _stream()))
     return sel, wt, logits
 
 
 def moe_gate(x_fp8, sel, fc, fc_scale, act, *, m: int, top_k: int, scratch: Scratch,
              x_scale=None, shared_fc=None, shared_fc_scale=None, pdl: bool = False):
     """Gate/Up + SiLU of the routed pairs of the first `m` rows (+ shared experts) into
-    `act [m*(top_k+n_shared), i_loc]` (e4m3 unscaled, or bf16)."""
+    `act [m*(top_k+n_shared), i_loc]` (e4m3 unscaled, or bf16).  `x_fp8` is e4m3 (with
+    `x_scale`, or unscaled) or bf16 (quantised per 1x128 group inside the kernel)."""
     e, two_i, h = fc.shape
     i_loc = two_i // 2
     dev = fc.device
     _need("fc", fc, E4M3, None, dev)
     _need("fc_scale", fc_scale, torch.float32, (e, two_i // 64, h // 128), dev)
-    _need("x_fp8", x_fp8, E4M3, None, dev)
+    x_is_bf16 = x_fp8.dtype == torch.bfloat16
+    _need("x", x_fp8, torch.bfloat16 if x_is_bf16 else E4M3, None, dev)
     if x_fp8.shape[-1] != h or x_fp8.shape[0] < m:
-        raise ValueError(f"x_fp8 must be [>= {m}, {h}], got {tuple(x_fp8.shape)}")
+        raise ValueError(f"x must be [>= {m}, {h}], got {tuple(x_fp8.shape)}")
     _need("sel", sel, torch.int32, None, dev)
     n_shared = 0
     if shared_fc is not None:
@@ -303,21 +267,24 @@ def moe_gate(x_fp8, sel, fc, fc_scale, act, *, m: int, top_k: int, scratch: Scra
     if x_scale is not None:
         _need("x_scale", x_scale, torch.float32, None, dev)
     a = _lib.MoeGateArgs()
-    a.x_fp8, a.x_scale = x_fp8.data_ptr(), _ptr(x_scale)
+    if x_is_bf16:
+        a.x_bf16 = x_fp8.data_ptr()
+    else:
+        a.x_fp8, a.x_scale = x_fp8.data_ptr(), _ptr(x_scale)
     a.m, a.h, a.i_loc, a.n_experts, a.top_k, a.n_shared = m, h, i_loc, e, top_k, n_shared
     a.sel, a.fc, a.fc_scale = sel.data_ptr(), fc.data_ptr(), fc_scale.data_ptr()
     a.shared_fc, a.shared_fc_scale = _ptr(shared_fc), _ptr(shared_fc_scale)
     a.act, a.act_kind = act.data_ptr(), ACT_E4M3 if act.dtype == E4M3 else ACT_BF16
     a.scratch, a.scratch_bytes, a.pdl = scratch.ptr, scratch.bytes, int(pdl)
-    _launch("iq_moe_gate", "gate", a)
+    _lib.check("iq_moe_gate", _lib.load().iq_moe_gate(C.byref(a), _stream()))
     return act
 
 
 def moe_down(act, sel, wt, proj, proj_scale, out, *, m: int, top_k: int, scratch: Scratch,
              shared_proj=None, shared_proj_scale=None, tail: TailSpec | None = None,
-             pdl: bool = False):
+             push=None, pdl: bool = False):
     """Down of the routed pairs (+ shared experts) into `out[:m]` bf16 `[m,h]`, optionally
-    followed in the same launch by `tail`."""
+    followed in the same launch by `tail`; `push` as in `linear`."""
     e, h, i_loc = proj.shape
     dev = proj.device
     _need("proj", proj, E4M3, None, dev)
@@ -347,8 +314,10 @@ def moe_down(act, sel, wt, proj, proj_scale, out, *, m: int, top_k: int, scratch
     if tail is not None:
         t = tail.to_c(scratch.ptr)
         a.tail = C.pointer(t)
+    elif push is not None and push.world > 1 and push.protocol == "push":
+        a.push = C.pointer(push.push_args())
     a.pdl = int(pdl)
-    _launch("iq_moe_down", "down", a, t)
+    _lib.check("iq_moe_down", _lib.load().iq_moe_down(C.byref(a), _stream()))
     return out[:m]
 
 
@@ -359,27 +328,18 @@ def linear_static(x, w, w_scale, out, *, x_kind=None, x_scale=None, block=(128, 
     the kernel's work area is a device array built into the library, so no scratch buffer
     is passed and `out` must be given.  Limits: n, k <= 65536, no fused tail.  All calls on
     a device share that array, so order them on one stream; the first call on a device
-    should come before any stream capture."""
-    m, k = x.shape
-    n = w.shape[0]
-    dev = x.device
-    _need("w", w, E4M3, (n, k), dev)
-    rg, kg = block
-    _need("w_scale", w_scale, torch.float32, (n // rg, k // kg), dev)
-    if x_kind is None:
-        if x.dtype == torch.bfloat16:
-            x_kind = X_BF16_GROUPQ
-        else:
-            x_kind = X_E4M3_GROUP if x_scale is not None else X_E4M3_UNSCALED
-    _need("x", x, torch.bfloat16 if x_kind in (X_BF16_GROUPQ, X_BF16_SPLIT2) else E4M3, None, dev)
-    if x_kind == X_E4M3_GROUP:
-        _need("x_scale", x_scale, torch.float32, (m, k // 128), dev)
-    _need("out", out, torch.bfloat16, (m, n), dev)
-    a = _lib.LinearArgs()
-    a.x, a.x_scale, a.x_kind = x.data_ptr(), _ptr(x_scale), x_kind
-    a.m, a.k, a.n = m, k, n
-    a.w, a.w_scale, a.rg, a.kg = w.data_ptr(), w_scale.data_ptr(), rg, kg
-    a.out = out.data_ptr()
+    should come before any stream capture.  A device-side error of the call stays readable
+    through `linear_static_status` until the next `linear_static` on the device."""
+    a = _linear_args(x, w, w_scale, out, x_kind, x_scale, block)
     a.pdl = int(pdl)
     _lib.check("iq_linear_static", _lib.load().iq_linear_static(C.byref(a), _stream()))
     return out
+
+
+def linear_static_status() -> int:
+    """Synchronises the current stream and returns the device status code the last
+    `linear_static` call on this device left (0 = none)."""
+    code = C.c_int(0)
+    _lib.check("iq_linear_static_status",
+               _lib.load().iq_linear_static_status(C.byref(code), _stream()))
+    return code.value

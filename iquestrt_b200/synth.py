@@ -15,6 +15,8 @@ from dataclasses import dataclass
 
 import torch
 
+from .blockfp8 import shard_scale
+
 E4M3 = torch.float8_e4m3fn
 BLOCK = 128
 EXPERT_GRAIN = 64
@@ -63,14 +65,6 @@ def block_scales(rows, cols, gen, device):
     u = torch.rand(rows // BLOCK, cols // BLOCK, generator=gen, device=device,
                    dtype=torch.float32)
     return torch.exp2(-12.0 + 6.0 * u)
-
-
-def shard_scale(scale, dim, start, length, grain):
-    """Scale table of a weight slice at `grain` (iquestrt/blockfp8.py:24-36)."""
-    if BLOCK % grain or start % grain or length % grain:
-        raise ValueError(f"grain {grain} does not tile slice [{start}, {start + length})")
-    blocks = (start + torch.arange(0, length, grain, device=scale.device)) // BLOCK
-    return scale.index_select(dim, blocks)
 
 
 def _expert_shard(shape: LayerShape, tp, rank, device, *seed):

@@ -1,105 +1,96 @@
-"""Aligned arena for decode buffers; addresses stay fixed while CUDA graphs use them.
+"""Fixed-address arena for the decode buffers.
 
-Mirrors the reference's `iquestrt/workspace.py` (L16-119): opaque keys, `slot(key, shape,
-dtype, symm=False)`, `freeze()`.  Symmetric slots are `parallel.SymmSlot`s, registered
-by the data pointer of their tensor so that the all-reduce holders can find the
-communication state of a buffer they are handed (the reference looks its multicast
+Same interface as the reference's `iquestrt/workspace.py` (L16-119): opaque keys,
+`slot(key, shape, dtype, symm=False)`, `freeze()`, 1024-byte aligned slots.  The design is
+a bump allocator over ONE buffer that exists from construction: a slot is a real view of
+the arena the moment it is requested, so an address never changes between the request
+and a later CUDA-graph capture, and `freeze()` only closes the arena to new requests.
+Symmetric slots are `parallel.SymmSlot`s (their own symmetric-memory allocations),
+registered by the data pointer of their tensor so that the all-reduce holders can find
+the communication state of a buffer they are handed (the reference looks its multicast
 pointers up the same way, iquestrt/kernels/ar_tail.py:1394-1402)."""
 
 from __future__ import annotations
+
+import math
 
 import torch
 
 from .parallel import SymmSlot, register
 
 ALIGN = 1024
-
-_DT_BYTES = {
-    torch.bfloat16: 2, torch.float16: 2, torch.float32: 4, torch.int32: 4, torch.int64: 8,
-    torch.uint8: 1, torch.bool: 1, torch.float8_e4m3fn: 1,
-}
+DEFAULT_CAPACITY = 32 << 20      # bytes; the holders of one decode layer use about 1.5 MB
 
 
 class Workspace:
-    """Byte arena handing out stable, `ALIGN`-aligned views."""
+    """Hands out stable, `align`-aligned views of one pre-sized device buffer."""
 
     def __init__(self, *, device="cuda", align: int = ALIGN, symm_group=None,
-                 use_multicast: bool = True):
+                 use_multicast: bool = True, protocol: str = "push",
+                 capacity: int = DEFAULT_CAPACITY):
+        if align <= 0 or align & (align - 1):
+            raise ValueError(f"align must be a power of two, got {align}")
         self.device = torch.device(device)
         self.align = align
         self.symm_group = symm_group
         self.use_multicast = use_multicast
+        self.protocol = protocol
+        self.capacity = int(capacity)
+        # One allocation, made now.  `_top` is the first free byte; the arena's own base
+        # address may be less aligned than `align`, so offsets are rounded on addresses.
+        self._arena = torch.zeros(self.capacity + align, dtype=torch.uint8, device=self.device)
+        self._base = self._arena.data_ptr()
+        self._top = 0
+        self._closed = False
+        self._local: dict[object, torch.Tensor] = {}
         self._symm: dict[object, SymmSlot] = {}
         self._symm_by_ptr: dict[int, SymmSlot] = {}
-        self._slots: dict[object, tuple[int, tuple[int, ...], torch.dtype]] = {}
-        self._cursor = 0
-        self._buf: torch.Tensor | None = None
-        self._views: dict[object, torch.Tensor] = {}
-        self._handed_out: dict[object, torch.Tensor] = {}
+
+    @staticmethod
+    def _same(t: torch.Tensor, shape, dtype) -> bool:
+        return tuple(t.shape) == shape and t.dtype == dtype
 
     def slot(self, key, shape, dtype: torch.dtype, symm: bool = False) -> torch.Tensor:
-        """Register (or look up) a slot and return a tensor for it."""
+        """The tensor registered under `key`, carved from the arena on first request."""
         shape = tuple(int(s) for s in shape)
+        known = (self._symm[key].data if key in self._symm else None) if symm \
+            else self._local.get(key)
+        if known is not None:
+            if not self._same(known, shape, dtype):
+                raise ValueError(f"slot {key!r} exists as {tuple(known.shape)}/{known.dtype}; a "
+                                 f"second request as {shape}/{dtype} would alias it")
+            return known
         if symm:
-            if key in self._symm:
-                t = self._symm[key].data
-                if tuple(t.shape) != shape or t.dtype != dtype:
-                    raise ValueError(f"symmetric slot {key!r} already registered as "
-                                     f"{tuple(t.shape)}/{t.dtype}, requested {shape}/{dtype}")
-                return t
             s = SymmSlot(shape, dtype, device=self.device, group=self.symm_group,
-                         use_multicast=self.use_multicast)
+                         use_multicast=self.use_multicast, protocol=self.protocol)
             self._symm[key] = register(s)
             self._symm_by_ptr[s.data.data_ptr()] = s
             return s.data
-        if key in self._slots:
-            _, sh, dt = self._slots[key]
-            if sh != shape or dt != dtype:
-                raise ValueError(f"slot {key!r} already registered as {sh}/{dt}, requested "
-                                 f"{shape}/{dtype}: two tensors under one key would alias")
-            return self._view(key)
-        if self._buf is not None:
-            raise RuntimeError(f"slot {key!r} requested after freeze(): growing the arena "
-                               "would move addresses captured graphs still write to")
-        if dtype not in _DT_BYTES:
-            raise ValueError(f"unsupported dtype {dtype}")
-        nbytes = _DT_BYTES[dtype]
-        for s in shape:
-            nbytes *= s
-        self._slots[key] = (self._cursor, shape, dtype)
-        self._cursor += -(-nbytes // self.align) * self.align
-        return self._view(key)
+        if self._closed:
+            raise RuntimeError(f"slot {key!r} requested after freeze(): the arena is closed so "
+                               "that captured graphs keep valid addresses")
+        try:
+            size = math.prod(shape) * dtype.itemsize
+        except AttributeError as exc:
+            raise ValueError(f"unsupported dtype {dtype}") from exc
+        start = -(-(self._base + self._top) // self.align) * self.align - self._base
+        if start + size > self._arena.numel():
+            raise MemoryError(f"workspace arena of {self.capacity} bytes is full at slot {key!r} "
+                              f"({size} bytes); construct Workspace(capacity=...) larger")
+        view = self._arena.narrow(0, start, size).view(dtype).view(shape)
+        self._top = start + size
+        self._local[key] = view
+        return view
 
     def symm_slot_of(self, tensor: torch.Tensor) -> SymmSlot | None:
         """The symmetric slot whose rows start at `tensor`'s address, if any."""
         return self._symm_by_ptr.get(tensor.data_ptr())
 
     def freeze(self) -> "Workspace":
-        """Allocate the arena once and move every placeholder, contents included, into it."""
-        if self._buf is None:
-            self._buf = torch.zeros(max(self._cursor, self.align), dtype=torch.uint8,
-                                    device=self.device)
-            self._views.clear()
-            for key, ph in self._handed_out.items():
-                final = self._view(key)
-                final.copy_(ph)
-                ph.set_(final)
-                if ph.data_ptr() != final.data_ptr():
-                    raise RuntimeError(f"failed to repoint placeholder for {key!r}")
-            self._handed_out.clear()
+        """Close the arena: later `slot` calls may only look existing slots up."""
+        self._closed = True
         return self
 
-    def _view(self, key) -> torch.Tensor:
-        if key in self._views:
-            return self._views[key]
-        off, shape, dtype = self._slots[key]
-        if self._buf is None:
-            if key not in self._handed_out:
-                self._handed_out[key] = torch.zeros(shape, dtype=dtype, device=self.device)
-            return self._handed_out[key]
-        n = 1
-        for s in shape:
-            n *= s
-        v = self._buf[off:off + n * _DT_BYTES[dtype]].view(dtype).view(shape)
-        self._views[key] = v
-        return v
+    @property
+    def used_bytes(self) -> int:
+        return self._top

@@ -2,13 +2,15 @@
 
     torchrun --nproc-per-node N tests/mp_worker.py --mode parity|timeout [--no-multicast]
 
-parity : the decode layer at TP = N, as four launches and as one cooperative launch
-         (bit-identical), against the CPU oracle computed from all ranks' shards;
-         identical outputs on every rank; the fused all-reduce against NCCL's all_reduce
-         of the same bf16 partials (untimed cross-check).
-timeout: a rank that does not launch its all-reduce (host-side fault): the peers' wait
-         runs out, they return IQ_ERR_PEER_TIMEOUT with the context still usable, the
-         late rank catches up and the next call is correct again."""
+parity : the decode layer at TP = N with both all-reduce protocols (push: tiles stored
+         into every rank's landing zone from the GEMV epilogue; pull: signal, wait,
+         switch read), against the CPU oracle computed from all ranks' shards; identical
+         outputs on every rank; the pull all-reduce alone against NCCL's all_reduce of
+         the same bf16 partials (untimed cross-check).
+timeout: a rank that does not launch its all-reduce (host-side fault), for both
+         protocols: the peers' wait runs out, they return IQ_ERR_PEER_TIMEOUT with the
+         context still usable, the late rank catches up and the next call is correct
+         again."""
 
 import argparse
 import os
@@ -62,14 +64,14 @@ def oracle_moe(shape, lws, hn, sel, wt):
 def run_parity(rank, world, dev, group, multicast):
     shape = synth.LayerShape(n_experts=16)
     a_scale, f_scale = 0.9, 1.1
-    for m in (1, 4):
+    for m, protocol in ((1, "push"), (4, "push"), (1, "pull"), (4, "pull")):
         layer = DecodeLayer(shape, q_len=m, tp=world, group=group, device=dev,
                             formats="benchmark", a_scale=a_scale, f_scale=f_scale,
-                            use_multicast=multicast)
+                            use_multicast=multicast, protocol=protocol)
         slot = layer.ws._symm[("oproj", "out")]
         if rank == 0:
-            print(f"[tp={world} m={m}] multicast={'yes' if slot.has_multicast else 'no'}",
-                  flush=True)
+            print(f"[tp={world} m={m} {protocol}] multicast="
+                  f"{'yes' if slot.has_multicast else 'no'}", flush=True)
         lws = [synth.make_layer(shape, tp=world, rank=r, device=dev, seed=2) for r in range(world)]
         ins = [synth.make_step_inputs(shape, m, tp=world, rank=r, device=dev, seed=2)
                for r in range(world)]
@@ -77,14 +79,13 @@ def run_parity(rank, world, dev, group, multicast):
         for rep in range(3):                      # both alternating slots, repeated epochs
             out, norm_out = layer.step(ao, res, lws[rank])
         layer.check()
-        four = (out.clone(), norm_out.clone())
-        # the same layer as ONE cooperative launch: bit-identical, all-reduce included
-        for rep in range(3):
-            out, norm_out = layer.step(ao, res, lws[rank], one_launch=True)
-        layer.check()
         out, norm_out = out.clone(), norm_out.clone()
-        assert torch.equal(out.view(torch.int16), four[0].view(torch.int16)), "one launch: out"
-        assert torch.equal(norm_out.view(torch.int16), four[1].view(torch.int16)), "one launch: norm"
+        # the two tails as launches of their own: same protocol, same bits
+        for rep in range(2):
+            out2, norm2 = layer.step(ao, res, lws[rank], fused=False)
+        layer.check()
+        assert torch.equal(out2.view(torch.int16), out.view(torch.int16)), "unfused: out"
+        assert torch.equal(norm2.view(torch.int16), norm_out.view(torch.int16)), "unfused: norm"
         # identical on every rank
         gathered = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(gathered, out)
@@ -104,11 +105,12 @@ def run_parity(rank, world, dev, group, multicast):
         e1, e2 = R.rel_fro(out.cpu(), want_out), R.rel_fro(norm_out.cpu(), want_norm)
         assert e1 <= 4e-3 and e2 <= 4e-3, (e1, e2)
         if rank == 0:
-            print(f"[tp={world} m={m}] layer vs oracle: out {e1:.2e} norm {e2:.2e}", flush=True)
+            print(f"[tp={world} m={m} {protocol}] layer vs oracle: out {e1:.2e} norm {e2:.2e}",
+                  flush=True)
         del layer, lws
 
-    # the all-reduce alone against NCCL and the oracle's fp32-accumulate sum
-    ws = Workspace(device=dev, symm_group=group, use_multicast=multicast)
+    # the pull all-reduce alone against NCCL and the oracle's fp32-accumulate sum
+    ws = Workspace(device=dev, symm_group=group, use_multicast=multicast, protocol="pull")
     bufs = [ws.slot(("t", i), (16, 6144), torch.bfloat16, symm=True) for i in range(2)]
     ws.freeze()
     scratch = ops.Scratch(dev)
@@ -146,40 +148,53 @@ def run_parity(rank, world, dev, group, multicast):
 
 
 def run_timeout(rank, world, dev, group):
-    """Host-side fault: the last rank skips one call."""
+    """Host-side fault: the last rank skips one call.  Both protocols, no multicast."""
     from iquestrt_b200 import parallel
-    ws = Workspace(device=dev, symm_group=group, use_multicast=False)
-    buf = ws.slot(("t", 0), (16, 1024), torch.bfloat16, symm=True)
-    ws.freeze()
-    scratch = ops.Scratch(dev)
+    late = world - 1
     zero = torch.zeros(1, 1024, dtype=torch.bfloat16, device=dev)
     ones = torch.ones(1024, dtype=torch.float32, device=dev)
     got = torch.empty(1, 1024, dtype=torch.bfloat16, device=dev)
     nrm = torch.empty_like(got)
+    # a GEMV whose output row is `value` in every column: x = value in element 0, weight
+    # column 0 all ones, unit scales
+    w = torch.zeros(1024, 256, dtype=torch.float32, device=dev)
+    w[:, 0] = 1.0
+    w = w.to(torch.float8_e4m3fn)
+    w_scale = torch.ones(1024 // 128, 256 // 128, dtype=torch.float32, device=dev)
+    for protocol in ("pull", "push"):
+        ws = Workspace(device=dev, symm_group=group, use_multicast=False, protocol=protocol)
+        buf = ws.slot(("t", protocol), (16, 1024), torch.bfloat16, symm=True)
+        ws.freeze()
+        scratch = ops.Scratch(dev)
 
-    def call(value, timeout_ms):
-        buf[:1].fill_(value)
-        spec = ops.TailSpec(kind=ops.TAIL_MLP, partial=buf[:1], residual=zero, w_norm=ones,
-                            h_out=got, norm_out=nrm, scale=1.0, eps=1e-6,
-                            comm=parallel.slot_of(buf), timeout_ms=timeout_ms)
-        ops.tail(spec, scratch)
-        return scratch.status()
+        def call(value, timeout_ms):
+            spec = ops.TailSpec(kind=ops.TAIL_MLP, partial=buf[:1], residual=zero, w_norm=ones,
+                                h_out=got, norm_out=nrm, scale=1.0, eps=1e-6,
+                                comm=parallel.slot_of(buf), timeout_ms=timeout_ms)
+            if protocol == "pull":
+                buf[:1].fill_(value)
+                ops.tail(spec, scratch)
+            else:
+                x = torch.zeros(1, 256, dtype=torch.bfloat16, device=dev)
+                x[0, 0] = value
+                ops.linear(x, w, w_scale, scratch=scratch, out=buf[:1], tail=spec)
+            return scratch.status()
 
-    late = world - 1
-    assert call(1.0, 2000) == 0 and float(got[0, 0]) == world          # a normal call
-    dist.barrier()
-    if rank != late:
-        code = call(2.0, 300)                                           # the peer is absent
-        assert code == 4, f"expected IQ_ERR_PEER_TIMEOUT, got {code}"
-    dist.barrier()
-    if rank == late:
-        assert call(2.0, 2000) == 0                                     # catches up at once
-    dist.barrier()
-    assert call(3.0, 2000) == 0                                         # healthy again
-    assert float(got[0, 0]) == 3.0 * world, float(got[0, 0])
-    if rank == 0:
-        print(f"[tp={world}] peer timeout reported, context usable, next call correct",
-              flush=True)
+        assert call(1.0, 2000) == 0 and float(got[0, 0]) == world          # a normal call
+        dist.barrier()
+        if rank != late:
+            code = call(2.0, 300)                                           # the peer is absent
+            assert code == 4, f"{protocol}: expected IQ_ERR_PEER_TIMEOUT, got {code}"
+        dist.barrier()
+        if rank == late:
+            assert call(2.0, 2000) == 0                                     # catches up at once
+        dist.barrier()
+        assert call(3.0, 2000) == 0                                         # healthy again
+        assert float(got[0, 0]) == 3.0 * world, float(got[0, 0])
+        dist.barrier()
+        if rank == 0:
+            print(f"[tp={world} {protocol}] peer timeout reported, context usable, next call "
+                  "correct", flush=True)
 
 
 def main():

@@ -30,10 +30,12 @@ def _synth():
 
 
 def _scratch_clean(scratch):
-    """Status word, ticket and tile counters are zero again after a launch (the fp32
-    partials area behind them is overwritten before every use and never cleared)."""
-    head = 256 + 4 * 16384
-    return int(scratch.buf[:head].view(torch.int32).abs().sum()) == 0
+    """Status word, tickets and tile counters are zero again after a launch (the fp32
+    partials area behind them is overwritten before every use and never cleared; the
+    launch counter at byte 128, which tags hand-off words, only ever grows)."""
+    head = scratch.buf[:256 + 4 * 16384].clone().view(torch.int32)
+    head[128 // 4] = 0
+    return int(head.abs().sum()) == 0
 
 
 def _close(got, want, tol=KERNEL_TOL, ulps=3):
@@ -251,6 +253,56 @@ def test_linear_fused_tail_world1(scratch):
     rout, rnorm = R.mlp_tail([part.cpu()], residual.cpu(), 1.0, gamma.cpu(), 1e-6)
     _close(h_out, rout, ulps=1)
     _close(nrm, rnorm, ulps=2)
+    assert _scratch_clean(scratch)
+
+
+@pytest.mark.parametrize("m,kind", [(4, "attn"), (8, "mlp"), (3, "attn")])
+def test_linear_fused_tail_rows_on_their_own_ctas(scratch, m, kind):
+    """Several rows: each row of the fused tail is finished by its own CTA of the GEMV
+    launch (polling the landing zone the epilogue fills).  Same bits as the GEMV followed
+    by the tail as a separate launch, and both against the oracle; three calls in a row
+    (the hand-off words carry a new tag each call)."""
+    ops, synth = _ops(), _synth()
+    n, k = 6144, 1024
+    g = torch.Generator().manual_seed(40 + m)
+    residual = torch.randn(m, n, generator=g).bfloat16().cuda()
+    w1 = (0.5 + torch.rand(n, generator=g)).cuda()
+    w2 = (0.5 + torch.rand(n, generator=g)).cuda()
+    attn = kind == "attn"
+
+    def spec_for(part, h_out, nrm, n8=None, n8s=None):
+        return ops.TailSpec(kind=ops.TAIL_ATTN if attn else ops.TAIL_MLP, partial=part,
+                            residual=residual, w_first=w1 if attn else None, w_norm=w2,
+                            h_out=h_out, norm_out=nrm, norm_fp8=n8, norm_fp8_scale=n8s,
+                            scale=0.8, eps=1e-6)
+
+    for call in range(3):
+        x, w, s = synth.make_linear_case(n, k, m, device="cuda", seed=60 + call)
+        part = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        h_out, nrm = torch.empty_like(part), torch.empty_like(part)
+        n8 = torch.empty(m, n, dtype=E4M3, device="cuda")
+        n8s = torch.empty(m, n // 128, dtype=torch.float32, device="cuda")
+        ops.linear(x, w, s, scratch=scratch, out=part, tail=spec_for(part, h_out, nrm, n8, n8s))
+        assert scratch.status() == 0
+        part2 = torch.empty_like(part)
+        h2, nrm2 = torch.empty_like(part), torch.empty_like(part)
+        ops.linear(x, w, s, scratch=scratch, out=part2)
+        ops.tail(spec_for(part2, h2, nrm2), scratch)
+        assert scratch.status() == 0
+        for a, b in ((part, part2), (h_out, h2), (nrm, nrm2)):
+            assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+        xq, xs = R.quant_act_group(x.cpu())
+        ref_part = R.linear_a8(xq, xs, w.cpu(), s.cpu())
+        _close(part, ref_part)
+        if attn:
+            rh, rn, _, _ = R.attention_tail([part.cpu()], residual.cpu(), w1.cpu(), w2.cpu(),
+                                            0.8, 1e-6)
+        else:
+            rh, rn = R.mlp_tail([part.cpu()], residual.cpu(), 0.8, w2.cpu(), 1e-6)
+        _close(h_out, rh, ulps=1)
+        _close(nrm, rn, ulps=2)
+        q, sq = R.quant_act_group(nrm.cpu())
+        assert torch.allclose(n8s.cpu(), sq, rtol=1e-6)
     assert _scratch_clean(scratch)
 
 

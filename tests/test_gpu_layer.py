@@ -1,4 +1,4 @@
-"""The four-launch decode layer (o_proj + attention tail, router, Gate, Down + MLP tail)
+"""The decode layer (o_proj + attention tail, router, Gate, Down + MLP tail: four launches)
 against the CPU oracle, through the reference-shaped holders, on one GPU.
 
 Two bars: (1) the decode numerics restated in the oracle, stage by stage, to bf16
@@ -84,6 +84,9 @@ def _dense_shared(hn, lw, s):
     (4, 8, "benchmark", True),     # M=4 (MTP verify)
     (4, 8, "benchmark", False),    # the two tails as their own launches
     (2, 8, "reference", True),     # the reference model's numerics at its own shapes
+    (1, 1, "benchmark", True),     # the benchmark's TP=1 layer at full width (what bench.py times)
+    (4, 1, "benchmark", True),
+    (3, 2, "benchmark", True),     # TP=2 shard widths (Down K = 1024)
 ])
 def test_decode_layer_against_oracle(m, tp, formats, fused):
     from iquestrt_b200 import synth
@@ -129,7 +132,7 @@ def test_decode_layer_against_oracle(m, tp, formats, fused):
     assert R.rel_fro(norm_out, norm_ref) <= PATH_TOL
 
 
-def _single_rank_layer(shape, m, tp, formats, a_scale, f_scale):
+def _single_rank_layer(shape, m, tp, formats, a_scale, f_scale, **kw):
     """A TP rank's shard run alone: the layer object is built for the shard's local
     widths with world size 1 (no all-reduce peers)."""
     from iquestrt_b200 import synth
@@ -139,7 +142,7 @@ def _single_rank_layer(shape, m, tp, formats, a_scale, f_scale):
                              top_k=shape.top_k, inter=i_loc, n_shared=shape.n_shared,
                              eps=shape.eps)
     return DecodeLayer(local, q_len=m, tp=1, formats=formats, a_scale=a_scale,
-                       f_scale=f_scale)
+                       f_scale=f_scale, **kw)
 
 
 def test_captured_layer_steps_replay_identically():
@@ -162,87 +165,48 @@ def test_captured_layer_steps_replay_identically():
     assert torch.equal(norm.view(torch.int16), eager_norm.view(torch.int16))
 
 
-def _bits(t):
-    t = t.contiguous()
-    return t.view({1: torch.uint8, 2: torch.int16, 4: torch.int32}[t.element_size()])
-
-
-@pytest.mark.parametrize("m,tp,formats", [
-    (1, 8, "benchmark"),     # configuration 2's rank shard
-    (4, 8, "benchmark"),
-    (1, 1, "benchmark"),     # full-width shapes: other tile geometries, tensor-map stages
-    (2, 4, "benchmark"),
-    (2, 8, "reference"),     # unscaled e4m3 activations, W8A16 o_proj, softmax routes
-])
-def test_one_launch_layer_is_bit_identical(m, tp, formats):
-    """`iq_decode_layer` (one cooperative launch) against the four-launch layer it fuses:
-    every intermediate and both outputs bit for bit, three calls in a row (the hand-off
-    words carry a new tag each launch), and the scratch's counters back at zero."""
-    from iquestrt_b200 import synth
-    if formats == "benchmark":
-        shape = synth.LayerShape(n_experts=32)
-    else:
-        # the reference model's hidden size and formats, with widths the one-launch layer
-        # covers at TP=8 (o_proj K a multiple of 1024, expert width a multiple of 256)
-        shape = synth.LayerShape(hidden=3072, q_dim=8192, n_experts=32, top_k=8, inter=2048,
-                                 n_shared=0)
-    layer = _single_rank_layer(shape, m, tp, formats, 0.9, 1.1)
-    rank = min(1, tp - 1)
-    lws = [synth.make_layer(shape, tp=tp, rank=rank, device="cuda", seed=11, layer=i)
-           for i in range(2)]
-
-    def snapshot(out, norm):
-        keep = (out, norm, layer.tail.h, layer.moe.x_pad, layer.moe.x_pad_fp8, layer.router.sel,
-                layer.router.wt, layer.moe.act)
-        return [_bits(t).clone() for t in keep]
-
-    for call in range(3):
-        ao, res = synth.make_step_inputs(shape, m, tp=tp, rank=rank, device="cuda",
-                                         seed=20 + call)
-        lw = lws[call % 2]
-        want = snapshot(*layer.step(ao, res, lw))
-        layer.check()
-        got = snapshot(*layer.step(ao, res, lw, one_launch=True))
-        layer.check()
-        for name, a, b in zip(("out", "norm_out", "h", "x_pad", "x_pad_fp8", "sel", "wt", "act"),
-                              want, got):
-            assert torch.equal(a, b), f"call {call}: {name} differs"
-        control = layer.scratch.buf[:256].clone()
-        control[96:100] = 0                      # the launch counter of the one-launch layer
-        assert int(control.to(torch.int32).abs().sum()) == 0
-
-
-def test_one_launch_layer_rejects_inconsistent_parts():
-    """The four argument structs must describe one layer: a router that reads something
-    other than the attention tail's normalised rows is refused before anything launches."""
-    from iquestrt_b200 import _lib, synth
-    shape = synth.LayerShape(n_experts=16)
-    layer = _single_rank_layer(shape, 1, 8, "benchmark", 1.0, 1.0)
-    lw, ao, res = _layer_case(shape, 8, 0, 1, seed=3)
-    other = torch.zeros_like(layer.moe.x_pad)
-    real = layer.moe.x_pad
-    try:
-        layer.router_input_override = other
-        with pytest.raises(_lib.IqError):
-            from iquestrt_b200 import ops
-            with ops.one_launch(pdl=False):
-                spec = layer.ar_tail.spec(
-                    layer.oproj.outputs[layer.oproj._next_output][:1], res, lw["attn_out_norm"],
-                    lw["feed_forward_norm"], 1.0, 1.0, norm_out=real,
-                    norm_fp8=layer.moe.x_pad_fp8, norm_fp8_scale=layer.moe.x_pad_scale,
-                    inv_out=layer.ar_tail.inv)
-                layer.oproj(ao, lw["o_proj"], lw["o_scale"], tail=spec)
-                sel, wt = layer.router(other, lw["router"])
-                mspec = layer.mlp_tail.spec(layer.moe.outputs[layer.moe._out_index][:1],
-                                            spec.h_out, 1.0, lw["next_attention_norm"])
-                layer.moe(sel, wt, lw["fc"], lw["fc_scale"], lw["proj"], lw["proj_scale"],
-                          x_scale=layer.moe.x_pad_scale,
-                          shared=(lw["shared_fc"], lw["shared_fc_scale"], lw["shared_proj"],
-                                  lw["shared_proj_scale"]), tail=mspec)
-    finally:
-        del layer.router_input_override
-    torch.cuda.synchronize()
+def _path_error(layer, shape, lw, ao, res, a_scale, f_scale):
+    """Relative Frobenius error of one layer step against the reference's bf16-activation
+    algebra evaluated on the kernel's own routes."""
+    out, norm_out = layer.step(ao, res, lw)
     layer.check()
+    c = _cpu(lw)
+    q = ao.shape[0]
+    sel = layer.router.sel.cpu().view(q, shape.top_k)
+    wt = layer.router.wt.cpu().view(q, shape.top_k)
+    part = R.linear(ao.cpu(), c["o_proj"], c["o_scale"])
+    h_ref, hn_ref = R.layer_residual_algebra([part], res.cpu(), c["attn_out_norm"],
+                                             c["feed_forward_norm"], a_scale, shape.eps)
+    mlp_ref = R.moe_prefill(hn_ref, sel, wt, c["fc"], c["fc_scale"], c["proj"], c["proj_scale"])
+    for s in range(shape.n_shared):
+        mlp_ref = mlp_ref + _dense_shared(hn_ref, c, s)
+    out_ref = h_ref + mlp_ref * f_scale
+    norm_ref = R.rms_norm(out_ref, c["next_attention_norm"], shape.eps)
+    return R.rel_fro(out.cpu(), out_ref), R.rel_fro(norm_out.cpu(), norm_ref)
+
+
+@pytest.mark.parametrize("m", [1, 4])
+def test_path_tolerance_over_seeds(m):
+    """The 2e-2 bar over eight seeds, not one draw.  With the W8A16-faithful o_proj (two
+    e4m3 terms per activation) every seed must pass.  With single-term 1x128-group e4m3
+    activations everywhere (the benchmark format) the quantisation of the activations
+    alone sits close to the bar: the maximum over the seeds is printed and must stay
+    within 2.5e-2."""
+    from iquestrt_b200 import synth
+    shape = synth.LayerShape(n_experts=16)
+    tp = 8
+    worst = {}
+    for act in ("w8a16", "group"):
+        layer = _single_rank_layer(shape, m, tp, "benchmark", 1.0, 1.0, oproj_activation=act)
+        errs = []
+        for seed in range(8):
+            lw, ao, res = _layer_case(shape, tp, seed % tp, m, seed=100 + seed)
+            errs.append(max(_path_error(layer, shape, lw, ao, res, 1.0, 1.0)))
+        worst[act] = max(errs)
+        print(f"m={m} o_proj activation {act}: rel. Frobenius over 8 seeds "
+              f"min {min(errs):.3e} max {max(errs):.3e}")
+    assert worst["w8a16"] <= PATH_TOL
+    assert worst["group"] <= 2.5e-2
 
 
 def test_host_step_matches_device_step():

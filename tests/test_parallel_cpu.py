@@ -70,12 +70,19 @@ def test_two_gloo_ranks_shard_and_reduce_consistently():
 
 
 def test_symm_slot_single_rank_layout():
-    """World-size-1 slots (no process group): plain memory with the same layout."""
-    from iquestrt_b200.parallel import CTRL_BYTES, SymmSlot
+    """World-size-1 slots (no process group): plain memory with the same layout -- rows,
+    control words, landing zone."""
+    from iquestrt_b200.parallel import CTRL_BYTES, ZONE_ROWS, SymmSlot
     s = SymmSlot((16, 1024), torch.bfloat16, device="cpu")
-    assert s.world == 1 and not s.has_multicast
-    assert s.buf.numel() == 16 * 1024 * 2 + CTRL_BYTES
+    assert s.world == 1 and not s.has_multicast and s.protocol == "push"
+    assert (s.zone_rows, s.zone_h) == (ZONE_ROWS, 1024)
+    assert s.buf.numel() == 16 * 1024 * 2 + CTRL_BYTES + 4 * ZONE_ROWS * 1024
     assert s.data.shape == (16, 1024) and int(s.buf.sum()) == 0
+    p = s.push_args()
+    assert (p.world, p.rank, p.rows, p.h) == (1, 0, ZONE_ROWS, 1024)
+    assert p.recv == s.base_ptr + s.zone_off and p.recv % 16 == 0
+    assert p.epoch == s.base_ptr + s.data_bytes + 64 and p.ticket == p.epoch + 4
+    assert not p.recv_mc and not p.peer_recv
 
     class A:
         pass
@@ -84,6 +91,118 @@ def test_symm_slot_single_rank_layout():
     assert (a.world, a.rank) == (1, 0)
     with pytest.raises(ValueError):
         s.fill(a, torch.zeros(4, 1024, dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        SymmSlot((16, 1024), torch.bfloat16, device="cpu", protocol="ring")
+    flat = SymmSlot((64,), torch.int32, device="cpu")        # no rows: no landing zone
+    assert flat.zone_bytes == 0
+    with pytest.raises(ValueError):
+        flat.push_args()
+
+
+def test_workspace_hands_out_fixed_aligned_views():
+    """Slots are real views of one buffer from the first request; `freeze()` closes the
+    arena; a key cannot be re-registered with another shape."""
+    from iquestrt_b200.workspace import ALIGN, Workspace
+    ws = Workspace(device="cpu", capacity=1 << 16)
+    a = ws.slot("a", (3, 5), torch.bfloat16)
+    b = ws.slot(("b", 1), (7,), torch.float32)
+    assert a.data_ptr() % ALIGN == 0 and b.data_ptr() % ALIGN == 0
+    assert b.data_ptr() >= a.data_ptr() + 30
+    a.fill_(1.5)
+    assert ws.slot("a", (3, 5), torch.bfloat16) is a and float(a[2, 4]) == 1.5
+    with pytest.raises(ValueError):
+        ws.slot("a", (3, 6), torch.bfloat16)
+    with pytest.raises(MemoryError):
+        ws.slot("big", (1 << 20,), torch.float32)
+    s = ws.slot("sym", (16, 256), torch.bfloat16, symm=True)
+    assert ws.symm_slot_of(s) is not None and ws.symm_slot_of(a) is None
+    before = a.data_ptr()
+    assert ws.freeze() is ws
+    assert ws.slot("a", (3, 5), torch.bfloat16).data_ptr() == before
+    with pytest.raises(RuntimeError):
+        ws.slot("late", (4,), torch.float32)
+    with pytest.raises(ValueError):
+        Workspace(device="cpu", align=1000)
+
+
+def test_block_fp8_helpers_match_the_reference_fixtures():
+    """`iquestrt_b200.blockfp8` (the package's mirror of the reference's module) against
+    outputs of the reference's own functions, bit for bit, and its error behaviour."""
+    from iquestrt_b200 import blockfp8, synth
+    gold = torch.load(os.path.join(os.path.dirname(__file__), "golden", "reference_outputs.pt"),
+                      weights_only=False)
+    d = gold["dequant"]
+    assert torch.equal(blockfp8.dequant(d["q"], d["s"]), d["f64"])
+    assert torch.equal(blockfp8.dequant(d["q"], d["s"], dtype=torch.float32), d["f32"])
+    d = gold["dequant_64x128"]
+    assert torch.equal(blockfp8.dequant(d["q"], d["s"], d["block"], torch.float32), d["f32"])
+    batch = blockfp8.dequant(torch.stack([d["q"], d["q"]]), torch.stack([d["s"], d["s"]]),
+                             d["block"], torch.float32)
+    assert torch.equal(batch[1], d["f32"])
+    with pytest.raises(ValueError):
+        blockfp8.dequant(torch.zeros(256, 256).to(torch.float8_e4m3fn), torch.ones(2, 3))
+    for c in gold["shard_scale"]:
+        got = blockfp8.shard_scale(c["table"], c["dim"], c["start"], c["length"], c["grain"])
+        assert torch.equal(got, c["out"])
+    with pytest.raises(ValueError):
+        blockfp8.shard_scale(gold["shard_scale"][0]["table"], 0, 32, 64, 64)
+    with pytest.raises(ValueError):
+        blockfp8.shard_scale(gold["shard_scale"][0]["table"], 0, 0, 96, 96)
+    assert synth.shard_scale is blockfp8.shard_scale
+
+
+def test_holders_keep_the_reference_call_signatures():
+    """Constructor and call parameters of the reference's holders (names and order as in
+    iquestrt/kernels/{oproj,router,moe_gemv,ar_tail,tail}.py and iquestrt/workspace.py),
+    followed only by keyword-only extensions."""
+    import inspect
+    from iquestrt_b200 import blockfp8, kernels
+    from iquestrt_b200.workspace import Workspace
+
+    def head(fn, n):
+        names = [p.name for p in inspect.signature(fn).parameters.values()
+                 if p.name != "self"]
+        return names[:n]
+
+    def keyword_only(fn, names):
+        params = inspect.signature(fn).parameters
+        return all(params[n].kind is inspect.Parameter.KEYWORD_ONLY for n in names)
+
+    assert head(blockfp8.dequant, 4) == ["q", "scale", "block", "dtype"]
+    assert head(blockfp8.shard_scale, 5) == ["scale", "dim", "start", "length", "grain"]
+    assert head(kernels.OProjGemv.__init__, 4) == ["q_dim", "hidden", "ws", "q_len"]
+    assert keyword_only(kernels.OProjGemv.__init__, ["ws", "q_len"])
+    assert head(kernels.OProjGemv.__call__, 3) == ["ao", "w_o", "w_scale"]
+    assert head(kernels.DenseMlp.__init__, 4) == ["hidden", "inter", "ws", "q_len"]
+    assert head(kernels.DenseMlp.__call__, 6) == ["hn", "w_gate_up", "gate_up_scale", "w_down",
+                                                  "down_scale", "out"]
+    assert head(kernels.RouterSelect.__init__, 6) == ["n_experts", "top_k", "hidden", "device",
+                                                      "ws", "q_len"]
+    assert keyword_only(kernels.RouterSelect.__init__, ["device", "ws", "q_len"])
+    assert head(kernels.RouterSelect.__call__, 2) == ["x_pad", "weight"]
+    assert head(kernels.MoeDecodeKernels.__init__, 7) == ["experts", "topk", "hidden", "i_loc",
+                                                          "ws", "q_len", "live_rows"]
+    assert head(kernels.MoeDecodeKernels.__call__, 7) == ["sel", "wt", "fc", "fc_scale", "proj",
+                                                          "proj_scale", "rows"]
+    assert keyword_only(kernels.MoeDecodeKernels.__call__, ["rows"])
+    for name in ("next_out",):
+        assert callable(getattr(kernels.MoeDecodeKernels, name))
+    assert head(kernels.MultimemARTail.__init__, 3) == ["ao_buffers", "group", "tail"]
+    assert head(kernels.MultimemARTail.__call__, 6) == ["ao", "residual", "w_ao", "w_ffn",
+                                                        "a_scale", "f_scale"]
+    assert head(kernels.MultimemARTail.h_inv_xpad_fp8_pdl_overlap_local, 10) == [
+        "ao", "residual", "w_ao", "w_ffn", "inv_out", "x_pad", "x_pad_fp8", "a_scale", "f_scale",
+        "fp32_residual"]
+    assert keyword_only(kernels.MultimemARTail.h_inv_xpad_fp8_pdl_overlap_local,
+                        ["fp32_residual"])
+    assert head(kernels.MultimemMLPTail.__init__, 4) == ["mlp_buffers", "group", "tail",
+                                                         "norm_out"]
+    assert head(kernels.MultimemMLPTail.__call__, 4) == ["mlp_out", "residual", "f_scale",
+                                                         "w_norm"]
+    assert head(kernels.TailKernels.__init__, 4) == ["hidden", "eps", "ws", "q_len"]
+    assert head(Workspace.__init__, 3) == ["device", "align", "symm_group"]
+    assert head(Workspace.slot, 4) == ["key", "shape", "dtype", "symm"]
+    assert inspect.signature(Workspace.slot).parameters["symm"].default is False
 
 
 def test_abi_library_exports_every_declared_symbol():
@@ -106,32 +225,6 @@ def test_abi_library_exports_every_declared_symbol():
     assert lib.iq_router(C.byref(a), None) == _lib.IQ_ERR_ARG
 
 
-def test_one_launch_context_checks_its_calls():
-    """`ops.one_launch` records the four calls of a layer and launches once on exit; on the
-    host it refuses nesting, a call recorded twice, and an exit with a part missing -- all
-    before anything reaches the library."""
-    from iquestrt_b200 import _lib, ops
-    with pytest.raises(RuntimeError, match="do not nest"):
-        with ops.one_launch():
-            with ops.one_launch():
-                pass
-    assert ops.one_launch._active is None
-    with pytest.raises(RuntimeError, match="called twice"):
-        with ops.one_launch() as ctx:
-            ctx.record("router", _lib.RouterArgs())
-            ctx.record("router", _lib.RouterArgs())
-    assert ops.one_launch._active is None
-    with pytest.raises(RuntimeError, match="no call recorded"):
-        with ops.one_launch() as ctx:
-            ctx.record("oproj", _lib.LinearArgs())
-    assert ops.one_launch._active is None
-    # an exception inside the context propagates and leaves no context open
-    with pytest.raises(ValueError):
-        with ops.one_launch():
-            raise ValueError("inside")
-    assert ops.one_launch._active is None
-
-
 def test_abi_rejects_null_arguments_without_a_gpu():
     """Argument checks come before any CUDA call: every entry point returns IQ_ERR_ARG for a
     null argument block, and the scratch size covers the one-launch layer's own area."""
@@ -148,7 +241,7 @@ def test_abi_rejects_null_arguments_without_a_gpu():
         assert fn(null, null) == _lib.IQ_ERR_ARG, name
     lib.iq_tail.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
     assert lib.iq_tail(null, null, 0) == _lib.IQ_ERR_ARG
-    lib.iq_decode_layer.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
-    assert lib.iq_decode_layer(null, null, 0) == _lib.IQ_ERR_ARG
+    lib.iq_linear_static_status.argtypes = [C.c_void_p, C.c_void_p]
+    assert lib.iq_linear_static_status(null, null) == _lib.IQ_ERR_ARG
     assert lib.iq_status_read(null, null, 0, null) == _lib.IQ_ERR_ARG
-    assert lib.iq_scratch_bytes() >= 7 * 1024 * 1024
+    assert lib.iq_scratch_bytes() >= 4 * 1024 * 1024

@@ -34,7 +34,7 @@ def test_static_work_area_matches_caller_scratch_twice_in_a_row():
         ops.linear(x, w, s, scratch=scratch, out=want)
         assert scratch.status() == 0
         ops.linear_static(x, w, s, got)
-        torch.cuda.synchronize()
+        assert ops.linear_static_status() == 0, f"call {call}"     # synchronises the stream
         assert torch.isfinite(got.float()).all(), f"call {call}"
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"call {call}"
     # and the same shape again right away: counters and ticket were left clean
