@@ -163,6 +163,8 @@ typedef struct iq_linear_args {
   const iq_tail_args* tail;
   int pdl;
   const iq_push_args* push;
+  float* out_f32;           /* optional fp32 [m,n]: the result before its bf16 rounding;
+                               with it `out` may be NULL (then no tail and no push) */
 } iq_linear_args;
 
 int iq_linear(const iq_linear_args* a, void* stream);
@@ -188,6 +190,34 @@ int iq_linear_static(const iq_linear_args* a, void* stream);
  * to *code after synchronising `stream` (0 when no call has been made yet).  Allocates
  * nothing.  It has no counterpart in the reference either. */
 int iq_linear_static_status(int* code, void* stream);
+
+/* The attention prologue after the column-parallel QKV product (iq_linear with out_f32):
+ * per (head, row) the fp32 product is normalised (q and k heads: RMSNorm over the head
+ * with w_qn / w_kn, bf16 result), q and k get the partial rotary embedding over their
+ * first rotary_dim channels (neox halves; products and sum each rounded to bf16), q goes
+ * to q_out and k, v into row slot[row] of the caches (bf16, or e4m3 saturating when
+ * kv_kind is IQ_ACT_E4M3).  Replaces the heads kernel of the reference's prologue
+ * (iquestrt/kernels/prologue.py:147-238 `build_heads`; algebra
+ * iquestrt/model/reference.py:101-112).  head_dim <= 256 and even, rotary_dim even. */
+typedef struct iq_heads_args {
+  const float* qkv;         /* fp32 [m, (q_heads + 2*kv_heads) * head_dim] */
+  int m, q_heads, kv_heads, head_dim, rotary_dim;
+  const float* w_qn;        /* [head_dim] fp32 */
+  const float* w_kn;
+  const void* cos;          /* bf16 [m, rotary_dim] */
+  const void* sin;
+  float eps;
+  const int64_t* slot;      /* [m] cache rows */
+  void* q_out;              /* bf16 [m, q_heads, head_dim] */
+  void* k_cache;            /* [capacity, kv_heads, head_dim] */
+  void* v_cache;
+  int capacity;
+  int kv_kind;              /* IQ_ACT_BF16 or IQ_ACT_E4M3 */
+  int* status;              /* optional device status word: IQ_ERR_ROUTE on a slot out of range */
+  int pdl;
+} iq_heads_args;
+
+int iq_qkv_heads(const iq_heads_args* a, void* stream);
 
 /* Router: logits = x[m,h] bf16 . w[e,h]^T bf16 (fp32 accumulate), top_k with ties to the
  * lower expert id, weights = softmax over the selected logits (reference) or their

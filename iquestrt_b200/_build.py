@@ -37,13 +37,16 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Compile the library if it is missing or older than its sources; returns its path."""
     if not force and not stale():
         return LIB
-    cmd = [_nvcc(), *NVCC_FLAGS, "-o", LIB, *(os.path.join(CSRC, s) for s in SOURCES)]
+    # compile beside the target and rename: a reader never sees a half-written library
+    staged = LIB + ".new"
+    cmd = [_nvcc(), *NVCC_FLAGS, "-o", staged, *(os.path.join(CSRC, s) for s in SOURCES)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed:\n{proc.stdout}\n{proc.stderr}")
+    os.replace(staged, LIB)
     if verbose:
         print(proc.stderr)
     return LIB

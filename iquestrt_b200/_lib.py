@@ -25,8 +25,8 @@ ROUTE_SOFTMAX, ROUTE_SIGMOID = range(2)
 ACT_E4M3, ACT_BF16 = range(2)
 
 EXPORTS = ("iq_scratch_bytes", "iq_status_read", "iq_sm_count", "iq_tail", "iq_linear",
-           "iq_linear_static", "iq_linear_static_status", "iq_router", "iq_moe_gate",
-           "iq_moe_down")
+           "iq_linear_static", "iq_linear_static_status", "iq_qkv_heads", "iq_router",
+           "iq_moe_gate", "iq_moe_down")
 
 
 class IqError(RuntimeError):
@@ -63,6 +63,19 @@ class LinearArgs(C.Structure):
         ("w", C.c_void_p), ("w_scale", C.c_void_p), ("rg", C.c_int), ("kg", C.c_int),
         ("out", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
         ("tail", C.POINTER(TailArgs)), ("pdl", C.c_int), ("push", C.POINTER(PushArgs)),
+        ("out_f32", C.c_void_p),
+    ]
+
+
+class HeadsArgs(C.Structure):
+    _fields_ = [
+        ("qkv", C.c_void_p),
+        ("m", C.c_int), ("q_heads", C.c_int), ("kv_heads", C.c_int), ("head_dim", C.c_int),
+        ("rotary_dim", C.c_int),
+        ("w_qn", C.c_void_p), ("w_kn", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p),
+        ("eps", C.c_float), ("slot", C.c_void_p), ("q_out", C.c_void_p),
+        ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("capacity", C.c_int),
+        ("kv_kind", C.c_int), ("status", C.c_void_p), ("pdl", C.c_int),
     ]
 
 
@@ -128,7 +141,7 @@ def load() -> C.CDLL:
         lib.iq_tail.restype = C.c_int
         lib.iq_tail.argtypes = [C.POINTER(TailArgs), C.c_void_p, C.c_int]
         for name, struct in (("iq_linear", LinearArgs), ("iq_linear_static", LinearArgs),
-                             ("iq_router", RouterArgs),
+                             ("iq_qkv_heads", HeadsArgs), ("iq_router", RouterArgs),
                              ("iq_moe_gate", MoeGateArgs), ("iq_moe_down", MoeDownArgs)):
             fn = getattr(lib, name)
             fn.restype = C.c_int

@@ -82,7 +82,7 @@ __device__ inline Carve<G> carve(uint8_t* base, const StreamShape& sh) {
 }
 
 // ------------------------------------------------------------------------------------
-// Activation staging (consumer threads only, tid in [0, 256)).
+// Activation staging (the CTA's `nthr` consumer threads, tid in [0, nthr)).
 
 // Both routines issue a batch of independent 16-byte global loads before touching any of
 // them, so a row set costs about one memory latency instead of one per group.  The loads
@@ -93,18 +93,19 @@ constexpr int kStageBatch = 8;
 // Raw e4m3 rows (16-byte vectors) + their scales (or 1).
 __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape& sh,
                                        const uint8_t* src, size_t src_pitch,
-                                       const float* src_scale, int rows, int k, int tid) {
+                                       const float* src_scale, int rows, int k, int tid,
+                                       int nthr) {
   const int vec = k / 16, nvec = rows * vec;
   // the first activation scale of this thread rides along with the first batch of loads
   const int nxs = rows * sh.x_blocks;
   float xs_first = 1.0f;
   if (src_scale && tid < nxs) xs_first = __ldcg(src_scale + tid);
-  for (int v0 = 0; v0 < nvec; v0 += kConsumerThreads * kStageBatch) {
+  for (int v0 = 0; v0 < nvec; v0 += nthr * kStageBatch) {
     uint4 raw[kStageBatch];
 #pragma unroll
     for (int j = 0; j < kStageBatch; ++j) {
-      if (v0 + j * kConsumerThreads >= nvec) break;   // same for every thread
-      const int i = v0 + j * kConsumerThreads + tid;
+      if (v0 + j * nthr >= nvec) break;   // same for every thread
+      const int i = v0 + j * nthr + tid;
       if (i < nvec) {
         const int r = i / vec, v = i - r * vec;
         raw[j] = __ldcg(reinterpret_cast<const uint4*>(src + r * src_pitch + v * 16));
@@ -112,8 +113,8 @@ __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape
     }
 #pragma unroll
     for (int j = 0; j < kStageBatch; ++j) {
-      if (v0 + j * kConsumerThreads >= nvec) break;
-      const int i = v0 + j * kConsumerThreads + tid;
+      if (v0 + j * nthr >= nvec) break;
+      const int i = v0 + j * nthr + tid;
       if (i < nvec) {
         const int r = i / vec, v = i - r * vec;
         *reinterpret_cast<uint4*>(xq + r * sh.x_pitch + v * 16) = raw[j];
@@ -121,7 +122,7 @@ __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape
     }
   }
   if (tid < nxs) xs[tid] = xs_first;
-  for (int i = tid + kConsumerThreads; i < nxs; i += kConsumerThreads)
+  for (int i = tid + nthr; i < nxs; i += nthr)
     xs[i] = src_scale ? __ldcg(src_scale + i) : 1.0f;
 }
 
@@ -131,14 +132,14 @@ __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape
 // 2r+1 (the e4m3 of what the first term missed), both under the same scale.
 __device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const StreamShape& sh,
                                               const __nv_bfloat16* src, size_t src_pitch,
-                                              int rows, int k, bool split2, int tid) {
+                                              int rows, int k, bool split2, int tid, int nthr) {
   const int vec = k / 8, nvec = rows * vec;
-  for (int v0 = 0; v0 < nvec; v0 += kConsumerThreads * kStageBatch) {
+  for (int v0 = 0; v0 < nvec; v0 += nthr * kStageBatch) {
     uint4 raw[kStageBatch];
 #pragma unroll
     for (int j = 0; j < kStageBatch; ++j) {
-      if (v0 + j * kConsumerThreads >= nvec) break;   // same for every thread
-      const int i = v0 + j * kConsumerThreads + tid;
+      if (v0 + j * nthr >= nvec) break;   // same for every thread
+      const int i = v0 + j * nthr + tid;
       raw[j] = make_uint4(0u, 0u, 0u, 0u);
       if (i < nvec) {
         const int r = i / vec, v = i - r * vec;
@@ -147,8 +148,8 @@ __device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const Stre
     }
 #pragma unroll
     for (int j = 0; j < kStageBatch; ++j) {
-      if (v0 + j * kConsumerThreads >= nvec) break;    // whole batch dead: nothing to do
-      const int i = v0 + j * kConsumerThreads + tid;   // uniform trip count: shuffles below
+      if (v0 + j * nthr >= nvec) break;    // whole batch dead: nothing to do
+      const int i = v0 + j * nthr + tid;   // uniform trip count: shuffles below
       const bool live = i < nvec;
       const int ii = live ? i : 0;
       const int r = ii / vec, v = ii - r * vec;
@@ -242,6 +243,7 @@ struct TailParams {
   PushView pv;
   int push;      // 1: rows arrive through the landing zone
   int n_tail;    // CTAs that share the rows
+  int per_round; // sources a tail CTA polls at a time
 };
 
 __device__ inline void bf16x8_to_f32(const U4& u, float (&f)[8]) {
@@ -285,7 +287,11 @@ __device__ inline float block_sum(float v, float* slots, const BlockBar& bar) {
   return s;
 }
 
-constexpr int kTailVecs = 2;   // 16-byte vectors of a row per thread: h <= 8 * 2 * threads
+// The tail runs on 256 threads wherever it runs (a tail CTA of any streaming kernel, the
+// last CTA of the pull protocol, the tail kernel), so that its block-wide sums add in one
+// order and every form gives the same bits.
+constexpr int kTailThreads = 256;
+constexpr int kTailVecs = 3;   // 16-byte vectors of a row per thread: h <= 8 * 3 * 256 = 6144
 
 __device__ __forceinline__ void ldg_f32x8(const float* p, float (&v)[8]) {
   const float4 a = __ldg(reinterpret_cast<const float4*>(p));
@@ -297,82 +303,97 @@ __device__ __forceinline__ void ldg_f32x8(const float* p, float (&v)[8]) {
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
 }
 
 // Row `r` of the landing zone, summed over the source ranks in rank order (fp32, one bf16
-// rounding), for this thread's vectors.  Every (vector, source) chunk of 8 words is copied
-// into shared memory `zs` ([world][h] words) with asynchronous 16-byte copies that go to
-// L2, all of them in flight together; a chunk whose words do not all show `tag` yet is
-// copied again.  A thread reads back only what it copied itself.  Returns false when the
-// budget ran out.
-__device__ __forceinline__ bool poll_zone_row(const PushView& pv, uint32_t* zs, int r,
-                                              uint32_t tag, int tid, int nthr, int vec_per_row,
-                                              uint64_t budget_ns, float (&f)[kTailVecs][8]) {
+// rounding), for this thread's vectors.  The sources are taken `per_round` at a time (as
+// many as the CTA's shared memory `zs` holds rows for: [per_round][h] words): every
+// (vector, source) chunk of 8 words of a round is copied into shared memory with
+// asynchronous 16-byte copies that go to L2, all of them in flight together; a chunk whose
+// words do not all show `tag` yet is copied again; a complete round is added up and the
+// next one starts.  A thread reads back only what it copied itself.  Returns false when
+// the budget ran out.
+__device__ __forceinline__ bool poll_zone_row(const PushView& pv, uint32_t* zs, int per_round,
+                                              int r, uint32_t tag, int tid, int nthr,
+                                              int vec_per_row, uint64_t budget_ns,
+                                              float (&f)[kTailVecs][8]) {
   const size_t src_stride = static_cast<size_t>(pv.rows) * pv.h;
   const uint32_t* row0 = pv.recv + static_cast<size_t>(r) * pv.h;
   const uint32_t zs_s = smem_u32(zs);
-  uint32_t pend = 0;                                      // bit i*8+p: chunk still incomplete
+  float acc[kTailVecs][8];
 #pragma unroll
   for (int i = 0; i < kTailVecs; ++i)
-    if (tid + i * nthr < vec_per_row) pend |= ((1u << pv.world) - 1u) << (8 * i);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
   uint64_t t0 = 0;
   bool ok = true;
-  while (pend) {
+  for (int p0 = 0; p0 < pv.world && ok; p0 += per_round) {
+    const int np = pv.world - p0 < per_round ? pv.world - p0 : per_round;
+    uint32_t pend = 0;                                    // bit i*8+p: chunk still incomplete
+#pragma unroll
+    for (int i = 0; i < kTailVecs; ++i)
+      if (tid + i * nthr < vec_per_row) pend |= ((1u << np) - 1u) << (8 * i);
+    while (pend) {
+#pragma unroll
+      for (int i = 0; i < kTailVecs; ++i) {
+        const int v = tid + i * nthr;
+        for (int p = 0; p < np; ++p) {
+          if (!((pend >> (8 * i + p)) & 1u)) continue;
+          const uint32_t* src = row0 + (p0 + p) * src_stride + v * 8;
+          const uint32_t dst = zs_s + (p * pv.h + v * 8) * 4;
+          cp_async16(dst, src);
+          cp_async16(dst + 16, src + 4);
+        }
+      }
+      cp_async_wait_all();
+#pragma unroll
+      for (int i = 0; i < kTailVecs; ++i) {
+        const int v = tid + i * nthr;
+        for (int p = 0; p < np; ++p) {
+          if (!((pend >> (8 * i + p)) & 1u)) continue;
+          const uint4 lo = lds128(zs_s + (p * pv.h + v * 8) * 4);
+          const uint4 hi = lds128(zs_s + (p * pv.h + v * 8) * 4 + 16);
+          const uint32_t all = (lo.x >> 16 == tag) & (lo.y >> 16 == tag) & (lo.z >> 16 == tag) &
+                               (lo.w >> 16 == tag) & (hi.x >> 16 == tag) & (hi.y >> 16 == tag) &
+                               (hi.z >> 16 == tag) & (hi.w >> 16 == tag);
+          if (all) pend &= ~(1u << (8 * i + p));
+        }
+      }
+      if (pend) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > budget_ns) { ok = false; break; }
+      }
+    }
+    if (!ok) break;
 #pragma unroll
     for (int i = 0; i < kTailVecs; ++i) {
       const int v = tid + i * nthr;
-      for (int p = 0; p < pv.world; ++p) {
-        if (!((pend >> (8 * i + p)) & 1u)) continue;
-        const uint32_t* src = row0 + p * src_stride + v * 8;
-        const uint32_t dst = zs_s + (p * pv.h + v * 8) * 4;
-        cp_async16(dst, src);
-        cp_async16(dst + 16, src + 4);
-      }
-    }
-    cp_async_wait_all();
-#pragma unroll
-    for (int i = 0; i < kTailVecs; ++i) {
-      const int v = tid + i * nthr;
-      for (int p = 0; p < pv.world; ++p) {
-        if (!((pend >> (8 * i + p)) & 1u)) continue;
+      if (v >= vec_per_row) continue;
+      for (int p = 0; p < np; ++p) {
         const uint4 lo = lds128(zs_s + (p * pv.h + v * 8) * 4);
         const uint4 hi = lds128(zs_s + (p * pv.h + v * 8) * 4 + 16);
-        const uint32_t all = (lo.x >> 16 == tag) & (lo.y >> 16 == tag) & (lo.z >> 16 == tag) &
-                             (lo.w >> 16 == tag) & (hi.x >> 16 == tag) & (hi.y >> 16 == tag) &
-                             (hi.z >> 16 == tag) & (hi.w >> 16 == tag);
-        if (all) pend &= ~(1u << (8 * i + p));
+        acc[i][0] += __uint_as_float(lo.x << 16); acc[i][1] += __uint_as_float(lo.y << 16);
+        acc[i][2] += __uint_as_float(lo.z << 16); acc[i][3] += __uint_as_float(lo.w << 16);
+        acc[i][4] += __uint_as_float(hi.x << 16); acc[i][5] += __uint_as_float(hi.y << 16);
+        acc[i][6] += __uint_as_float(hi.z << 16); acc[i][7] += __uint_as_float(hi.w << 16);
       }
-    }
-    if (pend) {
-      const uint64_t now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > budget_ns) { ok = false; break; }
     }
   }
 #pragma unroll
-  for (int i = 0; i < kTailVecs; ++i) {
-    const int v = tid + i * nthr;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (ok && v < vec_per_row) {
-      for (int p = 0; p < pv.world; ++p) {
-        const uint4 lo = lds128(zs_s + (p * pv.h + v * 8) * 4);
-        const uint4 hi = lds128(zs_s + (p * pv.h + v * 8) * 4 + 16);
-        acc[0] += __uint_as_float(lo.x << 16); acc[1] += __uint_as_float(lo.y << 16);
-        acc[2] += __uint_as_float(lo.z << 16); acc[3] += __uint_as_float(lo.w << 16);
-        acc[4] += __uint_as_float(hi.x << 16); acc[5] += __uint_as_float(hi.y << 16);
-        acc[6] += __uint_as_float(hi.z << 16); acc[7] += __uint_as_float(hi.w << 16);
-      }
-    }
-    bf16x8_to_f32(f32_to_bf16x8(acc), f[i]);
-  }
+  for (int i = 0; i < kTailVecs; ++i) bf16x8_to_f32(f32_to_bf16x8(acc[i]), f[i]);
   return ok;
 }
 
 // Runs on the threads of `bar` (a multiple of 32; h <= 16 * threads) for rows r_begin,
 // r_begin + r_step, ... of the call.  `red` is shared memory for 4 x 32 floats, `sflag`
-// one shared int, `zs` (push only) shared memory for world x h words.  Without `kPush`,
+// one shared int, `park` shared memory for h x 4 bytes (the residual row waits there),
+// `zs` (push only) shared memory for per_round x h words.  Without `kPush`,
 // rows written by other CTAs of this launch must already be visible (the caller passed
 // the ticket) and the pull protocol's signal / wait / switch read applies for world > 1.
 // Each row is handled entirely in registers and each RMSNorm costs one block barrier.  The
@@ -381,10 +402,12 @@ __device__ __forceinline__ bool poll_zone_row(const PushView& pv, uint32_t* zs, 
 // (the residual stays packed until it is used; each norm weight is fetched just before
 // the barrier of the reduction that precedes its use, which hides its latency).
 template <bool kPush>
-__device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& pv, uint32_t* zs,
-                                         float* red, int* sflag, const BlockBar bar = BlockBar{},
-                                         int r_begin = 0, int r_step = 1) {
+__device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& pv, uint8_t* park,
+                                         uint32_t* zs, int per_round, float* red, int* sflag,
+                                         const BlockBar bar = BlockBar{}, int r_begin = 0,
+                                         int r_step = 1) {
   const int tid = threadIdx.x, nthr = bar.threads();
+  const uint32_t res_s = smem_u32(park);
   const int m = a.m, h = a.h, vec_per_row = h / 8;
   const float inv_h = 1.0f / static_cast<float>(h);
   const bool attn = a.kind == IQ_TAIL_ATTN;
@@ -399,8 +422,9 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
     const size_t row_off = static_cast<size_t>(r) * h;
     float* slots0 = red + (r & 1) * 64;        // two reductions per row, alternating rows
     float* slots1 = slots0 + 32;
-    // ---- the row's residual, issued before the cross-rank wait and kept packed
-    uint4 res_raw[kTailVecs][2];
+    // ---- the row's residual: copied asynchronously into this thread's own 32-byte slots
+    // of shared memory before the cross-rank wait, so that it costs no registers while the
+    // row is awaited (a spilled register would cost an L2 round trip here)
 #pragma unroll
     for (int i = 0; i < kTailVecs; ++i) {
       const int v = tid + i * nthr;
@@ -408,18 +432,19 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
       const size_t off = row_off + static_cast<size_t>(v) * 8;
       if (a.residual_fp32) {
         const float* rp = static_cast<const float*>(a.residual) + off;
-        res_raw[i][0] = __ldcg(reinterpret_cast<const uint4*>(rp));
-        res_raw[i][1] = __ldcg(reinterpret_cast<const uint4*>(rp + 4));
+        cp_async16(res_s + v * 32, rp);
+        cp_async16(res_s + v * 32 + 16, rp + 4);
       } else {
-        res_raw[i][0] = __ldcg(
-            reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.residual) + off));
+        cp_async16(res_s + v * 32, static_cast<const __nv_bfloat16*>(a.residual) + off);
       }
     }
+    cp_async_commit();
     float f[kTailVecs][8];
     if (kPush) {
       // ---- the row arrives in the landing zone: poll it, add the ranks
       const uint64_t budget = 1000000ull * (a.timeout_ms ? a.timeout_ms : 2000u);
-      if (!poll_zone_row(pv, zs, r, tag, tid, nthr, vec_per_row, budget, f)) *sflag = 0;
+      if (!poll_zone_row(pv, zs, per_round, r, tag, tid, nthr, vec_per_row, budget, f))
+        *sflag = 0;
       bar.sync();
       if (!*sflag) {
         // A source is missing: leave the outputs untouched and let the host read the status.
@@ -496,6 +521,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
         }
         bf16x8_to_f32(part, f[i]);
       }
+      cp_async_wait_all();     // the residual (push: the zone's poll has waited for it)
     }
 
     float wv[kTailVecs][8];    // w_first, later w_norm
@@ -520,13 +546,15 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
       if (v >= vec_per_row) continue;
       const size_t off = row_off + static_cast<size_t>(v) * 8;
       float res[8];
+      const uint4 ra = lds128(res_s + v * 32);
       if (a.residual_fp32) {
-        const float* r0 = reinterpret_cast<const float*>(&res_raw[i][0]);
-        const float* r1 = reinterpret_cast<const float*>(&res_raw[i][1]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { res[j] = r0[j]; res[4 + j] = r1[j]; }
+        const uint4 rb = lds128(res_s + v * 32 + 16);
+        res[0] = __uint_as_float(ra.x); res[1] = __uint_as_float(ra.y);
+        res[2] = __uint_as_float(ra.z); res[3] = __uint_as_float(ra.w);
+        res[4] = __uint_as_float(rb.x); res[5] = __uint_as_float(rb.y);
+        res[6] = __uint_as_float(rb.z); res[7] = __uint_as_float(rb.w);
       } else {
-        bf16x8_to_f32(U4{res_raw[i][0].x, res_raw[i][0].y, res_raw[i][0].z, res_raw[i][0].w}, res);
+        bf16x8_to_f32(U4{ra.x, ra.y, ra.z, ra.w}, res);
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -595,15 +623,16 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
 
 // A tail CTA of the push protocol: CTA `index` of `n_tail` finishes rows index,
 // index + n_tail, ...  The last tail CTA to finish closes the call (the zone's epoch moves
-// on once every tail CTA has read it).  Sixteen warps run the tail wherever it runs, so
-// its block-wide sums add in one order.
-__device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& pv, int index,
-                                         int n_tail, uint8_t* smem) {
+// on once every tail CTA has read it).
+__device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& pv, int per_round,
+                                         int index, int n_tail, uint8_t* smem) {
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
-  uint32_t* zs = reinterpret_cast<uint32_t*>(smem + 1024);
-  if (threadIdx.x < kConsumerThreads)
-    run_tail<true>(a, pv, zs, red, sflag, BlockBar{2, kConsumerThreads}, index, n_tail);
+  uint8_t* park = smem + 1024;
+  uint32_t* zs = reinterpret_cast<uint32_t*>(smem + 1024 + static_cast<size_t>(a.h) * 4);
+  if (threadIdx.x < kTailThreads)
+    run_tail<true>(a, pv, park, zs, per_round, red, sflag, BlockBar{2, kTailThreads}, index,
+                   n_tail);
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -615,24 +644,30 @@ __device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& 
   }
 }
 
-// Shared memory a tail CTA of the push protocol needs.
-__host__ __device__ inline size_t tail_cta_smem(int world, int h) {
-  return 1024 + static_cast<size_t>(world) * h * 4;
+// Sources a tail CTA takes per round when it may use `limit` bytes of shared memory, and
+// the shared memory that takes.
+__host__ __device__ inline int tail_sources_per_round(int world, int h, size_t limit) {
+  const size_t row = static_cast<size_t>(h) * 4;
+  int n = limit > 1024 + 2 * row ? static_cast<int>((limit - 1024 - row) / row) : 0;
+  return n > world ? world : n;
+}
+// (control words, the parked residual row, the rows of one round)
+__host__ __device__ inline size_t tail_cta_smem(int per_round, int h) {
+  return 1024 + static_cast<size_t>(per_round + 1) * h * 4;
 }
 
-__global__ void __launch_bounds__(kThreads, 1) tail_kernel(const TailParams p) {
+__global__ void __launch_bounds__(kTailThreads) tail_kernel(const TailParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_wait();
   pdl_launch_dependents();   // after the wait: see the note on `after_wait` below
   if (p.push) {
-    tail_cta(p.a, p.pv, static_cast<int>(blockIdx.x), p.n_tail, smem);
+    tail_cta(p.a, p.pv, p.per_round, static_cast<int>(blockIdx.x), p.n_tail, smem);
     return;
   }
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
-  if (threadIdx.x < kConsumerThreads)
-    run_tail<false>(p.a, p.pv, nullptr, red, sflag, BlockBar{2, kConsumerThreads},
-                    static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+  run_tail<false>(p.a, p.pv, smem + 1024, nullptr, 0, red, sflag, BlockBar{},
+                  static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
 }
 
 // Programmatic dependent launch discipline shared by the kernels: a CTA lets its
@@ -664,10 +699,12 @@ struct LinearParams {
   const uint8_t* w;
   const float* w_scale;
   __nv_bfloat16* out;
+  float* out_f32;           // optional fp32 copy of the result
   void* scratch;
   int tail_run;             // TailRun
   int n_tail;               // tail CTAs at the end of the grid (kTailCtas)
   int push;                 // the epilogue also sends the rows to the landing zone
+  int per_round;            // sources a tail CTA polls at a time
   iq_tail_args tail;
   PushView pv;
 };
@@ -692,7 +729,7 @@ __device__ __forceinline__ void store_row4(__nv_bfloat16* out, size_t index, con
 }
 
 template <class G>
-__global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_constant__ LinearParams p) {
+__global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(const __grid_constant__ LinearParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const StreamShape& sh = p.sh;
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -701,7 +738,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
   const int stream_ctas = static_cast<int>(gridDim.x) - p.n_tail;
   if (cta >= stream_ctas) {
     after_wait();
-    tail_cta(p.tail, p.pv, cta - stream_ctas, p.n_tail, smem);
+    tail_cta(p.tail, p.pv, p.per_round, cta - stream_ctas, p.n_tail, smem);
     return;
   }
   const Carve<G> cv = carve<G>(smem, sh);
@@ -710,7 +747,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   stream_init<G>(sh, cv.sm);
-  if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1))
+  if (tid == G::PRODUCER_WARP * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1))
     prefetch_tensormap(&p.map0);   // only a map the host filled (K-sliced stages)
   if (tid == 0) {
     GroupDesc& g = cv.sm->groups[0];
@@ -727,22 +764,23 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
   __syncthreads();
   {
     const CtaWork wk = cta_share<G>(sh, stream_ctas, cta, grid);
-    if (warp == kProducerWarp) {
+    if (warp == G::PRODUCER_WARP) {
       // Weights never change: start streaming before the predecessor kernel has finished.
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
       pdl_wait();
-    } else if (warp < kConsumerWarps) {
+    } else if (warp < G::WARPS) {
       float held[kGatherHeld];
       gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);   // weights: before the wait
       after_wait();
       if (p.x_kind == IQ_X_BF16_GROUPQ || p.x_kind == IQ_X_BF16_SPLIT2)
         stage_rows_bf16_groupq(cv.xq, cv.xs, sh, static_cast<const __nv_bfloat16*>(p.x), p.k, p.m,
-                               p.k, p.x_kind == IQ_X_BF16_SPLIT2, tid);
+                               p.k, p.x_kind == IQ_X_BF16_SPLIT2, tid, G::CONSUMER_THREADS);
       else
         stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.x), p.k,
-                        p.x_kind == IQ_X_E4M3_GROUP ? p.x_scale : nullptr, p.m, p.k, tid);
+                        p.x_kind == IQ_X_E4M3_GROUP ? p.x_scale : nullptr, p.m, p.k, tid,
+                        G::CONSUMER_THREADS);
       gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
-      named_bar_sync(1, kConsumerThreads);
+      named_bar_sync(1, G::CONSUMER_THREADS);
       consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
     } else {
       pdl_wait();
@@ -767,7 +805,12 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
             row = col >> 1;
             live = (col & 1) == 0 && row < m;
           }
-          if (live) store_row4(out, static_cast<size_t>(row) * n + feat, v, push, pv, tag, row, feat);
+          if (live) {
+            const size_t index = static_cast<size_t>(row) * n + feat;
+            if (p.out_f32)
+              *reinterpret_cast<float4*>(p.out_f32 + index) = make_float4(v[0], v[1], v[2], v[3]);
+            if (out) store_row4(out, index, v, push, pv, tag, row, feat);
+          }
         }
       };
       epilogue<G, true>(sh, cv.sm, wk, total, grid, cta, scr, emit);
@@ -775,9 +818,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const __grid_consta
   }
   if (p.tail_run == kTailLastCta && last_cta<G>(cv.sm, scr, gridDim.x)) {
     float* red = reinterpret_cast<float*>(cv.sm->red);
-    if (threadIdx.x < kConsumerThreads)
-      run_tail<false>(p.tail, p.pv, nullptr, red, &cv.sm->is_last_tile,
-                      BlockBar{2, kConsumerThreads});
+    if (threadIdx.x < kTailThreads)
+      run_tail<false>(p.tail, p.pv, cv.ring, nullptr, 0, red, &cv.sm->is_last_tile,
+                      BlockBar{2, kTailThreads});   // (the ring is idle now)
   }
   stream_drain_on_abort<G>(cv.sm);
 }
@@ -876,7 +919,7 @@ __device__ void select_row(const float* logits, int e, int top_k, int score, int
 // side.  The tag is the scratch's launch counter, which the selecting CTA advances when
 // it is done.
 template <class G>
-__global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_constant__ RouterParams p) {
+__global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(const __grid_constant__ RouterParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const StreamShape& sh = p.sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -929,7 +972,7 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   stream_init<G>(sh, cv.sm);
-  if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1))
+  if (tid == G::PRODUCER_WARP * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1))
     prefetch_tensormap(&p.map0);   // only a map the host filled (K-sliced stages)
   if (tid == 0) {
     GroupDesc& g = cv.sm->groups[0];
@@ -946,20 +989,20 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
   __syncthreads();
   {
     const CtaWork wk = cta_share<G>(sh, stream_ctas, cta, grid);
-    if (warp == kProducerWarp) {
+    if (warp == G::PRODUCER_WARP) {
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
       pdl_wait();
-    } else if (warp < kConsumerWarps) {
+    } else if (warp < G::WARPS) {
       after_wait();
       if (wk.n_items > 0) {
         const int vec = p.h / 8;   // 16-byte vectors per bf16 row
-        for (int i = tid; i < p.m * vec; i += kConsumerThreads) {
+        for (int i = tid; i < p.m * vec; i += G::CONSUMER_THREADS) {
           const int r = i / vec, v = i - r * vec;
           *reinterpret_cast<uint4*>(cv.xq + r * sh.x_pitch + v * 16) =
               *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(r) * p.h + v * 8);
         }
       }
-      named_bar_sync(1, kConsumerThreads);
+      named_bar_sync(1, G::CONSUMER_THREADS);
       consume<G, ElemBF16>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
     } else {
       pdl_wait();
@@ -976,6 +1019,74 @@ __global__ void __launch_bounds__(kThreads, 1) router_kernel(const __grid_consta
     }
   }
   stream_drain_on_abort<G>(cv.sm);
+}
+
+// ------------------------------------------------------------------------------------
+// iq_qkv_heads: the attention prologue after the QKV product.  One CTA per (head, row),
+// one thread per channel pair's half: thread d owns channel d of the head.
+struct HeadsParams {
+  iq_heads_args a;
+};
+
+__global__ void __launch_bounds__(256) heads_kernel(const HeadsParams p) {
+  __shared__ float red[8];
+  __shared__ __nv_bfloat16 row[256];
+  const iq_heads_args& a = p.a;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int head = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
+  const int hd = a.head_dim, lane = d & 31, warp = d >> 5, nwarps = (blockDim.x + 31) >> 5;
+  const bool is_q = head < a.q_heads, is_k = !is_q && head < a.q_heads + a.kv_heads;
+  const int width = (a.q_heads + 2 * a.kv_heads) * hd;
+  const bool live = d < hd;
+  const float x = live ? a.qkv[static_cast<size_t>(r) * width + head * hd + d] : 0.f;
+  long long slot = 0;
+  if (!is_q) {
+    slot = a.slot[r];
+    if (slot < 0 || slot >= a.capacity) {
+      if (d == 0) set_status(a.status, IQ_ERR_ROUTE);
+      return;
+    }
+  }
+  auto store_kv = [&](void* cache, int kv_head, int ch, __nv_bfloat16 v) {
+    const size_t o = (static_cast<size_t>(slot) * a.kv_heads + kv_head) * hd + ch;
+    if (a.kv_kind == IQ_ACT_E4M3)
+      static_cast<uint8_t*>(cache)[o] = f32_to_e4m3_sat(__bfloat162float(v));
+    else
+      static_cast<__nv_bfloat16*>(cache)[o] = v;
+  };
+  if (!is_q && !is_k) {                        // a v head: round and store
+    if (live) store_kv(a.v_cache, head - a.q_heads - a.kv_heads, d, __float2bfloat16_rn(x));
+    return;
+  }
+  // RMSNorm over the head in fp32: warp sums in lane order, then the warps in order
+  float ss = warp_sum(x * x);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  ss = 0.f;
+  for (int w = 0; w < nwarps; ++w) ss += red[w];
+  const float inv = rsqrtf(ss / static_cast<float>(hd) + a.eps);
+  const float wn = live ? (is_q ? a.w_qn[d] : a.w_kn[d]) : 0.f;
+  if (live) row[d] = __float2bfloat16_rn(wn * (x * inv));
+  __syncthreads();
+  if (!live) return;
+  // Partial rotary embedding: channel i pairs with i + half inside the first rotary_dim
+  // channels; each product and the sum are rounded to bf16.
+  __nv_bfloat16 o = row[d];
+  const int rot = a.rotary_dim, half = rot / 2;
+  if (d < rot) {
+    const __nv_bfloat16* cs = static_cast<const __nv_bfloat16*>(a.cos) + static_cast<size_t>(r) * rot;
+    const __nv_bfloat16* sn = static_cast<const __nv_bfloat16*>(a.sin) + static_cast<size_t>(r) * rot;
+    const float mine = __bfloat162float(row[d]);
+    const float other = d < half ? -__bfloat162float(row[d + half]) : __bfloat162float(row[d - half]);
+    const float t0 = bf16_round(mine * __bfloat162float(cs[d]));
+    const float t1 = bf16_round(other * __bfloat162float(sn[d]));
+    o = __float2bfloat16_rn(t0 + t1);
+  }
+  if (is_q)
+    static_cast<__nv_bfloat16*>(a.q_out)[(static_cast<size_t>(r) * a.q_heads + head) * hd + d] = o;
+  else
+    store_kv(a.k_cache, head - a.q_heads, d, o);
 }
 
 // ------------------------------------------------------------------------------------
@@ -1159,9 +1270,11 @@ template <class G>
 __device__ __forceinline__ void gate_stage_x(const GateParams& p, const StreamShape& sh,
                                              const Carve<G>& cv, int tid) {
   if (p.x_bf16)
-    stage_rows_bf16_groupq(cv.xq, cv.xs, sh, p.x_bf16, p.mc.h, p.mc.m, p.mc.h, false, tid);
+    stage_rows_bf16_groupq(cv.xq, cv.xs, sh, p.x_bf16, p.mc.h, p.mc.m, p.mc.h, false, tid,
+                           G::CONSUMER_THREADS);
   else
-    stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid);
+    stage_rows_e4m3(cv.xq, cv.xs, sh, p.x_fp8, p.mc.h, p.x_scale, p.mc.m, p.mc.h, tid,
+                    G::CONSUMER_THREADS);
 }
 
 // One stream of the Gate: the tiles of `wk`, every role with its ring / reduction position
@@ -1172,17 +1285,17 @@ __device__ __forceinline__ void gate_stream(const GateParams& p, const StreamSha
                                             const CtaWork& wk, long long total, int grid, int cta,
                                             bool stage_x, RingPos& pos, RedPos& rpos) {
   const int tid = threadIdx.x, warp = tid >> 5;
-  if (warp == kProducerWarp) {
+  if (warp == G::PRODUCER_WARP) {
     // (both of the Gate's streams are consumed as they arrive: the first ahead of the
     // dependency wait by design, the second after every role has passed it)
     produce<G>(sh, cv.sm, cv.sm->groups, cv.ring, G::STAGE_BYTES, wk, scr.status, &p.map0, &p.map1,
                pos, false);
-  } else if (warp < kConsumerWarps) {
+  } else if (warp < G::WARPS) {
     float held[kGatherHeld];
     gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);
     if (stage_x) gate_stage_x<G>(p, sh, cv, tid);
     gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
-    named_bar_sync(1, kConsumerThreads);
+    named_bar_sync(1, G::CONSUMER_THREADS);
     consume<G, ElemE4M3>(sh, cv.sm, cv.sm->groups, cv.ring, G::STAGE_BYTES, cv.xq, cv.xs, cv.sc, wk,
                          scr, pos, rpos);
   } else {
@@ -1211,7 +1324,7 @@ __device__ __forceinline__ void gate_stream(const GateParams& p, const StreamSha
 }
 
 template <class G>
-__global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant__ GateParams p) {
+__global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) gate_kernel(const __grid_constant__ GateParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   StreamShape sh = p.sh;
   const Carve<G> cv = carve<G>(smem, sh);
@@ -1219,7 +1332,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
   const int tid = threadIdx.x, warp = tid >> 5;
   const int cta = blockIdx.x, n_cta = static_cast<int>(gridDim.x);
   stream_init<G>(sh, cv.sm);
-  if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
+  if (tid == G::PRODUCER_WARP * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
     prefetch_tensormap(&p.map0);   // only maps the host filled (K-sliced stages)
     if (p.mc.n_shared > 0) prefetch_tensormap(&p.map1);
   }
@@ -1228,7 +1341,7 @@ __global__ void __launch_bounds__(kThreads, 1) gate_kernel(const __grid_constant
   // Level 2: the activations were written two launches back (by the attention tail) and
   // can be staged while the router, the immediate predecessor, is still finishing.
   const bool early_x = p.pdl_level >= 2;
-  if (early_x && warp < kConsumerWarps) gate_stage_x<G>(p, sh, cv, tid);
+  if (early_x && warp < G::WARPS) gate_stage_x<G>(p, sh, cv, tid);
   // With `early_shared` (host: level 2, shared experts, whole tiles dealt round robin
   // whatever the routes) the shared experts are the first groups, CTA c's first tile is
   // tile c, and if that is a shared expert's tile the CTA streams and finishes it NOW:
@@ -1288,13 +1401,14 @@ struct DownParams {
   int tail_run;             // TailRun
   int n_tail;
   int push;
+  int per_round;
   int pdl_level;
   iq_tail_args tail;
   PushView pv;
 };
 
 template <class G>
-__global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant__ DownParams p) {
+__global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const __grid_constant__ DownParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   StreamShape sh = p.sh;
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -1302,13 +1416,13 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
   const int stream_ctas = static_cast<int>(gridDim.x) - p.n_tail;
   if (cta >= stream_ctas) {
     after_wait();
-    tail_cta(p.tail, p.pv, cta - stream_ctas, p.n_tail, smem);
+    tail_cta(p.tail, p.pv, p.per_round, cta - stream_ctas, p.n_tail, smem);
     return;
   }
   const Carve<G> cv = carve<G>(smem, sh);
   const StreamScratch scr = scratch_of(p.scratch);
   stream_init<G>(sh, cv.sm);
-  if (tid == kProducerWarp * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
+  if (tid == G::PRODUCER_WARP * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
     prefetch_tensormap(&p.map0);   // only maps the host filled (K-sliced stages)
     if (p.mc.n_shared > 0) prefetch_tensormap(&p.map1);
   }
@@ -1323,21 +1437,21 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   {
     const CtaWork wk = cta_share<G>(sh, stream_ctas, cta, grid);
-    if (warp == kProducerWarp) {
+    if (warp == G::PRODUCER_WARP) {
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
-    } else if (warp < kConsumerWarps) {
+    } else if (warp < G::WARPS) {
       float held[kGatherHeld];
       gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);
       if (early) after_wait();
       const int rows = p.mc.m * (p.mc.top_k + p.mc.n_shared);
       if (p.act_kind == IQ_ACT_E4M3)
         stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.act), p.mc.i_loc, nullptr,
-                        rows, p.mc.i_loc, tid);
+                        rows, p.mc.i_loc, tid, G::CONSUMER_THREADS);
       else
         stage_rows_bf16_groupq(cv.xq, cv.xs, sh, static_cast<const __nv_bfloat16*>(p.act),
-                               p.mc.i_loc, rows, p.mc.i_loc, false, tid);
+                               p.mc.i_loc, rows, p.mc.i_loc, false, tid, G::CONSUMER_THREADS);
       gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
-      named_bar_sync(1, kConsumerThreads);
+      named_bar_sync(1, G::CONSUMER_THREADS);
       consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
     } else {
       if (early) pdl_wait();
@@ -1360,9 +1474,9 @@ __global__ void __launch_bounds__(kThreads, 1) down_kernel(const __grid_constant
   }
   if (p.tail_run == kTailLastCta && last_cta<G>(cv.sm, scr, gridDim.x)) {
     float* red = reinterpret_cast<float*>(cv.sm->red);
-    if (threadIdx.x < kConsumerThreads)
-      run_tail<false>(p.tail, p.pv, nullptr, red, &cv.sm->is_last_tile,
-                      BlockBar{2, kConsumerThreads});
+    if (threadIdx.x < kTailThreads)
+      run_tail<false>(p.tail, p.pv, cv.ring, nullptr, 0, red, &cv.sm->is_last_tile,
+                      BlockBar{2, kTailThreads});   // (the ring is idle now)
   }
   stream_drain_on_abort<G>(cv.sm);
 }
@@ -1405,6 +1519,10 @@ static bool ensure_smem_optin(const void* fn) {
   if (done.count(key)) return true;
   if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
       cudaSuccess)
+    return false;
+  // all of the SM's configurable memory as shared memory: two half-size CTAs must fit
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           cudaSharedmemCarveoutMaxShared) != cudaSuccess)
     return false;
   done.insert(key);
   return true;
@@ -1485,12 +1603,13 @@ static int fill_maps(CUtensorMap* map0, CUtensorMap* map1, const StreamShape& sh
 }
 
 template <class Kernel, class Params>
-static int launch(Kernel kernel, const Params& p, int grid, size_t smem, void* stream, int pdl) {
+static int launch(Kernel kernel, const Params& p, int grid, int threads, size_t smem, void* stream,
+                  int pdl) {
   // One opt-in to the full shared memory per kernel and device.
   if (!ensure_smem_optin(reinterpret_cast<const void*>(kernel))) return IQ_ERR_CUDA;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[1] = {};
@@ -1537,6 +1656,12 @@ static int max_items_any(const StreamShape& sh, int max_groups, int grid) {
   return most + 1;
 }
 
+// What a CTA of geometry G may take of the SM's shared memory.
+template <class G>
+constexpr size_t smem_limit() {
+  return G::CTAS_PER_SM == 2 ? static_cast<size_t>(kSmemLimitShared) : static_cast<size_t>(kSmemLimit);
+}
+
 // Fills the geometry-dependent part of a shape and returns the dynamic shared memory to
 // request, or 0 when the ring does not fit.  `grid` is the number of CTAs that stream,
 // `max_groups` bounds the group count a kernel may derive from the routes, `other_bytes`
@@ -1546,20 +1671,25 @@ static size_t plan_smem(StreamShape& sh, int grid, size_t other_bytes, int max_g
   if (grid < 1) return 0;
   sh.max_items = max_items_any<G>(sh, max_groups, grid);
   if (sh.max_items == 0) return 0;
+  const size_t limit = smem_limit<G>();
   const size_t fixed = smem_fixed_bytes<G>(sh);
-  if (fixed + 2 * G::STAGE_BYTES > static_cast<size_t>(kSmemLimit)) return 0;
+  if (fixed + 2 * G::STAGE_BYTES > limit || other_bytes > limit) return 0;
   // Ring depth: a bare copy loop saturates HBM with ~96 KB in flight per SM, but the
-  // consumers hold a stage or two while they work on it; measured on the layer's kernels,
-  // 160 KB is where more depth stops paying (96 KB: Gate 46 us, 160 KB: 42 us).
-  int stages = static_cast<int>((kSmemLimit - fixed) / G::STAGE_BYTES);
+  // consumers hold a stage or two while they work on it; measured on the layer's kernels
+  // with one CTA per SM, 160 KB is where more depth stops paying (96 KB: Gate 46 us,
+  // 160 KB: 42 us).  A CTA that shares its SM takes what its half allows.
+  int stages = static_cast<int>((limit - fixed) / G::STAGE_BYTES);
   const int want = (160 * 1024 + G::STAGE_BYTES - 1) / G::STAGE_BYTES;
   if (stages > want) stages = want;
   if (stages > kMaxStages) stages = kMaxStages;
   sh.n_stages = stages;
   size_t need = fixed + static_cast<size_t>(stages) * G::STAGE_BYTES;
   if (need < other_bytes) need = other_bytes;
-  return need <= static_cast<size_t>(kSmemLimit) ? need : 0;
+  return need <= limit ? need : 0;
 }
+
+// Streams up to this many bytes per launch run with two CTAs per SM.
+constexpr long long kShortStreamBytes = 40ll << 20;
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -1575,7 +1705,7 @@ static int check_push(const iq_push_args* u, int m, int h) {
 static int check_tail(const iq_tail_args* t) {
   if (!t) return IQ_OK;
   if (t->kind != IQ_TAIL_ATTN && t->kind != IQ_TAIL_MLP) return IQ_ERR_ARG;
-  if (t->m < 1 || t->m > 8 || t->h < 128 || t->h % 128 || t->h > 8 * kTailVecs * kConsumerThreads)
+  if (t->m < 1 || t->m > 8 || t->h < 128 || t->h % 128 || t->h > 8 * kTailVecs * kTailThreads)
     return IQ_ERR_ARG;
   if (!t->partial || !t->residual || !t->w_norm || !t->h_out || !t->norm_out) return IQ_ERR_ARG;
   if (t->kind == IQ_TAIL_ATTN && !t->w_first) return IQ_ERR_ARG;
@@ -1627,20 +1757,21 @@ static int make_push_view(PushView& pv, const iq_push_args* u, void* scratch, si
 // How a fused tail runs, and through which zone: push when the tail names a zone or has
 // no peers, pull (last CTA) otherwise.
 struct TailPlan {
-  int tail_run = kTailNone, n_tail = 0, push = 0;
+  int tail_run = kTailNone, n_tail = 0, push = 0, per_round = 0;
   size_t smem = 0;      // what a tail CTA needs
   PushView pv{};
 };
 static int plan_tail(TailPlan& tp, const iq_tail_args* tail, const iq_push_args* push_only,
-                     void* scratch, size_t scratch_bytes, int m, int h) {
+                     void* scratch, size_t scratch_bytes, int m, int h, size_t smem_limit) {
   if (tail && (tail->push || tail->world == 1)) {
     const int rc = make_push_view(tp.pv, tail->push, scratch, scratch_bytes, h);
     if (rc != IQ_OK) return rc;
     tp.tail_run = kTailCtas;
     tp.n_tail = m;
     tp.push = 1;
-    tp.smem = tail_cta_smem(tp.pv.world, h);
-    if (tp.smem > static_cast<size_t>(kSmemLimit)) return IQ_ERR_UNSUPPORTED;
+    tp.per_round = tail_sources_per_round(tp.pv.world, h, smem_limit);
+    if (tp.per_round < 1) return IQ_ERR_UNSUPPORTED;
+    tp.smem = tail_cta_smem(tp.per_round, h);
   } else if (tail) {
     tp.tail_run = kTailLastCta;
   } else if (push_only) {
@@ -1668,7 +1799,8 @@ static int linear_launch(const iq_linear_args* a, void* stream) {
   sh.x_pitch = a->k + 64;
   sh.x_blocks = (a->k + 127) / 128;
   TailPlan tp;
-  int rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->n);
+  int rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->n,
+                     smem_limit<G>());
   if (rc != IQ_OK) return rc;
   const int grid = sm_count();
   const size_t smem = plan_smem<G>(sh, grid - tp.n_tail, tp.smem);
@@ -1684,16 +1816,18 @@ static int linear_launch(const iq_linear_args* a, void* stream) {
   p.w = static_cast<const uint8_t*>(a->w);
   p.w_scale = a->w_scale;
   p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.out_f32 = a->out_f32;
   p.scratch = a->scratch;
   p.tail_run = tp.tail_run;
   p.n_tail = tp.n_tail;
   p.push = tp.push;
+  p.per_round = tp.per_round;
   p.pv = tp.pv;
   if (a->tail) {
     p.tail = *a->tail;
     if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
   }
-  return launch(linear_kernel<G>, p, grid, smem, stream, a->pdl);
+  return launch(linear_kernel<G>, p, grid, G::THREADS, smem, stream, a->pdl);
 }
 
 }  // namespace iqb
@@ -1726,16 +1860,20 @@ extern "C" int iq_tail(const iq_tail_args* a, void* stream, int pdl) {
     if (make_push_view(p.pv, a->push, nullptr, 0, a->h) != IQ_OK) return IQ_ERR_ARG;
     p.push = 1;
     p.n_tail = a->m;
-    const size_t smem = tail_cta_smem(p.pv.world, a->h);
-    if (smem > static_cast<size_t>(kSmemLimit)) return IQ_ERR_UNSUPPORTED;
-    return launch(tail_kernel, p, a->m, smem, stream, pdl);
+    // a small CTA that can sit beside a streaming kernel's: half an SM's shared memory
+    p.per_round = tail_sources_per_round(p.pv.world, a->h, kSmemLimitShared);
+    if (p.per_round < 1) return IQ_ERR_UNSUPPORTED;
+    return launch(tail_kernel, p, a->m, kTailThreads, tail_cta_smem(p.per_round, a->h), stream,
+                  pdl);
   }
   // rows in `partial`: one CTA per row without peers, one CTA (one signal / wait) with
-  return launch(tail_kernel, p, a->world == 1 ? a->m : 1, 1024, stream, pdl);
+  return launch(tail_kernel, p, a->world == 1 ? a->m : 1, kTailThreads, tail_cta_smem(0, a->h),
+                stream, pdl);
 }
 
 extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
-  if (!a || !a->x || !a->w || !a->w_scale || !a->out || !a->scratch) return IQ_ERR_ARG;
+  if (!a || !a->x || !a->w || !a->w_scale || !a->scratch) return IQ_ERR_ARG;
+  if (!a->out && (!a->out_f32 || a->tail || a->push)) return IQ_ERR_ARG;
   if (a->scratch_bytes < kScrBasicBytes) return IQ_ERR_ARG;
   if (a->x_kind < IQ_X_BF16_GROUPQ || a->x_kind > IQ_X_E4M3_UNSCALED) return IQ_ERR_ARG;
   if (a->x_kind == IQ_X_E4M3_GROUP && !a->x_scale) return IQ_ERR_ARG;
@@ -1744,7 +1882,8 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   if (a->k < 64 || a->k % 64 || a->n < 16 || a->n % 16) return IQ_ERR_ARG;
   if (a->x_kind != IQ_X_E4M3_UNSCALED && a->k % 128) return IQ_ERR_ARG;   // 1x128 groups
   if ((a->rg != 64 && a->rg != 128) || (a->kg != 64 && a->kg != 128)) return IQ_ERR_ARG;
-  if (!aligned16(a->x) || !aligned16(a->w) || !aligned16(a->out)) return IQ_ERR_ARG;
+  if (!aligned16(a->x) || !aligned16(a->w) || !aligned16(a->out) || !aligned16(a->out_f32))
+    return IQ_ERR_ARG;
   if (a->tail) {
     const int rc = check_tail(a->tail);
     if (rc != IQ_OK) return rc;
@@ -1752,6 +1891,19 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   }
   if (sm_count() == 0) return IQ_ERR_CUDA;
   const int k = a->k, n = a->n;
+  // A short stream takes CTAs of eight (six) consumer warps, two of which share an SM, so
+  // that its successor's CTAs set up and prefetch beside it (see Geo); a long stream takes
+  // the whole SM.
+  if (static_cast<long long>(n) * k <= kShortStreamBytes) {
+    // (falls through to a whole-SM geometry when half an SM cannot hold the rows and a ring)
+    int rc = IQ_ERR_UNSUPPORTED;
+    if (k % 1024 == 0 && n % 16 == 0) rc = linear_launch<Geo<1, 8, 2>>(a, stream);
+    else if (k % 768 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 4, 3>>(a, stream);
+    else if (k % 512 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 4, 2>>(a, stream);
+    else if (k % 256 == 0 && n % 64 == 0) rc = linear_launch<Geo<4, 2, 2>>(a, stream);
+    else if (k % 192 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 3, 1>>(a, stream);
+    if (rc != IQ_ERR_UNSUPPORTED) return rc;
+  }
   if (k % 2048 == 0 && n % 16 == 0) return linear_launch<Geo<1, 16, 2>>(a, stream);
   // k = 1024: 32-row stages (half as many tile hand-offs) measured 0.25 us faster
   if (k % 1024 == 0 && n % 32 == 0) return linear_launch<Geo<2, 8, 2>>(a, stream);
@@ -1763,6 +1915,37 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   if (k % 128 == 0 && n % 128 == 0) return linear_launch<Geo<8, 2, 1>>(a, stream);
   if (k % 64 == 0 && n % 256 == 0) return linear_launch<Geo<16, 1, 1>>(a, stream);
   return IQ_ERR_UNSUPPORTED;
+}
+
+extern "C" int iq_qkv_heads(const iq_heads_args* a, void* stream) {
+  if (!a || !a->qkv || !a->w_qn || !a->w_kn || !a->cos || !a->sin || !a->slot || !a->q_out ||
+      !a->k_cache || !a->v_cache)
+    return IQ_ERR_ARG;
+  if (a->m < 1 || a->m > 64 || a->q_heads < 1 || a->kv_heads < 1 || a->capacity < 1)
+    return IQ_ERR_ARG;
+  if (a->head_dim < 2 || a->head_dim > 256 || a->head_dim % 2) return IQ_ERR_ARG;
+  if (a->rotary_dim < 0 || a->rotary_dim > a->head_dim || a->rotary_dim % 2) return IQ_ERR_ARG;
+  if (a->kv_kind != IQ_ACT_BF16 && a->kv_kind != IQ_ACT_E4M3) return IQ_ERR_ARG;
+  HeadsParams p{};
+  p.a = *a;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(a->q_heads + 2 * a->kv_heads),
+                     static_cast<unsigned>(a->m), 1);
+  cfg.blockDim = dim3(static_cast<unsigned>((a->head_dim + 31) / 32 * 32), 1, 1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1] = {};
+  if (a->pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, heads_kernel, p);
+  if (err != cudaSuccess) {
+    fprintf(stderr, "iqb200: launch failed: %s\n", cudaGetErrorString(err));
+    return IQ_ERR_CUDA;
+  }
+  return IQ_OK;
 }
 
 template <class G>
@@ -1797,7 +1980,7 @@ static int router_launch(const iq_router_args* a, void* stream) {
   p.wt = a->wt;
   p.logits = a->logits;
   p.scratch = a->scratch;
-  return launch(router_kernel<G>, p, grid, smem, stream, a->pdl);
+  return launch(router_kernel<G>, p, grid, G::THREADS, smem, stream, a->pdl);
 }
 
 extern "C" int iq_router(const iq_router_args* a, void* stream) {
@@ -1810,7 +1993,7 @@ extern "C" int iq_router(const iq_router_args* a, void* stream) {
   if (a->score != IQ_ROUTE_SOFTMAX && a->score != IQ_ROUTE_SIGMOID) return IQ_ERR_ARG;
   if (!aligned16(a->x) || !aligned16(a->w)) return IQ_ERR_ARG;
   if (sm_count() < 2) return IQ_ERR_CUDA;
-  if ((a->h * 2) % 2048 == 0) return router_launch<Geo<1, 16, 2>>(a, stream);
+  if ((a->h * 2) % 1024 == 0) return router_launch<Geo<1, 8, 2>>(a, stream);
   return router_launch<Geo<1, 16, 1>>(a, stream);
 }
 
@@ -1831,20 +2014,12 @@ static int fill_moe(MoeCommon& mc, int m, int h, int i_loc, int n_experts, int t
   return IQ_OK;
 }
 
-extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
-  if (!a || (!a->x_fp8 && !a->x_bf16) || !a->fc || !a->fc_scale || !a->act || !a->scratch)
-    return IQ_ERR_ARG;
-  if (a->scratch_bytes < kScrBasicBytes) return IQ_ERR_ARG;
-  if (a->n_shared > 0 && (!a->shared_fc || !a->shared_fc_scale)) return IQ_ERR_ARG;
-  if (a->act_kind != IQ_ACT_E4M3 && a->act_kind != IQ_ACT_BF16) return IQ_ERR_ARG;
-  if (a->h < 1024 || a->h % 1024 || a->i_loc < 64 || a->i_loc % 64) return IQ_ERR_ARG;
-  if (!aligned16(a->x_fp8) || !aligned16(a->x_bf16) || !aligned16(a->fc)) return IQ_ERR_ARG;
-  using G = Geo<2, 8, 2>;
+template <class G>
+static int gate_launch(const iq_moe_gate_args* a, void* stream) {
   GateParams p{};
   int rc = fill_moe(p.mc, a->m, a->h, a->i_loc, a->n_experts, a->top_k, a->n_shared, a->sel,
                     nullptr);
   if (rc != IQ_OK) return rc;
-  if (sm_count() == 0) return IQ_ERR_CUDA;
   p.mc.w = static_cast<const uint8_t*>(a->fc);
   p.mc.w_scale = a->fc_scale;
   p.mc.shared_w = static_cast<const uint8_t*>(a->shared_fc);
@@ -1892,7 +2067,33 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   p.act_kind = a->act_kind;
   p.scratch = a->scratch;
   p.pdl_level = a->pdl;
-  return launch(gate_kernel<G>, p, sm_count(), smem, stream, a->pdl);
+  return launch(gate_kernel<G>, p, sm_count(), G::THREADS, smem, stream, a->pdl);
+}
+
+// Bytes the expert kernels stream for `m` rows: every routed pair a distinct expert (the
+// most there can be), plus the shared experts.
+static long long expert_stream_bytes(int m, int top_k, int n_experts, int n_shared,
+                                     long long bytes_per_expert) {
+  const int routed = m * top_k < n_experts ? m * top_k : n_experts;
+  return (routed + n_shared) * bytes_per_expert;
+}
+
+extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
+  if (!a || (!a->x_fp8 && !a->x_bf16) || !a->fc || !a->fc_scale || !a->act || !a->scratch)
+    return IQ_ERR_ARG;
+  if (a->scratch_bytes < kScrBasicBytes) return IQ_ERR_ARG;
+  if (a->n_shared > 0 && (!a->shared_fc || !a->shared_fc_scale)) return IQ_ERR_ARG;
+  if (a->act_kind != IQ_ACT_E4M3 && a->act_kind != IQ_ACT_BF16) return IQ_ERR_ARG;
+  if (a->h < 1024 || a->h % 1024 || a->i_loc < 64 || a->i_loc % 64) return IQ_ERR_ARG;
+  if (!aligned16(a->x_fp8) || !aligned16(a->x_bf16) || !aligned16(a->fc)) return IQ_ERR_ARG;
+  if (sm_count() == 0) return IQ_ERR_CUDA;
+  const long long bytes = expert_stream_bytes(a->m, a->top_k, a->n_experts, a->n_shared,
+                                              2ll * a->i_loc * a->h);
+  if (bytes <= kShortStreamBytes) {
+    const int rc = gate_launch<Geo<2, 4, 2>>(a, stream);
+    if (rc != IQ_ERR_UNSUPPORTED) return rc;
+  }
+  return gate_launch<Geo<2, 8, 2>>(a, stream);
 }
 
 template <class G>
@@ -1919,7 +2120,7 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   sh.x_pitch = a->i_loc + 64;
   sh.x_blocks = (a->i_loc + 127) / 128;
   TailPlan tp;
-  rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->h);
+  rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->h, smem_limit<G>());
   if (rc != IQ_OK) return rc;
   const int grid = sm_count();
   const size_t smem = plan_smem<G>(sh, grid - tp.n_tail, tp.smem, a->m * a->top_k + a->n_shared);
@@ -1935,13 +2136,14 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   p.tail_run = tp.tail_run;
   p.n_tail = tp.n_tail;
   p.push = tp.push;
+  p.per_round = tp.per_round;
   p.pv = tp.pv;
   p.pdl_level = a->pdl;
   if (a->tail) {
     p.tail = *a->tail;
     if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
   }
-  return launch(down_kernel<G>, p, grid, smem, stream, a->pdl);
+  return launch(down_kernel<G>, p, grid, G::THREADS, smem, stream, a->pdl);
 }
 
 extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
@@ -1960,6 +2162,17 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   }
   if (sm_count() == 0) return IQ_ERR_CUDA;
   const int k = a->i_loc;
+  const long long bytes = expert_stream_bytes(a->m, a->top_k, a->n_experts, a->n_shared,
+                                              static_cast<long long>(a->h) * a->i_loc);
+  if (bytes <= kShortStreamBytes) {
+    // two CTAs per SM (see Geo); fall through when the staged activations leave no room
+    int rc = IQ_ERR_UNSUPPORTED;
+    if (k % 1024 == 0) rc = down_launch<Geo<1, 8, 2>>(a, stream);
+    else if (k % 512 == 0 && a->h % 32 == 0) rc = down_launch<Geo<2, 4, 2>>(a, stream);
+    else if (k % 256 == 0 && a->h % 32 == 0) rc = down_launch<Geo<2, 4, 1>>(a, stream);
+    else if (k % 192 == 0 && a->h % 32 == 0) rc = down_launch<Geo<2, 3, 1>>(a, stream);
+    if (rc != IQ_ERR_UNSUPPORTED) return rc;
+  }
   // k = 1024: 32 rows x 1 KB stages (two 64-byte runs per warp) measured 5 % faster than
   // 16 rows x 1 KB; at k = 512 the wider tile (64 rows) measured slower and is not used.
   if (k % 2048 == 0) return down_launch<Geo<1, 16, 2>>(a, stream);

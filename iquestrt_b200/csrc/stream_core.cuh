@@ -7,7 +7,8 @@
 // contiguous.  Completion is counted in bytes on an mbarrier per ring slot.  (Measured on
 // B200: one 16 KB copy per stage with six stages in flight streams at 7.0 TB/s; sixteen
 // 1 KB copies per stage reach 3.9 TB/s.)
-// Sixteen consumer warps read the ring with 16-byte shared loads and feed warp-level MMAs
+// The consumer warps (sixteen, or eight / six when two CTAs share an SM) read the ring with
+// 16-byte shared loads and feed warp-level MMAs
 // whose B operand carries the (at most eight) activation rows, so a byte of weight costs
 // 1/512 of an MMA and no conversion instruction.  The K index inside an MMA is permuted
 // so that every lane's A and B fragments are plain 16-byte runs (see `consume_stage`).
@@ -36,22 +37,33 @@
 
 namespace iqb {
 
-constexpr int kConsumerWarps = 16;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 64;   // + the producer warp + the epilogue warp
-constexpr int kProducerWarp = kConsumerWarps;
-constexpr int kEpilogueWarp = kConsumerWarps + 1;
 constexpr int kMaxStages = 16;
 constexpr int kMaxGroups = 72;                    // 8 rows x 8 routed + shared, with slack
 constexpr int kMaxCols = 8;                       // MMA N
 constexpr int kSmemLimit = 232448;                // 227 KiB per CTA on sm_100
+// What one of TWO CTAs on an SM may take: 228 KiB per SM, 1 KiB reserved per resident CTA.
+constexpr int kSmemLimitShared = (233472 - 2 * 1024) / 2;
 
 // Ring geometry: a stage is (16*RT) weight rows x (KW*RUNS*64) bytes; warp (rs, kp) of the
-// RT*KW = 16 consumer warps owns row sub-tile rs and the kp-th slice of RUNS 64-byte runs.
+// RT*KW consumer warps owns row sub-tile rs and the kp-th slice of RUNS 64-byte runs.  A
+// CTA is the consumer warps plus one producer and one epilogue warp.
+//
+// Sixteen consumer warps with a 160 KB ring (one CTA per SM) get the most out of HBM on a
+// long stream.  Eight (or six) consumer warps with a ring of about 96 KB leave room for a
+// SECOND CTA on the SM: the CTAs of the next kernel of a programmatic-dependent-launch chain
+// become resident while this kernel is still streaming, set themselves up and fill their
+// own ring with weights before their dependency wait, so a short stream does not pay the
+// launch, the set-up and the first-byte latency of its successor end to end.
 template <int RT_, int KW_, int RUNS_>
 struct Geo {
   static constexpr int RT = RT_, KW = KW_, RUNS = RUNS_;
-  static_assert(RT * KW == kConsumerWarps, "sixteen consumer warps");
+  static constexpr int WARPS = RT * KW;                 // consumer warps
+  static_assert(WARPS == 6 || WARPS == 8 || WARPS == 16, "6, 8 or 16 consumer warps");
+  static constexpr int CONSUMER_THREADS = WARPS * 32;
+  static constexpr int THREADS = CONSUMER_THREADS + 64; // + the producer warp + the epilogue warp
+  static constexpr int PRODUCER_WARP = WARPS;
+  static constexpr int EPILOGUE_WARP = WARPS + 1;
+  static constexpr int CTAS_PER_SM = WARPS <= 8 ? 2 : 1;
   static constexpr int ROWS = 16 * RT;
   static constexpr int KC = KW * RUNS * 64;
   // A stage lands as NBOX dense boxes of (ROWS x BOXK bytes), one TMA copy each (a tensor
@@ -65,7 +77,7 @@ struct Geo {
   static constexpr int PITCH = BOXK;
   static constexpr int STAGE_BYTES = ROWS * KC;
   // One weight scale per (warp, run) of a stage, gathered into shared memory.
-  static constexpr int SCALES_PER_STAGE = kConsumerWarps * RUNS;
+  static constexpr int SCALES_PER_STAGE = WARPS * RUNS;
 };
 
 // One weight matrix instance ("group"): an expert, the shared expert, or the only matrix.
@@ -139,7 +151,7 @@ struct StreamSmem {
   int pad;
   GroupDesc groups[kMaxGroups];
   int route_ids[64 + kMaxGroups + 1];   // routed expert ids while the group table is built
-  float red[2][kConsumerWarps][32][4];
+  float red[2][G::WARPS][32][4];
 };
 
 // Weight row `r` of a tile -> row index inside the group.
@@ -468,7 +480,7 @@ __device__ __forceinline__ void gather_scales_load(const StreamShape& sh, const 
   const int total = w.n_items * G::SCALES_PER_STAGE;
 #pragma unroll
   for (int j = 0; j < kGatherHeld; ++j) {
-    const int i = tid + j * kConsumerThreads;
+    const int i = tid + j * G::CONSUMER_THREADS;
     held[j] = i < total ? gather_one<G>(sh, groups, w, i) : 0.f;
   }
 }
@@ -481,10 +493,10 @@ __device__ __forceinline__ void gather_scales_store(const StreamShape& sh, const
   const int total = w.n_items * G::SCALES_PER_STAGE;
 #pragma unroll
   for (int j = 0; j < kGatherHeld; ++j) {
-    const int i = tid + j * kConsumerThreads;
+    const int i = tid + j * G::CONSUMER_THREADS;
     if (i < total) sc[i] = held[j];
   }
-  for (int i = tid + kGatherHeld * kConsumerThreads; i < total; i += kConsumerThreads)
+  for (int i = tid + kGatherHeld * G::CONSUMER_THREADS; i < total; i += G::CONSUMER_THREADS)
     sc[i] = gather_one<G>(sh, groups, w, i);
 }
 
@@ -573,8 +585,8 @@ struct TileId {
   int tile, group, tig;
 };
 
-// Consumers: sixteen warps (four per scheduler: the per-stage path is a latency chain, so
-// thread-level parallelism is what keeps the SM ahead of the stream).  At the end of a
+// Consumers: up to sixteen warps per SM (four per scheduler: the per-stage path is a latency
+// chain, so thread-level parallelism is what keeps the SM ahead of the stream).  At the end of a
 // tile each warp drops its fragment into `red[i]` and moves on; the epilogue warp folds
 // the fragments.
 template <class G, class E, class S>
@@ -775,7 +787,7 @@ __device__ __forceinline__ void epilogue(const StreamShape& sh, StreamSmem<G>* s
 }
 
 // After the CTA's last emit: returns true on the one CTA that arrives last, on every one of
-// its threads, with all other CTAs' global writes visible.  Call from all kThreads threads.
+// its threads, with all other CTAs' global writes visible.  Call from all threads of the CTA.
 template <class G>
 __device__ __forceinline__ bool last_cta(StreamSmem<G>* sm, const StreamScratch& scr, int grid) {
   __threadfence();
@@ -799,10 +811,10 @@ __device__ __forceinline__ void stream_init(const StreamShape& sh, StreamSmem<G>
   if (threadIdx.x == 0) {
     for (int s = 0; s < sh.n_stages; ++s) {
       mbar_init(&sm->full[s], 1);
-      mbar_init(&sm->empty[s], kConsumerWarps);
+      mbar_init(&sm->empty[s], G::WARPS);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&sm->red_full[i], kConsumerWarps);
+      mbar_init(&sm->red_full[i], G::WARPS);
       mbar_init(&sm->red_empty[i], 1);
     }
     sm->abort_flag = 0;

@@ -18,7 +18,8 @@ from ._lib import (ACT_BF16, ACT_E4M3, ROUTE_SIGMOID, ROUTE_SOFTMAX, TAIL_ATTN, 
 
 E4M3 = torch.float8_e4m3fn
 
-__all__ = ["Scratch", "TailSpec", "linear", "linear_static", "linear_static_status", "router",
+__all__ = ["Scratch", "TailSpec", "linear", "linear_static", "linear_static_status", "qkv_heads",
+           "router",
            "moe_gate", "moe_down", "tail",
            "X_BF16_GROUPQ", "X_BF16_SPLIT2", "X_E4M3_GROUP", "X_E4M3_UNSCALED",
            "TAIL_ATTN", "TAIL_MLP", "ROUTE_SOFTMAX", "ROUTE_SIGMOID", "ACT_E4M3", "ACT_BF16"]
@@ -174,27 +175,35 @@ def _linear_args(x, w, w_scale, out, x_kind, x_scale, block):
     _need("x", x, torch.bfloat16 if x_kind in (X_BF16_GROUPQ, X_BF16_SPLIT2) else E4M3, None, dev)
     if x_kind == X_E4M3_GROUP:
         _need("x_scale", x_scale, torch.float32, (m, k // 128), dev)
-    _need("out", out, torch.bfloat16, (m, n), dev)
+    if out is not None:
+        _need("out", out, torch.bfloat16, (m, n), dev)
     a = _lib.LinearArgs()
     a.x, a.x_scale, a.x_kind = x.data_ptr(), _ptr(x_scale), x_kind
     a.m, a.k, a.n = m, k, n
     a.w, a.w_scale, a.rg, a.kg = w.data_ptr(), w_scale.data_ptr(), rg, kg
-    a.out = out.data_ptr()
+    a.out = _ptr(out)
     return a
 
 
 def linear(x, w, w_scale, *, scratch: Scratch, out=None, x_kind=None, x_scale=None,
-           block=(128, 128), tail: TailSpec | None = None, push=None, pdl: bool = False):
+           block=(128, 128), tail: TailSpec | None = None, push=None, out_f32=None,
+           pdl: bool = False):
     """`out[m,n] bf16 = x[m,k] @ dequant(w[n,k], w_scale).T` on the streaming GEMV kernel,
     optionally followed in the same launch by `tail` (whose `partial` must be `out`).
 
     `x` is bf16 (quantised in the kernel per 1x128 group, or split in two e4m3 terms with
     `x_kind=X_BF16_SPLIT2`) or e4m3 (with `x_scale [m,k/128]`, or unscaled).  `push` (a
     `parallel.SymmSlot`) sends the rows to that slot's landing zone on every rank without
-    running a tail, for a later `tail(...)` on the same slot."""
-    if out is None:
+    running a tail, for a later `tail(...)` on the same slot.  `out_f32 [m,n]` receives the
+    result before its bf16 rounding; with it and no `out` only the fp32 result is written
+    (and returned)."""
+    only_f32 = out is None and out_f32 is not None and tail is None and push is None
+    if out is None and not only_f32:
         out = torch.empty(x.shape[0], w.shape[0], dtype=torch.bfloat16, device=x.device)
+    if out_f32 is not None:
+        _need("out_f32", out_f32, torch.float32, (x.shape[0], w.shape[0]), x.device)
     a = _linear_args(x, w, w_scale, out, x_kind, x_scale, block)
+    a.out_f32 = _ptr(out_f32)
     a.scratch, a.scratch_bytes = scratch.ptr, scratch.bytes
     t = None
     if tail is not None:
@@ -204,7 +213,42 @@ def linear(x, w, w_scale, *, scratch: Scratch, out=None, x_kind=None, x_scale=No
         a.push = C.pointer(push.push_args())
     a.pdl = int(pdl)
     _lib.check("iq_linear", _lib.load().iq_linear(C.byref(a), _stream()))
-    return out
+    return out_f32 if only_f32 else out
+
+
+def qkv_heads(qkv, w_qn, w_kn, cos, sin, slot, q_out, k_cache, v_cache, *, q_heads: int,
+              kv_heads: int, rotary_dim: int, eps: float, scratch: Scratch | None = None,
+              pdl: bool = False):
+    """The attention prologue after the QKV product (`iq_qkv_heads`): `qkv [m, (q_heads +
+    2 kv_heads) * D]` fp32 -> `q_out [m, q_heads, D]` bf16 (normalised, roped), k and v
+    into rows `slot [m]` (int64) of `k_cache` / `v_cache [capacity, kv_heads, D]` (bf16 or
+    e4m3)."""
+    m = qkv.shape[0]
+    dev = qkv.device
+    d = q_out.shape[-1]
+    _need("qkv", qkv, torch.float32, (m, (q_heads + 2 * kv_heads) * d), dev)
+    _need("w_qn", w_qn, torch.float32, (d,), dev)
+    _need("w_kn", w_kn, torch.float32, (d,), dev)
+    _need("cos", cos, torch.bfloat16, (m, rotary_dim), dev)
+    _need("sin", sin, torch.bfloat16, (m, rotary_dim), dev)
+    _need("slot", slot, torch.int64, (m,), dev)
+    _need("q_out", q_out, torch.bfloat16, (m, q_heads, d), dev)
+    if k_cache.dtype not in (torch.bfloat16, E4M3) or v_cache.dtype != k_cache.dtype:
+        raise ValueError("the KV caches must both be bf16 or both e4m3")
+    cap = k_cache.shape[0]
+    _need("k_cache", k_cache, k_cache.dtype, (cap, kv_heads, d), dev)
+    _need("v_cache", v_cache, k_cache.dtype, (cap, kv_heads, d), dev)
+    a = _lib.HeadsArgs()
+    a.qkv = qkv.data_ptr()
+    a.m, a.q_heads, a.kv_heads, a.head_dim, a.rotary_dim = m, q_heads, kv_heads, d, rotary_dim
+    a.w_qn, a.w_kn, a.cos, a.sin = w_qn.data_ptr(), w_kn.data_ptr(), cos.data_ptr(), sin.data_ptr()
+    a.eps, a.slot, a.q_out = float(eps), slot.data_ptr(), q_out.data_ptr()
+    a.k_cache, a.v_cache, a.capacity = k_cache.data_ptr(), v_cache.data_ptr(), cap
+    a.kv_kind = ACT_E4M3 if k_cache.dtype == E4M3 else ACT_BF16
+    a.status = None if scratch is None else scratch.ptr
+    a.pdl = int(pdl)
+    _lib.check("iq_qkv_heads", _lib.load().iq_qkv_heads(C.byref(a), _stream()))
+    return q_out
 
 
 def router(x, weight, *, top_k: int, scratch: Scratch, score: int = ROUTE_SOFTMAX, sel=None,

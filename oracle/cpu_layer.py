@@ -22,15 +22,19 @@ def shared_expert(hn, lw, s):
 
 
 def layer_cpu(lw_ranks, ao_ranks, residual, *, top_k, n_shared, eps, a_scale=1.0, f_scale=1.0,
-              score="softmax"):
+              score="softmax", routes=None):
     """One layer over `len(lw_ranks)` simulated TP ranks: per-rank partial products, a
-    Python sum for each all-reduce.  Returns (out, norm_out, sel, wt)."""
+    Python sum for each all-reduce.  `routes = (sel, wt)` replaces the layer's own top-k
+    (to compare two implementations on identical routes when a top-k margin is too small
+    for them to agree).  Returns (out, norm_out, sel, wt)."""
     parts = [R.linear(ao, lw["o_proj"], lw["o_scale"]) for lw, ao in zip(lw_ranks, ao_ranks)]
     lw0 = lw_ranks[0]
     h, hn = R.layer_residual_algebra(parts, residual, lw0["attn_out_norm"],
                                      lw0["feed_forward_norm"], a_scale, eps)
     logits = R.router_logits(hn, lw0["router"])
     sel, wt, _ = R.select_topk(logits, top_k, score)
+    if routes is not None:
+        sel, wt = routes
     mlp = None
     for lw in lw_ranks:
         part = R.moe_prefill(hn, sel, wt, lw["fc"], lw["fc_scale"], lw["proj"], lw["proj_scale"])

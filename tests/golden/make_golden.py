@@ -2,7 +2,8 @@
 
 Run where the reference is checked out, giving the checkout's root:
 
-    python tests/golden/make_golden.py <reference_root>
+    python tests/golden/make_golden.py <reference_root>          # both fixture files
+    python tests/golden/make_golden.py <reference_root> heads    # reference_heads.pt only
 
 The reference has no golden vectors for this path, so these fixtures are outputs of the
 reference itself on small seeded inputs: `iquestrt.blockfp8.dequant / shard_scale`,
@@ -183,7 +184,40 @@ def main(ref_root):
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def heads(ref_root):
+    """`tests/golden/reference_heads.pt`: the attention prologue after the QKV product
+    (iquestrt/model/reference.py:101-112: per-head q/k RMSNorm, then `apply_partial_rope`
+    with `rope_tables`), for a partial and a full rotary width."""
+    sys.path.insert(0, ref_root)
+    from iquestrt.model import reference
+    g = torch.Generator().manual_seed(4321)
+    cases = []
+    for q_heads, kv_heads, hd, rotary in ((8, 1, 128, 32), (6, 1, 128, 128), (4, 2, 64, 16)):
+        rows = 4
+        qkv = (torch.randn(rows, (q_heads + 2 * kv_heads) * hd, generator=g) * 2).bfloat16()
+        w_qn = 0.5 + torch.rand(hd, generator=g)
+        w_kn = 0.5 + torch.rand(hd, generator=g)
+        positions = torch.tensor([5, 100, 4095, 77])
+        cos, sin = reference.rope_tables(positions, rotary, 10000.0, "cpu", torch.bfloat16)
+        q, k, v = qkv.split([q_heads * hd, kv_heads * hd, kv_heads * hd], dim=-1)
+        q = reference.rms_norm(q.view(-1, q_heads, hd), w_qn, 1e-6)
+        k = reference.rms_norm(k.view(-1, kv_heads, hd), w_kn, 1e-6)
+        q = reference.apply_partial_rope(q, cos, sin, rotary)
+        k = reference.apply_partial_rope(k, cos, sin, rotary)
+        cases.append(dict(qkv=qkv, q_heads=q_heads, kv_heads=kv_heads, head_dim=hd,
+                          rotary_dim=rotary, w_qn=w_qn, w_kn=w_kn, positions=positions,
+                          theta=10000.0, cos=cos, sin=sin, eps=1e-6, q=q, k=k,
+                          v=v.view(-1, kv_heads, hd)))
+    path = os.path.join(HERE, "reference_heads.pt")
+    torch.save(cases, path)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        raise SystemExit("usage: python tests/golden/make_golden.py <reference_root>")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3):
+        raise SystemExit("usage: python tests/golden/make_golden.py <reference_root> [heads]")
+    if len(sys.argv) == 3 and sys.argv[2] == "heads":
+        heads(sys.argv[1])
+    else:
+        main(sys.argv[1])
+        heads(sys.argv[1])

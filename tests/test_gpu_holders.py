@@ -67,7 +67,7 @@ def test_attention_tail_for_moe_layers(fp32_residual):
     input `x_pad` (bf16) and the MoE input `x_pad_fp8` (unscaled e4m3, the reference's
     format; and with 1x128 group scales when a scale buffer is given)."""
     q, hidden, q_dim = 3, 3072, 768
-    ws, scratch, tail, oproj, moe, ar, mlp = _holders(hidden, q_dim, q, i_loc=192)
+    ws, scratch, tail, oproj, moe, ar, mlp = _holders(hidden, q_dim, q)
     g = torch.Generator().manual_seed(11)
     part = (torch.randn(q, hidden, generator=g) * 2).bfloat16()
     res = torch.randn(q, hidden, generator=g)
@@ -158,18 +158,29 @@ def test_dense_mlp_with_the_reference_signature(q, grain):
         got = dense(hn, gu, gus, dn, dns, out).clone()
     assert scratch.status() == 0
     x = hn.cpu()
+    # the kernels' own numerics (1x128-group e4m3 activations into both products)
+    gus64 = gus.cpu() if grain == 64 else gus.cpu().repeat_interleave(2, 0)
+    dns64 = dns.cpu() if grain == 64 else dns.cpu().repeat_interleave(2, 1)
+    xq, xs = R.quant_act_group(x)
+    sel0 = torch.zeros(q, 1, dtype=torch.int32)
+    act = R.gate_decode(xq, sel0, gu.cpu()[None], gus64[None], xs).bfloat16()     # [q,1,I]
+    aq, a_s = R.quant_act_group(act.reshape(q, inter))
+    want = R.down_decode(aq.view(q, 1, inter), sel0, torch.ones(q, 1), dn.cpu()[None],
+                         dns64[None], a_s.view(q, 1, inter // 128))
+    assert got.shape == (q, hidden)
+    assert R.rel_fro(got.cpu(), want) <= KERNEL_TOL
+    # the reference's bf16-activation algebra (iquestrt/model/reference.py:70-74): two
+    # single-term e4m3 activation casts sit between the two, about 2.6e-2 each
+    ref = R.dense_mlp(x, gu.cpu(), gus.cpu(), dn.cpu(), dns.cpu(), blk_gu) if grain == 128 else None
     w_gu = R.dequant(gu.cpu(), gus.cpu(), blk_gu, torch.float32)
     pre = torch.nn.functional.linear(x.float(), w_gu).bfloat16()
-    act = torch.nn.functional.silu(pre[:, :inter]) * pre[:, inter:]
+    mid = torch.nn.functional.silu(pre[:, :inter]) * pre[:, inter:]
     w_dn = R.dequant(dn.cpu(), dns.cpu(), blk_dn, torch.float32)
-    want = torch.nn.functional.linear(act.float(), w_dn).bfloat16()
-    if grain == 128:
-        ref = R.dense_mlp(x, gu.cpu(), gus.cpu(), dn.cpu(), dns.cpu())
-        assert torch.equal(ref.view(torch.int16), want.view(torch.int16))
-    assert got.shape == (q, hidden)
-    assert R.rel_fro(got.cpu(), want) <= PATH_TOL
+    algebra = torch.nn.functional.linear(mid.float(), w_dn).bfloat16()
+    if ref is not None:
+        assert torch.equal(ref.view(torch.int16), algebra.view(torch.int16))
+    assert R.rel_fro(got.cpu(), algebra) <= 6e-2
     # the pre-quantised form stays available as a keyword
-    xq, xs = R.quant_act_group(x)
     got8 = dense(xq.cuda(), gu, gus, dn, dns, out, x_scale=xs.cuda())
     assert scratch.status() == 0
     assert torch.equal(got8.view(torch.int16), got.view(torch.int16))

@@ -180,3 +180,28 @@ def test_mlp_tail_identity_cases():
     out, nrm = R.mlp_tail([m], zero, 1.0, torch.ones(h), 0.0)
     assert torch.equal(out, m)
     assert torch.allclose(nrm.float().pow(2).mean(-1), torch.ones(2), atol=2e-2)
+
+
+def test_attention_prologue_matches_reference_bitwise():
+    """`rope_tables`, `apply_partial_rope` and the per-head q/k norm of the oracle against
+    outputs of the reference's own torch functions (`tests/golden/reference_heads.pt`);
+    the decode form (fp32 product into the norm) stays within bf16 rounding of it."""
+    cases = torch.load(os.path.join(os.path.dirname(__file__), "golden", "reference_heads.pt"),
+                       weights_only=False)
+    assert len(cases) == 3
+    for c in cases:
+        cos, sin = R.rope_tables(c["positions"], c["rotary_dim"], c["theta"])
+        assert torch.equal(_bits(cos), _bits(c["cos"])) and torch.equal(_bits(sin), _bits(c["sin"]))
+        q, k, v = R.heads_prefill(c["qkv"], c["q_heads"], c["kv_heads"], c["head_dim"], c["w_qn"],
+                                  c["w_kn"], cos, sin, c["rotary_dim"], c["eps"])
+        assert torch.equal(_bits(q), _bits(c["q"]))
+        assert torch.equal(_bits(k), _bits(c["k"]))
+        assert torch.equal(_bits(v), _bits(c["v"]))
+        # unrotated channels pass through the rope bit-exact
+        plain = R.rms_norm(c["qkv"][:, :c["q_heads"] * c["head_dim"]]
+                           .reshape(-1, c["q_heads"], c["head_dim"]), c["w_qn"], c["eps"])
+        assert torch.equal(_bits(q[..., c["rotary_dim"]:]), _bits(plain[..., c["rotary_dim"]:]))
+        qd, kd, vd = R.heads_decode(c["qkv"].float(), c["q_heads"], c["kv_heads"], c["head_dim"],
+                                    c["w_qn"], c["w_kn"], cos, sin, c["rotary_dim"], c["eps"])
+        assert torch.equal(_bits(vd), _bits(c["v"]))
+        assert R.rel_fro(qd, c["q"]) <= 4e-3 and R.rel_fro(kd, c["k"]) <= 4e-3
