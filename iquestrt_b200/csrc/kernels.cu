@@ -392,7 +392,7 @@ __device__ __forceinline__ bool poll_zone_row(const PushView& pv, uint32_t* zs, 
 
 // Runs on the threads of `bar` (a multiple of 32; h <= 16 * threads) for rows r_begin,
 // r_begin + r_step, ... of the call.  `red` is shared memory for 4 x 32 floats, `sflag`
-// one shared int, `park` shared memory for h x 4 bytes (the residual row waits there),
+// one shared int, `park` shared memory for the residual row (it waits there),
 // `zs` (push only) shared memory for per_round x h words.  Without `kPush`,
 // rows written by other CTAs of this launch must already be visible (the caller passed
 // the ticket) and the pull protocol's signal / wait / switch read applies for world > 1.
@@ -408,6 +408,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
                                          int r_step = 1) {
   const int tid = threadIdx.x, nthr = bar.threads();
   const uint32_t res_s = smem_u32(park);
+  const int pstride = a.residual_fp32 ? 32 : 16;      // parked bytes per 8 elements
   const int m = a.m, h = a.h, vec_per_row = h / 8;
   const float inv_h = 1.0f / static_cast<float>(h);
   const bool attn = a.kind == IQ_TAIL_ATTN;
@@ -432,10 +433,10 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
       const size_t off = row_off + static_cast<size_t>(v) * 8;
       if (a.residual_fp32) {
         const float* rp = static_cast<const float*>(a.residual) + off;
-        cp_async16(res_s + v * 32, rp);
-        cp_async16(res_s + v * 32 + 16, rp + 4);
+        cp_async16(res_s + v * pstride, rp);
+        cp_async16(res_s + v * pstride + 16, rp + 4);
       } else {
-        cp_async16(res_s + v * 32, static_cast<const __nv_bfloat16*>(a.residual) + off);
+        cp_async16(res_s + v * pstride, static_cast<const __nv_bfloat16*>(a.residual) + off);
       }
     }
     cp_async_commit();
@@ -546,9 +547,9 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
       if (v >= vec_per_row) continue;
       const size_t off = row_off + static_cast<size_t>(v) * 8;
       float res[8];
-      const uint4 ra = lds128(res_s + v * 32);
+      const uint4 ra = lds128(res_s + v * pstride);
       if (a.residual_fp32) {
-        const uint4 rb = lds128(res_s + v * 32 + 16);
+        const uint4 rb = lds128(res_s + v * pstride + 16);
         res[0] = __uint_as_float(ra.x); res[1] = __uint_as_float(ra.y);
         res[2] = __uint_as_float(ra.z); res[3] = __uint_as_float(ra.w);
         res[4] = __uint_as_float(rb.x); res[5] = __uint_as_float(rb.y);
@@ -621,6 +622,11 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
   if (!kPush && a.world > 1 && tid == 0) *a.epoch = *a.epoch + 1u;
 }
 
+// Shared memory for a parked residual row.
+__host__ __device__ inline size_t tail_park_bytes(int h, int residual_fp32) {
+  return static_cast<size_t>(h) * (residual_fp32 ? 4 : 2);
+}
+
 // A tail CTA of the push protocol: CTA `index` of `n_tail` finishes rows index,
 // index + n_tail, ...  The last tail CTA to finish closes the call (the zone's epoch moves
 // on once every tail CTA has read it).
@@ -629,7 +635,7 @@ __device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& 
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
   uint8_t* park = smem + 1024;
-  uint32_t* zs = reinterpret_cast<uint32_t*>(smem + 1024 + static_cast<size_t>(a.h) * 4);
+  uint32_t* zs = reinterpret_cast<uint32_t*>(smem + 1024 + tail_park_bytes(a.h, a.residual_fp32));
   if (threadIdx.x < kTailThreads)
     run_tail<true>(a, pv, park, zs, per_round, red, sflag, BlockBar{2, kTailThreads}, index,
                    n_tail);
@@ -646,14 +652,15 @@ __device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& 
 
 // Sources a tail CTA takes per round when it may use `limit` bytes of shared memory, and
 // the shared memory that takes.
-__host__ __device__ inline int tail_sources_per_round(int world, int h, size_t limit) {
-  const size_t row = static_cast<size_t>(h) * 4;
-  int n = limit > 1024 + 2 * row ? static_cast<int>((limit - 1024 - row) / row) : 0;
+__host__ __device__ inline int tail_sources_per_round(int world, int h, int residual_fp32,
+                                                      size_t limit) {
+  const size_t row = static_cast<size_t>(h) * 4, fixed = 1024 + tail_park_bytes(h, residual_fp32);
+  int n = limit > fixed + row ? static_cast<int>((limit - fixed) / row) : 0;
   return n > world ? world : n;
 }
 // (control words, the parked residual row, the rows of one round)
-__host__ __device__ inline size_t tail_cta_smem(int per_round, int h) {
-  return 1024 + static_cast<size_t>(per_round + 1) * h * 4;
+__host__ __device__ inline size_t tail_cta_smem(int per_round, int h, int residual_fp32) {
+  return 1024 + tail_park_bytes(h, residual_fp32) + static_cast<size_t>(per_round) * h * 4;
 }
 
 __global__ void __launch_bounds__(kTailThreads) tail_kernel(const TailParams p) {
@@ -1769,9 +1776,9 @@ static int plan_tail(TailPlan& tp, const iq_tail_args* tail, const iq_push_args*
     tp.tail_run = kTailCtas;
     tp.n_tail = m;
     tp.push = 1;
-    tp.per_round = tail_sources_per_round(tp.pv.world, h, smem_limit);
+    tp.per_round = tail_sources_per_round(tp.pv.world, h, tail->residual_fp32, smem_limit);
     if (tp.per_round < 1) return IQ_ERR_UNSUPPORTED;
-    tp.smem = tail_cta_smem(tp.per_round, h);
+    tp.smem = tail_cta_smem(tp.per_round, h, tail->residual_fp32);
   } else if (tail) {
     tp.tail_run = kTailLastCta;
   } else if (push_only) {
@@ -1861,14 +1868,14 @@ extern "C" int iq_tail(const iq_tail_args* a, void* stream, int pdl) {
     p.push = 1;
     p.n_tail = a->m;
     // a small CTA that can sit beside a streaming kernel's: half an SM's shared memory
-    p.per_round = tail_sources_per_round(p.pv.world, a->h, kSmemLimitShared);
+    p.per_round = tail_sources_per_round(p.pv.world, a->h, a->residual_fp32, kSmemLimitShared);
     if (p.per_round < 1) return IQ_ERR_UNSUPPORTED;
-    return launch(tail_kernel, p, a->m, kTailThreads, tail_cta_smem(p.per_round, a->h), stream,
-                  pdl);
+    return launch(tail_kernel, p, a->m, kTailThreads,
+                  tail_cta_smem(p.per_round, a->h, a->residual_fp32), stream, pdl);
   }
   // rows in `partial`: one CTA per row without peers, one CTA (one signal / wait) with
-  return launch(tail_kernel, p, a->world == 1 ? a->m : 1, kTailThreads, tail_cta_smem(0, a->h),
-                stream, pdl);
+  return launch(tail_kernel, p, a->world == 1 ? a->m : 1, kTailThreads,
+                tail_cta_smem(0, a->h, a->residual_fp32), stream, pdl);
 }
 
 extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
