@@ -50,6 +50,27 @@ __host__ __device__ inline StreamScratch scratch_of(void* base) {
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Per-CTA timelines, compiled in with -DIQ_TRACE only: every launch made while a trace
+// buffer is set (iq_trace_set) takes the next slot of it, and each CTA stamps %globaltimer
+// at a few points of its life into `trace[cta][point]` (point 15: the SM it ran on).
+constexpr int kTraceCtas = 304;
+constexpr int kTraceWords = 16;
+#ifdef IQ_TRACE
+#define IQ_TRACE_FIELD unsigned long long* trace;
+#define IQ_STAMP(p, k)                                                                   \
+  do {                                                                                   \
+    if ((p).trace) (p).trace[blockIdx.x * kTraceWords + (k)] = globaltimer_ns();          \
+  } while (0)
+__device__ __forceinline__ unsigned long long smid_of() {
+  unsigned v;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(v));
+  return v;
+}
+#else
+#define IQ_TRACE_FIELD
+#define IQ_STAMP(p, k) do {} while (0)
+#endif
+
 // Shared-memory carve-up after StreamSmem: activation scales, staged activations, ring.
 template <class G>
 struct Carve {
@@ -698,6 +719,7 @@ enum TailRun : int {
 };
 
 struct LinearParams {
+  IQ_TRACE_FIELD
   CUtensorMap map0, map1;   // weight tensor maps (unused for whole-row stages)
   StreamShape sh;
   const void* x;
@@ -743,9 +765,17 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
   const int cta = blockIdx.x;
   // CTAs that stream; the rest of the grid (push protocol) finishes the rows.
   const int stream_ctas = static_cast<int>(gridDim.x) - p.n_tail;
+  if (tid == 0) {
+    IQ_STAMP(p, 0);
+#ifdef IQ_TRACE
+    if (p.trace) p.trace[blockIdx.x * kTraceWords + 15] = smid_of();
+#endif
+  }
   if (cta >= stream_ctas) {
     after_wait();
+    if (tid == 0) IQ_STAMP(p, 9);
     tail_cta(p.tail, p.pv, p.per_round, cta - stream_ctas, p.n_tail, smem);
+    if (tid == 0) IQ_STAMP(p, 11);
     return;
   }
   const Carve<G> cv = carve<G>(smem, sh);
@@ -774,11 +804,13 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
     if (warp == G::PRODUCER_WARP) {
       // Weights never change: start streaming before the predecessor kernel has finished.
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
+      if (tid == G::PRODUCER_WARP * 32) IQ_STAMP(p, 3);
       pdl_wait();
     } else if (warp < G::WARPS) {
       float held[kGatherHeld];
       gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);   // weights: before the wait
       after_wait();
+      if (tid == 0) IQ_STAMP(p, 1);
       if (p.x_kind == IQ_X_BF16_GROUPQ || p.x_kind == IQ_X_BF16_SPLIT2)
         stage_rows_bf16_groupq(cv.xq, cv.xs, sh, static_cast<const __nv_bfloat16*>(p.x), p.k, p.m,
                                p.k, p.x_kind == IQ_X_BF16_SPLIT2, tid, G::CONSUMER_THREADS);
@@ -788,7 +820,9 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
                         G::CONSUMER_THREADS);
       gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
       named_bar_sync(1, G::CONSUMER_THREADS);
+      if (tid == 0) IQ_STAMP(p, 2);
       consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
+      if (tid == 0) IQ_STAMP(p, 4);
     } else {
       pdl_wait();
       const bool split2 = p.x_kind == IQ_X_BF16_SPLIT2;
@@ -821,6 +855,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
         }
       };
       epilogue<G, true>(sh, cv.sm, wk, total, grid, cta, scr, emit);
+      if (tid == G::EPILOGUE_WARP * 32) IQ_STAMP(p, 5);
     }
   }
   if (p.tail_run == kTailLastCta && last_cta<G>(cv.sm, scr, gridDim.x)) {
@@ -835,6 +870,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
 // ------------------------------------------------------------------------------------
 // iq_router: bf16 GEMV into fp32 logits, then top-k on the last CTA (one warp per row).
 struct RouterParams {
+  IQ_TRACE_FIELD
   CUtensorMap map0, map1;   // weight tensor maps (unused for whole-row stages)
   StreamShape sh;
   const __nv_bfloat16* x;
@@ -936,9 +972,16 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
   uint32_t* launch_tag = reinterpret_cast<uint32_t*>(scratch + kScrLaunchTag);
   uint64_t* tagged = reinterpret_cast<uint64_t*>(scratch + kScrLogits);
   const StreamScratch scr = scratch_of(p.scratch);
+  if (tid == 0) {
+    IQ_STAMP(p, 0);
+#ifdef IQ_TRACE
+    if (p.trace) p.trace[blockIdx.x * kTraceWords + 15] = smid_of();
+#endif
+  }
   if (cta == stream_ctas) {
     // ---- the selecting CTA
     after_wait();
+    if (tid == 0) IQ_STAMP(p, 9);
     const uint32_t tag = ld_volatile_u32(launch_tag) + 1u;
     float* lg = reinterpret_cast<float*>(smem);          // [m][e]
     if (warp < p.m) {
@@ -972,6 +1015,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
     }
     __syncthreads();
     if (tid == 0) *launch_tag = tag;
+    if (tid == 0) IQ_STAMP(p, 11);
     return;
   }
   const Carve<G> cv = carve<G>(smem, sh);
@@ -998,9 +1042,11 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
     const CtaWork wk = cta_share<G>(sh, stream_ctas, cta, grid);
     if (warp == G::PRODUCER_WARP) {
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
+      if (tid == G::PRODUCER_WARP * 32) IQ_STAMP(p, 3);
       pdl_wait();
     } else if (warp < G::WARPS) {
       after_wait();
+      if (tid == 0) IQ_STAMP(p, 1);
       if (wk.n_items > 0) {
         const int vec = p.h / 8;   // 16-byte vectors per bf16 row
         for (int i = tid; i < p.m * vec; i += G::CONSUMER_THREADS) {
@@ -1010,7 +1056,9 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
         }
       }
       named_bar_sync(1, G::CONSUMER_THREADS);
+      if (tid == 0) IQ_STAMP(p, 2);
       consume<G, ElemBF16>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
+      if (tid == 0) IQ_STAMP(p, 4);
     } else {
       pdl_wait();
       const int m = p.m, e = p.e;
@@ -1023,6 +1071,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
                                tag | __float_as_uint(val[sub]));
       };
       epilogue<G, false>(sh, cv.sm, wk, total, grid, cta, scr, emit);
+      if (tid == G::EPILOGUE_WARP * 32) IQ_STAMP(p, 5);
     }
   }
   stream_drain_on_abort<G>(cv.sm);
@@ -1260,6 +1309,7 @@ __device__ __noinline__ int build_groups(GroupDesc* groups, const MoeCommon& mc,
 }
 
 struct GateParams {
+  IQ_TRACE_FIELD
   CUtensorMap map0, map1;   // weight tensor maps (unused for whole-row stages)
   StreamShape sh;
   MoeCommon mc;
@@ -1338,6 +1388,12 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) gate_kernel(const 
   const StreamScratch scr = scratch_of(p.scratch);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int cta = blockIdx.x, n_cta = static_cast<int>(gridDim.x);
+  if (tid == 0) {
+    IQ_STAMP(p, 0);
+#ifdef IQ_TRACE
+    if (p.trace) p.trace[blockIdx.x * kTraceWords + 15] = smid_of();
+#endif
+  }
   stream_init<G>(sh, cv.sm);
   if (tid == G::PRODUCER_WARP * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
     prefetch_tensormap(&p.map0);   // only maps the host filled (K-sliced stages)
@@ -1383,6 +1439,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) gate_kernel(const 
     __syncthreads();
   }
   after_wait();                     // the routes come from the predecessor
+  if (tid == 0) IQ_STAMP(p, 1);
   sh.n_groups = build_groups(cv.sm->groups, p.mc, false, false, scr.status, cv.sm->route_ids,
                              BlockBar{}, nullptr, nullptr, nullptr, nullptr, p.early_shared != 0);
   const long long total =
@@ -1393,11 +1450,15 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) gate_kernel(const 
     wk.tile0 += wk.tile_step;
     wk.n_items -= wk.spt;
   }
+  if (tid == 0) IQ_STAMP(p, 2);
   gate_stream<G>(p, sh, cv, scr, wk, total, grid, cta, !early_x, pos, rpos);
+  if (tid == 0) IQ_STAMP(p, 4);
+  if (tid == G::EPILOGUE_WARP * 32) IQ_STAMP(p, 5);
   stream_drain_on_abort<G>(cv.sm);
 }
 
 struct DownParams {
+  IQ_TRACE_FIELD
   CUtensorMap map0, map1;   // weight tensor maps (unused for whole-row stages)
   StreamShape sh;
   MoeCommon mc;
@@ -1421,9 +1482,17 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int cta = blockIdx.x;
   const int stream_ctas = static_cast<int>(gridDim.x) - p.n_tail;
+  if (tid == 0) {
+    IQ_STAMP(p, 0);
+#ifdef IQ_TRACE
+    if (p.trace) p.trace[blockIdx.x * kTraceWords + 15] = smid_of();
+#endif
+  }
   if (cta >= stream_ctas) {
     after_wait();
+    if (tid == 0) IQ_STAMP(p, 9);
     tail_cta(p.tail, p.pv, p.per_round, cta - stream_ctas, p.n_tail, smem);
+    if (tid == 0) IQ_STAMP(p, 11);
     return;
   }
   const Carve<G> cv = carve<G>(smem, sh);
@@ -1450,6 +1519,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const 
       float held[kGatherHeld];
       gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);
       if (early) after_wait();
+      if (tid == 0) IQ_STAMP(p, 1);
       const int rows = p.mc.m * (p.mc.top_k + p.mc.n_shared);
       if (p.act_kind == IQ_ACT_E4M3)
         stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.act), p.mc.i_loc, nullptr,
@@ -1459,7 +1529,9 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const 
                                p.mc.i_loc, rows, p.mc.i_loc, false, tid, G::CONSUMER_THREADS);
       gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
       named_bar_sync(1, G::CONSUMER_THREADS);
+      if (tid == 0) IQ_STAMP(p, 2);
       consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
+      if (tid == 0) IQ_STAMP(p, 4);
     } else {
       if (early) pdl_wait();
       const int m = p.mc.m, h = p.mc.h;
@@ -1477,6 +1549,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const 
         }
       };
       epilogue<G, true>(sh, cv.sm, wk, total, grid, cta, scr, emit);
+      if (tid == G::EPILOGUE_WARP * 32) IQ_STAMP(p, 5);
     }
   }
   if (p.tail_run == kTailLastCta && last_cta<G>(cv.sm, scr, gridDim.x)) {
@@ -1609,9 +1682,29 @@ static int fill_maps(CUtensorMap* map0, CUtensorMap* map1, const StreamShape& sh
   return rc;
 }
 
+#ifdef IQ_TRACE
+static unsigned long long* g_trace_base = nullptr;
+static int g_trace_slots = 0, g_trace_next = 0;
+template <class Params>
+static auto trace_assign(Params& p, int) -> decltype(p.trace, void()) {
+  std::lock_guard<std::mutex> lock(g_host_mutex);
+  p.trace = nullptr;
+  if (g_trace_base && g_trace_next < g_trace_slots)
+    p.trace = g_trace_base + static_cast<size_t>(g_trace_next++) * kTraceCtas * kTraceWords;
+}
+template <class Params>
+static void trace_assign(Params&, long) {}
+#endif
+
 template <class Kernel, class Params>
-static int launch(Kernel kernel, const Params& p, int grid, int threads, size_t smem, void* stream,
-                  int pdl) {
+static int launch(Kernel kernel, const Params& p_in, int grid, int threads, size_t smem,
+                  void* stream, int pdl) {
+#ifdef IQ_TRACE
+  Params p = p_in;
+  trace_assign(p, 0);
+#else
+  const Params& p = p_in;
+#endif
   // One opt-in to the full shared memory per kernel and device.
   if (!ensure_smem_optin(reinterpret_cast<const void*>(kernel))) return IQ_ERR_CUDA;
   cudaLaunchConfig_t cfg{};
@@ -1695,8 +1788,26 @@ static size_t plan_smem(StreamShape& sh, int grid, size_t other_bytes, int max_g
   return need <= limit ? need : 0;
 }
 
-// Streams up to this many bytes per launch run with two CTAs per SM.
-constexpr long long kShortStreamBytes = 40ll << 20;
+// Tuning knobs read once from the environment: IQB200_SHORT_STREAM_MB (streams up to
+// this many megabytes per launch run with two CTAs per SM; default 40, 0 = never) and
+// IQB200_SHARED_GRID (CTAs such a launch starts per SM: 1 leaves the other half of every
+// SM to the next kernel of the chain, 2 takes both halves; default 1).
+static long long env_number(const char* name, long long fallback) {
+  const char* v = getenv(name);
+  if (!v || !*v) return fallback;
+  char* end = nullptr;
+  const long long n = strtoll(v, &end, 10);
+  return end && *end == 0 && n >= 0 ? n : fallback;
+}
+static long long short_stream_bytes() {
+  static const long long v = env_number("IQB200_SHORT_STREAM_MB", 40) << 20;
+  return v;
+}
+template <class G>
+static int grid_for() {
+  static const int factor = env_number("IQB200_SHARED_GRID", 1) >= 2 ? 2 : 1;
+  return sm_count() * (G::CTAS_PER_SM == 2 ? factor : 1);
+}
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -1809,7 +1920,7 @@ static int linear_launch(const iq_linear_args* a, void* stream) {
   int rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->n,
                      smem_limit<G>());
   if (rc != IQ_OK) return rc;
-  const int grid = sm_count();
+  const int grid = grid_for<G>();
   const size_t smem = plan_smem<G>(sh, grid - tp.n_tail, tp.smem);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   rc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->n, nullptr, 0);
@@ -1901,7 +2012,7 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   // A short stream takes CTAs of eight (six) consumer warps, two of which share an SM, so
   // that its successor's CTAs set up and prefetch beside it (see Geo); a long stream takes
   // the whole SM.
-  if (static_cast<long long>(n) * k <= kShortStreamBytes) {
+  if (static_cast<long long>(n) * k <= short_stream_bytes()) {
     // (falls through to a whole-SM geometry when half an SM cannot hold the rows and a ring)
     int rc = IQ_ERR_UNSUPPORTED;
     if (k % 1024 == 0 && n % 16 == 0) rc = linear_launch<Geo<1, 8, 2>>(a, stream);
@@ -1970,7 +2081,7 @@ static int router_launch(const iq_router_args* a, void* stream) {
   sh.x_rows = a->m;
   sh.x_pitch = a->h * 2 + 64;
   sh.x_blocks = 1;
-  const int grid = sm_count();
+  const int grid = grid_for<G>();
   // the launch's last CTA selects; it keeps the rows' logits in shared memory
   const size_t smem = plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
@@ -2047,9 +2158,9 @@ static int gate_launch(const iq_moe_gate_args* a, void* stream) {
   sh.x_blocks = a->h / 128;
   // Early start on the shared experts (pdl level 2 only): needs whole tiles for every group
   // count valid routes can produce, so that a CTA's first tile is known before the routes.
+  const int grid = grid_for<G>();
   bool early = a->pdl >= 2 && a->n_shared > 0;
   if (early) {
-    const int grid = sm_count();
     for (int n = a->n_shared + a->top_k; n <= a->n_shared + a->m * a->top_k && early; ++n) {
       StreamShape t = sh;
       t.n_groups = n;
@@ -2061,7 +2172,7 @@ static int gate_launch(const iq_moe_gate_args* a, void* stream) {
     sh.round_robin = 1;
   }
   p.early_shared = early ? 1 : 0;
-  const size_t smem = plan_smem<G>(sh, sm_count(), 0, a->m * a->top_k + a->n_shared);
+  const size_t smem = plan_smem<G>(sh, grid, 0, a->m * a->top_k + a->n_shared);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->fc,
                                static_cast<long long>(a->n_experts) * 2 * a->i_loc, a->shared_fc,
@@ -2074,7 +2185,7 @@ static int gate_launch(const iq_moe_gate_args* a, void* stream) {
   p.act_kind = a->act_kind;
   p.scratch = a->scratch;
   p.pdl_level = a->pdl;
-  return launch(gate_kernel<G>, p, sm_count(), G::THREADS, smem, stream, a->pdl);
+  return launch(gate_kernel<G>, p, grid, G::THREADS, smem, stream, a->pdl);
 }
 
 // Bytes the expert kernels stream for `m` rows: every routed pair a distinct expert (the
@@ -2096,7 +2207,7 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   if (sm_count() == 0) return IQ_ERR_CUDA;
   const long long bytes = expert_stream_bytes(a->m, a->top_k, a->n_experts, a->n_shared,
                                               2ll * a->i_loc * a->h);
-  if (bytes <= kShortStreamBytes) {
+  if (bytes <= short_stream_bytes()) {
     const int rc = gate_launch<Geo<2, 4, 2>>(a, stream);
     if (rc != IQ_ERR_UNSUPPORTED) return rc;
   }
@@ -2129,7 +2240,7 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   TailPlan tp;
   rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->h, smem_limit<G>());
   if (rc != IQ_OK) return rc;
-  const int grid = sm_count();
+  const int grid = grid_for<G>();
   const size_t smem = plan_smem<G>(sh, grid - tp.n_tail, tp.smem, a->m * a->top_k + a->n_shared);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->proj,
@@ -2171,7 +2282,7 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   const int k = a->i_loc;
   const long long bytes = expert_stream_bytes(a->m, a->top_k, a->n_experts, a->n_shared,
                                               static_cast<long long>(a->h) * a->i_loc);
-  if (bytes <= kShortStreamBytes) {
+  if (bytes <= short_stream_bytes()) {
     // two CTAs per SM (see Geo); fall through when the staged activations leave no room
     int rc = IQ_ERR_UNSUPPORTED;
     if (k % 1024 == 0) rc = down_launch<Geo<1, 8, 2>>(a, stream);
@@ -2272,3 +2383,14 @@ extern "C" int iq_linear_static_status(int* code, void* stream) {
   if (cudaStreamSynchronize(s) != cudaSuccess) return IQ_ERR_CUDA;
   return IQ_OK;
 }
+
+#ifdef IQ_TRACE
+// Trace builds only: `base` receives slots x 304 x 16 u64 stamps, one slot per launch in
+// launch order from now on (NULL stops tracing).
+extern "C" void iq_trace_set(void* base, int slots) {
+  std::lock_guard<std::mutex> lock(iqb::g_host_mutex);
+  iqb::g_trace_base = static_cast<unsigned long long*>(base);
+  iqb::g_trace_slots = slots;
+  iqb::g_trace_next = 0;
+}
+#endif
