@@ -15,9 +15,16 @@ class PrologueKernels:
     """QKV + heads over arena slots for `q_len` rows of a rank's head shard."""
 
     def __init__(self, hidden: int, q_heads: int, kv_heads: int, head_dim: int, rotary_dim: int,
-                 eps: float, *, ws, q_len: int, scratch=None):
+                 eps: float, *, ws, q_len: int, activation: str | None = None, scratch=None):
         if not 1 <= q_len <= 8:
             raise ValueError(f"the prologue covers 1..8 rows, got {q_len}")
+        if activation is None:
+            # the reference's QKV product is W8A16: keep bf16 precision (two e4m3 terms per
+            # activation) where the rows fit the MMA's eight columns
+            activation = "w8a16" if q_len <= 4 else "group"
+        if activation not in ("group", "w8a16") or (activation == "w8a16" and q_len > 4):
+            raise ValueError(f"unsupported activation {activation!r} for {q_len} rows")
+        self.x_kind = ops.X_BF16_SPLIT2 if activation == "w8a16" else ops.X_BF16_GROUPQ
         if head_dim % 2 or head_dim > 256 or rotary_dim % 2 or rotary_dim > head_dim:
             raise ValueError(f"unsupported head shape D={head_dim}, rotary={rotary_dim}")
         self.hidden, self.q_len, self.eps = hidden, q_len, float(eps)
@@ -45,7 +52,8 @@ class PrologueKernels:
         caches.  `w_qkv [n_qkv, hidden]` is e4m3 with its rank-local `[n_qkv/128,
         hidden/128]` scale table."""
         xn = xn.reshape(self.q_len, self.hidden)
-        ops.linear(xn, w_qkv, w_scale, scratch=self.scratch, out_f32=self.qkv, pdl=pdl)
+        ops.linear(xn, w_qkv, w_scale, scratch=self.scratch, x_kind=self.x_kind,
+                   out_f32=self.qkv, pdl=pdl)
         return xn, self.heads(w_qn, w_kn, cos, sin, slot, k_cache, v_cache, pdl=pdl)
 
     def heads(self, w_qn, w_kn, cos, sin, slot, k_cache, v_cache, *, pdl=False):

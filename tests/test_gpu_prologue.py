@@ -100,11 +100,12 @@ def test_prologue_holder_qkv_then_heads(m, tp):
     for _ in range(2):
         _, q = pro.call_prenorm(xn, w, ws_, w_qn, w_kn, cos.cuda(), sin.cuda(), slot, kc, vc)
     assert scr.status() == 0
-    # the fp32 product against the oracle's quantised-activation product
-    xq, xs = R.quant_act_group(xn.cpu())
-    want = R.linear_a8(xq, xs, w.cpu(), ws_.cpu(), out_dtype=torch.float32)
+    # the fp32 product against the reference's W8A16 product before its rounding (bf16
+    # activations; the kernel carries them as two e4m3 terms)
+    want = torch.nn.functional.linear(xn.cpu().float(),
+                                      R.dequant(w.cpu(), ws_.cpu(), dtype=torch.float32))
     got = pro.qkv.cpu()
-    assert R.rel_fro(got, want) <= 1e-4
+    assert R.rel_fro(got, want) <= 4e-3
     # heads on the kernel's own product: bit-exact against the oracle's decode form
     wq, wk, wv = R.heads_decode(got, qh, kh, d, w_qn.cpu(), w_kn.cpu(), cos, sin, rot, 1e-6)
     assert torch.equal(_bits(q.cpu()), _bits(wq))
@@ -114,3 +115,12 @@ def test_prologue_holder_qkv_then_heads(m, tp):
     ref_qkv = R.linear(xn.cpu(), w.cpu(), ws_.cpu())
     rq, rk, rv = R.heads_prefill(ref_qkv, qh, kh, d, w_qn.cpu(), w_kn.cpu(), cos, sin, rot, 1e-6)
     assert R.rel_fro(q.cpu(), rq) <= 2e-2
+    # single-term 1x128-group activations (the benchmark format) stay within e4m3 precision
+    pro_g = PrologueKernels(hidden, qh, kh, d, rot, 1e-6, ws=Workspace(device="cuda"), q_len=m,
+                            activation="group", scratch=scr)
+    _, qg = pro_g.call_prenorm(xn, w, ws_, w_qn, w_kn, cos.cuda(), sin.cuda(), slot, kc, vc)
+    assert scr.status() == 0
+    xq, xs = R.quant_act_group(xn.cpu())
+    want_g = R.linear_a8(xq, xs, w.cpu(), ws_.cpu(), out_dtype=torch.float32)
+    assert R.rel_fro(pro_g.qkv.cpu(), want_g) <= 1e-4
+    assert R.rel_fro(qg.cpu(), rq) <= 4e-2
