@@ -229,8 +229,9 @@ struct PushView {
   uint32_t* recv_mc;          // multicast alias, or null
   uint32_t* const* peer_recv; // device array [world], or null
   uint32_t* epoch;            // local word: completed calls on the zone (the tag's source)
-  uint32_t* ticket;           // local word: tail CTAs of the running call that are done
+  uint32_t* ticket;           // local word: tail CTAs of the running call that have started
   int world, rank, rows, h;
+  unsigned long long* trace;  // trace builds: this CTA's stamps (else null)
 };
 
 // Tags run over 1..65535, so a zero-filled zone never looks complete.
@@ -411,9 +412,10 @@ __device__ __forceinline__ bool poll_zone_row(const PushView& pv, uint32_t* zs, 
   return ok;
 }
 
-// Runs on the threads of `bar` (a multiple of 32; h <= 16 * threads) for rows r_begin,
+// Runs on the threads of `bar` (a multiple of 32) for rows r_begin,
 // r_begin + r_step, ... of the call.  `red` is shared memory for 4 x 32 floats, `sflag`
-// one shared int, `park` shared memory for the residual row (it waits there),
+// one shared int (push: set to 1 by the caller), `tag` (push) the call's tag, `park` shared
+// memory for the residual row (it waits there),
 // `zs` (push only) shared memory for per_round x h words.  Without `kPush`,
 // rows written by other CTAs of this launch must already be visible (the caller passed
 // the ticket) and the pull protocol's signal / wait / switch read applies for world > 1.
@@ -423,22 +425,16 @@ __device__ __forceinline__ bool poll_zone_row(const PushView& pv, uint32_t* zs, 
 // (the residual stays packed until it is used; each norm weight is fetched just before
 // the barrier of the reduction that precedes its use, which hides its latency).
 template <bool kPush>
-__device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& pv, uint8_t* park,
-                                         uint32_t* zs, int per_round, float* red, int* sflag,
-                                         const BlockBar bar = BlockBar{}, int r_begin = 0,
-                                         int r_step = 1) {
+__device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& pv, uint32_t tag,
+                                         uint8_t* park, uint32_t* zs, int per_round, float* red,
+                                         int* sflag, const BlockBar bar = BlockBar{},
+                                         int r_begin = 0, int r_step = 1) {
   const int tid = threadIdx.x, nthr = bar.threads();
   const uint32_t res_s = smem_u32(park);
   const int pstride = a.residual_fp32 ? 32 : 16;      // parked bytes per 8 elements
   const int m = a.m, h = a.h, vec_per_row = h / 8;
   const float inv_h = 1.0f / static_cast<float>(h);
   const bool attn = a.kind == IQ_TAIL_ATTN;
-  uint32_t tag = 0;
-  if (kPush) {
-    tag = tag16_of(ld_volatile_u32(pv.epoch));
-    if (tid == 0) *sflag = 1;
-    bar.sync();
-  }
 
   for (int r = r_begin; r < m; r += r_step) {
     const size_t row_off = static_cast<size_t>(r) * h;
@@ -473,6 +469,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
         if (tid == 0) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
         return;
       }
+      if (tid == 0 && pv.trace) pv.trace[10] = globaltimer_ns();
     } else {
       // ---- cross-rank readiness: signal, then wait while the residual loads are in flight
       if (r == r_begin && a.world > 1) {
@@ -655,20 +652,30 @@ __device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& 
                                          int index, int n_tail, uint8_t* smem) {
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
+  uint32_t* word = reinterpret_cast<uint32_t*>(smem + 516);     // [epoch, closes the call]
   uint8_t* park = smem + 1024;
   uint32_t* zs = reinterpret_cast<uint32_t*>(smem + 1024 + tail_park_bytes(a.h, a.residual_fp32));
-  if (threadIdx.x < kTailThreads)
-    run_tail<true>(a, pv, park, zs, per_round, red, sflag, BlockBar{2, kTailThreads}, index,
-                   n_tail);
-  __syncthreads();
+  // The call's tag comes from the zone's epoch.  The epoch may move on once (a) every tail
+  // CTA has read it and (b) every producer has: the tail CTA that reads it LAST takes on
+  // the job, and does it after its own rows are complete (every producer of the launch
+  // contributes to every row, so by then all of them have read the epoch).  That keeps the
+  // atomic at the start of the tail, where it waits for data anyway, and off its end.
   if (threadIdx.x == 0) {
-    __threadfence();
-    const uint32_t prev = atomicAdd(pv.ticket, 1u);
-    if (prev == static_cast<uint32_t>(n_tail - 1)) {
-      *pv.ticket = 0;
-      *pv.epoch = ld_volatile_u32(pv.epoch) + 1u;
+    word[0] = ld_volatile_u32(pv.epoch);
+    uint32_t closes = 1;
+    if (n_tail > 1) {
+      closes = atomicAdd(pv.ticket, 1u) == static_cast<uint32_t>(n_tail - 1);
+      if (closes) *pv.ticket = 0;
     }
+    word[1] = closes;
+    *sflag = 1;
   }
+  __syncthreads();
+  const uint32_t epoch = word[0];
+  if (threadIdx.x < kTailThreads)
+    run_tail<true>(a, pv, tag16_of(epoch), park, zs, per_round, red, sflag,
+                   BlockBar{2, kTailThreads}, index, n_tail);
+  if (threadIdx.x == 0 && word[1]) *pv.epoch = epoch + 1u;
 }
 
 // Sources a tail CTA takes per round when it may use `limit` bytes of shared memory, and
@@ -694,7 +701,7 @@ __global__ void __launch_bounds__(kTailThreads) tail_kernel(const TailParams p) 
   }
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
-  run_tail<false>(p.a, p.pv, smem + 1024, nullptr, 0, red, sflag, BlockBar{},
+  run_tail<false>(p.a, p.pv, 0u, smem + 1024, nullptr, 0, red, sflag, BlockBar{},
                   static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
 }
 
@@ -774,7 +781,11 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
   if (cta >= stream_ctas) {
     after_wait();
     if (tid == 0) IQ_STAMP(p, 9);
-    tail_cta(p.tail, p.pv, p.per_round, cta - stream_ctas, p.n_tail, smem);
+    PushView pv = p.pv;
+#ifdef IQ_TRACE
+    pv.trace = p.trace ? p.trace + blockIdx.x * kTraceWords : nullptr;
+#endif
+    tail_cta(p.tail, pv, p.per_round, cta - stream_ctas, p.n_tail, smem);
     if (tid == 0) IQ_STAMP(p, 11);
     return;
   }
@@ -861,7 +872,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
   if (p.tail_run == kTailLastCta && last_cta<G>(cv.sm, scr, gridDim.x)) {
     float* red = reinterpret_cast<float*>(cv.sm->red);
     if (threadIdx.x < kTailThreads)
-      run_tail<false>(p.tail, p.pv, cv.ring, nullptr, 0, red, &cv.sm->is_last_tile,
+      run_tail<false>(p.tail, p.pv, 0u, cv.ring, nullptr, 0, red, &cv.sm->is_last_tile,
                       BlockBar{2, kTailThreads});   // (the ring is idle now)
   }
   stream_drain_on_abort<G>(cv.sm);
@@ -1491,7 +1502,11 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const 
   if (cta >= stream_ctas) {
     after_wait();
     if (tid == 0) IQ_STAMP(p, 9);
-    tail_cta(p.tail, p.pv, p.per_round, cta - stream_ctas, p.n_tail, smem);
+    PushView pv = p.pv;
+#ifdef IQ_TRACE
+    pv.trace = p.trace ? p.trace + blockIdx.x * kTraceWords : nullptr;
+#endif
+    tail_cta(p.tail, pv, p.per_round, cta - stream_ctas, p.n_tail, smem);
     if (tid == 0) IQ_STAMP(p, 11);
     return;
   }
@@ -1555,7 +1570,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const 
   if (p.tail_run == kTailLastCta && last_cta<G>(cv.sm, scr, gridDim.x)) {
     float* red = reinterpret_cast<float*>(cv.sm->red);
     if (threadIdx.x < kTailThreads)
-      run_tail<false>(p.tail, p.pv, cv.ring, nullptr, 0, red, &cv.sm->is_last_tile,
+      run_tail<false>(p.tail, p.pv, 0u, cv.ring, nullptr, 0, red, &cv.sm->is_last_tile,
                       BlockBar{2, kTailThreads});   // (the ring is idle now)
   }
   stream_drain_on_abort<G>(cv.sm);
@@ -1765,9 +1780,11 @@ constexpr size_t smem_limit() {
 // Fills the geometry-dependent part of a shape and returns the dynamic shared memory to
 // request, or 0 when the ring does not fit.  `grid` is the number of CTAs that stream,
 // `max_groups` bounds the group count a kernel may derive from the routes, `other_bytes`
-// is what another role of the launch (a tail CTA) needs.
+// is what another role of the launch (a tail CTA) needs, `ring_bytes` the ring depth to
+// aim for.
 template <class G>
-static size_t plan_smem(StreamShape& sh, int grid, size_t other_bytes, int max_groups = 1) {
+static size_t plan_smem(StreamShape& sh, int grid, size_t other_bytes, int max_groups = 1,
+                        size_t ring_bytes = 160 * 1024) {
   if (grid < 1) return 0;
   sh.max_items = max_items_any<G>(sh, max_groups, grid);
   if (sh.max_items == 0) return 0;
@@ -1779,7 +1796,7 @@ static size_t plan_smem(StreamShape& sh, int grid, size_t other_bytes, int max_g
   // with one CTA per SM, 160 KB is where more depth stops paying (96 KB: Gate 46 us,
   // 160 KB: 42 us).  A CTA that shares its SM takes what its half allows.
   int stages = static_cast<int>((limit - fixed) / G::STAGE_BYTES);
-  const int want = (160 * 1024 + G::STAGE_BYTES - 1) / G::STAGE_BYTES;
+  const int want = static_cast<int>((ring_bytes + G::STAGE_BYTES - 1) / G::STAGE_BYTES);
   if (stages > want) stages = want;
   if (stages > kMaxStages) stages = kMaxStages;
   sh.n_stages = stages;
@@ -1791,7 +1808,8 @@ static size_t plan_smem(StreamShape& sh, int grid, size_t other_bytes, int max_g
 // Tuning knobs read once from the environment: IQB200_SHORT_STREAM_MB (streams up to
 // this many megabytes per launch run with two CTAs per SM; default 40, 0 = never) and
 // IQB200_SHARED_GRID (CTAs such a launch starts per SM: 1 leaves the other half of every
-// SM to the next kernel of the chain, 2 takes both halves; default 1).
+// SM to the next kernel of the chain, 2 takes both halves; default 1; the expert Down
+// takes both halves on its own when it has more tiles than SMs).
 static long long env_number(const char* name, long long fallback) {
   const char* v = getenv(name);
   if (!v || !*v) return fallback;
@@ -1804,9 +1822,9 @@ static long long short_stream_bytes() {
   return v;
 }
 template <class G>
-static int grid_for() {
+static int grid_for(bool both_halves = false) {
   static const int factor = env_number("IQB200_SHARED_GRID", 1) >= 2 ? 2 : 1;
-  return sm_count() * (G::CTAS_PER_SM == 2 ? factor : 1);
+  return sm_count() * (G::CTAS_PER_SM == 2 ? (both_halves ? 2 : factor) : 1);
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -2083,7 +2101,10 @@ static int router_launch(const iq_router_args* a, void* stream) {
   sh.x_blocks = 1;
   const int grid = grid_for<G>();
   // the launch's last CTA selects; it keeps the rows' logits in shared memory
-  const size_t smem = plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e);
+  // (a ring for a CTA's whole row set when the SM has room for it)
+  const size_t tile_bytes = static_cast<size_t>(G::ROWS) * sh.k_bytes;
+  const size_t smem = plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e, 1,
+                                   tile_bytes > 160 * 1024 ? tile_bytes : 160 * 1024);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->e, nullptr, 0);
   if (mrc != IQ_OK) return mrc;
@@ -2111,7 +2132,10 @@ extern "C" int iq_router(const iq_router_args* a, void* stream) {
   if (a->score != IQ_ROUTE_SOFTMAX && a->score != IQ_ROUTE_SIGMOID) return IQ_ERR_ARG;
   if (!aligned16(a->x) || !aligned16(a->w)) return IQ_ERR_ARG;
   if (sm_count() < 2) return IQ_ERR_CUDA;
-  if ((a->h * 2) % 1024 == 0) return router_launch<Geo<1, 8, 2>>(a, stream);
+  // Sixteen experts per CTA: few CTAs, each with a long row set (196 KB at hidden 6144).  Eight
+  // consumer warps on a WHOLE SM keep a ring deep enough for all of it, so the CTA's entire
+  // stream is in shared memory before the dependency wait returns.
+  if ((a->h * 2) % 1024 == 0) return router_launch<Geo<1, 8, 2, 1>>(a, stream);
   return router_launch<Geo<1, 16, 1>>(a, stream);
 }
 
@@ -2240,7 +2264,11 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   TailPlan tp;
   rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->h, smem_limit<G>());
   if (rc != IQ_OK) return rc;
-  const int grid = grid_for<G>();
+  // The Down's tiles are known before the routes (rows of the hidden dimension).  With more
+  // tiles than SMs a launch on half of every SM leaves some CTAs with twice the others'
+  // stream; the launch that follows the Down waits for its all-reduce tail anyway and has
+  // time to become resident afterwards, so the Down takes both halves.
+  const int grid = grid_for<G>(stream_tiles_per_group<G>(sh) > sm_count());
   const size_t smem = plan_smem<G>(sh, grid - tp.n_tail, tp.smem, a->m * a->top_k + a->n_shared);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->proj,

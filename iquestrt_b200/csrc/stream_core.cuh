@@ -54,7 +54,10 @@ constexpr int kSmemLimitShared = (233472 - 2 * 1024) / 2;
 // become resident while this kernel is still streaming, set themselves up and fill their
 // own ring with weights before their dependency wait, so a short stream does not pay the
 // launch, the set-up and the first-byte latency of its successor end to end.
-template <int RT_, int KW_, int RUNS_>
+// `SHARE_` overrides how many CTAs are meant to share an SM (0: two for up to eight
+// consumer warps, else one): a few-warp CTA that takes a whole SM can keep a much deeper
+// ring than its share of an SM would allow.
+template <int RT_, int KW_, int RUNS_, int SHARE_ = 0>
 struct Geo {
   static constexpr int RT = RT_, KW = KW_, RUNS = RUNS_;
   static constexpr int WARPS = RT * KW;                 // consumer warps
@@ -63,7 +66,8 @@ struct Geo {
   static constexpr int THREADS = CONSUMER_THREADS + 64; // + the producer warp + the epilogue warp
   static constexpr int PRODUCER_WARP = WARPS;
   static constexpr int EPILOGUE_WARP = WARPS + 1;
-  static constexpr int CTAS_PER_SM = WARPS <= 8 ? 2 : 1;
+  static constexpr int CTAS_PER_SM = SHARE_ ? SHARE_ : (WARPS <= 8 ? 2 : 1);
+  static_assert(CTAS_PER_SM == 1 || (CTAS_PER_SM == 2 && WARPS <= 8), "one or two CTAs per SM");
   static constexpr int ROWS = 16 * RT;
   static constexpr int KC = KW * RUNS * 64;
   // A stage lands as NBOX dense boxes of (ROWS x BOXK bytes), one TMA copy each (a tensor
