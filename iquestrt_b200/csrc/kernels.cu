@@ -45,6 +45,7 @@ __host__ __device__ inline StreamScratch scratch_of(void* base) {
   s.ticket = reinterpret_cast<uint32_t*>(b + kScrTicket);
   s.tile_counter = reinterpret_cast<uint32_t*>(b + kScrCounters);
   s.partials = reinterpret_cast<float*>(b + kScrPartials);
+  s.trace = nullptr;
   return s;
 }
 
@@ -57,6 +58,8 @@ constexpr int kTraceCtas = 304;
 constexpr int kTraceWords = 16;
 #ifdef IQ_TRACE
 #define IQ_TRACE_FIELD unsigned long long* trace;
+#define IQ_TRACE_SCRATCH(scr, p) \
+  (scr).trace = (p).trace ? (p).trace + blockIdx.x * kTraceWords : nullptr
 #define IQ_STAMP(p, k)                                                                   \
   do {                                                                                   \
     if ((p).trace) (p).trace[blockIdx.x * kTraceWords + (k)] = globaltimer_ns();          \
@@ -68,6 +71,7 @@ __device__ __forceinline__ unsigned long long smid_of() {
 }
 #else
 #define IQ_TRACE_FIELD
+#define IQ_TRACE_SCRATCH(scr, p) do {} while (0)
 #define IQ_STAMP(p, k) do {} while (0)
 #endif
 
@@ -458,6 +462,14 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
     }
     cp_async_commit();
     float f[kTailVecs][8];
+    float wv[kTailVecs][8];    // w_first (attention tail), then / otherwise w_norm
+    // The first norm weight the row meets is loaded now, ahead of the wait for the row: its
+    // latency would otherwise sit between the row's arrival and its first use.
+#pragma unroll
+    for (int i = 0; i < kTailVecs; ++i) {
+      const int v = tid + i * nthr;
+      if (v < vec_per_row) ldg_f32x8((attn ? a.w_first : a.w_norm) + v * 8, wv[i]);
+    }
     if (kPush) {
       // ---- the row arrives in the landing zone: poll it, add the ranks
       const uint64_t budget = 1000000ull * (a.timeout_ms ? a.timeout_ms : 2000u);
@@ -543,7 +555,6 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
       cp_async_wait_all();     // the residual (push: the zone's poll has waited for it)
     }
 
-    float wv[kTailVecs][8];    // w_first, later w_norm
     float inv1 = 0.f;
     if (attn) {
       float ss = 0.f;
@@ -553,7 +564,6 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
         if (v >= vec_per_row) continue;
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss = fmaf(f[i][j], f[i][j], ss);
-        ldg_f32x8(a.w_first + v * 8, wv[i]);      // lands while the reduction's barrier is waited
       }
       inv1 = rsqrtf(block_sum(ss, slots0, bar) * inv_h + a.eps);
     }
@@ -597,7 +607,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss2 = fmaf(f[i][j], f[i][j], ss2);
-      ldg_f32x8(a.w_norm + v * 8, wv[i]);
+      if (attn) ldg_f32x8(a.w_norm + v * 8, wv[i]);   // (the MLP tail holds w_norm already)
     }
     const float inv2 = rsqrtf(block_sum(ss2, slots1, bar) * inv_h + a.eps);
     if (a.inv_out && tid == 0) a.inv_out[r] = inv2;
@@ -790,7 +800,8 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
     return;
   }
   const Carve<G> cv = carve<G>(smem, sh);
-  const StreamScratch scr = scratch_of(p.scratch);
+  StreamScratch scr = scratch_of(p.scratch);
+  IQ_TRACE_SCRATCH(scr, p);
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
@@ -982,7 +993,8 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
   uint8_t* scratch = static_cast<uint8_t*>(p.scratch);
   uint32_t* launch_tag = reinterpret_cast<uint32_t*>(scratch + kScrLaunchTag);
   uint64_t* tagged = reinterpret_cast<uint64_t*>(scratch + kScrLogits);
-  const StreamScratch scr = scratch_of(p.scratch);
+  StreamScratch scr = scratch_of(p.scratch);
+  IQ_TRACE_SCRATCH(scr, p);
   if (tid == 0) {
     IQ_STAMP(p, 0);
 #ifdef IQ_TRACE
@@ -1396,7 +1408,8 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) gate_kernel(const 
   extern __shared__ __align__(128) uint8_t smem[];
   StreamShape sh = p.sh;
   const Carve<G> cv = carve<G>(smem, sh);
-  const StreamScratch scr = scratch_of(p.scratch);
+  StreamScratch scr = scratch_of(p.scratch);
+  IQ_TRACE_SCRATCH(scr, p);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int cta = blockIdx.x, n_cta = static_cast<int>(gridDim.x);
   if (tid == 0) {
@@ -1511,7 +1524,8 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const 
     return;
   }
   const Carve<G> cv = carve<G>(smem, sh);
-  const StreamScratch scr = scratch_of(p.scratch);
+  StreamScratch scr = scratch_of(p.scratch);
+  IQ_TRACE_SCRATCH(scr, p);
   stream_init<G>(sh, cv.sm);
   if (tid == G::PRODUCER_WARP * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
     prefetch_tensormap(&p.map0);   // only maps the host filled (K-sliced stages)
@@ -1774,7 +1788,8 @@ static int max_items_any(const StreamShape& sh, int max_groups, int grid) {
 // What a CTA of geometry G may take of the SM's shared memory.
 template <class G>
 constexpr size_t smem_limit() {
-  return G::CTAS_PER_SM == 2 ? static_cast<size_t>(kSmemLimitShared) : static_cast<size_t>(kSmemLimit);
+  return G::CTAS_PER_SM == 1 ? static_cast<size_t>(kSmemLimit)
+                             : static_cast<size_t>(G::SPREAD ? kSmemSpread : kSmemLimitSmall);
 }
 
 // Fills the geometry-dependent part of a shape and returns the dynamic shared memory to
@@ -1802,14 +1817,15 @@ static size_t plan_smem(StreamShape& sh, int grid, size_t other_bytes, int max_g
   sh.n_stages = stages;
   size_t need = fixed + static_cast<size_t>(stages) * G::STAGE_BYTES;
   if (need < other_bytes) need = other_bytes;
-  return need <= limit ? need : 0;
+  if (need > limit) return 0;
+  return G::SPREAD ? limit : need;      // a spread CTA asks for exactly its class's size
 }
 
 // Tuning knobs read once from the environment: IQB200_SHORT_STREAM_MB (streams up to
 // this many megabytes per launch run with two CTAs per SM; default 40, 0 = never) and
 // IQB200_SHARED_GRID (CTAs such a launch starts per SM: 1 leaves the other half of every
-// SM to the next kernel of the chain, 2 takes both halves; default 1; the expert Down
-// takes both halves on its own when it has more tiles than SMs).
+// SM to the next kernel of the chain, 2 takes both halves; default 1; applies to the small
+// kind of half-SM CTA only).
 static long long env_number(const char* name, long long fallback) {
   const char* v = getenv(name);
   if (!v || !*v) return fallback;
@@ -1824,7 +1840,7 @@ static long long short_stream_bytes() {
 template <class G>
 static int grid_for(bool both_halves = false) {
   static const int factor = env_number("IQB200_SHARED_GRID", 1) >= 2 ? 2 : 1;
-  return sm_count() * (G::CTAS_PER_SM == 2 ? (both_halves ? 2 : factor) : 1);
+  return sm_count() * (G::CTAS_PER_SM == 2 && !G::SPREAD ? (both_halves ? 2 : factor) : 1);
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -1997,7 +2013,7 @@ extern "C" int iq_tail(const iq_tail_args* a, void* stream, int pdl) {
     p.push = 1;
     p.n_tail = a->m;
     // a small CTA that can sit beside a streaming kernel's: half an SM's shared memory
-    p.per_round = tail_sources_per_round(p.pv.world, a->h, a->residual_fp32, kSmemLimitShared);
+    p.per_round = tail_sources_per_round(p.pv.world, a->h, a->residual_fp32, kSmemLimitSmall);
     if (p.per_round < 1) return IQ_ERR_UNSUPPORTED;
     return launch(tail_kernel, p, a->m, kTailThreads,
                   tail_cta_smem(p.per_round, a->h, a->residual_fp32), stream, pdl);
@@ -2027,17 +2043,17 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   }
   if (sm_count() == 0) return IQ_ERR_CUDA;
   const int k = a->k, n = a->n;
-  // A short stream takes CTAs of eight (six) consumer warps, two of which share an SM, so
-  // that its successor's CTAs set up and prefetch beside it (see Geo); a long stream takes
-  // the whole SM.
+  // A short stream takes CTAs of eight (six) consumer warps on half an SM each, one per SM
+  // (the spread kind), so that a neighbour in the launch chain can set up and prefetch
+  // beside it (see Geo); a long stream takes the whole SM.
   if (static_cast<long long>(n) * k <= short_stream_bytes()) {
     // (falls through to a whole-SM geometry when half an SM cannot hold the rows and a ring)
     int rc = IQ_ERR_UNSUPPORTED;
-    if (k % 1024 == 0 && n % 16 == 0) rc = linear_launch<Geo<1, 8, 2>>(a, stream);
-    else if (k % 768 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 4, 3>>(a, stream);
-    else if (k % 512 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 4, 2>>(a, stream);
-    else if (k % 256 == 0 && n % 64 == 0) rc = linear_launch<Geo<4, 2, 2>>(a, stream);
-    else if (k % 192 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 3, 1>>(a, stream);
+    if (k % 1024 == 0 && n % 16 == 0) rc = linear_launch<Geo<1, 8, 2, 3>>(a, stream);
+    else if (k % 768 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 4, 3, 3>>(a, stream);
+    else if (k % 512 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 4, 2, 3>>(a, stream);
+    else if (k % 256 == 0 && n % 64 == 0) rc = linear_launch<Geo<4, 2, 2, 3>>(a, stream);
+    else if (k % 192 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 3, 1, 3>>(a, stream);
     if (rc != IQ_ERR_UNSUPPORTED) return rc;
   }
   if (k % 2048 == 0 && n % 16 == 0) return linear_launch<Geo<1, 16, 2>>(a, stream);
@@ -2132,9 +2148,11 @@ extern "C" int iq_router(const iq_router_args* a, void* stream) {
   if (a->score != IQ_ROUTE_SOFTMAX && a->score != IQ_ROUTE_SIGMOID) return IQ_ERR_ARG;
   if (!aligned16(a->x) || !aligned16(a->w)) return IQ_ERR_ARG;
   if (sm_count() < 2) return IQ_ERR_CUDA;
-  // Sixteen experts per CTA: few CTAs, each with a long row set (196 KB at hidden 6144).  Eight
-  // consumer warps on a WHOLE SM keep a ring deep enough for all of it, so the CTA's entire
-  // stream is in shared memory before the dependency wait returns.
+  // Sixteen experts per CTA: few CTAs, each with a long row set (192 KiB at hidden 6144) on a
+  // WHOLE SM, with a ring deep enough for all of it where the staged rows leave room: the
+  // CTA's entire stream is then in shared memory before the dependency wait returns, and
+  // few large stages keep the serial per-stage chain short.
+  if ((a->h * 2) % 2048 == 0) return router_launch<Geo<1, 16, 2>>(a, stream);
   if ((a->h * 2) % 1024 == 0) return router_launch<Geo<1, 8, 2, 1>>(a, stream);
   return router_launch<Geo<1, 16, 1>>(a, stream);
 }
@@ -2232,7 +2250,7 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   const long long bytes = expert_stream_bytes(a->m, a->top_k, a->n_experts, a->n_shared,
                                               2ll * a->i_loc * a->h);
   if (bytes <= short_stream_bytes()) {
-    const int rc = gate_launch<Geo<2, 4, 2>>(a, stream);
+    const int rc = gate_launch<Geo<2, 4, 2, 3>>(a, stream);
     if (rc != IQ_ERR_UNSUPPORTED) return rc;
   }
   return gate_launch<Geo<2, 8, 2>>(a, stream);
@@ -2264,11 +2282,9 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   TailPlan tp;
   rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->h, smem_limit<G>());
   if (rc != IQ_OK) return rc;
-  // The Down's tiles are known before the routes (rows of the hidden dimension).  With more
-  // tiles than SMs a launch on half of every SM leaves some CTAs with twice the others'
-  // stream; the launch that follows the Down waits for its all-reduce tail anyway and has
-  // time to become resident afterwards, so the Down takes both halves.
-  const int grid = grid_for<G>(stream_tiles_per_group<G>(sh) > sm_count());
+  // (a short Down runs as small half-SM CTAs beside the spread CTAs of the Gate before it
+  // and of the o_proj after it: one per SM, because every SM has exactly one half free)
+  const int grid = grid_for<G>();
   const size_t smem = plan_smem<G>(sh, grid - tp.n_tail, tp.smem, a->m * a->top_k + a->n_shared);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->proj,

@@ -41,8 +41,14 @@ constexpr int kMaxStages = 16;
 constexpr int kMaxGroups = 72;                    // 8 rows x 8 routed + shared, with slack
 constexpr int kMaxCols = 8;                       // MMA N
 constexpr int kSmemLimit = 232448;                // 227 KiB per CTA on sm_100
-// What one of TWO CTAs on an SM may take: 228 KiB per SM, 1 KiB reserved per resident CTA.
-constexpr int kSmemLimitShared = (233472 - 2 * 1024) / 2;
+// Two CTAs on an SM: 228 KiB per SM, 1 KiB reserved per resident CTA.  The hardware packs
+// the CTAs of a launch onto as few SMs as their resources allow, so two kinds of half-SM
+// CTA exist.  A "spread" CTA asks for a little more than half of the SM's shared memory:
+// two of them never share an SM, so a launch of one CTA per SM really lands one per SM
+// (a stream that needs every SM's bandwidth), yet a "small" CTA of the next or previous
+// kernel of the chain still fits beside it.  A small CTA may pack two to an SM.
+constexpr int kSmemSpread = 117 * 1024;           // exactly what a spread CTA requests
+constexpr int kSmemLimitSmall = 233472 - 2 * 1024 - kSmemSpread;   // a small CTA: up to 108 KiB
 
 // Ring geometry: a stage is (16*RT) weight rows x (KW*RUNS*64) bytes; warp (rs, kp) of the
 // RT*KW consumer warps owns row sub-tile rs and the kp-th slice of RUNS 64-byte runs.  A
@@ -54,9 +60,9 @@ constexpr int kSmemLimitShared = (233472 - 2 * 1024) / 2;
 // become resident while this kernel is still streaming, set themselves up and fill their
 // own ring with weights before their dependency wait, so a short stream does not pay the
 // launch, the set-up and the first-byte latency of its successor end to end.
-// `SHARE_` overrides how many CTAs are meant to share an SM (0: two for up to eight
-// consumer warps, else one): a few-warp CTA that takes a whole SM can keep a much deeper
-// ring than its share of an SM would allow.
+// `SHARE_`: 0 = by warp count (up to eight consumer warps: a small half-SM CTA, else a
+// whole SM), 1 = a whole SM whatever the warp count (a few-warp CTA with a much deeper
+// ring), 2 = small half-SM CTA, 3 = spread half-SM CTA (see kSmemSpread).
 template <int RT_, int KW_, int RUNS_, int SHARE_ = 0>
 struct Geo {
   static constexpr int RT = RT_, KW = KW_, RUNS = RUNS_;
@@ -66,8 +72,9 @@ struct Geo {
   static constexpr int THREADS = CONSUMER_THREADS + 64; // + the producer warp + the epilogue warp
   static constexpr int PRODUCER_WARP = WARPS;
   static constexpr int EPILOGUE_WARP = WARPS + 1;
-  static constexpr int CTAS_PER_SM = SHARE_ ? SHARE_ : (WARPS <= 8 ? 2 : 1);
-  static_assert(CTAS_PER_SM == 1 || (CTAS_PER_SM == 2 && WARPS <= 8), "one or two CTAs per SM");
+  static constexpr int CTAS_PER_SM = SHARE_ == 1 ? 1 : (SHARE_ >= 2 ? 2 : (WARPS <= 8 ? 2 : 1));
+  static constexpr bool SPREAD = SHARE_ == 3;
+  static_assert(CTAS_PER_SM == 1 || WARPS <= 8, "two CTAs per SM need few warps");
   static constexpr int ROWS = 16 * RT;
   static constexpr int KC = KW * RUNS * 64;
   // A stage lands as NBOX dense boxes of (ROWS x BOXK bytes), one TMA copy each (a tensor
@@ -128,7 +135,13 @@ struct StreamScratch {
   uint32_t* tile_counter; // [tiles]
   uint32_t* ticket;       // [1]
   int* status;            // [1] first error code of any launch using this scratch
+  unsigned long long* trace;   // trace builds: this CTA's 16 stamps (else null)
 };
+
+// One %globaltimer stamp into slot `k` of the CTA's trace words (trace builds only).
+__device__ __forceinline__ void trace_stamp(const StreamScratch& scr, int k) {
+  if (scr.trace) scr.trace[k] = globaltimer_ns();
+}
 
 __device__ __forceinline__ void set_status(int* status, int code) {
   if (status) atomicCAS(status, 0, code);
@@ -630,8 +643,10 @@ __device__ __forceinline__ void consume(const StreamShape& sh, S* sm, const Grou
           sm->abort_flag = 1;
           return;
         }
+        if (tid == 0 && k == 0 && s == tv.s_begin) trace_stamp(scr, 6);
         consume_stage<G, E>(ring_s + slot * slot_bytes + a_off, gc, ks * G::KC, kwarp0, wsc, acc);
         __syncwarp();
+        if (tid == 0 && k == 0 && s == tv.s_begin) trace_stamp(scr, 7);
         if (lane == 0) mbar_arrive(&sm->empty[slot]);
         if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
         wsc += G::SCALES_PER_STAGE * 4;
@@ -652,6 +667,7 @@ __device__ __forceinline__ void consume(const StreamShape& sh, S* sm, const Grou
     for (int i = 0; i < 4; ++i) { red[warp][lane][i] = acc[i]; acc[i] = 0.f; }
     __syncwarp();
     if (lane == 0) mbar_arrive(&sm->red_full[red_buf]);
+    if (tid == 0 && k == 0) trace_stamp(scr, 8);
     if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
   }
   pos.slot = slot;
@@ -719,6 +735,7 @@ __device__ __forceinline__ void epilogue(const StreamShape& sh, S* sm, const Cta
       sm->abort_flag = 1;
       return;
     }
+    if (lane == 0 && k == 0) trace_stamp(scr, 13);
     const float(*red)[32][4] = sm->red[red_buf];
     float val[4][G::RT];
 #pragma unroll
@@ -738,6 +755,7 @@ __device__ __forceinline__ void epilogue(const StreamShape& sh, S* sm, const Cta
     if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
     if (whole) {
       epilogue_emit<G, kVec>(emit, id, lane, val);
+      if (lane == 0 && k == 0) trace_stamp(scr, 14);
     } else {
       const int pslot = (tile == w.tile0) ? 0 : 1;
       float* mine = scr.partials + (static_cast<size_t>(cta) * 2 + pslot) * (G::ROWS * 8);
