@@ -219,6 +219,18 @@ __device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const Stre
   }
 }
 
+// Programmatic dependent launch discipline shared by the kernels: a CTA lets its
+// dependents be scheduled only AFTER its own wait on its predecessor has returned.  The
+// successor kernel therefore starts no earlier than the completion of this kernel's
+// predecessor, so before ITS wait it may already read anything written two or more
+// launches back (pdl level 2: the Down reads the router's routes, the Gate reads the
+// attention tail's activations) as well as weights, and only has to wait for what its
+// immediate predecessor writes.
+__device__ __forceinline__ void after_wait() {
+  pdl_wait();
+  pdl_launch_dependents();
+}
+
 // ------------------------------------------------------------------------------------
 // The tail: all-reduce of the ranks' bf16 rows, residual add and RMSNorm(s).
 //
@@ -343,10 +355,10 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // asynchronous 16-byte copies that go to L2, all of them in flight together; a chunk whose
 // words do not all show `tag` yet is copied again; a complete round is added up and the
 // next one starts.  A thread reads back only what it copied itself.  Returns false when
-// the budget ran out.
+// the budget ran out.  `warm`: copy each chunk once and take it as it is (see run_tail).
 __device__ __forceinline__ bool poll_zone_row(const PushView& pv, uint32_t* zs, int per_round,
                                               int r, uint32_t tag, int tid, int nthr,
-                                              int vec_per_row, uint64_t budget_ns,
+                                              int vec_per_row, uint64_t budget_ns, bool warm,
                                               float (&f)[kTailVecs][8]) {
   const size_t src_stride = static_cast<size_t>(pv.rows) * pv.h;
   const uint32_t* row0 = pv.recv + static_cast<size_t>(r) * pv.h;
@@ -390,6 +402,7 @@ __device__ __forceinline__ bool poll_zone_row(const PushView& pv, uint32_t* zs, 
           if (all) pend &= ~(1u << (8 * i + p));
         }
       }
+      if (warm) pend = 0;          // a rehearsal takes whatever the zone holds
       if (pend) {
         const uint64_t now = globaltimer_ns();
         if (t0 == 0) t0 = now;
@@ -423,6 +436,12 @@ __device__ __forceinline__ bool poll_zone_row(const PushView& pv, uint32_t* zs, 
 // `zs` (push only) shared memory for per_round x h words.  Without `kPush`,
 // rows written by other CTAs of this launch must already be visible (the caller passed
 // the ticket) and the pull protocol's signal / wait / switch read applies for world > 1.
+// `warm` (push only): a rehearsal -- the same instructions on whatever the buffers hold,
+// without waiting and without a single global store.  Code that runs once per launch runs
+// at the speed its instructions arrive from L2 (measured here: about 2 us for the 10 KB of
+// one row's arithmetic), so a tail CTA, which has nothing to do until its rows arrive,
+// goes through the whole path once ahead of time and finds it in the instruction cache
+// when it matters.
 // Each row is handled entirely in registers and each RMSNorm costs one block barrier.  The
 // kernels this runs in keep almost all of the SM's L1 as shared memory, so a spilled
 // register would cost an L2 round trip: the loads are ordered to keep few values live
@@ -432,7 +451,7 @@ template <bool kPush>
 __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& pv, uint32_t tag,
                                          uint8_t* park, uint32_t* zs, int per_round, float* red,
                                          int* sflag, const BlockBar bar = BlockBar{},
-                                         int r_begin = 0, int r_step = 1) {
+                                         int r_begin = 0, int r_step = 1, bool warm = false) {
   const int tid = threadIdx.x, nthr = bar.threads();
   const uint32_t res_s = smem_u32(park);
   const int pstride = a.residual_fp32 ? 32 : 16;      // parked bytes per 8 elements
@@ -473,7 +492,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
     if (kPush) {
       // ---- the row arrives in the landing zone: poll it, add the ranks
       const uint64_t budget = 1000000ull * (a.timeout_ms ? a.timeout_ms : 2000u);
-      if (!poll_zone_row(pv, zs, per_round, r, tag, tid, nthr, vec_per_row, budget, f))
+      if (!poll_zone_row(pv, zs, per_round, r, tag, tid, nthr, vec_per_row, budget, warm, f))
         *sflag = 0;
       bar.sync();
       if (!*sflag) {
@@ -481,7 +500,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
         if (tid == 0) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
         return;
       }
-      if (tid == 0 && pv.trace) pv.trace[10] = globaltimer_ns();
+      if (tid == 0 && pv.trace && !warm) pv.trace[10] = globaltimer_ns();
     } else {
       // ---- cross-rank readiness: signal, then wait while the residual loads are in flight
       if (r == r_begin && a.world > 1) {
@@ -566,6 +585,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
         for (int j = 0; j < 8; ++j) ss = fmaf(f[i][j], f[i][j], ss);
       }
       inv1 = rsqrtf(block_sum(ss, slots0, bar) * inv_h + a.eps);
+      if (kPush && tid == 0 && pv.trace && !warm) pv.trace[12] = globaltimer_ns();
     }
     // ---- h = residual + (ATTN: bf16(bf16(w1*(ao*inv))*scale) | MLP: bf16(m*scale))
     float ss2 = 0.f;
@@ -598,19 +618,23 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
       }
       if (a.residual_fp32) {
         float* ho = static_cast<float*>(a.h_out) + off;
-        *reinterpret_cast<float4*>(ho) = make_float4(f[i][0], f[i][1], f[i][2], f[i][3]);
-        *reinterpret_cast<float4*>(ho + 4) = make_float4(f[i][4], f[i][5], f[i][6], f[i][7]);
+        if (!warm) {
+          *reinterpret_cast<float4*>(ho) = make_float4(f[i][0], f[i][1], f[i][2], f[i][3]);
+          *reinterpret_cast<float4*>(ho + 4) = make_float4(f[i][4], f[i][5], f[i][6], f[i][7]);
+        }
       } else {
         const U4 hb = f32_to_bf16x8(f[i]);
-        *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.h_out) + off) = hb;
+        if (!warm) *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.h_out) + off) = hb;
         bf16x8_to_f32(hb, f[i]);            // the norm sees the rounded stream
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss2 = fmaf(f[i][j], f[i][j], ss2);
       if (attn) ldg_f32x8(a.w_norm + v * 8, wv[i]);   // (the MLP tail holds w_norm already)
     }
+    if (kPush && tid == 0 && pv.trace && !warm) pv.trace[13] = globaltimer_ns();
     const float inv2 = rsqrtf(block_sum(ss2, slots1, bar) * inv_h + a.eps);
-    if (a.inv_out && tid == 0) a.inv_out[r] = inv2;
+    if (kPush && tid == 0 && pv.trace && !warm) pv.trace[14] = globaltimer_ns();
+    if (a.inv_out && tid == 0 && !warm) a.inv_out[r] = inv2;
 
     // ---- norm_out = bf16(w_norm * (h * inv)) (+ e4m3 copy, unscaled or per 1x128 group)
 #pragma unroll
@@ -625,7 +649,8 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
         o[j] = live ? bf16_round(wv[i][j] * (f[i][j] * inv2)) : 0.f;
         amax = fmaxf(amax, fabsf(o[j]));
       }
-      if (live)
+      const bool store = live && !warm;
+      if (store)
         *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.norm_out) + off) = f32_to_bf16x8(o);
       if (a.norm_fp8) {
         float sc = 1.0f;
@@ -634,7 +659,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
 #pragma unroll
           for (int o2 = 8; o2; o2 >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o2));
           sc = amax > 0.f ? amax / 448.0f : 1.0f;
-          if (live && (v & 15) == 0) a.norm_fp8_scale[static_cast<size_t>(r) * (h / 128) + (v >> 4)] = sc;
+          if (store && (v & 15) == 0) a.norm_fp8_scale[static_cast<size_t>(r) * (h / 128) + (v >> 4)] = sc;
         }
         const float rcp = 1.0f / sc;
         uint32_t q0 = 0, q1 = 0;
@@ -643,7 +668,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
           q0 |= static_cast<uint32_t>(f32_to_e4m3_sat(o[j] * rcp)) << (8 * j);
           q1 |= static_cast<uint32_t>(f32_to_e4m3_sat(o[j + 4] * rcp)) << (8 * j);
         }
-        if (live) *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.norm_fp8) + off) = make_uint2(q0, q1);
+        if (store) *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.norm_fp8) + off) = make_uint2(q0, q1);
       }
     }
   }
@@ -665,27 +690,42 @@ __device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& 
   uint32_t* word = reinterpret_cast<uint32_t*>(smem + 516);     // [epoch, closes the call]
   uint8_t* park = smem + 1024;
   uint32_t* zs = reinterpret_cast<uint32_t*>(smem + 1024 + tail_park_bytes(a.h, a.residual_fp32));
-  // The call's tag comes from the zone's epoch.  The epoch may move on once (a) every tail
-  // CTA has read it and (b) every producer has: the tail CTA that reads it LAST takes on
-  // the job, and does it after its own rows are complete (every producer of the launch
-  // contributes to every row, so by then all of them have read the epoch).  That keeps the
-  // atomic at the start of the tail, where it waits for data anyway, and off its end.
-  if (threadIdx.x == 0) {
-    word[0] = ld_volatile_u32(pv.epoch);
-    uint32_t closes = 1;
-    if (n_tail > 1) {
-      closes = atomicAdd(pv.ticket, 1u) == static_cast<uint32_t>(n_tail - 1);
-      if (closes) *pv.ticket = 0;
+  // Two passes through ONE copy of the tail's code: a rehearsal ahead of the dependency
+  // wait (nothing is awaited, nothing is stored; see run_tail), then the call itself.
+#pragma unroll 1
+  for (int pass = 0; pass < 2; ++pass) {
+    const bool warm = pass == 0;
+    if (!warm) {
+      after_wait();
+      if (threadIdx.x == 0 && pv.trace) pv.trace[9] = globaltimer_ns();
     }
-    word[1] = closes;
-    *sflag = 1;
+    // The call's tag comes from the zone's epoch.  The epoch may move on once (a) every
+    // tail CTA has read it and (b) every producer has: the tail CTA that reads it LAST takes
+    // on the job, and does it after its own rows are complete (every producer of the launch
+    // contributes to every row, so by then all of them have read the epoch).  That keeps the
+    // atomic at the start of the tail, where it waits for data anyway, and off its end.
+    if (threadIdx.x == 0) {
+      uint32_t closes = 0, epoch = 0;
+      if (!warm) {
+        epoch = ld_volatile_u32(pv.epoch);
+        closes = 1;
+        if (n_tail > 1) {
+          closes = atomicAdd(pv.ticket, 1u) == static_cast<uint32_t>(n_tail - 1);
+          if (closes) *pv.ticket = 0;
+        }
+      }
+      word[0] = epoch;
+      word[1] = closes;
+      *sflag = 1;
+    }
+    __syncthreads();
+    const uint32_t epoch = word[0];
+    if (threadIdx.x < kTailThreads)
+      run_tail<true>(a, pv, tag16_of(epoch), park, zs, per_round, red, sflag,
+                     BlockBar{2, kTailThreads}, index, n_tail, warm);
+    if (threadIdx.x == 0 && word[1]) *pv.epoch = epoch + 1u;
+    __syncthreads();
   }
-  __syncthreads();
-  const uint32_t epoch = word[0];
-  if (threadIdx.x < kTailThreads)
-    run_tail<true>(a, pv, tag16_of(epoch), park, zs, per_round, red, sflag,
-                   BlockBar{2, kTailThreads}, index, n_tail);
-  if (threadIdx.x == 0 && word[1]) *pv.epoch = epoch + 1u;
 }
 
 // Sources a tail CTA takes per round when it may use `limit` bytes of shared memory, and
@@ -703,28 +743,16 @@ __host__ __device__ inline size_t tail_cta_smem(int per_round, int h, int residu
 
 __global__ void __launch_bounds__(kTailThreads) tail_kernel(const TailParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  pdl_wait();
-  pdl_launch_dependents();   // after the wait: see the note on `after_wait` below
   if (p.push) {
     tail_cta(p.a, p.pv, p.per_round, static_cast<int>(blockIdx.x), p.n_tail, smem);
     return;
   }
+  pdl_wait();
+  pdl_launch_dependents();   // after the wait: see the note on `after_wait`
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
   run_tail<false>(p.a, p.pv, 0u, smem + 1024, nullptr, 0, red, sflag, BlockBar{},
                   static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
-}
-
-// Programmatic dependent launch discipline shared by the kernels: a CTA lets its
-// dependents be scheduled only AFTER its own wait on its predecessor has returned.  The
-// successor kernel therefore starts no earlier than the completion of this kernel's
-// predecessor, so before ITS wait it may already read anything written two or more
-// launches back (pdl level 2: the Down reads the router's routes, the Gate reads the
-// attention tail's activations) as well as weights, and only has to wait for what its
-// immediate predecessor writes.
-__device__ __forceinline__ void after_wait() {
-  pdl_wait();
-  pdl_launch_dependents();
 }
 
 // ------------------------------------------------------------------------------------
@@ -789,8 +817,6 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
 #endif
   }
   if (cta >= stream_ctas) {
-    after_wait();
-    if (tid == 0) IQ_STAMP(p, 9);
     PushView pv = p.pv;
 #ifdef IQ_TRACE
     pv.trace = p.trace ? p.trace + blockIdx.x * kTraceWords : nullptr;
@@ -916,7 +942,7 @@ __device__ inline uint32_t ordered_key(float v) {
 template <int kMaxPerLane>
 __device__ __forceinline__ void select_row_impl(const float* logits, int e, int top_k, int score,
                                                 int row, int* sel, float* wt,
-                                                bool logits_in_smem) {
+                                                bool logits_in_smem, bool store) {
   const int lane = threadIdx.x & 31;
   uint32_t key[kMaxPerLane];
   const int per = (e + 31) / 32;
@@ -961,7 +987,7 @@ __device__ __forceinline__ void select_row_impl(const float* logits, int e, int 
     const int other = __shfl_sync(0xffffffffu, my_id, t);
     rank += (other < my_id) ? 1 : 0;
   }
-  if (lane < top_k && my_id != 0x7fffffff) {
+  if (store && lane < top_k && my_id != 0x7fffffff) {
     sel[row * top_k + rank] = my_id;
     wt[row * top_k + rank] = my_p / sum;
   }
@@ -970,11 +996,11 @@ __device__ __forceinline__ void select_row_impl(const float* logits, int e, int 
 // The selection runs on one warp at the end of the router's critical path, so its length
 // in instructions matters: up to 256 experts take the variant with 8 keys per lane.
 __device__ void select_row(const float* logits, int e, int top_k, int score, int row, int* sel,
-                           float* wt, bool logits_in_smem = false) {
+                           float* wt, bool logits_in_smem = false, bool store = true) {
   if (e <= 256)
-    select_row_impl<8>(logits, e, top_k, score, row, sel, wt, logits_in_smem);
+    select_row_impl<8>(logits, e, top_k, score, row, sel, wt, logits_in_smem, store);
   else
-    select_row_impl<16>(logits, e, top_k, score, row, sel, wt, logits_in_smem);   // e <= 512
+    select_row_impl<16>(logits, e, top_k, score, row, sel, wt, logits_in_smem, store);   // e <= 512
 }
 
 // The router's hand-off inside one launch: the CTAs that stream the weight rows store
@@ -1002,42 +1028,51 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
 #endif
   }
   if (cta == stream_ctas) {
-    // ---- the selecting CTA
-    after_wait();
-    if (tid == 0) IQ_STAMP(p, 9);
-    const uint32_t tag = ld_volatile_u32(launch_tag) + 1u;
+    // ---- the selecting CTA.  Two passes through one copy of its code: a rehearsal ahead of
+    // the dependency wait (words taken as they are, nothing stored) that brings the
+    // instructions in, then the launch's own selection.
     float* lg = reinterpret_cast<float*>(smem);          // [m][e]
-    if (warp < p.m) {
-      const int per = (p.e + 31) / 32;                   // <= 16
-      uint32_t pend = (1u << per) - 1u;
-      uint64_t t0 = 0;
-      bool ok = true;
-      while (true) {
-        for (int j = 0; j < per; ++j) {
-          const int id = lane + 32 * j;
-          if (!((pend >> j) & 1u) || id >= p.e) { pend &= ~(1u << j); continue; }
-          const uint64_t wv = ld_relaxed_gpu_u64(tagged + static_cast<size_t>(warp) * p.e + id);
-          if (static_cast<uint32_t>(wv >> 32) == tag) {
-            lg[warp * p.e + id] = __uint_as_float(static_cast<uint32_t>(wv));
-            pend &= ~(1u << j);
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+      const bool warm = pass == 0;
+      if (!warm) {
+        after_wait();
+        if (tid == 0) IQ_STAMP(p, 9);
+      }
+      const uint32_t tag = warm ? 0u : ld_volatile_u32(launch_tag) + 1u;
+      if (warp < p.m) {
+        const int per = (p.e + 31) / 32;                   // <= 16
+        uint32_t pend = (1u << per) - 1u;
+        uint64_t t0 = 0;
+        bool ok = true;
+        while (true) {
+          for (int j = 0; j < per; ++j) {
+            const int id = lane + 32 * j;
+            if (!((pend >> j) & 1u) || id >= p.e) { pend &= ~(1u << j); continue; }
+            const uint64_t wv = ld_relaxed_gpu_u64(tagged + static_cast<size_t>(warp) * p.e + id);
+            if (warm || static_cast<uint32_t>(wv >> 32) == tag) {
+              lg[warp * p.e + id] = __uint_as_float(static_cast<uint32_t>(wv));
+              pend &= ~(1u << j);
+            }
           }
+          if (__all_sync(0xffffffffu, pend == 0u)) break;
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > kPipeBudgetNs) { ok = false; break; }
         }
-        if (__all_sync(0xffffffffu, pend == 0u)) break;
-        const uint64_t now = globaltimer_ns();
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > kPipeBudgetNs) { ok = false; break; }
+        __syncwarp();
+        if (ok) {
+          if (!warm)
+            for (int id = lane; id < p.e; id += 32)
+              p.logits[static_cast<size_t>(warp) * p.e + id] = lg[warp * p.e + id];
+          select_row(lg, p.e, p.top_k, p.score, warp, p.sel, p.wt, true, !warm);
+        } else if (lane == 0) {
+          set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+        }
       }
-      __syncwarp();
-      if (ok) {
-        for (int id = lane; id < p.e; id += 32)
-          p.logits[static_cast<size_t>(warp) * p.e + id] = lg[warp * p.e + id];
-        select_row(lg, p.e, p.top_k, p.score, warp, p.sel, p.wt, true);
-      } else if (lane == 0) {
-        set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
-      }
+      __syncthreads();
+      if (tid == 0 && !warm) *launch_tag = tag;
     }
-    __syncthreads();
-    if (tid == 0) *launch_tag = tag;
     if (tid == 0) IQ_STAMP(p, 11);
     return;
   }
@@ -1513,8 +1548,6 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const 
 #endif
   }
   if (cta >= stream_ctas) {
-    after_wait();
-    if (tid == 0) IQ_STAMP(p, 9);
     PushView pv = p.pv;
 #ifdef IQ_TRACE
     pv.trace = p.trace ? p.trace + blockIdx.x * kTraceWords : nullptr;
