@@ -60,6 +60,14 @@ def parse_args():
     ap.add_argument("--passes", type=int, default=0,
                     help="timed passes of K steps (default: 11, more when K steps are short)")
     ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="with --gpus 1: time ONE rank's shard of a tensor-parallel group of this "
+                         "size run alone (no peers, no all-reduce traffic): the shard's kernels at "
+                         "their real widths on a single GPU, e.g. for profiler captures")
+    ap.add_argument("--unfused", action="store_true",
+                    help="run the two all-reduce tails as launches of their own (the reference's "
+                         "kernel boundaries) instead of inside the GEMV launches")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-multicast", action="store_true",
                     help="all-reduce over plain peer loads instead of NVLS multimem")
@@ -319,7 +327,14 @@ def run_ours(args):
 
     shape = synth.BASELINE if args.experts == 256 else synth.LayerShape(n_experts=args.experts)
     rows = args.rows
-    bank_bytes = 37.75e6 * (args.experts + 1) / tp
+    shard_of = args.shard_of if tp == 1 else 0
+    if shard_of > 1:
+        # one rank's slice of every sharded dimension, as a layer of its own
+        ql, il = shape.local(shard_of)
+        shape = synth.LayerShape(hidden=shape.hidden, q_dim=ql, n_experts=shape.n_experts,
+                                 top_k=shape.top_k, inter=il, n_shared=shape.n_shared,
+                                 eps=shape.eps)
+    bank_bytes = 37.75e6 * (args.experts + 1) / max(tp, shard_of, 1)
     n_layers = args.layers or max(2, min(4, int(24e9 // bank_bytes)))
     layer = DecodeLayer(shape, q_len=rows, tp=tp, group=group, device=dev,
                         formats="benchmark", use_multicast=not args.no_multicast,
@@ -330,11 +345,13 @@ def run_ours(args):
     inputs = [synth.make_step_inputs(shape, rows, tp=tp, rank=rank, device=dev, seed=0, step=i)
               for i in range(n_inputs)]
     K, W = max(1, args.steps), max(3, args.warmup)
-    launches_per_step = 4
 
-    def call(i, **kw):
+    fused = not args.unfused
+    launches_per_step = 4 if fused else 6
+
+    def call(i):
         ao, res = inputs[i % n_inputs]
-        return layer.step(ao, res, weights[i % n_layers], **kw)
+        return layer.step(ao, res, weights[i % n_layers], fused=fused)
 
     def barrier():
         if tp > 1:
@@ -440,18 +457,19 @@ def run_ours(args):
         # ---- end to end from HOST buffers: `HostStep` (one graph launch per step holding
         # the H2D copies of the step's inputs, the layer, and the D2H copy of its output),
         # one synchronise per step, weights rotating over the layers as above.
-        h_in = [(ao.cpu(), res.cpu()) for ao, res in inputs]
-        host_steps = [HostStep(layer, weights[j]) for j in range(n_layers)]
-        n_e2e = min(K, 256)
-        for i in range(4):
-            host_steps[i % n_layers](*h_in[i % n_inputs])
-        barrier()
-        t_e2e = time.perf_counter()
-        for i in range(n_e2e):
-            host_steps[i % n_layers](*h_in[i % n_inputs])
-        e2e_ms = (time.perf_counter() - t_e2e) * 1e3
-        h2d_bytes, d2h_bytes = host_steps[0].h2d_bytes, host_steps[0].d2h_bytes
-        layer.check()
+        n_e2e, e2e_ms, h2d_bytes, d2h_bytes = min(K, 256), float("nan"), 0, 0
+        if not args.no_e2e:
+            h_in = [(ao.cpu(), res.cpu()) for ao, res in inputs]
+            host_steps = [HostStep(layer, weights[j]) for j in range(n_layers)]
+            for i in range(4):
+                host_steps[i % n_layers](*h_in[i % n_inputs])
+            barrier()
+            t_e2e = time.perf_counter()
+            for i in range(n_e2e):
+                host_steps[i % n_layers](*h_in[i % n_inputs])
+            e2e_ms = (time.perf_counter() - t_e2e) * 1e3
+            h2d_bytes, d2h_bytes = host_steps[0].h2d_bytes, host_steps[0].d2h_bytes
+            layer.check()
 
     med_ms = max_over_ranks(statistics.median(pass_ms))
     min_ms = max_over_ranks(min(pass_ms))
@@ -462,7 +480,7 @@ def run_ours(args):
     if rank == 0:
         us = med_ms * 1e3 / K
         peak, peak_kind = measured_peak()
-        by = layer_bytes(shape, tp, rows, distinct)
+        by = layer_bytes(shape, tp, rows, distinct)      # (a --shard-of shape is local already)
         frac = {k: by[k] / (med[k] * 1e-3) / 1e9 / peak for k in med}
         cpu = None
         if not args.no_cpu_baseline and tp == 1:
@@ -477,6 +495,7 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "e4m3 x e4m3 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows": rows, "tp": tp,
                        "launches_per_step": launches_per_step, "experts_in_bank": args.experts,
+                       "shard_of": shard_of or None,
                        "timing": f"{passes} passes of {K} steps back to back, first dropped, "
                                  "median pass",
                        "l2": f"weights rotate over {n_layers} distinct layers "
@@ -485,7 +504,8 @@ def run_ours(args):
                                      f"{args.protocol}, " +
                                      ("peer stores/loads" if args.no_multicast else "NVLS multimem")},
             "clocks": clocks.summary(),
-            "e2e": {"value": e2e_ms * 1e3 / n_e2e, "unit": UNIT, "steps": n_e2e,
+            "e2e": None if args.no_e2e else
+                   {"value": e2e_ms * 1e3 / n_e2e, "unit": UNIT, "steps": n_e2e,
                     "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": int(d2h_bytes)},
             "gpu_launches": launches_per_step * unit * (passes - 1),
             "passes_timed": passes - 1,
