@@ -246,7 +246,9 @@ def parity_check(args, tp, rank, dev, group):
         out, norm = out.clone(), norm.clone()
         same = True
         if tp > 1:
-            both = torch.cat([out.view(torch.int16), norm.view(torch.int16)])
+            # (raw bytes: NCCL moves uint8, not int16)
+            both = torch.cat([out.contiguous().view(torch.uint8).flatten(),
+                              norm.contiguous().view(torch.uint8).flatten()])
             gathered = [torch.empty_like(both) for _ in range(tp)]
             dist.all_gather(gathered, both)
             same = all(torch.equal(g, both) for g in gathered)

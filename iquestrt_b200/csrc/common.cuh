@@ -200,6 +200,13 @@ __device__ __forceinline__ void multimem_st_u32(void* mc, uint32_t v) {
 __device__ __forceinline__ void multimem_red_add_release_u32(void* mc, uint32_t v) {
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
 }
+// An add whose result nobody waits for.
+__device__ __forceinline__ void red_add_relaxed_u32(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void nanosleep_ns(uint32_t ns) {
+  asm volatile("nanosleep.u32 %0;" ::"r"(ns));
+}
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

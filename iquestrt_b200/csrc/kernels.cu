@@ -10,6 +10,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 #include <unordered_set>
@@ -26,6 +27,7 @@ namespace iqb {
 constexpr size_t kScrTicket = 64;
 constexpr size_t kScrLaunchTag = 128;    // u32: launches that handed results off as tagged words
 constexpr size_t kScrTailTicket = 132;   // u32: tail CTAs of the running launch that are done
+constexpr size_t kScrGateDone = 136;     // u32: working CTAs of all Gate launches that have finished (only grows)
 constexpr size_t kScrCounters = 256;
 constexpr int kMaxTiles = 16384;
 constexpr size_t kScrPartials = kScrCounters + sizeof(uint32_t) * kMaxTiles;
@@ -34,8 +36,10 @@ constexpr size_t kScrBasicBytes = kScrPartials + sizeof(float) * kMaxGrid * 2 * 
 constexpr int kMaxRows = 8;
 constexpr int kMaxExperts = 512;
 constexpr int kZoneMaxH = 8192;
-constexpr size_t kScrLogits = kScrBasicBytes;                                    // u64 [8][512]
-constexpr size_t kScrZone = kScrLogits + sizeof(uint64_t) * kMaxRows * kMaxExperts;   // u32 [8][8192]
+constexpr int kMaxKSlices = 8;          // K slices a router launch may split its rows into
+constexpr size_t kScrLogits = kScrBasicBytes;                                    // u64 [8][8][512]
+constexpr size_t kScrZone =
+    kScrLogits + sizeof(uint64_t) * kMaxKSlices * kMaxRows * kMaxExperts;         // u32 [8][8192]
 constexpr size_t kScrBytes = kScrZone + sizeof(uint32_t) * kMaxRows * kZoneMaxH;
 
 __host__ __device__ inline StreamScratch scratch_of(void* base) {
@@ -803,7 +807,7 @@ __device__ __forceinline__ void store_row4(__nv_bfloat16* out, size_t index, con
 }
 
 template <class G>
-__global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(const __grid_constant__ LinearParams p) {
+__global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) linear_kernel(const __grid_constant__ LinearParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const StreamShape& sh = p.sh;
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -832,7 +836,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   stream_init<G>(sh, cv.sm);
-  if (tid == G::PRODUCER_WARP * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1))
+  if (tid == G::PRODUCER_WARP * 32 && !stream_whole_rows<G>(sh))
     prefetch_tensormap(&p.map0);   // only a map the host filled (K-sliced stages)
   if (tid == 0) {
     GroupDesc& g = cv.sm->groups[0];
@@ -840,6 +844,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) linear_kernel(cons
     g.scale = p.w_scale;
     g.row_base = 0;
     g.map_id = 0;
+    g.k_base = 0;
     for (int c = 0; c < kMaxCols; ++c) {
       g.col_row[c] = c < sh.x_rows ? c : -1;
       g.col_mul[c] = 1.0f;
@@ -924,6 +929,7 @@ struct RouterParams {
   const __nv_bfloat16* x;
   const uint8_t* w;
   int m, h, e, top_k, score;
+  int k_slices;             // the rows' K range is split over this many groups of tiles
   int* sel;
   float* wt;
   float* logits;
@@ -1003,14 +1009,18 @@ __device__ void select_row(const float* logits, int e, int top_k, int score, int
     select_row_impl<16>(logits, e, top_k, score, row, sel, wt, logits_in_smem, store);   // e <= 512
 }
 
-// The router's hand-off inside one launch: the CTAs that stream the weight rows store
-// each logit as a 64-bit word (fp32 value, 32-bit tag of the launch) with one relaxed
-// store; the launch's LAST CTA streams nothing and polls those words (one warp per row),
-// writes the plain logits and selects.  No fence, ticket or counter on the producers'
-// side.  The tag is the scratch's launch counter, which the selecting CTA advances when
-// it is done.
+// The router's work is cut into many small pieces: a tile is sixteen experts' rows over ONE
+// K slice of `k_slices`, and every CTA takes one tile (the whole matrix is a few megabytes:
+// what counts is how little each SM has to pull through, and that the CTAs are small
+// enough to sit beside those of the kernels before and after).
+// The hand-off inside the launch: a streaming CTA stores each partial logit as a 64-bit
+// word (fp32 value, 32-bit tag of the launch) with one relaxed store into
+// tagged[slice][row][expert]; the launch's LAST CTA streams nothing and polls those words
+// (one warp per row), adds an expert's slices in slice order, writes the plain logits and
+// selects.  No fence, ticket or counter on the producers' side.  The tag is the scratch's
+// launch counter, which the selecting CTA advances when it is done.
 template <class G>
-__global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(const __grid_constant__ RouterParams p) {
+__global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) router_kernel(const __grid_constant__ RouterParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const StreamShape& sh = p.sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -1045,13 +1055,32 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
         uint32_t pend = (1u << per) - 1u;
         uint64_t t0 = 0;
         bool ok = true;
+        const size_t slice_stride = static_cast<size_t>(kMaxRows) * p.e;
         while (true) {
           for (int j = 0; j < per; ++j) {
             const int id = lane + 32 * j;
             if (!((pend >> j) & 1u) || id >= p.e) { pend &= ~(1u << j); continue; }
-            const uint64_t wv = ld_relaxed_gpu_u64(tagged + static_cast<size_t>(warp) * p.e + id);
-            if (warm || static_cast<uint32_t>(wv >> 32) == tag) {
-              lg[warp * p.e + id] = __uint_as_float(static_cast<uint32_t>(wv));
+            const uint64_t* src = tagged + static_cast<size_t>(warp) * p.e + id;
+            uint32_t val[kMaxKSlices], seen[kMaxKSlices];
+#pragma unroll
+            for (int ks = 0; ks < kMaxKSlices; ++ks) {
+              val[ks] = 0u;                                   // (+0 beyond k_slices)
+              seen[ks] = tag;
+              if (ks < p.k_slices) {
+                const uint64_t wv = ld_relaxed_gpu_u64(src + ks * slice_stride);
+                val[ks] = static_cast<uint32_t>(wv);
+                seen[ks] = static_cast<uint32_t>(wv >> 32);
+              }
+            }
+            bool all = true;
+            float sum = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < kMaxKSlices; ++ks) {
+              all = all && seen[ks] == tag;
+              sum += __uint_as_float(val[ks]);
+            }
+            if (warm || all) {
+              lg[warp * p.e + id] = sum;
               pend &= ~(1u << j);
             }
           }
@@ -1081,14 +1110,15 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
   int grid = 0;   // CTAs that take part in the stream (set by cta_share)
   stream_init<G>(sh, cv.sm);
-  if (tid == G::PRODUCER_WARP * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1))
+  if (tid == G::PRODUCER_WARP * 32 && !stream_whole_rows<G>(sh))
     prefetch_tensormap(&p.map0);   // only a map the host filled (K-sliced stages)
-  if (tid == 0) {
-    GroupDesc& g = cv.sm->groups[0];
+  if (tid < p.k_slices) {
+    GroupDesc& g = cv.sm->groups[tid];
     g.w = p.w;
     g.scale = nullptr;
     g.row_base = 0;
     g.map_id = 0;
+    g.k_base = tid * sh.k_bytes;
     for (int c = 0; c < kMaxCols; ++c) {
       g.col_row[c] = c < p.m ? c : -1;
       g.col_mul[c] = 1.0f;
@@ -1098,6 +1128,9 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
   __syncthreads();
   {
     const CtaWork wk = cta_share<G>(sh, stream_ctas, cta, grid);
+    // (the host starts one CTA per tile: a CTA's stages all belong to one K slice, whose
+    // part of the activation rows is all it stages)
+    const int my_slice = wk.n_items > 0 ? wk.tile0 / wk.tpg : 0;
     if (warp == G::PRODUCER_WARP) {
       produce<G>(sh, cv.sm, cv.ring, wk, scr.status, &p.map0, &p.map1);
       if (tid == G::PRODUCER_WARP * 32) IQ_STAMP(p, 3);
@@ -1106,11 +1139,12 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
       after_wait();
       if (tid == 0) IQ_STAMP(p, 1);
       if (wk.n_items > 0) {
-        const int vec = p.h / 8;   // 16-byte vectors per bf16 row
+        const int vec = sh.k_bytes / 16;   // 16-byte vectors of the slice per bf16 row
+        const __nv_bfloat16* x0 = p.x + my_slice * (sh.k_bytes / 2);
         for (int i = tid; i < p.m * vec; i += G::CONSUMER_THREADS) {
           const int r = i / vec, v = i - r * vec;
           *reinterpret_cast<uint4*>(cv.xq + r * sh.x_pitch + v * 16) =
-              *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(r) * p.h + v * 8);
+              __ldcg(reinterpret_cast<const uint4*>(x0 + static_cast<size_t>(r) * p.h + v * 8));
         }
       }
       named_bar_sync(1, G::CONSUMER_THREADS);
@@ -1125,7 +1159,8 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) router_kernel(cons
 #pragma unroll
         for (int sub = 0; sub < G::RT; ++sub)
           if (col < m)
-            st_relaxed_gpu_u64(tagged + static_cast<size_t>(col) * e + id.tig * G::ROWS + sub * 16 + r,
+            st_relaxed_gpu_u64(tagged + (static_cast<size_t>(id.group) * kMaxRows + col) * e +
+                                   id.tig * G::ROWS + sub * 16 + r,
                                tag | __float_as_uint(val[sub]));
       };
       epilogue<G, false>(sh, cv.sm, wk, total, grid, cta, scr, emit);
@@ -1306,6 +1341,7 @@ __device__ __noinline__ int build_groups(GroupDesc* groups, const MoeCommon& mc,
       gd.scale = c.w_scale + static_cast<size_t>(expert) * c.scale_stride;
       gd.row_base = expert * c.rows_per_expert;
       gd.map_id = 0;
+      gd.k_base = 0;
       // all columns unused: multipliers 0, rows -1, outputs 0 (8-byte stores)
       unsigned long long* mul = reinterpret_cast<unsigned long long*>(gd.col_mul);
       unsigned long long* row = reinterpret_cast<unsigned long long*>(gd.col_row);
@@ -1320,6 +1356,7 @@ __device__ __noinline__ int build_groups(GroupDesc* groups, const MoeCommon& mc,
       gd.scale = c.shared_scale + static_cast<size_t>(sidx) * c.scale_stride;
       gd.row_base = sidx * c.rows_per_expert;
       gd.map_id = 1;
+      gd.k_base = 0;
       for (int col = 0; col < kMaxCols; ++col) {
         const bool live = col < c.m;
         const int pair_row = col * slots + c.top_k + sidx;
@@ -1439,7 +1476,7 @@ __device__ __forceinline__ void gate_stream(const GateParams& p, const StreamSha
 }
 
 template <class G>
-__global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) gate_kernel(const __grid_constant__ GateParams p) {
+__global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) gate_kernel(const __grid_constant__ GateParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   StreamShape sh = p.sh;
   const Carve<G> cv = carve<G>(smem, sh);
@@ -1447,14 +1484,17 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) gate_kernel(const 
   IQ_TRACE_SCRATCH(scr, p);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int cta = blockIdx.x, n_cta = static_cast<int>(gridDim.x);
+  uint32_t* gate_done = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(p.scratch) + kScrGateDone);
+  uint32_t done0 = 0;
   if (tid == 0) {
     IQ_STAMP(p, 0);
 #ifdef IQ_TRACE
     if (p.trace) p.trace[blockIdx.x * kTraceWords + 15] = smid_of();
 #endif
+    done0 = ld_volatile_u32(gate_done);
   }
   stream_init<G>(sh, cv.sm);
-  if (tid == G::PRODUCER_WARP * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
+  if (tid == G::PRODUCER_WARP * 32 && !stream_whole_rows<G>(sh)) {
     prefetch_tensormap(&p.map0);   // only maps the host filled (K-sliced stages)
     if (p.mc.n_shared > 0) prefetch_tensormap(&p.map1);
   }
@@ -1479,6 +1519,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) gate_kernel(const 
       gd.scale = p.mc.shared_scale + static_cast<size_t>(tid) * p.mc.scale_stride;
       gd.row_base = tid * p.mc.rows_per_expert;
       gd.map_id = 1;
+      gd.k_base = 0;
       for (int c = 0; c < kMaxCols; ++c) {
         const bool live = c < p.mc.m;
         gd.col_row[c] = static_cast<int16_t>(live ? c : -1);
@@ -1513,6 +1554,20 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) gate_kernel(const 
   gate_stream<G>(p, sh, cv, scr, wk, total, grid, cta, !early_x, pos, rpos);
   if (tid == 0) IQ_STAMP(p, 4);
   if (tid == G::EPILOGUE_WARP * 32) IQ_STAMP(p, 5);
+  // A CTA without work stays on its SM until a working CTA of the launch has finished.
+  // The Down's CTAs are placed while this launch runs, next to its CTAs, as many per SM as
+  // fit: an SM that an idle CTA left at once would take TWO of them, which then share one
+  // SM's shared-memory bandwidth and finish last (measured: 11 us instead of 4.4 us for
+  // the Down's consume phase on 4 of 148 SMs).  The counter only grows; its value cannot
+  // change between this CTA's start and the launch's first finished CTA.
+  if (wk.n_items <= 0 && done_tiles == 0) {
+    if (tid == 0) {
+      const uint64_t t0 = globaltimer_ns();
+      while (ld_volatile_u32(gate_done) == done0 && globaltimer_ns() - t0 < 30000ull) nanosleep_ns(200);
+    }
+  } else if (tid == G::EPILOGUE_WARP * 32) {
+    red_add_relaxed_u32(gate_done, 1u);
+  }
   stream_drain_on_abort<G>(cv.sm);
 }
 
@@ -1535,7 +1590,7 @@ struct DownParams {
 };
 
 template <class G>
-__global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const __grid_constant__ DownParams p) {
+__global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) down_kernel(const __grid_constant__ DownParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   StreamShape sh = p.sh;
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -1560,7 +1615,7 @@ __global__ void __launch_bounds__(G::THREADS, G::CTAS_PER_SM) down_kernel(const 
   StreamScratch scr = scratch_of(p.scratch);
   IQ_TRACE_SCRATCH(scr, p);
   stream_init<G>(sh, cv.sm);
-  if (tid == G::PRODUCER_WARP * 32 && !(sh.k_bytes == G::KC && G::NBOX == 1)) {
+  if (tid == G::PRODUCER_WARP * 32 && !stream_whole_rows<G>(sh)) {
     prefetch_tensormap(&p.map0);   // only maps the host filled (K-sliced stages)
     if (p.mc.n_shared > 0) prefetch_tensormap(&p.map1);
   }
@@ -1736,11 +1791,12 @@ static int weight_map(CUtensorMap* out, const void* ptr, long long rows, int k_b
 template <class G>
 static int fill_maps(CUtensorMap* map0, CUtensorMap* map1, const StreamShape& sh, const void* w,
                      long long rows, const void* shared_w, long long shared_rows) {
-  if (sh.k_bytes == G::KC && G::NBOX == 1) return IQ_OK;      // whole-row stages: untiled copies
+  if (stream_whole_rows<G>(sh)) return IQ_OK;      // whole-row stages: untiled copies
   const int box_rows = sh.pair_half > 0 ? G::ROWS / 2 : G::ROWS;
-  int rc = weight_map(map0, w, rows, sh.k_bytes, box_rows, G::BOXK);
+  const int row_bytes = sh.row_bytes ? sh.row_bytes : sh.k_bytes;
+  int rc = weight_map(map0, w, rows, row_bytes, box_rows, G::BOXK);
   if (rc != IQ_OK) return rc;
-  if (shared_w) rc = weight_map(map1, shared_w, shared_rows, sh.k_bytes, box_rows, G::BOXK);
+  if (shared_w) rc = weight_map(map1, shared_w, shared_rows, row_bytes, box_rows, G::BOXK);
   return rc;
 }
 
@@ -2137,24 +2193,34 @@ template <class G>
 static int router_launch(const iq_router_args* a, void* stream) {
   RouterParams p{};
   StreamShape& sh = p.sh;
-  sh.whole_tiles = 1;
+  // One CTA per tile, K cut into as many slices as gives every SM at most one CTA (and a
+  // slice a whole number of stages).
+  const int row_tiles = (a->e + G::ROWS - 1) / G::ROWS;
+  const int row_stages = a->h * 2 / G::KC;
+  int k_slices = 1;
+  for (int ks = 2; ks <= kMaxKSlices; ++ks)
+    if (row_stages % ks == 0 && row_tiles * ks + 1 <= sm_count()) k_slices = ks;
+  if (row_tiles + 1 > sm_count()) return IQ_ERR_UNSUPPORTED;
+  sh.whole_tiles = 2;
   sh.mode = kRowsPerGroup;
-  sh.n_groups = 1;
+  sh.n_groups = k_slices;
   sh.rows_per_group = a->e;
-  sh.k_bytes = a->h * 2;
+  sh.k_bytes = a->h * 2 / k_slices;
+  sh.row_bytes = a->h * 2;
   sh.rg_shift = 7;
   sh.kg_shift = 7;
   sh.pair_half = 0;
   sh.x_rows = a->m;
-  sh.x_pitch = a->h * 2 + 64;
+  sh.x_pitch = sh.k_bytes + 64;
   sh.x_blocks = 1;
-  const int grid = grid_for<G>();
+  const int grid = row_tiles * k_slices + 1;
   // the launch's last CTA selects; it keeps the rows' logits in shared memory
-  // (a ring for a CTA's whole row set when the SM has room for it)
+  // (the ring holds a CTA's whole tile: it is in shared memory before the dependency wait
+  // returns)
   const size_t tile_bytes = static_cast<size_t>(G::ROWS) * sh.k_bytes;
-  const size_t smem = plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e, 1,
-                                   tile_bytes > 160 * 1024 ? tile_bytes : 160 * 1024);
+  const size_t smem = plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e, k_slices, tile_bytes);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
+  p.k_slices = k_slices;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->e, nullptr, 0);
   if (mrc != IQ_OK) return mrc;
   p.x = static_cast<const __nv_bfloat16*>(a->x);
@@ -2181,13 +2247,8 @@ extern "C" int iq_router(const iq_router_args* a, void* stream) {
   if (a->score != IQ_ROUTE_SOFTMAX && a->score != IQ_ROUTE_SIGMOID) return IQ_ERR_ARG;
   if (!aligned16(a->x) || !aligned16(a->w)) return IQ_ERR_ARG;
   if (sm_count() < 2) return IQ_ERR_CUDA;
-  // Sixteen experts per CTA: few CTAs, each with a long row set (192 KiB at hidden 6144) on a
-  // WHOLE SM, with a ring deep enough for all of it where the staged rows leave room: the
-  // CTA's entire stream is then in shared memory before the dependency wait returns, and
-  // few large stages keep the serial per-stage chain short.
-  if ((a->h * 2) % 2048 == 0) return router_launch<Geo<1, 16, 2>>(a, stream);
-  if ((a->h * 2) % 1024 == 0) return router_launch<Geo<1, 8, 2, 1>>(a, stream);
-  return router_launch<Geo<1, 16, 1>>(a, stream);
+  // (h % 512 == 0: a row is a whole number of 1 KiB stages)
+  return router_launch<Geo<1, 8, 2, 2>>(a, stream);
 }
 
 static int fill_moe(MoeCommon& mc, int m, int h, int i_loc, int n_experts, int top_k, int n_shared,
@@ -2364,7 +2425,16 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
     int rc = IQ_ERR_UNSUPPORTED;
     if (k % 1024 == 0) rc = down_launch<Geo<1, 8, 2>>(a, stream);
     else if (k % 512 == 0 && a->h % 32 == 0) rc = down_launch<Geo<2, 4, 2>>(a, stream);
-    else if (k % 256 == 0 && a->h % 32 == 0) rc = down_launch<Geo<2, 4, 1>>(a, stream);
+    else if (k % 256 == 0 && a->h % 32 == 0) {
+      // Whole tiles per CTA: the launch takes as long as the CTA with the most rows.  With
+      // 32-row tiles 6144 rows are 192 tiles, two for every third of 147 CTAs (64 rows);
+      // 48-row tiles give 128 CTAs one tile each.
+      const int ctas = std::max(1, sm_count() - a->m);
+      const int most32 = (a->h / 32 + ctas - 1) / ctas * 32;
+      const int most48 = a->h % 48 == 0 ? (a->h / 48 + ctas - 1) / ctas * 48 : 1 << 30;
+      if (most48 < most32) rc = down_launch<Geo<3, 2, 2, 2>>(a, stream);
+      if (rc == IQ_ERR_UNSUPPORTED) rc = down_launch<Geo<2, 4, 1>>(a, stream);
+    }
     else if (k % 192 == 0 && a->h % 32 == 0) rc = down_launch<Geo<2, 3, 1>>(a, stream);
     if (rc != IQ_ERR_UNSUPPORTED) return rc;
   }

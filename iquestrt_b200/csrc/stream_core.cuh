@@ -73,6 +73,13 @@ struct Geo {
   static constexpr int PRODUCER_WARP = WARPS;
   static constexpr int EPILOGUE_WARP = WARPS + 1;
   static constexpr int CTAS_PER_SM = SHARE_ == 1 ? 1 : (SHARE_ >= 2 ? 2 : (WARPS <= 8 ? 2 : 1));
+  // The thread count the kernels declare as their launch bound.  A half-SM CTA has to fit
+  // beside a ten-warp CTA of 96 registers per thread of another kernel, and registers are
+  // handed out per scheduler (16 K each): that neighbour leaves room for two warps of at
+  // most 112 registers on each scheduler.  An eight-warp (six consumer warps) CTA bound to
+  // 256 threads and two CTAs per SM may use 128 and then does NOT fit (measured: its CTAs
+  // only started when the neighbours left); bound to 288 threads it gets 112.
+  static constexpr int BOUND_THREADS = (WARPS == 6 && CTAS_PER_SM == 2) ? 288 : THREADS;
   static constexpr bool SPREAD = SHARE_ == 3;
   static_assert(CTAS_PER_SM == 1 || WARPS <= 8, "two CTAs per SM need few warps");
   static constexpr int ROWS = 16 * RT;
@@ -97,6 +104,8 @@ struct GroupDesc {
   const float* scale;      // its scale table (row-major [rows/rg, k/kg]); unused for bf16
   int row_base;            // the group's first row inside its tensor map
   int map_id;              // which of the launch's tensor maps covers the group
+  int k_base;              // first byte of the group's K range inside its rows (tiled copies;
+  int pad_;                //   the scale tables and the staged activations are not offset)
   float col_mul[kMaxCols]; // per MMA column multiplier (routing weight; 1 otherwise)
   int16_t col_row[kMaxCols];  // staged activation row per MMA column, -1 = column unused
   int16_t col_out[kMaxCols];  // output row per MMA column
@@ -116,7 +125,8 @@ struct StreamShape {
   int mode;
   int n_groups;
   int rows_per_group;  // weight rows per group
-  int k_bytes;         // bytes per weight row
+  int k_bytes;         // bytes of a weight row that a tile contracts over
+  int row_bytes;       // bytes between weight rows in memory; 0 = k_bytes (rows are dense)
   int rg_shift;        // log2(weight rows per scale entry)
   int kg_shift;        // log2(weight bytes along K per scale entry)
   int pair_half;       // >0: a tile takes ROWS/2 rows at f and ROWS/2 rows at pair_half + f
@@ -292,6 +302,12 @@ __device__ __forceinline__ CtaWork cta_share(const StreamShape& sh, int grid, in
   return cta_work<G>(sh, item_begin(total, g, cta), item_begin(total, g, cta + 1));
 }
 
+// A stage is a set of whole, dense rows: one untiled copy moves it.
+template <class G>
+__host__ __device__ __forceinline__ bool stream_whole_rows(const StreamShape& sh) {
+  return sh.k_bytes == G::KC && G::NBOX == 1 && (sh.row_bytes == 0 || sh.row_bytes == sh.k_bytes);
+}
+
 // (group, tile-in-group, k-stage) of stage `s` of tile `tile`.
 struct StagePos {
   int group, tig, kstage;
@@ -374,7 +390,7 @@ __device__ __forceinline__ void produce(const StreamShape& sh, S* sm, const Grou
   const int lane = threadIdx.x & 31;
   int slot = pos.slot;
   uint32_t phase = pos.phase;
-  const bool whole_rows = sh.k_bytes == G::KC && G::NBOX == 1;
+  const bool whole_rows = stream_whole_rows<G>(sh);
   const int halves = sh.pair_half > 0 ? 2 : 1;
   constexpr int kHalfRows = G::ROWS / 2;
   const int copy_rows = halves == 2 ? kHalfRows : G::ROWS;
@@ -414,7 +430,7 @@ __device__ __forceinline__ void produce(const StreamShape& sh, S* sm, const Grou
             for (int b = 0; b < G::NBOX; ++b)
               tma_2d_g2s_evict_first(dst + b * (G::ROWS * G::BOXK) + hf * kHalfRows * G::PITCH,
                                      gd.map_id ? map1 : map0,
-                                     p.kstage * (G::KC / 4) + b * (G::BOXK / 4),
+                                     gd.k_base / 4 + p.kstage * (G::KC / 4) + b * (G::BOXK / 4),
                                      gd.row_base + row, bar, policy);
           }
         }

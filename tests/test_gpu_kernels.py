@@ -32,9 +32,11 @@ def _synth():
 def _scratch_clean(scratch):
     """Status word, tickets and tile counters are zero again after a launch (the fp32
     partials area behind them is overwritten before every use and never cleared; the
-    launch counter at byte 128, which tags hand-off words, only ever grows)."""
+    launch counter at byte 128, which tags hand-off words, and the Gate's count of finished
+    CTAs at byte 136 only ever grow)."""
     head = scratch.buf[:256 + 4 * 16384].clone().view(torch.int32)
     head[128 // 4] = 0
+    head[136 // 4] = 0
     return int(head.abs().sum()) == 0
 
 
