@@ -59,7 +59,7 @@ __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a -
 // buffer is set (iq_trace_set) takes the next slot of it, and each CTA stamps %globaltimer
 // at a few points of its life into `trace[cta][point]` (point 15: the SM it ran on).
 constexpr int kTraceCtas = 304;
-constexpr int kTraceWords = 16;
+constexpr int kTraceWords = 32;   // 16 %globaltimer stamps, then 16 SM-clock stamps
 #ifdef IQ_TRACE
 #define IQ_TRACE_FIELD unsigned long long* trace;
 #define IQ_TRACE_SCRATCH(scr, p) \
@@ -67,6 +67,11 @@ constexpr int kTraceWords = 16;
 #define IQ_STAMP(p, k)                                                                   \
   do {                                                                                   \
     if ((p).trace) (p).trace[blockIdx.x * kTraceWords + (k)] = globaltimer_ns();          \
+  } while (0)
+#define IQ_CLOCK(p, k)                                                                   \
+  do {                                                                                   \
+    if ((p).trace)                                                                       \
+      (p).trace[blockIdx.x * kTraceWords + 16 + (k)] = static_cast<unsigned long long>(clock64()); \
   } while (0)
 __device__ __forceinline__ unsigned long long smid_of() {
   unsigned v;
@@ -77,6 +82,7 @@ __device__ __forceinline__ unsigned long long smid_of() {
 #define IQ_TRACE_FIELD
 #define IQ_TRACE_SCRATCH(scr, p) do {} while (0)
 #define IQ_STAMP(p, k) do {} while (0)
+#define IQ_CLOCK(p, k) do {} while (0)
 #endif
 
 // Shared-memory carve-up after StreamSmem: activation scales, staged activations, ring.
@@ -305,6 +311,20 @@ __device__ inline U4 f32_to_bf16x8(const float (&f)[8]) {
   return u;
 }
 __device__ inline float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// Two values rounded to bf16 by ONE conversion instruction: the packed pair (what a store
+// wants) and the two rounded values back in fp32 (two moves).  The tail rounds every element
+// up to five times; single conversions were a third of its instructions.
+__device__ __forceinline__ uint32_t bf16x2_round(float lo, float hi, float& rlo, float& rhi) {
+  const __nv_bfloat162 p = __float22bfloat162_rn(make_float2(lo, hi));
+  const uint32_t u = *reinterpret_cast<const uint32_t*>(&p);
+  rlo = __uint_as_float(u << 16);
+  rhi = __uint_as_float(u & 0xffff0000u);
+  return u;
+}
+// Two values to e4m3 (saturating) by one conversion: low byte = lo.
+__device__ __forceinline__ uint32_t e4m3x2_sat(float lo, float hi) {
+  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+}
 
 // The threads that run a block-wide helper together: the whole CTA (n == 0), or threads
 // [0, n) of it meeting on named barrier `id` while the CTA's other warps do something else.
@@ -504,7 +524,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
         if (tid == 0) set_status(a.status, IQ_ERR_PEER_TIMEOUT);
         return;
       }
-      if (tid == 0 && pv.trace && !warm) pv.trace[10] = globaltimer_ns();
+      if (tid == 0 && pv.trace && !warm) { pv.trace[10] = globaltimer_ns(); pv.trace[16 + 12] = clock64(); }
     } else {
       // ---- cross-rank readiness: signal, then wait while the residual loads are in flight
       if (r == r_begin && a.world > 1) {
@@ -589,7 +609,7 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
         for (int j = 0; j < 8; ++j) ss = fmaf(f[i][j], f[i][j], ss);
       }
       inv1 = rsqrtf(block_sum(ss, slots0, bar) * inv_h + a.eps);
-      if (kPush && tid == 0 && pv.trace && !warm) pv.trace[12] = globaltimer_ns();
+      if (kPush && tid == 0 && pv.trace && !warm) { pv.trace[12] = globaltimer_ns(); pv.trace[16 + 13] = clock64(); }
     }
     // ---- h = residual + (ATTN: bf16(bf16(w1*(ao*inv))*scale) | MLP: bf16(m*scale))
     float ss2 = 0.f;
@@ -609,16 +629,21 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
       } else {
         bf16x8_to_f32(U4{ra.x, ra.y, ra.z, ra.w}, res);
       }
+      uint32_t hb[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float add;
+      for (int j = 0; j < 8; j += 2) {
+        float add0, add1;
         if (attn) {
-          const float nrm = bf16_round(wv[i][j] * (f[i][j] * inv1));
-          add = bf16_round(nrm * a.scale);
+          float n0, n1;
+          bf16x2_round(wv[i][j] * (f[i][j] * inv1), wv[i][j + 1] * (f[i][j + 1] * inv1), n0, n1);
+          bf16x2_round(n0 * a.scale, n1 * a.scale, add0, add1);
         } else {
-          add = bf16_round(f[i][j] * a.scale);
+          bf16x2_round(f[i][j] * a.scale, f[i][j + 1] * a.scale, add0, add1);
         }
-        f[i][j] = res[j] + add;                 // f now holds h
+        f[i][j] = res[j] + add0;                 // f now holds h
+        f[i][j + 1] = res[j + 1] + add1;
+        if (!a.residual_fp32)                    // the norm sees the rounded stream
+          hb[j >> 1] = bf16x2_round(f[i][j], f[i][j + 1], f[i][j], f[i][j + 1]);
       }
       if (a.residual_fp32) {
         float* ho = static_cast<float*>(a.h_out) + off;
@@ -626,18 +651,16 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
           *reinterpret_cast<float4*>(ho) = make_float4(f[i][0], f[i][1], f[i][2], f[i][3]);
           *reinterpret_cast<float4*>(ho + 4) = make_float4(f[i][4], f[i][5], f[i][6], f[i][7]);
         }
-      } else {
-        const U4 hb = f32_to_bf16x8(f[i]);
-        if (!warm) *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.h_out) + off) = hb;
-        bf16x8_to_f32(hb, f[i]);            // the norm sees the rounded stream
+      } else if (!warm) {
+        *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.h_out) + off) = U4{hb[0], hb[1], hb[2], hb[3]};
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss2 = fmaf(f[i][j], f[i][j], ss2);
       if (attn) ldg_f32x8(a.w_norm + v * 8, wv[i]);   // (the MLP tail holds w_norm already)
     }
-    if (kPush && tid == 0 && pv.trace && !warm) pv.trace[13] = globaltimer_ns();
+    if (kPush && tid == 0 && pv.trace && !warm) { pv.trace[13] = globaltimer_ns(); pv.trace[16 + 14] = clock64(); }
     const float inv2 = rsqrtf(block_sum(ss2, slots1, bar) * inv_h + a.eps);
-    if (kPush && tid == 0 && pv.trace && !warm) pv.trace[14] = globaltimer_ns();
+    if (kPush && tid == 0 && pv.trace && !warm) { pv.trace[14] = globaltimer_ns(); pv.trace[16 + 15] = clock64(); }
     if (a.inv_out && tid == 0 && !warm) a.inv_out[r] = inv2;
 
     // ---- norm_out = bf16(w_norm * (h * inv)) (+ e4m3 copy, unscaled or per 1x128 group)
@@ -647,15 +670,17 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
       const bool live = v < vec_per_row;       // uniform over each 16-lane group
       const size_t off = row_off + static_cast<size_t>(live ? v : 0) * 8;
       float o[8];
+      uint32_t ob[4];
       float amax = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        o[j] = live ? bf16_round(wv[i][j] * (f[i][j] * inv2)) : 0.f;
-        amax = fmaxf(amax, fabsf(o[j]));
+      for (int j = 0; j < 8; j += 2) {
+        ob[j >> 1] = bf16x2_round(live ? wv[i][j] * (f[i][j] * inv2) : 0.f,
+                                  live ? wv[i][j + 1] * (f[i][j + 1] * inv2) : 0.f, o[j], o[j + 1]);
+        amax = fmaxf(amax, fmaxf(fabsf(o[j]), fabsf(o[j + 1])));
       }
       const bool store = live && !warm;
       if (store)
-        *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.norm_out) + off) = f32_to_bf16x8(o);
+        *reinterpret_cast<U4*>(static_cast<__nv_bfloat16*>(a.norm_out) + off) = U4{ob[0], ob[1], ob[2], ob[3]};
       if (a.norm_fp8) {
         float sc = 1.0f;
         if (a.norm_fp8_scale) {
@@ -666,12 +691,8 @@ __device__ __forceinline__ void run_tail(const iq_tail_args& a, const PushView& 
           if (store && (v & 15) == 0) a.norm_fp8_scale[static_cast<size_t>(r) * (h / 128) + (v >> 4)] = sc;
         }
         const float rcp = 1.0f / sc;
-        uint32_t q0 = 0, q1 = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          q0 |= static_cast<uint32_t>(f32_to_e4m3_sat(o[j] * rcp)) << (8 * j);
-          q1 |= static_cast<uint32_t>(f32_to_e4m3_sat(o[j + 4] * rcp)) << (8 * j);
-        }
+        const uint32_t q0 = e4m3x2_sat(o[0] * rcp, o[1] * rcp) | (e4m3x2_sat(o[2] * rcp, o[3] * rcp) << 16);
+        const uint32_t q1 = e4m3x2_sat(o[4] * rcp, o[5] * rcp) | (e4m3x2_sat(o[6] * rcp, o[7] * rcp) << 16);
         if (store) *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.norm_fp8) + off) = make_uint2(q0, q1);
       }
     }
@@ -687,28 +708,66 @@ __host__ __device__ inline size_t tail_park_bytes(int h, int residual_fp32) {
 // A tail CTA of the push protocol: CTA `index` of `n_tail` finishes rows index,
 // index + n_tail, ...  The last tail CTA to finish closes the call (the zone's epoch moves
 // on once every tail CTA has read it).
+//
+// A tail CTA has nothing to do until its rows arrive, and its code runs once per launch:
+// fetched cold from L2 it was measured at about 18 cycles per instruction (11 us for one
+// pass through the tail of a 6144-wide row, against 2.4 us with the instructions at hand).
+// So its 256 working threads REHEARSE: the same instructions on whatever the buffers hold,
+// nothing awaited, not a single global store (`warm`, see run_tail), pass after pass, until
+// the launch's dependency has resolved -- which one further thread (the "watcher", thread
+// 256, present in every streaming kernel's CTA) finds out by executing the dependency
+// wait itself and raising a flag in shared memory.  Then the working threads pass the wait
+// too (it returns at once) and make the real pass with the code still warm.  Instructions
+// fetched by a single rehearsal at the CTA's start were found half gone ten microseconds
+// later; a rehearsal placed after the wait finished too late for the rows.
+// A launch without a spare thread (the tail kernel) rehearses once, ahead of the wait.
 __device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& pv, int per_round,
                                          int index, int n_tail, uint8_t* smem) {
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
   uint32_t* word = reinterpret_cast<uint32_t*>(smem + 516);     // [epoch, closes the call]
+  volatile int* released = reinterpret_cast<volatile int*>(smem + 524);
+  volatile int* decided = reinterpret_cast<volatile int*>(smem + 528);
   uint8_t* park = smem + 1024;
   uint32_t* zs = reinterpret_cast<uint32_t*>(smem + 1024 + tail_park_bytes(a.h, a.residual_fp32));
-  // Two passes through ONE copy of the tail's code: a rehearsal ahead of the dependency
-  // wait (nothing is awaited, nothing is stored; see run_tail), then the call itself.
+  const int tid = threadIdx.x;
+#ifndef IQ_REHEARSE_MODE
+#define IQ_REHEARSE_MODE 2
+#endif
+  const bool watched = IQ_REHEARSE_MODE >= 2 && blockDim.x > kTailThreads;
+  if (tid == 0) { *released = 0; *sflag = 1; }
+  __syncthreads();
+  if (tid >= kTailThreads) {
+    if (watched && tid == kTailThreads) {
+      after_wait();
+      *released = 1;
+    }
+    return;
+  }
+  const BlockBar bar{2, kTailThreads};
+  // Every pass goes through ONE copy of the tail's code.
 #pragma unroll 1
-  for (int pass = 0; pass < 2; ++pass) {
-    const bool warm = pass == 0;
+  for (int pass = 0;; ++pass) {
+    bool warm;
+    if (watched) {
+      if (IQ_REHEARSE_MODE == 3 && pass > 0) nanosleep_ns(1500);
+      if (tid == 0) *decided = *released;
+      bar.sync();
+      warm = *decided == 0;
+    } else {
+      warm = pass == 0;
+      if (IQ_REHEARSE_MODE == 0 && warm) continue;
+    }
     if (!warm) {
       after_wait();
-      if (threadIdx.x == 0 && pv.trace) pv.trace[9] = globaltimer_ns();
+      if (tid == 0 && pv.trace) { pv.trace[9] = globaltimer_ns(); pv.trace[16 + 11] = clock64(); }
     }
     // The call's tag comes from the zone's epoch.  The epoch may move on once (a) every
     // tail CTA has read it and (b) every producer has: the tail CTA that reads it LAST takes
     // on the job, and does it after its own rows are complete (every producer of the launch
     // contributes to every row, so by then all of them have read the epoch).  That keeps the
     // atomic at the start of the tail, where it waits for data anyway, and off its end.
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
       uint32_t closes = 0, epoch = 0;
       if (!warm) {
         epoch = ld_volatile_u32(pv.epoch);
@@ -722,13 +781,13 @@ __device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& 
       word[1] = closes;
       *sflag = 1;
     }
-    __syncthreads();
+    bar.sync();
     const uint32_t epoch = word[0];
-    if (threadIdx.x < kTailThreads)
-      run_tail<true>(a, pv, tag16_of(epoch), park, zs, per_round, red, sflag,
-                     BlockBar{2, kTailThreads}, index, n_tail, warm);
-    if (threadIdx.x == 0 && word[1]) *pv.epoch = epoch + 1u;
-    __syncthreads();
+    run_tail<true>(a, pv, tag16_of(epoch), park, zs, per_round, red, sflag, bar, index, n_tail,
+                   warm);
+    if (tid == 0 && word[1]) *pv.epoch = epoch + 1u;
+    bar.sync();
+    if (!warm) break;
   }
 }
 
@@ -826,7 +885,7 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) linear_kerne
     pv.trace = p.trace ? p.trace + blockIdx.x * kTraceWords : nullptr;
 #endif
     tail_cta(p.tail, pv, p.per_round, cta - stream_ctas, p.n_tail, smem);
-    if (tid == 0) IQ_STAMP(p, 11);
+    if (tid == 0) { IQ_STAMP(p, 11); IQ_CLOCK(p, 10); }
     return;
   }
   const Carve<G> cv = carve<G>(smem, sh);
@@ -862,8 +921,10 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) linear_kerne
     } else if (warp < G::WARPS) {
       float held[kGatherHeld];
       gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);   // weights: before the wait
+      // (the walk through the CTA's share: ahead of the wait)
+      const ConsumeHead<G> head = consume_head<G>(sh, cv.sm->groups, cv.xq, cv.xs, wk);
       after_wait();
-      if (tid == 0) IQ_STAMP(p, 1);
+      if (tid == 0) { IQ_STAMP(p, 1); IQ_CLOCK(p, 7); }
       if (p.x_kind == IQ_X_BF16_GROUPQ || p.x_kind == IQ_X_BF16_SPLIT2)
         stage_rows_bf16_groupq(cv.xq, cv.xs, sh, static_cast<const __nv_bfloat16*>(p.x), p.k, p.m,
                                p.k, p.x_kind == IQ_X_BF16_SPLIT2, tid, G::CONSUMER_THREADS);
@@ -871,12 +932,13 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) linear_kerne
         stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.x), p.k,
                         p.x_kind == IQ_X_E4M3_GROUP ? p.x_scale : nullptr, p.m, p.k, tid,
                         G::CONSUMER_THREADS);
+      if (tid == 0) IQ_CLOCK(p, 8);
       gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
       named_bar_sync(1, G::CONSUMER_THREADS);
-      if (tid == 0) IQ_STAMP(p, 2);
-      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
+      if (tid == 0) { IQ_STAMP(p, 2); IQ_CLOCK(p, 9); }
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr, &head);
       if (tid == 0) IQ_STAMP(p, 4);
-    } else {
+    } else if (warp == G::EPILOGUE_WARP) {
       pdl_wait();
       const bool split2 = p.x_kind == IQ_X_BF16_SPLIT2;
       const int m = p.m, n = p.n;
@@ -945,12 +1007,44 @@ __device__ inline uint32_t ordered_key(float v) {
 
 // One warp selects row `row`: top_k rounds of (largest key, then smallest id), softmax
 // or renormalised sigmoid summed in descending-value order, pairs stored by ascending id.
+// The rounds are a serial chain on the router's critical path, so each is kept to two
+// warp reductions and a few moves: every lane first sorts its own keys (a compile-time
+// odd-even merge network, ties to the lower id), then a round compares the lanes' heads and
+// the winning lane drops its head.  The winners' probabilities are worked out afterwards,
+// one per lane, all at once.
+template <int N>
+__device__ __forceinline__ void sort_keys_desc(uint32_t (&key)[N], int (&slot)[N]) {
+#pragma unroll
+  for (int p = 1; p < N; p <<= 1) {
+#pragma unroll
+    for (int k = p; k >= 1; k >>= 1) {
+#pragma unroll
+      for (int j = k % p; j + k < N; j += 2 * k) {
+#pragma unroll
+        for (int i = 0; i < k; ++i) {
+          const int a = i + j, b = i + j + k;
+          if (b < N && a / (2 * p) == b / (2 * p)) {
+            const bool sw = key[b] > key[a] || (key[b] == key[a] && slot[b] < slot[a]);
+            const uint32_t ka = key[a], kb = key[b];
+            const int sa = slot[a], sb = slot[b];
+            key[a] = sw ? kb : ka;
+            key[b] = sw ? ka : kb;
+            slot[a] = sw ? sb : sa;
+            slot[b] = sw ? sa : sb;
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int kMaxPerLane>
 __device__ __forceinline__ void select_row_impl(const float* logits, int e, int top_k, int score,
                                                 int row, int* sel, float* wt,
                                                 bool logits_in_smem, bool store) {
   const int lane = threadIdx.x & 31;
   uint32_t key[kMaxPerLane];
+  int slot[kMaxPerLane];
   const int per = (e + 31) / 32;
 #pragma unroll
   for (int j = 0; j < kMaxPerLane; ++j) {
@@ -960,40 +1054,41 @@ __device__ __forceinline__ void select_row_impl(const float* logits, int e, int 
       lv = logits_in_smem ? logits[static_cast<size_t>(row) * e + id]
                           : __ldcg(logits + static_cast<size_t>(row) * e + id);
     key[j] = (j < per && id < e) ? ordered_key(lv) : 0u;
+    slot[j] = j;
   }
-  int my_id = 0x7fffffff;
-  float top_val = 0.f, sum = 0.f, my_p = 0.f;
+  sort_keys_desc<kMaxPerLane>(key, slot);
+  int my_id = 0x7fffffff;      // lane t keeps the winner of round t
+  uint32_t my_key = 0u;
+  int n_sel = 0;
   for (int t = 0; t < top_k; ++t) {
-    uint32_t best = 0;
-    int best_id = 0x7fffffff;
-#pragma unroll
-    for (int j = 0; j < kMaxPerLane; ++j) {
-      const int id = lane + 32 * j;
-      if (key[j] > best) { best = key[j]; best_id = id; }   // ascending id: first max wins
-    }
-    const uint32_t wmax = __reduce_max_sync(0xffffffffu, best);
-    const int cand = (best == wmax && best != 0u) ? best_id : 0x7fffffff;
+    const uint32_t head = key[0];
+    const int head_id = lane + 32 * slot[0];
+    const uint32_t wmax = __reduce_max_sync(0xffffffffu, head);
+    const int cand = (head == wmax && head != 0u) ? head_id : 0x7fffffff;
     const int win = __reduce_min_sync(0xffffffffu, cand);
     if (win == 0x7fffffff) break;            // fewer than top_k finite logits
-    const uint32_t kbits = wmax;
-    const uint32_t raw = (kbits & 0x80000000u) ? (kbits & 0x7fffffffu) : ~kbits;
-    const float val = __uint_as_float(raw);
-    if (t == 0) top_val = val;
-    const float p = score == IQ_ROUTE_SOFTMAX ? expf(__fsub_rn(val, top_val))
-                                              : 1.0f / (1.0f + expf(-val));
-    sum = __fadd_rn(sum, p);
-    if (lane == t) { my_id = win; my_p = p; }
+    if (lane == t) { my_id = win; my_key = wmax; }
+    if (head_id == win && head != 0u) {      // the winning lane drops its head
 #pragma unroll
-    for (int j = 0; j < kMaxPerLane; ++j)
-      if ((win & 31) == lane && (win >> 5) == j) key[j] = 0u;
+      for (int j = 0; j + 1 < kMaxPerLane; ++j) { key[j] = key[j + 1]; slot[j] = slot[j + 1]; }
+      key[kMaxPerLane - 1] = 0u;
+    }
+    ++n_sel;
   }
-  // rank of my id among the selected ids
+  const uint32_t raw = (my_key & 0x80000000u) ? (my_key & 0x7fffffffu) : ~my_key;
+  const float val = __uint_as_float(raw);
+  const float top_val = __shfl_sync(0xffffffffu, val, 0);
+  float my_p = 0.f;
+  if (lane < n_sel)
+    my_p = score == IQ_ROUTE_SOFTMAX ? expf(__fsub_rn(val, top_val)) : 1.0f / (1.0f + expf(-val));
+  // the sum in descending-value order, and the rank of my id among the selected ids
+  float sum = 0.f;
   int rank = 0;
-  for (int t = 0; t < top_k; ++t) {
-    const int other = __shfl_sync(0xffffffffu, my_id, t);
-    rank += (other < my_id) ? 1 : 0;
+  for (int t = 0; t < n_sel; ++t) {
+    sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, my_p, t));
+    rank += (__shfl_sync(0xffffffffu, my_id, t) < my_id) ? 1 : 0;
   }
-  if (store && lane < top_k && my_id != 0x7fffffff) {
+  if (store && lane < n_sel) {
     sel[row * top_k + rank] = my_id;
     wt[row * top_k + rank] = my_p / sum;
   }
@@ -1038,16 +1133,39 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) router_kerne
 #endif
   }
   if (cta == stream_ctas) {
-    // ---- the selecting CTA.  Two passes through one copy of its code: a rehearsal ahead of
-    // the dependency wait (words taken as they are, nothing stored) that brings the
-    // instructions in, then the launch's own selection.
+    // ---- the selecting CTA.  Its code runs once per launch, on the launch's critical path:
+    // like a tail CTA (see tail_cta) its working threads rehearse it -- words taken as they
+    // are, nothing stored -- until thread 256, which executes the dependency wait, raises
+    // the flag; then they make the launch's own selection with the instructions at hand.
     float* lg = reinterpret_cast<float*>(smem);          // [m][e]
+    volatile int* released = reinterpret_cast<volatile int*>(lg + p.m * p.e);
+    volatile int* decided = released + 1;
+    if (tid == 0) *released = 0;
+    __syncthreads();
+    const bool watched = IQ_REHEARSE_MODE >= 2;
+    if (tid >= 256) {
+      if (watched && tid == 256) {
+        after_wait();
+        *released = 1;
+      }
+      return;
+    }
+    const BlockBar bar{2, 256};
 #pragma unroll 1
-    for (int pass = 0; pass < 2; ++pass) {
-      const bool warm = pass == 0;
+    for (int pass = 0;; ++pass) {
+      bool warm;
+      if (watched) {
+        if (IQ_REHEARSE_MODE == 3 && pass > 0) nanosleep_ns(1500);
+        if (tid == 0) *decided = *released;
+        bar.sync();
+        warm = *decided == 0;
+      } else {
+        warm = pass == 0;
+        if (IQ_REHEARSE_MODE == 0 && warm) continue;
+      }
       if (!warm) {
         after_wait();
-        if (tid == 0) IQ_STAMP(p, 9);
+        if (tid == 0) { IQ_STAMP(p, 9); IQ_CLOCK(p, 7); }
       }
       const uint32_t tag = warm ? 0u : ld_volatile_u32(launch_tag) + 1u;
       if (warp < p.m) {
@@ -1090,19 +1208,23 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) router_kerne
           else if (now - t0 > kPipeBudgetNs) { ok = false; break; }
         }
         __syncwarp();
+        if (tid == 0 && !warm) { IQ_STAMP(p, 10); IQ_CLOCK(p, 8); }
         if (ok) {
           if (!warm)
             for (int id = lane; id < p.e; id += 32)
               p.logits[static_cast<size_t>(warp) * p.e + id] = lg[warp * p.e + id];
+          if (tid == 0 && !warm) IQ_CLOCK(p, 9);
           select_row(lg, p.e, p.top_k, p.score, warp, p.sel, p.wt, true, !warm);
+          if (tid == 0 && !warm) IQ_CLOCK(p, 10);
         } else if (lane == 0) {
           set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
         }
       }
-      __syncthreads();
+      bar.sync();
       if (tid == 0 && !warm) *launch_tag = tag;
+      if (!warm) break;
     }
-    if (tid == 0) IQ_STAMP(p, 11);
+    if (tid == 0) { IQ_STAMP(p, 11); IQ_CLOCK(p, 11); }
     return;
   }
   const Carve<G> cv = carve<G>(smem, sh);
@@ -1136,11 +1258,12 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) router_kerne
       if (tid == G::PRODUCER_WARP * 32) IQ_STAMP(p, 3);
       pdl_wait();
     } else if (warp < G::WARPS) {
+      const int vec = sh.k_bytes / 16;   // 16-byte vectors of the slice per bf16 row
+      const __nv_bfloat16* x0 = p.x + my_slice * (sh.k_bytes / 2);
+      const ConsumeHead<G> head = consume_head<G>(sh, cv.sm->groups, cv.xq, cv.xs, wk);
       after_wait();
       if (tid == 0) IQ_STAMP(p, 1);
       if (wk.n_items > 0) {
-        const int vec = sh.k_bytes / 16;   // 16-byte vectors of the slice per bf16 row
-        const __nv_bfloat16* x0 = p.x + my_slice * (sh.k_bytes / 2);
         for (int i = tid; i < p.m * vec; i += G::CONSUMER_THREADS) {
           const int r = i / vec, v = i - r * vec;
           *reinterpret_cast<uint4*>(cv.xq + r * sh.x_pitch + v * 16) =
@@ -1149,9 +1272,9 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) router_kerne
       }
       named_bar_sync(1, G::CONSUMER_THREADS);
       if (tid == 0) IQ_STAMP(p, 2);
-      consume<G, ElemBF16>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
+      consume<G, ElemBF16>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr, &head);
       if (tid == 0) IQ_STAMP(p, 4);
-    } else {
+    } else if (warp == G::EPILOGUE_WARP) {
       pdl_wait();
       const int m = p.m, e = p.e;
       const uint64_t tag = static_cast<uint64_t>(ld_volatile_u32(launch_tag) + 1u) << 32;
@@ -1450,7 +1573,7 @@ __device__ __forceinline__ void gate_stream(const GateParams& p, const StreamSha
     named_bar_sync(1, G::CONSUMER_THREADS);
     consume<G, ElemE4M3>(sh, cv.sm, cv.sm->groups, cv.ring, G::STAGE_BYTES, cv.xq, cv.xs, cv.sc, wk,
                          scr, pos, rpos);
-  } else {
+  } else if (warp == G::EPILOGUE_WARP) {
     const int i_loc = p.mc.i_loc, m = p.mc.m;
     const int act_kind = p.act_kind;
     void* act = p.act;
@@ -1510,6 +1633,28 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) gate_kernel(
   // nothing in it depends on the routes.  A whole tile needs no scratch, and the
   // activation buffer's last reader (the previous layer's Down) finished before the
   // router could start.
+  // One row: its routed experts are top_k distinct ids unless the routes are malformed, so
+  // everything about the step except WHICH experts is known before the routes are: the
+  // number of groups, this CTA's share of the tiles, and the whole group table apart from
+  // three fields per routed group.  All of that is worked out here, ahead of the wait
+  // (the table from stand-in ids 0..top_k-1).  After the wait every warp reads the routes
+  // itself, checks that they are as assumed and fills in those fields -- every warp
+  // writes the same values and relies only on its own writes, so no block-wide barrier
+  // stands between the routes and the first copy or the scale gather.  (Measured before:
+  // 1.8 us for the table and 1 us for the share, in series, after the wait.)
+  const bool one_row = p.mc.m == 1 && p.mc.top_k <= 32;
+  StreamShape sh_one = sh;
+  sh_one.n_groups = p.mc.top_k + p.mc.n_shared;
+  int grid = 0;   // CTAs that take part in the stream (set by cta_share)
+  CtaWork wk = cta_work<G>(sh, 0, 0);
+  if (one_row) {
+    int* stand_in = cv.sm->route_ids + 64 + kMaxGroups + 1;
+    if (tid < p.mc.top_k) stand_in[tid] = tid;
+    __syncthreads();
+    build_groups(cv.sm->groups, p.mc, false, false, nullptr, cv.sm->route_ids, BlockBar{},
+                 stand_in, nullptr, nullptr, nullptr, p.early_shared != 0);
+    wk = cta_share<G>(sh_one, n_cta, cta, grid);
+  }
   int done_tiles = 0;
   if (p.early_shared) {
     const int tpg = stream_tiles_per_group<G>(sh);
@@ -1539,18 +1684,41 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) gate_kernel(
     __syncthreads();
   }
   after_wait();                     // the routes come from the predecessor
-  if (tid == 0) IQ_STAMP(p, 1);
-  sh.n_groups = build_groups(cv.sm->groups, p.mc, false, false, scr.status, cv.sm->route_ids,
-                             BlockBar{}, nullptr, nullptr, nullptr, nullptr, p.early_shared != 0);
+  if (tid == 0) { IQ_STAMP(p, 1); IQ_CLOCK(p, 7); }
+  bool as_assumed = false;
+  if (one_row) {
+    const int lane = tid & 31;
+    const int e = lane < p.mc.top_k ? __ldcg(p.mc.sel + lane) : -1 - lane;
+    const bool bad = lane < p.mc.top_k && (e < 0 || e >= p.mc.n_experts);
+    const bool dup = __popc(__match_any_sync(0xffffffffu, e)) > 1;
+    as_assumed = !__any_sync(0xffffffffu, bad || dup);
+    if (as_assumed) {
+      if (lane < p.mc.top_k) {
+        GroupDesc& gd = cv.sm->groups[(p.early_shared ? p.mc.n_shared : 0) + lane];
+        gd.w = p.mc.w + static_cast<size_t>(e) * p.mc.w_stride;
+        gd.scale = p.mc.w_scale + static_cast<size_t>(e) * p.mc.scale_stride;
+        gd.row_base = e * p.mc.rows_per_expert;
+      }
+      __syncwarp();
+      sh.n_groups = sh_one.n_groups;
+    } else {
+      // Malformed routes (every warp sees that, from the same words): the general path.
+      __syncthreads();
+    }
+  }
+  if (!as_assumed) {
+    sh.n_groups = build_groups(cv.sm->groups, p.mc, false, false, scr.status, cv.sm->route_ids,
+                               BlockBar{}, nullptr, nullptr, nullptr, nullptr, p.early_shared != 0);
+  }
+  if (tid == 0) IQ_CLOCK(p, 8);
   const long long total =
       static_cast<long long>(stream_num_tiles<G>(sh)) * stream_stages_per_tile<G>(sh);
-  int grid = 0;   // CTAs that take part in the stream (set by cta_share)
-  CtaWork wk = cta_share<G>(sh, n_cta, cta, grid);
+  if (!as_assumed) wk = cta_share<G>(sh, n_cta, cta, grid);
   if (done_tiles) {                 // the first tile is finished already
     wk.tile0 += wk.tile_step;
     wk.n_items -= wk.spt;
   }
-  if (tid == 0) IQ_STAMP(p, 2);
+  if (tid == 0) { IQ_STAMP(p, 2); IQ_CLOCK(p, 9); }
   gate_stream<G>(p, sh, cv, scr, wk, total, grid, cta, !early_x, pos, rpos);
   if (tid == 0) IQ_STAMP(p, 4);
   if (tid == G::EPILOGUE_WARP * 32) IQ_STAMP(p, 5);
@@ -1608,7 +1776,7 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) down_kernel(
     pv.trace = p.trace ? p.trace + blockIdx.x * kTraceWords : nullptr;
 #endif
     tail_cta(p.tail, pv, p.per_round, cta - stream_ctas, p.n_tail, smem);
-    if (tid == 0) IQ_STAMP(p, 11);
+    if (tid == 0) { IQ_STAMP(p, 11); IQ_CLOCK(p, 10); }
     return;
   }
   const Carve<G> cv = carve<G>(smem, sh);
@@ -1635,21 +1803,24 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) down_kernel(
     } else if (warp < G::WARPS) {
       float held[kGatherHeld];
       gather_scales_load<G, ElemE4M3>(sh, cv.sm, wk, tid, held);
-      if (early) after_wait();
-      if (tid == 0) IQ_STAMP(p, 1);
       const int rows = p.mc.m * (p.mc.top_k + p.mc.n_shared);
+      // (the walk through the CTA's share: ahead of the wait)
+      const ConsumeHead<G> head = consume_head<G>(sh, cv.sm->groups, cv.xq, cv.xs, wk);
+      if (early) after_wait();
+      if (tid == 0) { IQ_STAMP(p, 1); IQ_CLOCK(p, 7); }
       if (p.act_kind == IQ_ACT_E4M3)
         stage_rows_e4m3(cv.xq, cv.xs, sh, static_cast<const uint8_t*>(p.act), p.mc.i_loc, nullptr,
                         rows, p.mc.i_loc, tid, G::CONSUMER_THREADS);
       else
         stage_rows_bf16_groupq(cv.xq, cv.xs, sh, static_cast<const __nv_bfloat16*>(p.act),
                                p.mc.i_loc, rows, p.mc.i_loc, false, tid, G::CONSUMER_THREADS);
+      if (tid == 0) IQ_CLOCK(p, 8);
       gather_scales_store<G, ElemE4M3>(sh, cv.sm, wk, cv.sc, tid, held);
       named_bar_sync(1, G::CONSUMER_THREADS);
-      if (tid == 0) IQ_STAMP(p, 2);
-      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr);
+      if (tid == 0) { IQ_STAMP(p, 2); IQ_CLOCK(p, 9); }
+      consume<G, ElemE4M3>(sh, cv.sm, cv.ring, cv.xq, cv.xs, cv.sc, wk, scr, &head);
       if (tid == 0) IQ_STAMP(p, 4);
-    } else {
+    } else if (warp == G::EPILOGUE_WARP) {
       if (early) pdl_wait();
       const int m = p.mc.m, h = p.mc.h;
       __nv_bfloat16* out = p.out;
@@ -2138,6 +2309,17 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   if (static_cast<long long>(n) * k <= short_stream_bytes()) {
     // (falls through to a whole-SM geometry when half an SM cannot hold the rows and a ring)
     int rc = IQ_ERR_UNSUPPORTED;
+    // One 48-row tile per CTA (its k-stages worked on in batches) where that leaves no CTA
+    // with more rows than 16-row tiles would: a CTA pays the hand-over of a finished tile
+    // to its epilogue warp once instead of three times (IQB200_LINEAR_TILE48=0 turns it off).
+    static const bool tile48 = env_number("IQB200_LINEAR_TILE48", 1) != 0;
+    if (tile48 && k % 256 == 0 && n % 48 == 0) {
+      const int ctas = std::max(1, sm_count() - (a->tail || a->push ? a->m : 0));
+      const int most16 = (n / 16 + ctas - 1) / ctas * 16;
+      const int most48 = (n / 48 + ctas - 1) / ctas * 48;
+      if (most48 <= most16) rc = linear_launch<Geo<3, 2, 2, 3>>(a, stream);
+    }
+    if (rc != IQ_ERR_UNSUPPORTED) return rc;
     if (k % 1024 == 0 && n % 16 == 0) rc = linear_launch<Geo<1, 8, 2, 3>>(a, stream);
     else if (k % 768 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 4, 3, 3>>(a, stream);
     else if (k % 512 == 0 && n % 32 == 0) rc = linear_launch<Geo<2, 4, 2, 3>>(a, stream);
@@ -2218,7 +2400,8 @@ static int router_launch(const iq_router_args* a, void* stream) {
   // (the ring holds a CTA's whole tile: it is in shared memory before the dependency wait
   // returns)
   const size_t tile_bytes = static_cast<size_t>(G::ROWS) * sh.k_bytes;
-  const size_t smem = plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e, k_slices, tile_bytes);
+  const size_t smem =
+      plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e + 16, k_slices, tile_bytes);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   p.k_slices = k_slices;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->e, nullptr, 0);
@@ -2296,6 +2479,15 @@ static int gate_launch(const iq_moe_gate_args* a, void* stream) {
   // count valid routes can produce, so that a CTA's first tile is known before the routes.
   const int grid = grid_for<G>();
   bool early = a->pdl >= 2 && a->n_shared > 0;
+  if (early) {
+    // Only where a CTA has several tiles: with one tile per CTA the early CTAs gain nothing
+    // for the launch (they have no second tile to move on to), but they reach their
+    // dependency wait -- and release the NEXT kernel's CTAs -- microseconds late (measured:
+    // 8 us at one tile of 196 KB per CTA).
+    StreamShape t = sh;
+    t.n_groups = a->n_shared + a->top_k;
+    if (stream_num_tiles<G>(t) <= grid) early = false;
+  }
   if (early) {
     for (int n = a->n_shared + a->top_k; n <= a->n_shared + a->m * a->top_k && early; ++n) {
       StreamShape t = sh;

@@ -69,17 +69,18 @@ struct Geo {
   static constexpr int WARPS = RT * KW;                 // consumer warps
   static_assert(WARPS == 6 || WARPS == 8 || WARPS == 16, "6, 8 or 16 consumer warps");
   static constexpr int CONSUMER_THREADS = WARPS * 32;
-  static constexpr int THREADS = CONSUMER_THREADS + 64; // + the producer warp + the epilogue warp
+  // + the producer warp + the epilogue warp; never fewer than ten warps: a tail CTA of the
+  // launch needs 256 working threads and one more that watches the dependency (see tail_cta)
+  static constexpr int THREADS = CONSUMER_THREADS + 64 < 320 ? 320 : CONSUMER_THREADS + 64;
   static constexpr int PRODUCER_WARP = WARPS;
   static constexpr int EPILOGUE_WARP = WARPS + 1;
   static constexpr int CTAS_PER_SM = SHARE_ == 1 ? 1 : (SHARE_ >= 2 ? 2 : (WARPS <= 8 ? 2 : 1));
   // The thread count the kernels declare as their launch bound.  A half-SM CTA has to fit
   // beside a ten-warp CTA of 96 registers per thread of another kernel, and registers are
-  // handed out per scheduler (16 K each): that neighbour leaves room for two warps of at
-  // most 112 registers on each scheduler.  An eight-warp (six consumer warps) CTA bound to
-  // 256 threads and two CTAs per SM may use 128 and then does NOT fit (measured: its CTAs
-  // only started when the neighbours left); bound to 288 threads it gets 112.
-  static constexpr int BOUND_THREADS = (WARPS == 6 && CTAS_PER_SM == 2) ? 288 : THREADS;
+  // handed out per scheduler (16 K each): bound to 320 threads and two CTAs per SM a kernel
+  // gets 96 registers and fits.  (A 256-thread CTA bound to two per SM may use 128 and then
+  // does NOT fit: measured, its CTAs only started when the neighbours left.)
+  static constexpr int BOUND_THREADS = THREADS;
   static constexpr bool SPREAD = SHARE_ == 3;
   static_assert(CTAS_PER_SM == 1 || WARPS <= 8, "two CTAs per SM need few warps");
   static constexpr int ROWS = 16 * RT;
@@ -152,14 +153,24 @@ struct StreamScratch {
 __device__ __forceinline__ void trace_stamp(const StreamScratch& scr, int k) {
   if (scr.trace) scr.trace[k] = globaltimer_ns();
 }
+// One SM-clock stamp into fine slot `k` (words 16..31 of the CTA's trace words).
+__device__ __forceinline__ void trace_clock(const StreamScratch& scr, int k) {
+#ifdef IQ_TRACE
+  if (scr.trace) scr.trace[16 + k] = static_cast<unsigned long long>(clock64());
+#endif
+}
 
 __device__ __forceinline__ void set_status(int* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
 // Item range of CTA `cta` of `grid` over `total` items.
+// (total < 2^31: floor(total * cta / grid) from 32-bit divisions only -- a 64-bit division
+// is a subroutine of a few hundred instructions, and this runs at the head of every CTA)
 __host__ __device__ __forceinline__ long long item_begin(long long total, int grid, int cta) {
-  return total * cta / grid;
+  const uint32_t t = static_cast<uint32_t>(total), g = static_cast<uint32_t>(grid);
+  const uint32_t q = t / g, r = t - q * g;
+  return static_cast<long long>(q) * cta + (r * static_cast<uint32_t>(cta)) / g;
 }
 // The CTA that owns item q (inverse of item_begin; needs grid <= total).
 __host__ __device__ __forceinline__ int item_owner(long long total, int grid, long long q) {
@@ -177,7 +188,7 @@ struct StreamSmem {
   int is_last_cta;    // broadcast: this CTA runs the global epilogue
   int pad;
   GroupDesc groups[kMaxGroups];
-  int route_ids[64 + kMaxGroups + 1];   // routed expert ids while the group table is built
+  int route_ids[64 + kMaxGroups + 1 + 32];   // routed expert ids while the group table is built (+ stand-in ids)
   float red[2][G::WARPS][32][4];
 };
 
@@ -210,7 +221,9 @@ __host__ __device__ __forceinline__ int stream_stages_per_tile(const StreamShape
 // gather runs on every CTA's critical path; a runtime integer division costs ~30
 // instructions, this costs one.
 __host__ __device__ __forceinline__ uint32_t div_magic(int d) {
-  return d <= 1 ? 0u : static_cast<uint32_t>(0x100000000ull / static_cast<uint32_t>(d)) + 1u;
+  // (floor((2^32 - 1) / d) + 1: the same number unless d is a power of two, where it is
+  // one less and still exact; a 32-bit division instead of a 64-bit one)
+  return d <= 1 ? 0u : 0xffffffffu / static_cast<uint32_t>(d) + 1u;
 }
 __device__ __forceinline__ int fast_div(int a, uint32_t magic) {
   return magic ? static_cast<int>(__umulhi(static_cast<uint32_t>(a), magic)) : a;
@@ -237,7 +250,7 @@ __device__ __forceinline__ CtaWork cta_work(const StreamShape& sh, long long it0
   w.mg_spt = div_magic(w.spt);
   w.mg_kstages = div_magic(w.kstages);
   w.mg_tpg = div_magic(w.tpg);
-  w.tile0 = static_cast<int>(it0 / w.spt);
+  w.tile0 = static_cast<int>(static_cast<uint32_t>(it0) / static_cast<uint32_t>(w.spt));
   w.tile_step = 1;
   w.stage0 = static_cast<int>(it0 - static_cast<long long>(w.tile0) * w.spt);
   w.n_items = static_cast<int>(it1 - it0);
@@ -262,7 +275,9 @@ __host__ __device__ __forceinline__ bool tile_aligned_split(int n_tiles, int spt
     return true;                                        // balanced to within an eighth
   const long long stage_ns = G::STAGE_BYTES / 44;
   const long long total = static_cast<long long>(n_tiles) * spt;
-  const long long even_ns = (total + grid - 1) / grid * stage_ns;
+  const long long even_ns =
+      static_cast<long long>((static_cast<uint32_t>(total) + grid - 1) / static_cast<uint32_t>(grid)) *
+      stage_ns;
   const long long whole_ns = static_cast<long long>(per) * spt * stage_ns;
   const long long tile_ns = spt * stage_ns;
   const long long settle_ns = tile_ns < 4000 ? 3000 : 500;   // exposed unless tiles are long
@@ -292,8 +307,8 @@ __device__ __forceinline__ CtaWork cta_share(const StreamShape& sh, int grid, in
       w.tile_step = grid;
       return w;
     }
-    const long long t0 = static_cast<long long>(n_tiles) * cta / g;
-    const long long t1 = static_cast<long long>(n_tiles) * (cta + 1) / g;
+    const long long t0 = static_cast<uint32_t>(n_tiles * cta) / static_cast<uint32_t>(g);
+    const long long t1 = static_cast<uint32_t>(n_tiles * (cta + 1)) / static_cast<uint32_t>(g);
     return cta_work<G>(sh, t0 * spt, t1 * spt);
   }
   const int g = total < grid ? static_cast<int>(total) : grid;
@@ -570,33 +585,47 @@ __device__ __forceinline__ GroupCtx group_ctx(const StreamShape& sh, const Group
   return c;
 }
 
-// One stage on one consumer warp.  Lane = 4g + t reads bytes [16t, 16t+16) of each 64-byte
-// run of rows g and g+8 of its sub-tile, and the same bytes of activation row col_row[g].
-// MMA k-slot 4t+j (resp. 16+4t+j) of the first MMA is byte 16t+j (resp. 16t+4+j) of the
-// run, of the second MMA byte 16t+8+j (resp. 16t+12+j): A and B use the same permutation
-// of K, which a dot product does not see.
-template <class G, class E>
-__device__ __forceinline__ void consume_stage(uint32_t a_lo, const GroupCtx& gc, int kbyte0,
-                                              int kwarp0, uint32_t wsc, float (&acc)[4]) {
-  const uint32_t a_hi = a_lo + 8 * G::PITCH;
+// One stage on one consumer warp, in three steps so that a caller can interleave several
+// stages (`StageRegs` holds what is in flight).  Lane = 4g + t reads bytes [16t, 16t+16) of
+// each 64-byte run of rows g and g+8 of its sub-tile, and the same bytes of activation row
+// col_row[g].  MMA k-slot 4t+j (resp. 16+4t+j) of the first MMA is byte 16t+j (resp.
+// 16t+4+j) of the run, of the second MMA byte 16t+8+j (resp. 16t+12+j): A and B use the
+// same permutation of K, which a dot product does not see.
+template <class G>
+struct StageRegs {
   uint4 wa[G::RUNS], wb[G::RUNS], xv[G::RUNS];
-#pragma unroll
-  for (int run = 0; run < G::RUNS; ++run) {
-    wa[run] = lds128(a_lo + run * 64);
-    wb[run] = lds128(a_hi + run * 64);
-    xv[run] = make_uint4(0u, 0u, 0u, 0u);
-    if (gc.xb) xv[run] = lds128(gc.xb + kbyte0 + run * 64);
-  }
-  // Every MMA of the stage gets its own accumulator: the tensor pipe's latency is paid
-  // once per stage, not once per dependent MMA.
   float pa[G::RUNS][4], pb[G::RUNS][4];
+};
+
+template <class G>
+__device__ __forceinline__ void stage_load(StageRegs<G>& r, uint32_t a_lo, const GroupCtx& gc,
+                                           int kbyte0) {
+  const uint32_t a_hi = a_lo + 8 * G::PITCH;
+#pragma unroll
+  for (int run = 0; run < G::RUNS; ++run) {
+    r.wa[run] = lds128(a_lo + run * 64);
+    r.wb[run] = lds128(a_hi + run * 64);
+    r.xv[run] = make_uint4(0u, 0u, 0u, 0u);
+    if (gc.xb) r.xv[run] = lds128(gc.xb + kbyte0 + run * 64);
+  }
+}
+
+// Every MMA of the stage gets its own accumulator: the tensor pipe's latency is paid once
+// per stage (or per batch of stages), not once per dependent MMA.
+template <class G, class E>
+__device__ __forceinline__ void stage_mma(StageRegs<G>& r) {
 #pragma unroll
   for (int run = 0; run < G::RUNS; ++run) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { pa[run][i] = 0.f; pb[run][i] = 0.f; }
-    E::mma(pa[run], wa[run].x, wb[run].x, wa[run].y, wb[run].y, xv[run].x, xv[run].y);
-    E::mma(pb[run], wa[run].z, wb[run].z, wa[run].w, wb[run].w, xv[run].z, xv[run].w);
+    for (int i = 0; i < 4; ++i) { r.pa[run][i] = 0.f; r.pb[run][i] = 0.f; }
+    E::mma(r.pa[run], r.wa[run].x, r.wb[run].x, r.wa[run].y, r.wb[run].y, r.xv[run].x, r.xv[run].y);
+    E::mma(r.pb[run], r.wa[run].z, r.wb[run].z, r.wa[run].w, r.wb[run].w, r.xv[run].z, r.xv[run].w);
   }
+}
+
+template <class G, class E>
+__device__ __forceinline__ void stage_fold(const StageRegs<G>& r, const GroupCtx& gc, int kbyte0,
+                                           int kwarp0, uint32_t wsc, float (&acc)[4]) {
 #pragma unroll
   for (int run = 0; run < G::RUNS; ++run) {
     float s0 = gc.m0, s1 = gc.m1;
@@ -606,10 +635,10 @@ __device__ __forceinline__ void consume_stage(uint32_t a_lo, const GroupCtx& gc,
       s0 *= ws * lds_f32(gc.xs0 + xblk * 4);
       s1 *= ws * lds_f32(gc.xs1 + xblk * 4);
     }
-    acc[0] = fmaf(pa[run][0] + pb[run][0], s0, acc[0]);
-    acc[1] = fmaf(pa[run][1] + pb[run][1], s1, acc[1]);
-    acc[2] = fmaf(pa[run][2] + pb[run][2], s0, acc[2]);
-    acc[3] = fmaf(pa[run][3] + pb[run][3], s1, acc[3]);
+    acc[0] = fmaf(r.pa[run][0] + r.pb[run][0], s0, acc[0]);
+    acc[1] = fmaf(r.pa[run][1] + r.pb[run][1], s1, acc[1]);
+    acc[2] = fmaf(r.pa[run][2] + r.pb[run][2], s0, acc[2]);
+    acc[3] = fmaf(r.pa[run][3] + r.pb[run][3], s1, acc[3]);
   }
 }
 
@@ -618,15 +647,58 @@ struct TileId {
   int tile, group, tig;
 };
 
-// Consumers: up to sixteen warps per SM (four per scheduler: the per-stage path is a latency
-// chain, so thread-level parallelism is what keeps the SM ahead of the stream).  At the end of a
-// tile each warp drops its fragment into `red[i]` and moves on; the epilogue warp folds
-// the fragments.
+// Stages a consumer warp works on together.  The path of one stage is a chain of
+// latencies (barrier test, shared loads, MMA, scale, release) a few hundred cycles long,
+// and a half-SM CTA has only two warps per scheduler to hide it behind: with several
+// stages in flight the chain is paid once per batch.  Bounded by registers (twelve per
+// run and stage in flight).  The fold order is the stage order, whatever the batch.
+template <class G>
+constexpr int stage_batch() {
+#ifdef IQ_STAGE_BATCH
+  return IQ_STAGE_BATCH;
+#else
+  return 1;   // (two stages of two runs in flight spilled registers at the 96 a half-SM CTA
+              // may use, and ran half as fast: measured)
+#endif
+}
+
+// Consumers: up to sixteen warps per SM.  At the end of a tile each warp drops its fragment
+// into `red[i]` and moves on; the epilogue warp folds the fragments.
+//
+// `head` (optional): the walk through the CTA's share and the first tile's group context,
+// worked out by `consume_head` beforehand.  A kernel whose activations come from its
+// predecessor calls that BEFORE its dependency wait: the index arithmetic then runs while
+// the predecessor is still finishing instead of between the wait and the first stage.
+template <class G>
+struct ConsumeHead {
+  TileWalk walk;
+  TileVisit tv;
+  StagePos p;
+  GroupCtx gc;
+};
+template <class G>
+__device__ __forceinline__ ConsumeHead<G> consume_head(const StreamShape& sh,
+                                                       const GroupDesc* groups,
+                                                       const uint8_t* xq, const float* xs,
+                                                       const CtaWork& w) {
+  ConsumeHead<G> h;
+  h.walk.init(w);
+  h.tv = h.walk.visit(w, 0);
+  h.p = stage_pos(sh, w, h.tv.tile, h.tv.s_begin);
+  h.gc = GroupCtx{};
+  if (h.walk.n_tiles > 0)
+    h.gc = group_ctx<G>(sh, groups[h.p.group], smem_u32(xq), smem_u32(xs), threadIdx.x >> 5,
+                        threadIdx.x & 31);
+  return h;
+}
+
 template <class G, class E, class S>
 __device__ __forceinline__ void consume(const StreamShape& sh, S* sm, const GroupDesc* groups,
                                         const uint8_t* ring, int slot_bytes, const uint8_t* xq,
                                         const float* xs, const float* sc, const CtaWork& w,
-                                        const StreamScratch& scr, RingPos& pos, RedPos& rpos) {
+                                        const StreamScratch& scr, RingPos& pos, RedPos& rpos,
+                                        const ConsumeHead<G>* head = nullptr) {
+  constexpr int B = stage_batch<G>();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int rs = warp / G::KW, kp = warp - rs * G::KW;
@@ -641,34 +713,78 @@ __device__ __forceinline__ void consume(const StreamShape& sh, S* sm, const Grou
   const uint32_t sc_s = smem_u32(sc) + warp * G::RUNS * 4;
   const uint32_t ring_s = smem_u32(ring), xq_s = smem_u32(xq), xs_s = smem_u32(xs);
   TileWalk walk;
-  walk.init(w);
+  if (head) walk = head->walk;
+  else walk.init(w);
   for (int k = 0; k < walk.n_tiles; ++k) {
-    const TileVisit tv = walk.visit(w, k);
+    const bool from_head = head && k == 0;
+    const TileVisit tv = from_head ? head->tv : walk.visit(w, k);
     uint32_t wsc = sc_s + tv.local0 * (G::SCALES_PER_STAGE * 4);
     int s = tv.s_begin;
     const int s_end = tv.s_end;
-    StagePos p = stage_pos(sh, w, tv.tile, s);
-    // ---- stages [s_begin, s_end) of this tile, group by group
+    StagePos p = from_head ? head->p : stage_pos(sh, w, tv.tile, s);
+    GroupCtx cur = from_head ? head->gc : group_ctx<G>(sh, groups[p.group], xq_s, xs_s, warp, lane);
+    // ---- stages [s_begin, s_end) of this tile, up to B at a time
     while (s < s_end) {
-      const GroupCtx gc = group_ctx<G>(sh, groups[p.group], xq_s, xs_s, warp, lane);
-      int ks_end = w.kstages;
-      if (s_end - s < ks_end - p.kstage) ks_end = p.kstage + (s_end - s);
-      for (int ks = p.kstage; ks < ks_end; ++ks, ++s) {
-        if (!mbar_wait(&sm->full[slot], phase, &sm->abort_flag)) {
-          if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
-          sm->abort_flag = 1;
-          return;
+      int nb = s_end - s < B ? s_end - s : B;
+      if (nb > sh.n_stages) nb = sh.n_stages;     // (a batch is filled before any of it is released)
+      GroupCtx gc[B];
+      int kb[B];
+      uint32_t a_lo[B];
+      int bslot[B];
+      uint32_t bphase[B];
+      // which group and k-stage each stage of the batch belongs to (kConcatK: a new group
+      // every `kstages` stages)
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        gc[b] = cur;
+        kb[b] = p.kstage * G::KC;
+        bslot[b] = slot;
+        bphase[b] = phase;
+        a_lo[b] = ring_s + slot * slot_bytes + a_off;
+        if (b < nb) {
+          if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
+          if (++p.kstage == w.kstages) {
+            p.kstage = 0;
+            ++p.group;
+            if (s + b + 1 < s_end)
+              cur = group_ctx<G>(sh, groups[p.group], xq_s, xs_s, warp, lane);
+          }
         }
-        if (tid == 0 && k == 0 && s == tv.s_begin) trace_stamp(scr, 6);
-        consume_stage<G, E>(ring_s + slot * slot_bytes + a_off, gc, ks * G::KC, kwarp0, wsc, acc);
-        __syncwarp();
-        if (tid == 0 && k == 0 && s == tv.s_begin) trace_stamp(scr, 7);
-        if (lane == 0) mbar_arrive(&sm->empty[slot]);
-        if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
-        wsc += G::SCALES_PER_STAGE * 4;
       }
-      p.kstage = 0;
-      ++p.group;        // kConcatK: next group's K; kRowsPerGroup: loop ends here
+      StageRegs<G> regs[B];
+      if (tid == 0 && k == 0 && s == tv.s_begin) trace_clock(scr, 0);
+      if (tid == 0 && k == 0 && s == tv.s_begin + nb) trace_clock(scr, 3);
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        if (b < nb) {
+          if (!mbar_wait(&sm->full[bslot[b]], bphase[b], &sm->abort_flag)) {
+            if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+            sm->abort_flag = 1;
+            return;
+          }
+        }
+      }
+      if (tid == 0 && k == 0 && s == tv.s_begin) { trace_stamp(scr, 6); trace_clock(scr, 1); }
+      if (tid == 0 && k == 0 && s == tv.s_begin + nb) trace_clock(scr, 4);
+#pragma unroll
+      for (int b = 0; b < B; ++b)
+        if (b < nb) stage_load<G>(regs[b], a_lo[b], gc[b], kb[b]);
+#pragma unroll
+      for (int b = 0; b < B; ++b)
+        if (b < nb) stage_mma<G, E>(regs[b]);
+#pragma unroll
+      for (int b = 0; b < B; ++b)
+        if (b < nb) stage_fold<G, E>(regs[b], gc[b], kb[b], kwarp0, wsc + b * (G::SCALES_PER_STAGE * 4), acc);
+      __syncwarp();
+      if (tid == 0 && k == 0 && s == tv.s_begin) { trace_stamp(scr, 7); trace_clock(scr, 2); }
+      if (tid == 0 && k == 0 && s == tv.s_begin + nb) trace_clock(scr, 5);
+      if (lane == 0) {
+#pragma unroll
+        for (int b = 0; b < B; ++b)
+          if (b < nb) mbar_arrive(&sm->empty[bslot[b]]);
+      }
+      wsc += nb * (G::SCALES_PER_STAGE * 4);
+      s += nb;
     }
 
     // ---- the CTA's share of this tile is complete: hand the warp's partial to the
@@ -683,7 +799,7 @@ __device__ __forceinline__ void consume(const StreamShape& sh, S* sm, const Grou
     for (int i = 0; i < 4; ++i) { red[warp][lane][i] = acc[i]; acc[i] = 0.f; }
     __syncwarp();
     if (lane == 0) mbar_arrive(&sm->red_full[red_buf]);
-    if (tid == 0 && k == 0) trace_stamp(scr, 8);
+    if (tid == 0 && k == 0) { trace_stamp(scr, 8); trace_clock(scr, 6); }
     if (++red_buf == 2) { red_buf = 0; red_phase ^= 1u; }
   }
   pos.slot = slot;
@@ -695,10 +811,11 @@ template <class G, class E>
 __device__ __forceinline__ void consume(const StreamShape& sh, StreamSmem<G>* sm,
                                         const uint8_t* ring, const uint8_t* xq, const float* xs,
                                         const float* sc, const CtaWork& w,
-                                        const StreamScratch& scr) {
+                                        const StreamScratch& scr,
+                                        const ConsumeHead<G>* head = nullptr) {
   RingPos pos;
   RedPos rpos;
-  consume<G, E>(sh, sm, sm->groups, ring, G::STAGE_BYTES, xq, xs, sc, w, scr, pos, rpos);
+  consume<G, E>(sh, sm, sm->groups, ring, G::STAGE_BYTES, xq, xs, sc, w, scr, pos, rpos, head);
 }
 
 // The epilogue warp: for every tile of the CTA, in order, folds the consumers' fragments
