@@ -709,55 +709,30 @@ __host__ __device__ inline size_t tail_park_bytes(int h, int residual_fp32) {
 // index + n_tail, ...  The last tail CTA to finish closes the call (the zone's epoch moves
 // on once every tail CTA has read it).
 //
-// A tail CTA has nothing to do until its rows arrive, and its code runs once per launch:
-// fetched cold from L2 it was measured at about 18 cycles per instruction (11 us for one
-// pass through the tail of a 6144-wide row, against 2.4 us with the instructions at hand).
-// So its 256 working threads REHEARSE: the same instructions on whatever the buffers hold,
-// nothing awaited, not a single global store (`warm`, see run_tail), pass after pass, until
-// the launch's dependency has resolved -- which one further thread (the "watcher", thread
-// 256, present in every streaming kernel's CTA) finds out by executing the dependency
-// wait itself and raising a flag in shared memory.  Then the working threads pass the wait
-// too (it returns at once) and make the real pass with the code still warm.  Instructions
-// fetched by a single rehearsal at the CTA's start were found half gone ten microseconds
-// later; a rehearsal placed after the wait finished too late for the rows.
-// A launch without a spare thread (the tail kernel) rehearses once, ahead of the wait.
+// A tail CTA has nothing to do until its rows arrive, and its code runs once per launch.
+// With one row it first makes a REHEARSAL pass ahead of the dependency wait: the same
+// instructions on whatever the buffers hold, nothing awaited, not a single global store
+// (`warm`, see run_tail), which brings the instructions in.  Measured on the layer of one
+// row (hidden 6144, one rank's shard of eight): 45.9 us with the rehearsal, 47.2 us
+// without, 47.5 us when the pass was repeated until the dependency resolved (the
+// rehearsing CTA takes issue slots from the streaming CTA it shares its SM with), 49.7 us
+// when it was made after the wait (it then ends after the rows have arrived).  With
+// several rows (several tail CTAs) the rehearsal did not pay (71.0 us without, 72.2 with)
+// and is left out.
 __device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& pv, int per_round,
                                          int index, int n_tail, uint8_t* smem) {
   float* red = reinterpret_cast<float*>(smem);
   int* sflag = reinterpret_cast<int*>(smem + 512);
   uint32_t* word = reinterpret_cast<uint32_t*>(smem + 516);     // [epoch, closes the call]
-  volatile int* released = reinterpret_cast<volatile int*>(smem + 524);
-  volatile int* decided = reinterpret_cast<volatile int*>(smem + 528);
   uint8_t* park = smem + 1024;
   uint32_t* zs = reinterpret_cast<uint32_t*>(smem + 1024 + tail_park_bytes(a.h, a.residual_fp32));
   const int tid = threadIdx.x;
-#ifndef IQ_REHEARSE_MODE
-#define IQ_REHEARSE_MODE 2
-#endif
-  const bool watched = IQ_REHEARSE_MODE >= 2 && blockDim.x > kTailThreads;
-  if (tid == 0) { *released = 0; *sflag = 1; }
-  __syncthreads();
-  if (tid >= kTailThreads) {
-    if (watched && tid == kTailThreads) {
-      after_wait();
-      *released = 1;
-    }
-    return;
-  }
+  if (tid >= kTailThreads) return;       // (the tail runs on 256 threads: see kTailThreads)
   const BlockBar bar{2, kTailThreads};
-  // Every pass goes through ONE copy of the tail's code.
+  // Both passes go through ONE copy of the tail's code.
 #pragma unroll 1
-  for (int pass = 0;; ++pass) {
-    bool warm;
-    if (watched) {
-      if (IQ_REHEARSE_MODE == 3 && pass > 0) nanosleep_ns(1500);
-      if (tid == 0) *decided = *released;
-      bar.sync();
-      warm = *decided == 0;
-    } else {
-      warm = pass == 0;
-      if (IQ_REHEARSE_MODE == 0 && warm) continue;
-    }
+  for (int pass = n_tail == 1 ? 0 : 1; pass < 2; ++pass) {
+    const bool warm = pass == 0;
     if (!warm) {
       after_wait();
       if (tid == 0 && pv.trace) { pv.trace[9] = globaltimer_ns(); pv.trace[16 + 11] = clock64(); }
@@ -787,7 +762,6 @@ __device__ __forceinline__ void tail_cta(const iq_tail_args& a, const PushView& 
                    warm);
     if (tid == 0 && word[1]) *pv.epoch = epoch + 1u;
     bar.sync();
-    if (!warm) break;
   }
 }
 
@@ -1133,36 +1107,15 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) router_kerne
 #endif
   }
   if (cta == stream_ctas) {
-    // ---- the selecting CTA.  Its code runs once per launch, on the launch's critical path:
-    // like a tail CTA (see tail_cta) its working threads rehearse it -- words taken as they
-    // are, nothing stored -- until thread 256, which executes the dependency wait, raises
-    // the flag; then they make the launch's own selection with the instructions at hand.
+    // ---- the selecting CTA.  With one row, two passes through one copy of its code: a
+    // rehearsal ahead of the dependency wait (words taken as they are, nothing stored) that
+    // brings the instructions in, then the launch's own selection (see tail_cta).
     float* lg = reinterpret_cast<float*>(smem);          // [m][e]
-    volatile int* released = reinterpret_cast<volatile int*>(lg + p.m * p.e);
-    volatile int* decided = released + 1;
-    if (tid == 0) *released = 0;
-    __syncthreads();
-    const bool watched = IQ_REHEARSE_MODE >= 2;
-    if (tid >= 256) {
-      if (watched && tid == 256) {
-        after_wait();
-        *released = 1;
-      }
-      return;
-    }
+    if (tid >= 256) return;                              // (one warp per row, eight at most)
     const BlockBar bar{2, 256};
 #pragma unroll 1
-    for (int pass = 0;; ++pass) {
-      bool warm;
-      if (watched) {
-        if (IQ_REHEARSE_MODE == 3 && pass > 0) nanosleep_ns(1500);
-        if (tid == 0) *decided = *released;
-        bar.sync();
-        warm = *decided == 0;
-      } else {
-        warm = pass == 0;
-        if (IQ_REHEARSE_MODE == 0 && warm) continue;
-      }
+    for (int pass = p.m == 1 ? 0 : 1; pass < 2; ++pass) {
+      const bool warm = pass == 0;
       if (!warm) {
         after_wait();
         if (tid == 0) { IQ_STAMP(p, 9); IQ_CLOCK(p, 7); }
@@ -1210,19 +1163,20 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) router_kerne
         __syncwarp();
         if (tid == 0 && !warm) { IQ_STAMP(p, 10); IQ_CLOCK(p, 8); }
         if (ok) {
-          if (!warm)
-            for (int id = lane; id < p.e; id += 32)
-              p.logits[static_cast<size_t>(warp) * p.e + id] = lg[warp * p.e + id];
           if (tid == 0 && !warm) IQ_CLOCK(p, 9);
           select_row(lg, p.e, p.top_k, p.score, warp, p.sel, p.wt, true, !warm);
           if (tid == 0 && !warm) IQ_CLOCK(p, 10);
+          // (the plain logits are for the caller: after the routes, which the next kernel
+          // is waiting for)
+          if (!warm)
+            for (int id = lane; id < p.e; id += 32)
+              p.logits[static_cast<size_t>(warp) * p.e + id] = lg[warp * p.e + id];
         } else if (lane == 0) {
           set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
         }
       }
       bar.sync();
       if (tid == 0 && !warm) *launch_tag = tag;
-      if (!warm) break;
     }
     if (tid == 0) { IQ_STAMP(p, 11); IQ_CLOCK(p, 11); }
     return;
@@ -2317,7 +2271,9 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
       const int ctas = std::max(1, sm_count() - (a->tail || a->push ? a->m : 0));
       const int most16 = (n / 16 + ctas - 1) / ctas * 16;
       const int most48 = (n / 48 + ctas - 1) / ctas * 48;
-      if (most48 <= most16) rc = linear_launch<Geo<3, 2, 2, 3>>(a, stream);
+      static const bool runs4 = env_number("IQB200_LINEAR_RUNS4", 0) != 0;
+      if (most48 <= most16 && runs4 && k % 512 == 0) rc = linear_launch<Geo<3, 2, 4, 3>>(a, stream);
+      if (most48 <= most16 && rc == IQ_ERR_UNSUPPORTED) rc = linear_launch<Geo<3, 2, 2, 3>>(a, stream);
     }
     if (rc != IQ_ERR_UNSUPPORTED) return rc;
     if (k % 1024 == 0 && n % 16 == 0) rc = linear_launch<Geo<1, 8, 2, 3>>(a, stream);
@@ -2379,8 +2335,9 @@ static int router_launch(const iq_router_args* a, void* stream) {
   // slice a whole number of stages).
   const int row_tiles = (a->e + G::ROWS - 1) / G::ROWS;
   const int row_stages = a->h * 2 / G::KC;
+  static const int max_slices = static_cast<int>(env_number("IQB200_ROUTER_SLICES", kMaxKSlices));
   int k_slices = 1;
-  for (int ks = 2; ks <= kMaxKSlices; ++ks)
+  for (int ks = 2; ks <= kMaxKSlices && ks <= max_slices; ++ks)
     if (row_stages % ks == 0 && row_tiles * ks + 1 <= sm_count()) k_slices = ks;
   if (row_tiles + 1 > sm_count()) return IQ_ERR_UNSUPPORTED;
   sh.whole_tiles = 2;
@@ -2400,8 +2357,7 @@ static int router_launch(const iq_router_args* a, void* stream) {
   // (the ring holds a CTA's whole tile: it is in shared memory before the dependency wait
   // returns)
   const size_t tile_bytes = static_cast<size_t>(G::ROWS) * sh.k_bytes;
-  const size_t smem =
-      plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e + 16, k_slices, tile_bytes);
+  const size_t smem = plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e, k_slices, tile_bytes);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   p.k_slices = k_slices;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->e, nullptr, 0);
@@ -2536,7 +2492,10 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   const long long bytes = expert_stream_bytes(a->m, a->top_k, a->n_experts, a->n_shared,
                                               2ll * a->i_loc * a->h);
   if (bytes <= short_stream_bytes()) {
-    const int rc = gate_launch<Geo<2, 4, 2, 3>>(a, stream);
+    static const bool runs3 = env_number("IQB200_GATE_RUNS3", 0) != 0;
+    int rc = IQ_ERR_UNSUPPORTED;
+    if (runs3 && a->h % 768 == 0) rc = gate_launch<Geo<2, 4, 3, 3>>(a, stream);
+    if (rc == IQ_ERR_UNSUPPORTED) rc = gate_launch<Geo<2, 4, 2, 3>>(a, stream);
     if (rc != IQ_ERR_UNSUPPORTED) return rc;
   }
   return gate_launch<Geo<2, 8, 2>>(a, stream);

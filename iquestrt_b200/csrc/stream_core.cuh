@@ -69,8 +69,8 @@ struct Geo {
   static constexpr int WARPS = RT * KW;                 // consumer warps
   static_assert(WARPS == 6 || WARPS == 8 || WARPS == 16, "6, 8 or 16 consumer warps");
   static constexpr int CONSUMER_THREADS = WARPS * 32;
-  // + the producer warp + the epilogue warp; never fewer than ten warps: a tail CTA of the
-  // launch needs 256 working threads and one more that watches the dependency (see tail_cta)
+  // + the producer warp + the epilogue warp; never fewer than ten warps, so that every
+  // half-SM kernel asks the register file for the same shape (see below)
   static constexpr int THREADS = CONSUMER_THREADS + 64 < 320 ? 320 : CONSUMER_THREADS + 64;
   static constexpr int PRODUCER_WARP = WARPS;
   static constexpr int EPILOGUE_WARP = WARPS + 1;
