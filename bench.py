@@ -303,6 +303,63 @@ def dram_traffic(kernel, tp, rows):
         return None
 
 
+def prologue_probe(torch, stream, shape, rows, tp, dev, n_probe=32):
+    """us per call of `PrologueKernels.call_prenorm` (QKV product over this rank's heads, 64 q
+    and 8 kv heads of 128 channels shared out over `tp`, then q/k RMSNorm, partial rotary
+    embedding and the e4m3 KV-cache write) in a PDL chain of `n_probe` calls per graph, the
+    QKV weights rotating over enough copies to stay out of L2."""
+    import math
+    from iquestrt_b200 import ops, synth
+    from iquestrt_b200.kernels import PrologueKernels
+    from iquestrt_b200.workspace import Workspace
+    if 64 % tp or 8 % tp:
+        return None
+    hidden, d, rot = shape.hidden, 128, 32
+    qh, kh = 64 // tp, 8 // tp
+    n_qkv = (qh + 2 * kh) * d
+    ws = Workspace(device=dev)
+    pro = PrologueKernels(hidden, qh, kh, d, rot, 1e-6, ws=ws, q_len=rows)
+    ws.freeze()
+    g = synth._gen(dev, 11, rows, tp)
+    copies = max(2, int(300e6 // (n_qkv * hidden)) + 1)
+    w = [synth.fp8_weight(n_qkv, hidden, g, dev) for _ in range(copies)]
+    wsc = [synth.block_scales(n_qkv, hidden, g, dev) for _ in range(copies)]
+    xn = torch.randn(rows, hidden, generator=g, device=dev).bfloat16()
+    w_qn = 0.5 + torch.rand(d, generator=g, device=dev)
+    w_kn = 0.5 + torch.rand(d, generator=g, device=dev)
+    pos = torch.arange(rows, dtype=torch.float32) + 32000.0
+    inv = 10000.0 ** (-torch.arange(0, rot, 2, dtype=torch.float32) / rot)
+    ang = torch.cat([pos[:, None] * inv[None, :]] * 2, dim=-1)
+    cos, sin = ang.cos().bfloat16().to(dev), ang.sin().bfloat16().to(dev)
+    kc = torch.zeros(4096, kh, d, dtype=torch.float8_e4m3fn, device=dev)
+    vc = torch.zeros_like(kc)
+    slot = torch.arange(100, 100 + rows, dtype=torch.int64, device=dev)
+
+    def call(i):
+        pro.call_prenorm(xn, w[i % copies], wsc[i % copies], w_qn, w_kn, cos, sin, slot, kc, vc,
+                         pdl=True)
+    with torch.cuda.stream(stream):
+        for i in range(2):
+            call(i)
+        stream.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=stream):
+            for i in range(n_probe):
+                call(i)
+        gr.replay()
+        stream.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
+        ev[0].record(stream)
+        for j in range(6):
+            gr.replay()
+            ev[j + 1].record(stream)
+        stream.synchronize()
+    ops.default_scratch(dev).raise_on_error()
+    ms = sorted(ev[j].elapsed_time(ev[j + 1]) / n_probe for j in range(1, 6))
+    return {"qkv_heads": ms[len(ms) // 2] * 1e3, "unit": "us per call (2 launches)",
+            "qkv_bytes": n_qkv * hidden, "q_heads": qh, "kv_heads": kh, "weight_copies": copies}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -453,6 +510,11 @@ def run_ours(args):
             kern_ms[name] = [ev[j].elapsed_time(ev[j + 1]) / n_probe for j in range(1, 6)]
             layer.check()
 
+        # ---- the attention prologue of the same rank (the next row of the scope table on
+        # the input side of the path: column-parallel QKV product + heads step), timed the
+        # same way.  Not part of `value`: the layer above starts at the attention output.
+        prologue_us = prologue_probe(torch, stream, shape, rows, shard_of or tp, dev)
+
         # distinct routed experts per step (1 row -> top_k)
         distinct = shape.top_k if rows == 1 else len(set(layer.router.sel.cpu().tolist()))
 
@@ -522,6 +584,7 @@ def run_ours(args):
                                "router": frac["router"], "unit": "fraction of the HBM peak",
                                "bytes": {k: by[k] for k in ("oproj_tail", "down_tail", "router")}},
             "kernel_us": {k: v * 1e3 for k, v in med.items()},
+            "prologue_us": prologue_us,
             "layer_bytes": by["total"],
             "tokens_per_s_per_layer": rows / (us * 1e-6),
             "spread_us": {"passes": passes - 1, "min": min_ms * 1e3 / K,

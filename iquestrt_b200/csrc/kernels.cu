@@ -1121,48 +1121,57 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) router_kerne
         if (tid == 0) { IQ_STAMP(p, 9); IQ_CLOCK(p, 7); }
       }
       const uint32_t tag = warm ? 0u : ld_volatile_u32(launch_tag) + 1u;
-      if (warp < p.m) {
-        const int per = (p.e + 31) / 32;                   // <= 16
-        uint32_t pend = (1u << per) - 1u;
-        uint64_t t0 = 0;
-        bool ok = true;
+      // Polling: the rows' experts are cut into chunks of 32 (one expert per lane) and the
+      // chunks dealt over the eight warps, so that a lane has only its expert's K slices in
+      // flight and the whole table costs one round trip to L2 per pass when there are no
+      // more chunks than warps (one row of 256 experts), not one per group of 32 experts.
+      volatile int* failed = reinterpret_cast<volatile int*>(lg + p.m * p.e);
+      if (tid == 0) *failed = 0;
+      bar.sync();
+      {
+        const int chunks = (p.e + 31) / 32;
+        const int items = p.m * chunks;
         const size_t slice_stride = static_cast<size_t>(kMaxRows) * p.e;
-        while (true) {
-          for (int j = 0; j < per; ++j) {
-            const int id = lane + 32 * j;
-            if (!((pend >> j) & 1u) || id >= p.e) { pend &= ~(1u << j); continue; }
-            const uint64_t* src = tagged + static_cast<size_t>(warp) * p.e + id;
-            uint32_t val[kMaxKSlices], seen[kMaxKSlices];
+        for (int it = warp; it < items; it += 8) {
+          const int row = it / chunks, id = (it - row * chunks) * 32 + lane;
+          const uint64_t* src = tagged + static_cast<size_t>(row) * p.e + id;
+          uint64_t t0 = 0;
+          bool done = id >= p.e;
+          float sum = 0.f;
+          while (true) {
+            if (!done) {
+              uint32_t val[kMaxKSlices], seen[kMaxKSlices];
 #pragma unroll
-            for (int ks = 0; ks < kMaxKSlices; ++ks) {
-              val[ks] = 0u;                                   // (+0 beyond k_slices)
-              seen[ks] = tag;
-              if (ks < p.k_slices) {
-                const uint64_t wv = ld_relaxed_gpu_u64(src + ks * slice_stride);
-                val[ks] = static_cast<uint32_t>(wv);
-                seen[ks] = static_cast<uint32_t>(wv >> 32);
+              for (int ks = 0; ks < kMaxKSlices; ++ks) {
+                val[ks] = 0u;                                   // (+0 beyond k_slices)
+                seen[ks] = tag;
+                if (ks < p.k_slices) {
+                  const uint64_t wv = ld_relaxed_gpu_u64(src + ks * slice_stride);
+                  val[ks] = static_cast<uint32_t>(wv);
+                  seen[ks] = static_cast<uint32_t>(wv >> 32);
+                }
               }
-            }
-            bool all = true;
-            float sum = 0.f;
+              bool all = true;
+              sum = 0.f;
 #pragma unroll
-            for (int ks = 0; ks < kMaxKSlices; ++ks) {
-              all = all && seen[ks] == tag;
-              sum += __uint_as_float(val[ks]);
+              for (int ks = 0; ks < kMaxKSlices; ++ks) {
+                all = all && seen[ks] == tag;
+                sum += __uint_as_float(val[ks]);
+              }
+              done = warm || all;
             }
-            if (warm || all) {
-              lg[warp * p.e + id] = sum;
-              pend &= ~(1u << j);
-            }
+            if (__all_sync(0xffffffffu, done)) break;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kPipeBudgetNs) { *failed = 1; break; }
           }
-          if (__all_sync(0xffffffffu, pend == 0u)) break;
-          const uint64_t now = globaltimer_ns();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > kPipeBudgetNs) { ok = false; break; }
+          if (id < p.e) lg[row * p.e + id] = sum;
         }
-        __syncwarp();
-        if (tid == 0 && !warm) { IQ_STAMP(p, 10); IQ_CLOCK(p, 8); }
-        if (ok) {
+      }
+      bar.sync();
+      if (tid == 0 && !warm) { IQ_STAMP(p, 10); IQ_CLOCK(p, 8); }
+      if (warp < p.m) {
+        if (*failed == 0) {
           if (tid == 0 && !warm) IQ_CLOCK(p, 9);
           select_row(lg, p.e, p.top_k, p.score, warp, p.sel, p.wt, true, !warm);
           if (tid == 0 && !warm) IQ_CLOCK(p, 10);
@@ -2357,7 +2366,8 @@ static int router_launch(const iq_router_args* a, void* stream) {
   // (the ring holds a CTA's whole tile: it is in shared memory before the dependency wait
   // returns)
   const size_t tile_bytes = static_cast<size_t>(G::ROWS) * sh.k_bytes;
-  const size_t smem = plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e, k_slices, tile_bytes);
+  const size_t smem =
+      plan_smem<G>(sh, grid - 1, sizeof(float) * a->m * a->e + 16, k_slices, tile_bytes);
   if (smem == 0) return IQ_ERR_UNSUPPORTED;
   p.k_slices = k_slices;
   const int mrc = fill_maps<G>(&p.map0, &p.map1, sh, a->w, a->e, nullptr, 0);

@@ -647,28 +647,10 @@ struct TileId {
   int tile, group, tig;
 };
 
-// Stages a consumer warp works on together.  The path of one stage is a chain of
-// latencies (barrier test, shared loads, MMA, scale, release) a few hundred cycles long,
-// and a half-SM CTA has only two warps per scheduler to hide it behind: with several
-// stages in flight the chain is paid once per batch.  Bounded by registers (twelve per
-// run and stage in flight).  The fold order is the stage order, whatever the batch.
-template <class G>
-constexpr int stage_batch() {
-#ifdef IQ_STAGE_BATCH
-  return IQ_STAGE_BATCH;
-#else
-  return 1;   // (two stages of two runs in flight spilled registers at the 96 a half-SM CTA
-              // may use, and ran half as fast: measured)
-#endif
-}
-
-// Consumers: up to sixteen warps per SM.  At the end of a tile each warp drops its fragment
-// into `red[i]` and moves on; the epilogue warp folds the fragments.
-//
-// `head` (optional): the walk through the CTA's share and the first tile's group context,
-// worked out by `consume_head` beforehand.  A kernel whose activations come from its
-// predecessor calls that BEFORE its dependency wait: the index arithmetic then runs while
-// the predecessor is still finishing instead of between the wait and the first stage.
+// The walk through the CTA's share and the first tile's group context, worked out by
+// `consume_head` beforehand.  A kernel whose activations come from its predecessor calls
+// that BEFORE its dependency wait: the index arithmetic then runs while the predecessor is
+// still finishing instead of between the wait and the first stage.
 template <class G>
 struct ConsumeHead {
   TileWalk walk;
@@ -692,13 +674,17 @@ __device__ __forceinline__ ConsumeHead<G> consume_head(const StreamShape& sh,
   return h;
 }
 
+// Consumers: up to sixteen warps per SM (four per scheduler: the per-stage path is a latency
+// chain, so thread-level parallelism is what keeps the SM ahead of the stream).  At the end of a
+// tile each warp drops its fragment into `red[i]` and moves on; the epilogue warp folds
+// the fragments.  (Two stages in flight per warp were tried: at the 96 registers a
+// half-SM CTA may use they spilled, and the layer ran half as fast.)
 template <class G, class E, class S>
 __device__ __forceinline__ void consume(const StreamShape& sh, S* sm, const GroupDesc* groups,
                                         const uint8_t* ring, int slot_bytes, const uint8_t* xq,
                                         const float* xs, const float* sc, const CtaWork& w,
                                         const StreamScratch& scr, RingPos& pos, RedPos& rpos,
                                         const ConsumeHead<G>* head = nullptr) {
-  constexpr int B = stage_batch<G>();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int rs = warp / G::KW, kp = warp - rs * G::KW;
@@ -722,69 +708,38 @@ __device__ __forceinline__ void consume(const StreamShape& sh, S* sm, const Grou
     int s = tv.s_begin;
     const int s_end = tv.s_end;
     StagePos p = from_head ? head->p : stage_pos(sh, w, tv.tile, s);
-    GroupCtx cur = from_head ? head->gc : group_ctx<G>(sh, groups[p.group], xq_s, xs_s, warp, lane);
-    // ---- stages [s_begin, s_end) of this tile, up to B at a time
+    bool first_group = true;
+    // ---- stages [s_begin, s_end) of this tile, group by group
     while (s < s_end) {
-      int nb = s_end - s < B ? s_end - s : B;
-      if (nb > sh.n_stages) nb = sh.n_stages;     // (a batch is filled before any of it is released)
-      GroupCtx gc[B];
-      int kb[B];
-      uint32_t a_lo[B];
-      int bslot[B];
-      uint32_t bphase[B];
-      // which group and k-stage each stage of the batch belongs to (kConcatK: a new group
-      // every `kstages` stages)
-#pragma unroll
-      for (int b = 0; b < B; ++b) {
-        gc[b] = cur;
-        kb[b] = p.kstage * G::KC;
-        bslot[b] = slot;
-        bphase[b] = phase;
-        a_lo[b] = ring_s + slot * slot_bytes + a_off;
-        if (b < nb) {
-          if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
-          if (++p.kstage == w.kstages) {
-            p.kstage = 0;
-            ++p.group;
-            if (s + b + 1 < s_end)
-              cur = group_ctx<G>(sh, groups[p.group], xq_s, xs_s, warp, lane);
-          }
+      const GroupCtx gc = (from_head && first_group)
+                              ? head->gc
+                              : group_ctx<G>(sh, groups[p.group], xq_s, xs_s, warp, lane);
+      first_group = false;
+      int ks_end = w.kstages;
+      if (s_end - s < ks_end - p.kstage) ks_end = p.kstage + (s_end - s);
+      for (int ks = p.kstage; ks < ks_end; ++ks, ++s) {
+        if (tid == 0 && k == 0 && s == tv.s_begin) trace_clock(scr, 0);
+        if (tid == 0 && k == 0 && s == tv.s_begin + 1) trace_clock(scr, 3);
+        if (!mbar_wait(&sm->full[slot], phase, &sm->abort_flag)) {
+          if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
+          sm->abort_flag = 1;
+          return;
         }
+        if (tid == 0 && k == 0 && s == tv.s_begin) { trace_stamp(scr, 6); trace_clock(scr, 1); }
+        if (tid == 0 && k == 0 && s == tv.s_begin + 1) trace_clock(scr, 4);
+        StageRegs<G> regs;
+        stage_load<G>(regs, ring_s + slot * slot_bytes + a_off, gc, ks * G::KC);
+        stage_mma<G, E>(regs);
+        stage_fold<G, E>(regs, gc, ks * G::KC, kwarp0, wsc, acc);
+        __syncwarp();
+        if (tid == 0 && k == 0 && s == tv.s_begin) { trace_stamp(scr, 7); trace_clock(scr, 2); }
+        if (tid == 0 && k == 0 && s == tv.s_begin + 1) trace_clock(scr, 5);
+        if (lane == 0) mbar_arrive(&sm->empty[slot]);
+        if (++slot == sh.n_stages) { slot = 0; phase ^= 1u; }
+        wsc += G::SCALES_PER_STAGE * 4;
       }
-      StageRegs<G> regs[B];
-      if (tid == 0 && k == 0 && s == tv.s_begin) trace_clock(scr, 0);
-      if (tid == 0 && k == 0 && s == tv.s_begin + nb) trace_clock(scr, 3);
-#pragma unroll
-      for (int b = 0; b < B; ++b) {
-        if (b < nb) {
-          if (!mbar_wait(&sm->full[bslot[b]], bphase[b], &sm->abort_flag)) {
-            if (!sm->abort_flag) set_status(scr.status, IQ_ERR_PIPE_TIMEOUT);
-            sm->abort_flag = 1;
-            return;
-          }
-        }
-      }
-      if (tid == 0 && k == 0 && s == tv.s_begin) { trace_stamp(scr, 6); trace_clock(scr, 1); }
-      if (tid == 0 && k == 0 && s == tv.s_begin + nb) trace_clock(scr, 4);
-#pragma unroll
-      for (int b = 0; b < B; ++b)
-        if (b < nb) stage_load<G>(regs[b], a_lo[b], gc[b], kb[b]);
-#pragma unroll
-      for (int b = 0; b < B; ++b)
-        if (b < nb) stage_mma<G, E>(regs[b]);
-#pragma unroll
-      for (int b = 0; b < B; ++b)
-        if (b < nb) stage_fold<G, E>(regs[b], gc[b], kb[b], kwarp0, wsc + b * (G::SCALES_PER_STAGE * 4), acc);
-      __syncwarp();
-      if (tid == 0 && k == 0 && s == tv.s_begin) { trace_stamp(scr, 7); trace_clock(scr, 2); }
-      if (tid == 0 && k == 0 && s == tv.s_begin + nb) trace_clock(scr, 5);
-      if (lane == 0) {
-#pragma unroll
-        for (int b = 0; b < B; ++b)
-          if (b < nb) mbar_arrive(&sm->empty[bslot[b]]);
-      }
-      wsc += nb * (G::SCALES_PER_STAGE * 4);
-      s += nb;
+      p.kstage = 0;
+      ++p.group;        // kConcatK: next group's K; kRowsPerGroup: loop ends here
     }
 
     // ---- the CTA's share of this tile is complete: hand the warp's partial to the

@@ -308,6 +308,81 @@ def test_linear_fused_tail_rows_on_their_own_ctas(scratch, m, kind):
     assert _scratch_clean(scratch)
 
 
+class _RanksOnOneGpu:
+    """Eight "ranks" whose landing zones are ONE buffer on this GPU: every rank's peer
+    table points at it, so rank r's GEMV stores its tagged rows into zone[r] (eight times
+    over), and a tail that polls eight sources finds them all locally."""
+
+    def __init__(self, world, h):
+        self.world, self.h = world, h
+        self.zone = torch.zeros(world * 8 * h, dtype=torch.int32, device="cuda")
+        self.ctrl = torch.zeros(64, dtype=torch.int32, device="cuda")
+        self.peers = torch.tensor([self.zone.data_ptr()] * world, dtype=torch.int64, device="cuda")
+
+    def rank(self, r):
+        owner = self
+
+        class Slot:
+            world, protocol = owner.world, "push"
+
+            def push_args(self):
+                from iquestrt_b200 import _lib
+                a = _lib.PushArgs()
+                a.world, a.rank, a.rows, a.h = owner.world, r, 8, owner.h
+                a.recv = owner.zone.data_ptr()
+                a.recv_mc = None
+                a.peer_recv = owner.peers.data_ptr()
+                a.epoch = owner.ctrl.data_ptr()
+                a.ticket = owner.ctrl.data_ptr() + 4
+                self._keep = a
+                return a
+
+            def fill(self, a, partial):
+                import ctypes as C
+                a.world, a.rank = owner.world, r
+                a.push = C.pointer(self.push_args())
+        return Slot()
+
+
+@pytest.mark.parametrize("m,kind", [(1, "attn"), (4, "mlp")])
+def test_fused_tail_adds_eight_sources(scratch, m, kind):
+    """World 8 on one GPU: seven ranks' GEMVs send their rows, the eighth runs the fused
+    tail, whose CTAs take the eight sources in rounds of what their shared memory holds
+    (four at a time beside a half-SM stream).  Rank-order fp32 sum, one bf16 rounding."""
+    ops, synth = _ops(), _synth()
+    n, k, world = 6144, 1024, 8
+    ranks = _RanksOnOneGpu(world, n)
+    g = torch.Generator().manual_seed(90 + m)
+    residual = torch.randn(m, n, generator=g).bfloat16().cuda()
+    w1 = (0.5 + torch.rand(n, generator=g)).cuda()
+    w2 = (0.5 + torch.rand(n, generator=g)).cuda()
+    attn = kind == "attn"
+    for call in range(2):                              # a new tag on the second call
+        parts = []
+        for r in range(world):
+            x, w, s = synth.make_linear_case(n, k, m, device="cuda", seed=700 + 10 * call + r)
+            part = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            if r < world - 1:
+                ops.linear(x, w, s, scratch=scratch, out=part, push=ranks.rank(r))
+            else:
+                h_out, nrm = torch.empty_like(part), torch.empty_like(part)
+                spec = ops.TailSpec(kind=ops.TAIL_ATTN if attn else ops.TAIL_MLP, partial=part,
+                                    residual=residual, w_first=w1 if attn else None, w_norm=w2,
+                                    h_out=h_out, norm_out=nrm, scale=0.8, eps=1e-6,
+                                    comm=ranks.rank(r), timeout_ms=200)
+                ops.linear(x, w, s, scratch=scratch, out=part, tail=spec)
+            parts.append(part)
+        assert scratch.status() == 0
+        assert int(ranks.ctrl[0]) == call + 1          # the tail closed the call
+        cpu_parts = [p.cpu() for p in parts]
+        if attn:
+            rh, rn, _, _ = R.attention_tail(cpu_parts, residual.cpu(), w1.cpu(), w2.cpu(), 0.8, 1e-6)
+        else:
+            rh, rn = R.mlp_tail(cpu_parts, residual.cpu(), 0.8, w2.cpu(), 1e-6)
+        _close(h_out, rh, ulps=1)
+        _close(nrm, rn, ulps=2)
+
+
 # ------------------------------------------------------------------------------ router
 
 @pytest.mark.parametrize("m,h,e,score", [(1, 6144, 256, "sigmoid"), (4, 6144, 256, "softmax"),
