@@ -1814,6 +1814,8 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) down_kernel(
 
 }  // namespace iqb
 
+#include "direct.cuh"
+
 namespace iqb {
 
 // ------------------------------------------------------------------------------------
@@ -2205,6 +2207,43 @@ static int linear_launch(const iq_linear_args* a, void* stream) {
   return launch(linear_kernel<G>, p, grid, G::THREADS, smem, stream, a->pdl);
 }
 
+// The direct form (direct.cuh): 32 weight rows per CTA, no ring.
+static int linear_direct_launch(const iq_linear_args* a, void* stream) {
+  LinearDirectParams p{};
+  const bool split2 = a->x_kind == IQ_X_BF16_SPLIT2;
+  TailPlan tp;
+  int rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->n,
+                     direct_tail_limit(a->tail));
+  if (rc != IQ_OK) return rc;
+  if (tp.tail_run == kTailLastCta) return IQ_ERR_UNSUPPORTED;     // (pull protocol: the engine)
+  size_t smem = linear_direct_smem(split2 ? 2 * a->m : a->m, a->k);
+  if (smem > 96 * 1024) return IQ_ERR_UNSUPPORTED;
+  if (tp.smem > smem) smem = tp.smem;
+  p.x = a->x;
+  p.x_scale = a->x_scale;
+  p.x_kind = a->x_kind;
+  p.m = a->m;
+  p.k = a->k;
+  p.n = a->n;
+  p.rg_shift = ilog2(a->rg);
+  p.kg_shift = ilog2(a->kg);
+  p.w = static_cast<const uint8_t*>(a->w);
+  p.w_scale = a->w_scale;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.out_f32 = a->out_f32;
+  p.scratch = a->scratch;
+  p.n_tail = tp.n_tail;
+  p.push = tp.push;
+  p.per_round = tp.per_round;
+  p.pv = tp.pv;
+  if (a->tail) {
+    p.tail = *a->tail;
+    if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
+  }
+  const int grid = a->n / kDirectRows + tp.n_tail;
+  return launch(linear_direct_kernel, p, grid, kDirectThreads, smem, stream, a->pdl);
+}
+
 }  // namespace iqb
 
 using namespace iqb;
@@ -2272,6 +2311,13 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
   if (static_cast<long long>(n) * k <= short_stream_bytes()) {
     // (falls through to a whole-SM geometry when half an SM cannot hold the rows and a ring)
     int rc = IQ_ERR_UNSUPPORTED;
+    // The direct form (direct.cuh) for streams of up to IQB200_LINEAR_DIRECT_MB megabytes
+    // (default 16; 0 turns it off): K a multiple of 256, rows a multiple of 32.
+    static const long long direct_bytes = env_number("IQB200_LINEAR_DIRECT_MB", 16) << 20;
+    if (static_cast<long long>(n) * k <= direct_bytes && k % 256 == 0 && n % kDirectRows == 0 &&
+        a->kg >= 64)
+      rc = linear_direct_launch(a, stream);
+    if (rc != IQ_ERR_UNSUPPORTED) return rc;
     // One 48-row tile per CTA (its k-stages worked on in batches) where that leaves no CTA
     // with more rows than 16-row tiles would: a CTA pays the hand-over of a finished tile
     // to its epilogue warp once instead of three times (IQB200_LINEAR_TILE48=0 turns it off).
@@ -2563,6 +2609,50 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   return launch(down_kernel<G>, p, grid, G::THREADS, smem, stream, a->pdl);
 }
 
+// A tail CTA's shared memory is every CTA's of its launch.  Without peers (or with one) the
+// sources of a row fit in 72 KB and several tile CTAs share an SM; with more peers the tail
+// takes what a small half-SM CTA may (three sources per round at hidden 6144).
+static size_t direct_tail_limit(const iq_tail_args* tail) {
+  return tail && tail->world > 2 ? static_cast<size_t>(kSmemLimitSmall) : 72 * 1024;
+}
+
+// The direct form (direct.cuh): 32 weight rows per CTA, no ring.
+template <int RT, int RPU>
+static int down_direct_launch(const iq_moe_down_args* a, void* stream) {
+  DownDirectParams p{};
+  int rc = fill_moe(p.mc, a->m, a->h, a->i_loc, a->n_experts, a->top_k, a->n_shared, a->sel, a->wt);
+  if (rc != IQ_OK) return rc;
+  p.mc.w = static_cast<const uint8_t*>(a->proj);
+  p.mc.w_scale = a->proj_scale;
+  p.mc.shared_w = static_cast<const uint8_t*>(a->shared_proj);
+  p.mc.shared_scale = a->shared_proj_scale;
+  p.mc.w_stride = static_cast<size_t>(a->h) * a->i_loc;
+  p.mc.scale_stride = static_cast<size_t>(a->h / 128) * (a->i_loc / 64);
+  p.mc.rows_per_expert = a->h;
+  TailPlan tp;
+  rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->h,
+                 direct_tail_limit(a->tail));
+  if (rc != IQ_OK) return rc;
+  if (tp.tail_run == kTailLastCta) return IQ_ERR_UNSUPPORTED;     // (pull protocol: the engine)
+  size_t smem = sizeof(DirectSmem);
+  if (tp.smem > smem) smem = tp.smem;
+  p.act = a->act;
+  p.act_kind = a->act_kind;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.scratch = a->scratch;
+  p.n_tail = tp.n_tail;
+  p.push = tp.push;
+  p.per_round = tp.per_round;
+  p.pv = tp.pv;
+  p.pdl_level = a->pdl;
+  if (a->tail) {
+    p.tail = *a->tail;
+    if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
+  }
+  const int grid = a->h / kDirectRows + tp.n_tail;
+  return launch(down_direct_kernel<RT, RPU>, p, grid, kDirectThreads, smem, stream, a->pdl);
+}
+
 extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   if (!a || !a->act || !a->proj || !a->proj_scale || !a->out || !a->wt || !a->scratch)
     return IQ_ERR_ARG;
@@ -2582,6 +2672,17 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   const long long bytes = expert_stream_bytes(a->m, a->top_k, a->n_experts, a->n_shared,
                                               static_cast<long long>(a->h) * a->i_loc);
   if (bytes <= short_stream_bytes()) {
+    // A stream this short runs in the direct form where that exists (e4m3 activations, an
+    // expert width of at most 256): see direct.cuh.  IQB200_DOWN_DIRECT=0 turns it off.
+    static const bool direct = env_number("IQB200_DOWN_DIRECT", 1) != 0;
+    if (direct && a->h % kDirectRows == 0) {
+      int rc = IQ_ERR_UNSUPPORTED;
+      if (k == 256) rc = down_direct_launch<4, 2>(a, stream);
+      else if (k == 192) rc = down_direct_launch<3, 1>(a, stream);
+      else if (k == 128) rc = down_direct_launch<2, 2>(a, stream);
+      else if (k == 64) rc = down_direct_launch<1, 1>(a, stream);
+      if (rc != IQ_ERR_UNSUPPORTED) return rc;
+    }
     // two CTAs per SM (see Geo); fall through when the staged activations leave no room
     int rc = IQ_ERR_UNSUPPORTED;
     if (k % 1024 == 0) rc = down_launch<Geo<1, 8, 2>>(a, stream);
