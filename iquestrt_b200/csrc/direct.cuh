@@ -40,15 +40,16 @@ struct DownDirectParams {
   PushView pv;
 };
 
-constexpr int kDirectThreads = 256;
-constexpr int kDirectRows = 32;        // weight rows per CTA
+// Weight rows per CTA: 32 (two sub-tiles of four warps, 256 threads), or 48 (three sub-tiles of
+// three warps, 288 threads; an option, see the launches).
+constexpr int kDirectRows = 32;
 
 constexpr int kDirectMaxX = 72 * (256 + 16);     // staged activation bytes (rows x padded row)
 
 struct DirectSmem {
   GroupDesc groups[kMaxGroups];
   int route_ids[64 + kMaxGroups + 1];
-  float red[8][32][4];
+  float red[9][32][4];
   float xs[72 * 2];                      // activation scales: rows x (i_loc / 128)
   __align__(16) uint8_t xq[kDirectMaxX];
 };
@@ -97,10 +98,12 @@ __device__ __forceinline__ void direct_load_w(DirectW<RPU>& w, const GroupDesc& 
 // RT: 64-byte runs per weight row (i_loc / 64); RPU: runs per unit (RT / RPU units per group).
 // (Bound to 320 threads and two CTAs per SM like the half-SM streaming kernels: 96 registers,
 // so that a CTA fits beside a ten-warp neighbour -- the register file is per scheduler.)
-template <int RT, int RPU>
+template <int RT, int RPU, int SUBS>
 __global__ void __launch_bounds__(320, 2) down_direct_kernel(const __grid_constant__ DownDirectParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kParts = RT / RPU;
+  constexpr int kQ = SUBS == 3 ? 3 : 4;            // warps per row sub-tile
+  constexpr int kThreads = SUBS * kQ * 32;
   static_assert(RT % RPU == 0, "whole units");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x;
@@ -126,8 +129,8 @@ __global__ void __launch_bounds__(320, 2) down_direct_kernel(const __grid_consta
   if (!early) after_wait();
   const int n_groups = build_groups(sm->groups, p.mc, true, true, status, sm->route_ids);
   const int i_loc = p.mc.i_loc, m = p.mc.m, h = p.mc.h;
-  const int sub = warp >> 2, q = warp & 3;
-  const int row0 = cta * kDirectRows + sub * 16;
+  const int sub = warp / kQ, q = warp - sub * kQ;
+  const int row0 = cta * (SUBS * 16) + sub * 16;
   const int g8 = lane >> 2, t = lane & 3;
   const int n_units = n_groups * kParts;
   const int xpitch = i_loc + 16;
@@ -138,7 +141,7 @@ __global__ void __launch_bounds__(320, 2) down_direct_kernel(const __grid_consta
   int unit = q;
   if (unit < n_units)
     direct_load_w<RPU>(cur, sm->groups[unit / kParts], i_loc, row0, (unit % kParts) * RPU, lane);
-  for (int u = unit + 4; u < n_units; u += 4) {
+  for (int u = unit + kQ; u < n_units; u += kQ) {
     const GroupDesc& gd = sm->groups[u / kParts];
     const int line = lane;                       // 16 rows x (RPU * 64 bytes) in 128-byte lines
     const int lines_per_row = (RPU * 64 + 127) / 128;
@@ -160,11 +163,11 @@ __global__ void __launch_bounds__(320, 2) down_direct_kernel(const __grid_consta
       sh.x_pitch = xpitch;
       sh.x_blocks = x_blocks;
       stage_rows_bf16_groupq(sm->xq, sm->xs, sh, static_cast<const __nv_bfloat16*>(p.act), i_loc,
-                             rows, i_loc, false, tid, kDirectThreads);
+                             rows, i_loc, false, tid, kThreads);
     } else {
       const int vec = i_loc >> 4;
       const uint8_t* act = static_cast<const uint8_t*>(p.act);
-      for (int i = tid; i < rows * vec; i += kDirectThreads) {
+      for (int i = tid; i < rows * vec; i += kThreads) {
         const int r = i / vec, v = i - r * vec;
         *reinterpret_cast<uint4*>(sm->xq + r * xpitch + v * 16) =
             ldg_cg_u4(act + static_cast<size_t>(r) * i_loc + v * 16);
@@ -177,9 +180,9 @@ __global__ void __launch_bounds__(320, 2) down_direct_kernel(const __grid_consta
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   const uint32_t xq_s = smem_u32(sm->xq);
   while (unit < n_units) {
-    if (unit + 4 < n_units)
-      direct_load_w<RPU>(nxt, sm->groups[(unit + 4) / kParts], i_loc, row0,
-                         ((unit + 4) % kParts) * RPU, lane);
+    if (unit + kQ < n_units)
+      direct_load_w<RPU>(nxt, sm->groups[(unit + kQ) / kParts], i_loc, row0,
+                         ((unit + kQ) % kParts) * RPU, lane);
     const GroupDesc& gd = sm->groups[unit / kParts];
     const int run0 = (unit % kParts) * RPU;
     const int xrow = gd.col_row[g8];
@@ -209,7 +212,7 @@ __global__ void __launch_bounds__(320, 2) down_direct_kernel(const __grid_consta
       acc[2] = fmaf(part[run][2], s0, acc[2]);
       acc[3] = fmaf(part[run][3], s1, acc[3]);
     }
-    unit += 4;
+    unit += kQ;
     cur = nxt;
   }
 #pragma unroll
@@ -227,7 +230,7 @@ __global__ void __launch_bounds__(320, 2) down_direct_kernel(const __grid_consta
       const int fl = 4 * (r & 7) + (col >> 1), fi = (r >> 3) * 2 + (col & 1);
       float s = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) s += sm->red[sub * 4 + w][fl][fi];
+      for (int w = 0; w < kQ; ++w) s += sm->red[sub * kQ + w][fl][fi];
       v[j] = s;
     }
     if (col < m) {
@@ -271,13 +274,16 @@ constexpr int kDirectUnitBytes = kDirectUnitRuns * 64;
 // Shared memory of a tile CTA: the reduction buffer, then the staged activation rows
 // (x_rows x (k + 64) bytes) and their scales (x_rows x k/128 floats).
 __host__ __device__ inline size_t linear_direct_smem(int x_rows, int k) {
-  return sizeof(float) * 8 * 32 * 4 + static_cast<size_t>(x_rows) * (k + 64) +
+  return sizeof(float) * 9 * 32 * 4 + static_cast<size_t>(x_rows) * (k + 64) +
          sizeof(float) * x_rows * ((k + 127) / 128) + 64;
 }
 
+template <int SUBS>
 __global__ void __launch_bounds__(320, 2) linear_direct_kernel(const __grid_constant__ LinearDirectParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int RPU = kDirectUnitRuns;
+  constexpr int kQ = SUBS == 3 ? 3 : 4;            // warps per row sub-tile
+  constexpr int kThreads = SUBS * kQ * 32;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x;
   const int tile_ctas = static_cast<int>(gridDim.x) - p.n_tail;
@@ -300,13 +306,13 @@ __global__ void __launch_bounds__(320, 2) linear_direct_kernel(const __grid_cons
   const int k = p.k, m = p.m, n = p.n;
   const int x_rows = split2 ? 2 * m : m;
   float(*red)[32][4] = reinterpret_cast<float(*)[32][4]>(smem);
-  uint8_t* xq = smem + sizeof(float) * 8 * 32 * 4;
+  uint8_t* xq = smem + sizeof(float) * 9 * 32 * 4;
   float* xs = reinterpret_cast<float*>(xq + static_cast<size_t>(x_rows) * (k + 64));
   StreamShape sh{};                       // (what the staging routines read of it)
   sh.x_pitch = k + 64;
   sh.x_blocks = (k + 127) / 128;
-  const int sub = warp >> 2, q = warp & 3;
-  const int row0 = cta * kDirectRows + sub * 16;
+  const int sub = warp / kQ, q = warp - sub * kQ;
+  const int row0 = cta * (SUBS * 16) + sub * 16;
   const int g8 = lane >> 2, t = lane & 3;
   const int n_units = k / kDirectUnitBytes;
   const int krow = k >> p.kg_shift;       // weight scale entries per row block
@@ -327,7 +333,7 @@ __global__ void __launch_bounds__(320, 2) linear_direct_kernel(const __grid_cons
   DirectW<RPU> cur, nxt;
   int unit = q;
   if (unit < n_units) load_w(cur, unit);
-  for (int u = unit + 4; u < n_units; u += 4)
+  for (int u = unit + kQ; u < n_units; u += kQ)
     prefetch_l2(p.w + static_cast<size_t>(row0 + (lane >> 1)) * k + u * kDirectUnitBytes + (lane & 1) * 128);
   after_wait();
   if (tid == 0) IQ_STAMP(p, 1);
@@ -335,10 +341,10 @@ __global__ void __launch_bounds__(320, 2) linear_direct_kernel(const __grid_cons
   // ---- the activations: staged (and quantised) once per CTA
   if (p.x_kind == IQ_X_BF16_GROUPQ || split2)
     stage_rows_bf16_groupq(xq, xs, sh, static_cast<const __nv_bfloat16*>(p.x), k, m, k, split2,
-                           tid, kDirectThreads);
+                           tid, kThreads);
   else
     stage_rows_e4m3(xq, xs, sh, static_cast<const uint8_t*>(p.x), k,
-                    p.x_kind == IQ_X_E4M3_GROUP ? p.x_scale : nullptr, m, k, tid, kDirectThreads);
+                    p.x_kind == IQ_X_E4M3_GROUP ? p.x_scale : nullptr, m, k, tid, kThreads);
   __syncthreads();
   if (tid == 0) IQ_STAMP(p, 2);
 
@@ -346,7 +352,7 @@ __global__ void __launch_bounds__(320, 2) linear_direct_kernel(const __grid_cons
   const uint32_t xq_s = smem_u32(xq), xs_s = smem_u32(xs);
   const bool live_g = g8 < x_rows, live0 = 2 * t < x_rows, live1 = 2 * t + 1 < x_rows;
   while (unit < n_units) {
-    if (unit + 4 < n_units) load_w(nxt, unit + 4);
+    if (unit + kQ < n_units) load_w(nxt, unit + kQ);
     const int kb0 = unit * kDirectUnitBytes;
     float part[RPU][4];
 #pragma unroll
@@ -368,7 +374,7 @@ __global__ void __launch_bounds__(320, 2) linear_direct_kernel(const __grid_cons
       acc[2] = fmaf(part[run][2], s0, acc[2]);
       acc[3] = fmaf(part[run][3], s1, acc[3]);
     }
-    unit += 4;
+    unit += kQ;
     cur = nxt;
   }
 #pragma unroll
@@ -386,7 +392,7 @@ __global__ void __launch_bounds__(320, 2) linear_direct_kernel(const __grid_cons
       const int fl = 4 * (r & 7) + (col >> 1), fi = (r >> 3) * 2 + (col & 1);
       float s = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) s += red[sub * 4 + w][fl][fi];
+      for (int w = 0; w < kQ; ++w) s += red[sub * kQ + w][fl][fi];
       v[j] = s;
     }
     int row = col;

@@ -2207,6 +2207,13 @@ static int linear_launch(const iq_linear_args* a, void* stream) {
   return launch(linear_kernel<G>, p, grid, G::THREADS, smem, stream, a->pdl);
 }
 
+// A tail CTA's shared memory is every CTA's of its launch.  Without peers (or with one) the
+// sources of a row fit in 72 KB and several tile CTAs share an SM; with more peers the tail
+// takes what a small half-SM CTA may (three sources per round at hidden 6144).
+static size_t direct_tail_limit(const iq_tail_args* tail) {
+  return tail && tail->world > 2 ? static_cast<size_t>(kSmemLimitSmall) : 72 * 1024;
+}
+
 // The direct form (direct.cuh): 32 weight rows per CTA, no ring.
 static int linear_direct_launch(const iq_linear_args* a, void* stream) {
   LinearDirectParams p{};
@@ -2240,8 +2247,11 @@ static int linear_direct_launch(const iq_linear_args* a, void* stream) {
     p.tail = *a->tail;
     if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
   }
-  const int grid = a->n / kDirectRows + tp.n_tail;
-  return launch(linear_direct_kernel, p, grid, kDirectThreads, smem, stream, a->pdl);
+  // (32 rows per CTA measured faster than 48 for the o_proj: 9.3 against 10.1 us)
+  static const bool rows48 = env_number("IQB200_LINEAR_DIRECT_ROWS48", 0) != 0;
+  if (rows48 && a->n % 48 == 0)
+    return launch(linear_direct_kernel<3>, p, a->n / 48 + tp.n_tail, 288, smem, stream, a->pdl);
+  return launch(linear_direct_kernel<2>, p, a->n / 32 + tp.n_tail, 256, smem, stream, a->pdl);
 }
 
 }  // namespace iqb
@@ -2609,13 +2619,6 @@ static int down_launch(const iq_moe_down_args* a, void* stream) {
   return launch(down_kernel<G>, p, grid, G::THREADS, smem, stream, a->pdl);
 }
 
-// A tail CTA's shared memory is every CTA's of its launch.  Without peers (or with one) the
-// sources of a row fit in 72 KB and several tile CTAs share an SM; with more peers the tail
-// takes what a small half-SM CTA may (three sources per round at hidden 6144).
-static size_t direct_tail_limit(const iq_tail_args* tail) {
-  return tail && tail->world > 2 ? static_cast<size_t>(kSmemLimitSmall) : 72 * 1024;
-}
-
 // The direct form (direct.cuh): 32 weight rows per CTA, no ring.
 template <int RT, int RPU>
 static int down_direct_launch(const iq_moe_down_args* a, void* stream) {
@@ -2649,8 +2652,15 @@ static int down_direct_launch(const iq_moe_down_args* a, void* stream) {
     p.tail = *a->tail;
     if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
   }
-  const int grid = a->h / kDirectRows + tp.n_tail;
-  return launch(down_direct_kernel<RT, RPU>, p, grid, kDirectThreads, smem, stream, a->pdl);
+  // (48 rows per CTA -- one CTA per SM beside the Gate's, all resident at once -- made the
+  // Down itself faster, 11.1 against 12.4 us, but the layer slower, 40.4 against 39.5 us:
+  // 32 rows is the default, IQB200_DOWN_DIRECT_ROWS48=1 selects 48 for one or two rows)
+  static const bool rows48 = env_number("IQB200_DOWN_DIRECT_ROWS48", 0) != 0;
+  if (rows48 && a->h % 48 == 0 && a->m <= 2)
+    return launch(down_direct_kernel<RT, RPU, 3>, p, a->h / 48 + tp.n_tail, 288, smem, stream,
+                  a->pdl);
+  return launch(down_direct_kernel<RT, RPU, 2>, p, a->h / 32 + tp.n_tail, 256, smem, stream,
+                a->pdl);
 }
 
 extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
