@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libiqb200.so")
 SOURCES = ("kernels.cu",)
-HEADERS = ("common.cuh", "stream_core.cuh", "direct.cuh")
+HEADERS = ("common.cuh", "stream_core.cuh", "direct.cuh", "direct_gate.cuh")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-shared", "-Xcompiler", "-fPIC",

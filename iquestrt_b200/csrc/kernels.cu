@@ -1815,6 +1815,7 @@ __global__ void __launch_bounds__(G::BOUND_THREADS, G::CTAS_PER_SM) down_kernel(
 }  // namespace iqb
 
 #include "direct.cuh"
+#include "direct_gate.cuh"
 
 namespace iqb {
 
@@ -2546,6 +2547,29 @@ static long long expert_stream_bytes(int m, int top_k, int n_experts, int n_shar
   return (routed + n_shared) * bytes_per_expert;
 }
 
+// The direct form for one row (direct_gate.cuh): sixteen features of one group per CTA.
+static int gate_direct_launch(const iq_moe_gate_args* a, void* stream) {
+  GateDirectParams p{};
+  int rc = fill_moe(p.mc, a->m, a->h, a->i_loc, a->n_experts, a->top_k, a->n_shared, a->sel, nullptr);
+  if (rc != IQ_OK) return rc;
+  p.mc.w = static_cast<const uint8_t*>(a->fc);
+  p.mc.w_scale = a->fc_scale;
+  p.mc.shared_w = static_cast<const uint8_t*>(a->shared_fc);
+  p.mc.shared_scale = a->shared_fc_scale;
+  p.mc.w_stride = static_cast<size_t>(2) * a->i_loc * a->h;
+  p.mc.scale_stride = static_cast<size_t>(2 * a->i_loc / 64) * (a->h / 128);
+  p.mc.rows_per_expert = 2 * a->i_loc;
+  p.x_fp8 = static_cast<const uint8_t*>(a->x_fp8);
+  p.x_scale = a->x_scale;
+  p.x_bf16 = static_cast<const __nv_bfloat16*>(a->x_bf16);
+  p.act = a->act;
+  p.act_kind = a->act_kind;
+  p.scratch = a->scratch;
+  p.pdl_level = a->pdl;
+  const int grid = (a->top_k + a->n_shared) * (a->i_loc / 16);
+  return launch(gate_direct_kernel, p, grid, 256, gate_direct_smem(a->h), stream, a->pdl);
+}
+
 extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   if (!a || (!a->x_fp8 && !a->x_bf16) || !a->fc || !a->fc_scale || !a->act || !a->scratch)
     return IQ_ERR_ARG;
@@ -2558,6 +2582,14 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
   const long long bytes = expert_stream_bytes(a->m, a->top_k, a->n_experts, a->n_shared,
                                               2ll * a->i_loc * a->h);
   if (bytes <= short_stream_bytes()) {
+    // One row and a stream of up to IQB200_GATE_DIRECT_MB megabytes (default 12; 0 turns it
+    // off): the direct form.  Measured, one row: 6.3 against 8.1 us at 9.4 MB (hidden 3072,
+    // expert width 192), but 15.5 against 12.2 us at 28 MB (hidden 6144, width 256), where a
+    // warp's three units in flight are too few to keep HBM busy.
+    static const long long direct_bytes = env_number("IQB200_GATE_DIRECT_MB", 12) << 20;
+    if (bytes <= direct_bytes && a->m == 1 && a->h % 512 == 0 && a->i_loc % 64 == 0 &&
+        a->top_k <= 32)
+      return gate_direct_launch(a, stream);
     static const bool runs3 = env_number("IQB200_GATE_RUNS3", 0) != 0;
     int rc = IQ_ERR_UNSUPPORTED;
     if (runs3 && a->h % 768 == 0) rc = gate_launch<Geo<2, 4, 3, 3>>(a, stream);
