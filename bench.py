@@ -578,7 +578,7 @@ def run_ours(args):
                          "frac": frac["gate"], "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": by["gate"],
                          "launch_us": med["gate"] * 1e3,
-                         "traffic": dram_traffic("gate_kernel", tp, rows),
+                         "traffic": dram_traffic("gate_kernel", shard_of or tp, rows),
                          "layer_frac": by["total"] / (us * 1e-6) / 1e9 / peak},
             "roofline_fused": {"oproj_tail": frac["oproj_tail"], "down_tail": frac["down_tail"],
                                "router": frac["router"], "unit": "fraction of the HBM peak",

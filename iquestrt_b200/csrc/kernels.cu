@@ -2323,10 +2323,13 @@ extern "C" int iq_linear(const iq_linear_args* a, void* stream) {
     // (falls through to a whole-SM geometry when half an SM cannot hold the rows and a ring)
     int rc = IQ_ERR_UNSUPPORTED;
     // The direct form (direct.cuh) for streams of up to IQB200_LINEAR_DIRECT_MB megabytes
-    // (default 16; 0 turns it off): K a multiple of 256, rows a multiple of 32.
+    // (default 16; 0 turns it off) of many short rows -- the row-parallel o_proj of a shard:
+    // K a multiple of 256 and at most 2048, at least 2048 rows (32 per CTA).  (The
+    // column-parallel QKV of a shard, 1280 rows of 6144, would be 40 CTAs with long rows:
+    // measured 14.8 against the engine's 9.5 us.)
     static const long long direct_bytes = env_number("IQB200_LINEAR_DIRECT_MB", 16) << 20;
-    if (static_cast<long long>(n) * k <= direct_bytes && k % 256 == 0 && n % kDirectRows == 0 &&
-        a->kg >= 64)
+    if (static_cast<long long>(n) * k <= direct_bytes && k % 256 == 0 && k <= 2048 && n >= 2048 &&
+        n % kDirectRows == 0 && a->kg >= 64)
       rc = linear_direct_launch(a, stream);
     if (rc != IQ_ERR_UNSUPPORTED) return rc;
     // One 48-row tile per CTA (its k-stages worked on in batches) where that leaves no CTA
