@@ -2551,7 +2551,7 @@ static long long expert_stream_bytes(int m, int top_k, int n_experts, int n_shar
 }
 
 // The direct form for one row (direct_gate.cuh): sixteen features of one group per CTA.
-static int gate_direct_launch(const iq_moe_gate_args* a, void* stream) {
+static int gate_direct_launch(const iq_moe_gate_args* a, void* stream, bool eight) {
   GateDirectParams p{};
   int rc = fill_moe(p.mc, a->m, a->h, a->i_loc, a->n_experts, a->top_k, a->n_shared, a->sel, nullptr);
   if (rc != IQ_OK) return rc;
@@ -2569,6 +2569,10 @@ static int gate_direct_launch(const iq_moe_gate_args* a, void* stream) {
   p.act_kind = a->act_kind;
   p.scratch = a->scratch;
   p.pdl_level = a->pdl;
+  if (eight) {
+    const int grid = (a->top_k + a->n_shared) * (a->i_loc / 8);
+    return launch(gate_direct8_kernel, p, grid, 256, gate_direct_smem(a->h), stream, a->pdl);
+  }
   const int grid = (a->top_k + a->n_shared) * (a->i_loc / 16);
   return launch(gate_direct_kernel, p, grid, 256, gate_direct_smem(a->h), stream, a->pdl);
 }
@@ -2592,7 +2596,11 @@ extern "C" int iq_moe_gate(const iq_moe_gate_args* a, void* stream) {
     static const long long direct_bytes = env_number("IQB200_GATE_DIRECT_MB", 12) << 20;
     if (bytes <= direct_bytes && a->m == 1 && a->h % 512 == 0 && a->i_loc % 64 == 0 &&
         a->top_k <= 32)
-      return gate_direct_launch(a, stream);
+      return gate_direct_launch(a, stream, false);
+    // Longer one-row streams: eight features per CTA (IQB200_GATE_DIRECT8=0 turns it off).
+    static const bool direct8 = env_number("IQB200_GATE_DIRECT8", 0) != 0;
+    if (direct8 && a->m == 1 && a->h % 1024 == 0 && a->i_loc % 64 == 0 && a->top_k <= 32)
+      return gate_direct_launch(a, stream, true);
     static const bool runs3 = env_number("IQB200_GATE_RUNS3", 0) != 0;
     int rc = IQ_ERR_UNSUPPORTED;
     if (runs3 && a->h % 768 == 0) rc = gate_launch<Geo<2, 4, 3, 3>>(a, stream);
