@@ -44,13 +44,14 @@ struct DownDirectParams {
 // three warps, 288 threads; an option, see the launches).
 constexpr int kDirectRows = 32;
 
-constexpr int kDirectMaxX = 72 * (256 + 16);     // staged activation bytes (rows x padded row)
+constexpr int kDirectMaxRows = 72;               // staged activation rows (pairs + shared rows)
+constexpr int kDirectMaxX = kDirectMaxRows * (256 + 16);   // their bytes (rows x padded row)
 
 struct DirectSmem {
   GroupDesc groups[kMaxGroups];
   int route_ids[64 + kMaxGroups + 1];
   float red[9][32][4];
-  float xs[72 * 2];                      // activation scales: rows x (i_loc / 128)
+  float xs[kDirectMaxRows * 2];          // activation scales: rows x (i_loc / 128)
   __align__(16) uint8_t xq[kDirectMaxX];
 };
 

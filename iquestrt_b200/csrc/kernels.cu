@@ -2728,7 +2728,7 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
     // A stream this short runs in the direct form where that exists (e4m3 activations, an
     // expert width of at most 256): see direct.cuh.  IQB200_DOWN_DIRECT=0 turns it off.
     static const bool direct = env_number("IQB200_DOWN_DIRECT", 1) != 0;
-    if (direct && a->h % kDirectRows == 0) {
+    if (direct && a->h % kDirectRows == 0 && a->m * (a->top_k + a->n_shared) <= kDirectMaxRows) {
       int rc = IQ_ERR_UNSUPPORTED;
       if (k == 256) rc = down_direct_launch<4, 2>(a, stream);
       else if (k == 192) rc = down_direct_launch<3, 1>(a, stream);
