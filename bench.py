@@ -407,6 +407,15 @@ def run_ours(args):
 
     fused = not args.unfused
     launches_per_step = 4 if fused else 6
+    if fused and (tp > 2 or (tp > 1 and args.protocol == "pull")):
+        # With more than one peer (with any peer under the pull protocol) the direct forms of
+        # o_proj and Down (short streams) leave their all-reduce tail to a launch of its own
+        # (see the library's dispatch).
+        ql_rank, il_rank = shape.q_dim // tp, shape.inter // tp
+        if ql_rank % 256 == 0 and ql_rank <= 2048 and shape.hidden * ql_rank <= 16 << 20:
+            launches_per_step += 1
+        if il_rank in (64, 128, 192, 256):
+            launches_per_step += 1
 
     def call(i):
         ao, res = inputs[i % n_inputs]

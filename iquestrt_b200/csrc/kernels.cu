@@ -2208,6 +2208,20 @@ static int linear_launch(const iq_linear_args* a, void* stream) {
   return launch(linear_kernel<G>, p, grid, G::THREADS, smem, stream, a->pdl);
 }
 
+// The tail of rows pushed by an earlier launch: one polling CTA per row, taking as many
+// sources per round as `smem_limit` bytes of shared memory hold.
+static int launch_pushed_tail(const iq_tail_args* a, void* stream, int pdl, size_t smem_limit) {
+  TailParams p{};
+  p.a = *a;
+  if (make_push_view(p.pv, a->push, nullptr, 0, a->h) != IQ_OK) return IQ_ERR_ARG;
+  p.push = 1;
+  p.n_tail = a->m;
+  p.per_round = tail_sources_per_round(p.pv.world, a->h, a->residual_fp32, smem_limit);
+  if (p.per_round < 1) return IQ_ERR_UNSUPPORTED;
+  return launch(tail_kernel, p, a->m, kTailThreads,
+                tail_cta_smem(p.per_round, a->h, a->residual_fp32), stream, pdl);
+}
+
 // A tail CTA's shared memory is every CTA's of its launch.  Without peers (or with one) the
 // sources of a row fit in 72 KB and several tile CTAs share an SM; with more peers the tail
 // takes what a small half-SM CTA may (three sources per round at hidden 6144).
@@ -2220,10 +2234,18 @@ static int linear_direct_launch(const iq_linear_args* a, void* stream) {
   LinearDirectParams p{};
   const bool split2 = a->x_kind == IQ_X_BF16_SPLIT2;
   TailPlan tp;
-  int rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->n,
-                     direct_tail_limit(a->tail));
+  // With more than one peer a tail CTA needs 100-200 KB for its sources, and a launch's
+  // CTAs all get the same shared memory: the tile CTAs would no longer fit beside their
+  // neighbours.  Then the rows are only pushed here and the tail follows as a launch of
+  // its own, with half an SM's shared memory (four sources per round at hidden 6144): its
+  // CTA then finds room beside the tile CTAs while they run and rehearses meanwhile.
+  // The pull protocol's tail (signal, wait, switch read) always follows as its own launch.
+  const bool pull_tail = a->tail && !a->tail->push && a->tail->world > 1;
+  const bool split_tail = pull_tail || (a->tail && a->tail->push && a->tail->world > 2);
+  int rc = plan_tail(tp, split_tail ? nullptr : a->tail,
+                     pull_tail ? nullptr : (split_tail ? a->tail->push : a->push), a->scratch,
+                     a->scratch_bytes, a->m, a->n, direct_tail_limit(a->tail));
   if (rc != IQ_OK) return rc;
-  if (tp.tail_run == kTailLastCta) return IQ_ERR_UNSUPPORTED;     // (pull protocol: the engine)
   size_t smem = linear_direct_smem(split2 ? 2 * a->m : a->m, a->k);
   if (smem > 96 * 1024) return IQ_ERR_UNSUPPORTED;
   if (tp.smem > smem) smem = tp.smem;
@@ -2244,15 +2266,21 @@ static int linear_direct_launch(const iq_linear_args* a, void* stream) {
   p.push = tp.push;
   p.per_round = tp.per_round;
   p.pv = tp.pv;
-  if (a->tail) {
+  if (a->tail && !split_tail) {
     p.tail = *a->tail;
     if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
   }
   // (32 rows per CTA measured faster than 48 for the o_proj: 9.3 against 10.1 us)
   static const bool rows48 = env_number("IQB200_LINEAR_DIRECT_ROWS48", 0) != 0;
   if (rows48 && a->n % 48 == 0)
-    return launch(linear_direct_kernel<3>, p, a->n / 48 + tp.n_tail, 288, smem, stream, a->pdl);
-  return launch(linear_direct_kernel<2>, p, a->n / 32 + tp.n_tail, 256, smem, stream, a->pdl);
+    rc = launch(linear_direct_kernel<3>, p, a->n / 48 + tp.n_tail, 288, smem, stream, a->pdl);
+  else
+    rc = launch(linear_direct_kernel<2>, p, a->n / 32 + tp.n_tail, 256, smem, stream, a->pdl);
+  if (rc != IQ_OK || !split_tail) return rc;
+  iq_tail_args t = *a->tail;
+  if (!t.status) t.status = scratch_of(a->scratch).status;
+  if (pull_tail) return iq_tail(&t, stream, a->pdl);
+  return launch_pushed_tail(&t, stream, a->pdl, kSmemSpread);
 }
 
 }  // namespace iqb
@@ -2281,15 +2309,8 @@ extern "C" int iq_tail(const iq_tail_args* a, void* stream, int pdl) {
   TailParams p{};
   p.a = *a;
   if (a->push) {
-    // rows pushed by an earlier iq_linear / iq_moe_down: one polling CTA per row
-    if (make_push_view(p.pv, a->push, nullptr, 0, a->h) != IQ_OK) return IQ_ERR_ARG;
-    p.push = 1;
-    p.n_tail = a->m;
     // a small CTA that can sit beside a streaming kernel's: half an SM's shared memory
-    p.per_round = tail_sources_per_round(p.pv.world, a->h, a->residual_fp32, kSmemLimitSmall);
-    if (p.per_round < 1) return IQ_ERR_UNSUPPORTED;
-    return launch(tail_kernel, p, a->m, kTailThreads,
-                  tail_cta_smem(p.per_round, a->h, a->residual_fp32), stream, pdl);
+    return launch_pushed_tail(a, stream, pdl, kSmemLimitSmall);
   }
   // rows in `partial`: one CTA per row without peers, one CTA (one signal / wait) with
   return launch(tail_kernel, p, a->world == 1 ? a->m : 1, kTailThreads,
@@ -2676,10 +2697,13 @@ static int down_direct_launch(const iq_moe_down_args* a, void* stream) {
   p.mc.scale_stride = static_cast<size_t>(a->h / 128) * (a->i_loc / 64);
   p.mc.rows_per_expert = a->h;
   TailPlan tp;
-  rc = plan_tail(tp, a->tail, a->push, a->scratch, a->scratch_bytes, a->m, a->h,
-                 direct_tail_limit(a->tail));
+  // (see linear_direct_launch)
+  const bool pull_tail = a->tail && !a->tail->push && a->tail->world > 1;
+  const bool split_tail = pull_tail || (a->tail && a->tail->push && a->tail->world > 2);
+  rc = plan_tail(tp, split_tail ? nullptr : a->tail,
+                 pull_tail ? nullptr : (split_tail ? a->tail->push : a->push), a->scratch,
+                 a->scratch_bytes, a->m, a->h, direct_tail_limit(a->tail));
   if (rc != IQ_OK) return rc;
-  if (tp.tail_run == kTailLastCta) return IQ_ERR_UNSUPPORTED;     // (pull protocol: the engine)
   size_t smem = sizeof(DirectSmem);
   if (tp.smem > smem) smem = tp.smem;
   p.act = a->act;
@@ -2691,7 +2715,7 @@ static int down_direct_launch(const iq_moe_down_args* a, void* stream) {
   p.per_round = tp.per_round;
   p.pv = tp.pv;
   p.pdl_level = a->pdl;
-  if (a->tail) {
+  if (a->tail && !split_tail) {
     p.tail = *a->tail;
     if (!p.tail.status) p.tail.status = scratch_of(a->scratch).status;
   }
@@ -2700,10 +2724,16 @@ static int down_direct_launch(const iq_moe_down_args* a, void* stream) {
   // 32 rows is the default, IQB200_DOWN_DIRECT_ROWS48=1 selects 48 for one or two rows)
   static const bool rows48 = env_number("IQB200_DOWN_DIRECT_ROWS48", 0) != 0;
   if (rows48 && a->h % 48 == 0 && a->m <= 2)
-    return launch(down_direct_kernel<RT, RPU, 3>, p, a->h / 48 + tp.n_tail, 288, smem, stream,
-                  a->pdl);
-  return launch(down_direct_kernel<RT, RPU, 2>, p, a->h / 32 + tp.n_tail, 256, smem, stream,
+    rc = launch(down_direct_kernel<RT, RPU, 3>, p, a->h / 48 + tp.n_tail, 288, smem, stream,
                 a->pdl);
+  else
+    rc = launch(down_direct_kernel<RT, RPU, 2>, p, a->h / 32 + tp.n_tail, 256, smem, stream,
+                a->pdl);
+  if (rc != IQ_OK || !split_tail) return rc;
+  iq_tail_args t = *a->tail;
+  if (!t.status) t.status = scratch_of(a->scratch).status;
+  if (pull_tail) return iq_tail(&t, stream, a->pdl);
+  return launch_pushed_tail(&t, stream, a->pdl, kSmemSpread);
 }
 
 extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
