@@ -2240,8 +2240,10 @@ static int linear_direct_launch(const iq_linear_args* a, void* stream) {
   // its own, with half an SM's shared memory (four sources per round at hidden 6144): its
   // CTA then finds room beside the tile CTAs while they run and rehearses meanwhile.
   // The pull protocol's tail (signal, wait, switch read) always follows as its own launch.
+  static const bool split_push = env_number("IQB200_DIRECT_SPLIT_TAIL", 1) != 0;
   const bool pull_tail = a->tail && !a->tail->push && a->tail->world > 1;
-  const bool split_tail = pull_tail || (a->tail && a->tail->push && a->tail->world > 2);
+  const bool split_tail =
+      pull_tail || (split_push && a->tail && a->tail->push && a->tail->world > 2);
   int rc = plan_tail(tp, split_tail ? nullptr : a->tail,
                      pull_tail ? nullptr : (split_tail ? a->tail->push : a->push), a->scratch,
                      a->scratch_bytes, a->m, a->n, direct_tail_limit(a->tail));
@@ -2698,8 +2700,10 @@ static int down_direct_launch(const iq_moe_down_args* a, void* stream) {
   p.mc.rows_per_expert = a->h;
   TailPlan tp;
   // (see linear_direct_launch)
+  static const bool split_push = env_number("IQB200_DIRECT_SPLIT_TAIL", 1) != 0;
   const bool pull_tail = a->tail && !a->tail->push && a->tail->world > 1;
-  const bool split_tail = pull_tail || (a->tail && a->tail->push && a->tail->world > 2);
+  const bool split_tail =
+      pull_tail || (split_push && a->tail && a->tail->push && a->tail->world > 2);
   rc = plan_tail(tp, split_tail ? nullptr : a->tail,
                  pull_tail ? nullptr : (split_tail ? a->tail->push : a->push), a->scratch,
                  a->scratch_bytes, a->m, a->h, direct_tail_limit(a->tail));
