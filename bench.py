@@ -407,14 +407,21 @@ def run_ours(args):
 
     fused = not args.unfused
     launches_per_step = 4 if fused else 6
-    if fused and (tp > 2 or (tp > 1 and args.protocol == "pull")):
-        # With more than one peer (with any peer under the pull protocol) the direct forms of
-        # o_proj and Down (short streams) leave their all-reduce tail to a launch of its own
-        # (see the library's dispatch).
+
+    def knob(name, default):
+        return float(os.environ.get(name, default))
+
+    own_tail = tp > 1 and (args.protocol == "pull" or
+                           (tp > 2 and knob("IQB200_DIRECT_SPLIT_TAIL", 0) != 0))
+    if fused and own_tail:
+        # Where the direct forms of o_proj and Down (short streams) leave their all-reduce
+        # tail to a launch of its own (the library's dispatch: always under the pull protocol,
+        # under push only with more than one peer and when the knob asks for it), count it.
         ql_rank, il_rank = shape.q_dim // tp, shape.inter // tp
-        if ql_rank % 256 == 0 and ql_rank <= 2048 and shape.hidden * ql_rank <= 16 << 20:
+        direct_mb = knob("IQB200_LINEAR_DIRECT_MB", 16)
+        if ql_rank % 256 == 0 and ql_rank <= 2048 and shape.hidden * ql_rank <= direct_mb * 2**20:
             launches_per_step += 1
-        if il_rank in (64, 128, 192, 256):
+        if il_rank in (64, 128, 192, 256, 512) and knob("IQB200_DOWN_DIRECT", 1) != 0:
             launches_per_step += 1
 
     def call(i):

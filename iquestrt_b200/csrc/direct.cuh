@@ -45,15 +45,19 @@ struct DownDirectParams {
 constexpr int kDirectRows = 32;
 
 constexpr int kDirectMaxRows = 72;               // staged activation rows (pairs + shared rows)
-constexpr int kDirectMaxX = kDirectMaxRows * (256 + 16);   // their bytes (rows x padded row)
+constexpr int kDirectMaxWidth = 512;             // widest expert slice (bytes per activation row)
 
 struct DirectSmem {
   GroupDesc groups[kMaxGroups];
   int route_ids[64 + kMaxGroups + 1];
   float red[9][32][4];
-  float xs[kDirectMaxRows * 2];          // activation scales: rows x (i_loc / 128)
-  __align__(16) uint8_t xq[kDirectMaxX];
+  float xs[kDirectMaxRows * (kDirectMaxWidth / 128)];   // activation scales: rows x (i_loc / 128)
+  __align__(16) uint8_t xq[16];          // the staged rows start here: rows x (i_loc + 16) bytes
 };
+// Shared memory of a tile CTA for `rows` staged activation rows of `i_loc` bytes.
+__host__ __device__ inline size_t down_direct_smem(int rows, int i_loc) {
+  return offsetof(DirectSmem, xq) + static_cast<size_t>(rows) * (i_loc + 16);
+}
 
 __device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
   uint4 v;

@@ -2234,13 +2234,14 @@ static int linear_direct_launch(const iq_linear_args* a, void* stream) {
   LinearDirectParams p{};
   const bool split2 = a->x_kind == IQ_X_BF16_SPLIT2;
   TailPlan tp;
-  // With more than one peer a tail CTA needs 100-200 KB for its sources, and a launch's
-  // CTAs all get the same shared memory: the tile CTAs would no longer fit beside their
-  // neighbours.  Then the rows are only pushed here and the tail follows as a launch of
-  // its own, with half an SM's shared memory (four sources per round at hidden 6144): its
-  // CTA then finds room beside the tile CTAs while they run and rehearses meanwhile.
+  // With more than one peer a tail CTA needs about 100 KB for its sources, and a launch's
+  // CTAs all get the same shared memory, so only two tile CTAs fit on an SM.  The other
+  // form (IQB200_DIRECT_SPLIT_TAIL=1) only pushes the rows here and lets the tail follow
+  // as a launch of its own with half an SM's shared memory.  Measured per layer: 62.9 (own
+  // launch) against 63.4 us on four GPUs, 64.3 against 57.2 us on eight, so the tail stays
+  // in this launch unless the knob says otherwise.
   // The pull protocol's tail (signal, wait, switch read) always follows as its own launch.
-  static const bool split_push = env_number("IQB200_DIRECT_SPLIT_TAIL", 1) != 0;
+  static const bool split_push = env_number("IQB200_DIRECT_SPLIT_TAIL", 0) != 0;
   const bool pull_tail = a->tail && !a->tail->push && a->tail->world > 1;
   const bool split_tail =
       pull_tail || (split_push && a->tail && a->tail->push && a->tail->world > 2);
@@ -2700,7 +2701,7 @@ static int down_direct_launch(const iq_moe_down_args* a, void* stream) {
   p.mc.rows_per_expert = a->h;
   TailPlan tp;
   // (see linear_direct_launch)
-  static const bool split_push = env_number("IQB200_DIRECT_SPLIT_TAIL", 1) != 0;
+  static const bool split_push = env_number("IQB200_DIRECT_SPLIT_TAIL", 0) != 0;
   const bool pull_tail = a->tail && !a->tail->push && a->tail->world > 1;
   const bool split_tail =
       pull_tail || (split_push && a->tail && a->tail->push && a->tail->world > 2);
@@ -2708,7 +2709,7 @@ static int down_direct_launch(const iq_moe_down_args* a, void* stream) {
                  pull_tail ? nullptr : (split_tail ? a->tail->push : a->push), a->scratch,
                  a->scratch_bytes, a->m, a->h, direct_tail_limit(a->tail));
   if (rc != IQ_OK) return rc;
-  size_t smem = sizeof(DirectSmem);
+  size_t smem = down_direct_smem(a->m * (a->top_k + a->n_shared), a->i_loc);
   if (tp.smem > smem) smem = tp.smem;
   p.act = a->act;
   p.act_kind = a->act_kind;
@@ -2759,12 +2760,13 @@ extern "C" int iq_moe_down(const iq_moe_down_args* a, void* stream) {
   const long long bytes = expert_stream_bytes(a->m, a->top_k, a->n_experts, a->n_shared,
                                               static_cast<long long>(a->h) * a->i_loc);
   if (bytes <= short_stream_bytes()) {
-    // A stream this short runs in the direct form where that exists (e4m3 activations, an
-    // expert width of at most 256): see direct.cuh.  IQB200_DOWN_DIRECT=0 turns it off.
+    // A stream this short runs in the direct form where that exists (an expert width of at
+    // most 512): see direct.cuh.  IQB200_DOWN_DIRECT=0 turns it off.
     static const bool direct = env_number("IQB200_DOWN_DIRECT", 1) != 0;
     if (direct && a->h % kDirectRows == 0 && a->m * (a->top_k + a->n_shared) <= kDirectMaxRows) {
       int rc = IQ_ERR_UNSUPPORTED;
-      if (k == 256) rc = down_direct_launch<4, 2>(a, stream);
+      if (k == 512) rc = down_direct_launch<8, 2>(a, stream);
+      else if (k == 256) rc = down_direct_launch<4, 2>(a, stream);
       else if (k == 192) rc = down_direct_launch<3, 1>(a, stream);
       else if (k == 128) rc = down_direct_launch<2, 2>(a, stream);
       else if (k == 64) rc = down_direct_launch<1, 1>(a, stream);

@@ -456,6 +456,9 @@ def _moe_case(m, h, inter, tp, e, seed, n_shared, dev="cuda"):
     (1, 3072, 1536, 8, 0, "unscaled"),  # the reference's shard (I_loc 192) and formats
     (8, 3072, 1536, 8, 0, "unscaled"),
     (2, 1024, 2048, 1, 1, "group"),     # deep Down contraction (TP=1 width)
+    (1, 6144, 2048, 4, 1, "group"),     # the TP=4 shard (I_loc 512): widest direct Down
+    (4, 6144, 2048, 4, 1, "group"),
+    (3, 3072, 2048, 4, 0, "unscaled"),
 ])
 def test_moe_gate_down(scratch, m, h, inter, tp, n_shared, mode):
     ops = _ops()
