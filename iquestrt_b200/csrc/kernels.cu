@@ -125,12 +125,29 @@ __device__ inline Carve<G> carve(uint8_t* base, const StreamShape& sh) {
 // of the same launch.
 constexpr int kStageBatch = 8;
 
+// Two values to e4m3 (saturating) by one conversion: low byte = lo.
+__device__ __forceinline__ uint32_t e4m3x2_sat(float lo, float hi) {
+  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+}
+// Vector `i` of a row set with `vec` vectors per row -> (row, vector in the row).  Every
+// CTA of a launch stages the same rows, so the staging is bound by instruction issue on
+// each SM; a power-of-two row length (the usual case) saves two integer divisions per
+// vector.
+struct RowVec { int r, v; };
+__device__ __forceinline__ RowVec row_vec(int i, int vec, int vec_shift) {
+  const int r = vec_shift >= 0 ? i >> vec_shift : i / vec;
+  return {r, i - r * vec};
+}
+__device__ __forceinline__ int shift_of(int vec) {
+  return (vec & (vec - 1)) == 0 ? 31 - __clz(vec) : -1;
+}
+
 // Raw e4m3 rows (16-byte vectors) + their scales (or 1).
 __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape& sh,
                                        const uint8_t* src, size_t src_pitch,
                                        const float* src_scale, int rows, int k, int tid,
                                        int nthr) {
-  const int vec = k / 16, nvec = rows * vec;
+  const int vec = k / 16, nvec = rows * vec, vsh = shift_of(vec);
   // the first activation scale of this thread rides along with the first batch of loads
   const int nxs = rows * sh.x_blocks;
   float xs_first = 1.0f;
@@ -142,8 +159,8 @@ __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape
       if (v0 + j * nthr >= nvec) break;   // same for every thread
       const int i = v0 + j * nthr + tid;
       if (i < nvec) {
-        const int r = i / vec, v = i - r * vec;
-        raw[j] = __ldcg(reinterpret_cast<const uint4*>(src + r * src_pitch + v * 16));
+        const RowVec rv = row_vec(i, vec, vsh);
+        raw[j] = __ldcg(reinterpret_cast<const uint4*>(src + rv.r * src_pitch + rv.v * 16));
       }
     }
 #pragma unroll
@@ -151,8 +168,8 @@ __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape
       if (v0 + j * nthr >= nvec) break;
       const int i = v0 + j * nthr + tid;
       if (i < nvec) {
-        const int r = i / vec, v = i - r * vec;
-        *reinterpret_cast<uint4*>(xq + r * sh.x_pitch + v * 16) = raw[j];
+        const RowVec rv = row_vec(i, vec, vsh);
+        *reinterpret_cast<uint4*>(xq + rv.r * sh.x_pitch + rv.v * 16) = raw[j];
       }
     }
   }
@@ -168,7 +185,7 @@ __device__ inline void stage_rows_e4m3(uint8_t* xq, float* xs, const StreamShape
 __device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const StreamShape& sh,
                                               const __nv_bfloat16* src, size_t src_pitch,
                                               int rows, int k, bool split2, int tid, int nthr) {
-  const int vec = k / 8, nvec = rows * vec;
+  const int vec = k / 8, nvec = rows * vec, vsh = shift_of(vec);
   for (int v0 = 0; v0 < nvec; v0 += nthr * kStageBatch) {
     uint4 raw[kStageBatch];
 #pragma unroll
@@ -177,8 +194,8 @@ __device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const Stre
       const int i = v0 + j * nthr + tid;
       raw[j] = make_uint4(0u, 0u, 0u, 0u);
       if (i < nvec) {
-        const int r = i / vec, v = i - r * vec;
-        raw[j] = __ldcg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * src_pitch + v * 8));
+        const RowVec rv = row_vec(i, vec, vsh);
+        raw[j] = __ldcg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(rv.r) * src_pitch + rv.v * 8));
       }
     }
 #pragma unroll
@@ -186,15 +203,15 @@ __device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const Stre
       if (v0 + j * nthr >= nvec) break;    // whole batch dead: nothing to do
       const int i = v0 + j * nthr + tid;   // uniform trip count: shuffles below
       const bool live = i < nvec;
-      const int ii = live ? i : 0;
-      const int r = ii / vec, v = ii - r * vec;
+      const RowVec rv = row_vec(live ? i : 0, vec, vsh);
+      const int r = rv.r, v = rv.v;
+      // (bf16 -> fp32 is a shift: two logic operations per pair)
+      const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
       float f[8];
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float2 t = __bfloat1622float2(p[q]);
-        f[2 * q] = t.x;
-        f[2 * q + 1] = t.y;
+        f[2 * q] = __uint_as_float(w[q] << 16);
+        f[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u);
       }
       float amax = 0.f;
 #pragma unroll
@@ -204,17 +221,16 @@ __device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const Stre
       if (!live) continue;               // after the shuffles: dead lanes skip the math
       const float s = amax > 0.f ? amax / 448.0f : 1.0f;
       const float rcp = 1.0f / s;        // one division per vector; values use x * (1/s)
-      uint32_t q0[2] = {0u, 0u}, q1[2] = {0u, 0u};
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const float xn = f[q] * rcp;
-        const uint8_t a = f32_to_e4m3_sat(xn);
-        q0[q >> 2] |= static_cast<uint32_t>(a) << (8 * (q & 3));
-        if (split2)
-          q1[q >> 2] |= static_cast<uint32_t>(f32_to_e4m3_sat(xn - e4m3_to_f32(a))) << (8 * (q & 3));
-      }
       const int blk = v >> 4;
       if (split2) {
+        uint32_t q0[2] = {0u, 0u}, q1[2] = {0u, 0u};
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float xn = f[q] * rcp;
+          const uint8_t a = f32_to_e4m3_sat(xn);
+          q0[q >> 2] |= static_cast<uint32_t>(a) << (8 * (q & 3));
+          q1[q >> 2] |= static_cast<uint32_t>(f32_to_e4m3_sat(xn - e4m3_to_f32(a))) << (8 * (q & 3));
+        }
         *reinterpret_cast<uint2*>(xq + (2 * r) * sh.x_pitch + v * 8) = make_uint2(q0[0], q0[1]);
         *reinterpret_cast<uint2*>(xq + (2 * r + 1) * sh.x_pitch + v * 8) = make_uint2(q1[0], q1[1]);
         if ((v & 15) == 0) {
@@ -222,7 +238,10 @@ __device__ inline void stage_rows_bf16_groupq(uint8_t* xq, float* xs, const Stre
           xs[(2 * r + 1) * sh.x_blocks + blk] = s;
         }
       } else {
-        *reinterpret_cast<uint2*>(xq + r * sh.x_pitch + v * 8) = make_uint2(q0[0], q0[1]);
+        // (packed conversions: one instruction per pair of values)
+        const uint32_t lo = e4m3x2_sat(f[0] * rcp, f[1] * rcp) | (e4m3x2_sat(f[2] * rcp, f[3] * rcp) << 16);
+        const uint32_t hi = e4m3x2_sat(f[4] * rcp, f[5] * rcp) | (e4m3x2_sat(f[6] * rcp, f[7] * rcp) << 16);
+        *reinterpret_cast<uint2*>(xq + r * sh.x_pitch + v * 8) = make_uint2(lo, hi);
         if ((v & 15) == 0) xs[r * sh.x_blocks + blk] = s;
       }
     }
@@ -320,10 +339,6 @@ __device__ __forceinline__ uint32_t bf16x2_round(float lo, float hi, float& rlo,
   rlo = __uint_as_float(u << 16);
   rhi = __uint_as_float(u & 0xffff0000u);
   return u;
-}
-// Two values to e4m3 (saturating) by one conversion: low byte = lo.
-__device__ __forceinline__ uint32_t e4m3x2_sat(float lo, float hi) {
-  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
 }
 
 // The threads that run a block-wide helper together: the whole CTA (n == 0), or threads
