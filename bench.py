@@ -57,6 +57,11 @@ def parse_args():
     ap.add_argument("--protocol", default="push", choices=("push", "pull"),
                     help="all-reduce of the two tails: tiles pushed into every rank's landing "
                          "zone from the GEMV epilogue, or signal / wait / switch read")
+    ap.add_argument("--workload", default="layer", choices=("layer", "slice4"),
+                    help="layer: the decode layer (the headline metric).  slice4: four chained "
+                         "decoder layers with distinct weights in one CUDA graph, each the "
+                         "attention prologue (QKV product + heads + KV write) and the decode "
+                         "layer, the attention core replaced by a stand-in output")
     ap.add_argument("--passes", type=int, default=0,
                     help="timed passes of K steps (default: 11, more when K steps are short)")
     ap.add_argument("--no-parity", action="store_true")
@@ -620,6 +625,316 @@ def run_ours(args):
         raise SystemExit("parity check failed (see the `parity` object of the JSON line)")
 
 
+# ------------------------------------------------------------------------------ 4-layer slice
+
+SLICE_LAYERS = 4
+SLICE_WORKLOAD = ("4 chained decoder layers, distinct block-FP8 weights per layer, one CUDA graph: "
+                  "per layer the QKV product (64 q / 8 kv heads of 128) + q/k norm + rope + "
+                  "e4m3 KV write, then o_proj + all-reduce tail, router top-8, expert Gate, "
+                  "expert Down + all-reduce tail; layer i's output and norm feed layer i+1; "
+                  "the attention core is NOT run (its output is a seeded stand-in per layer)")
+
+
+def slice_inputs(synth, shape, rows, tp, rank, dev, n_layers):
+    """Stand-in attention outputs per layer, the stream entering layer 0 and its norm."""
+    aos = [synth.make_step_inputs(shape, rows, tp=tp, rank=rank, device=dev, seed=0, step=i)[0]
+           for i in range(n_layers)]
+    res0 = synth.make_step_inputs(shape, rows, tp=tp, rank=rank, device=dev, seed=0, step=0)[1]
+    xn0 = synth.make_step_inputs(shape, rows, tp=tp, rank=rank, device=dev, seed=0, step=77)[1]
+    return aos, res0, xn0
+
+
+def slice_check(rows, tp, shape, heads, seen, lws, pws, ins, cos, sin, same, tol):
+    """Rank 0's comparison of one slice step (`seen[i]`: what the kernels produced at layer
+    i) with the reference's algebra; returns the case report."""
+    import torch
+    from oracle import ref_path as R
+    from oracle.cpu_layer import layer_cpu
+    host_threads()
+    L = len(seen)
+    res_ref = res_in = ins[0][1].cpu()
+    xn_in = ins[0][2].cpu()
+    case = {"rows": rows, "layers": [], "ranks_bit_identical": same}
+    good = same
+    for i in range(L):
+        got = {k: v.cpu() for k, v in seen[i].items()}
+        cl = [{k: v.cpu() for k, v in lw.items()} for lw in lws[i]]
+        sel = got["sel"].view(rows, shape.top_k)
+        wt = got["wt"].view(rows, shape.top_k)
+        r_sel, _, margin = R.select_topk(R.router_logits(got["x_pad"], cl[0]["router"]),
+                                         shape.top_k, "sigmoid")
+        clear = margin > 1e-3
+        routes_equal = bool(torch.equal(sel[clear], r_sel[clear]))
+        ao_ranks = [ins[r][0][i].cpu() for r in range(tp)]
+        kw = dict(top_k=shape.top_k, n_shared=shape.n_shared, eps=shape.eps,
+                  score="sigmoid", routes=(sel, wt))
+        # (a) the layer on the residual the kernel's layer received: the per-layer bar
+        ref_out, ref_norm, _, _ = layer_cpu(cl, ao_ranks, res_in, **kw)
+        e_out = R.rel_fro(got["out"], ref_out)
+        e_norm = R.rel_fro(got["norm"], ref_norm)
+        # (b) the oracle's own chain from the step's input: reported, not gated (the
+        # e4m3 activation error of every layer so far is in it)
+        chain_out, chain_norm, _, _ = layer_cpu(cl, ao_ranks, res_ref, **kw)
+        c_out = R.rel_fro(got["out"], chain_out)
+        # the prologue on the norm the kernel read (layer 0: the step's input)
+        pw = {k: v.cpu() for k, v in pws[i].items()}
+        qh, kh = heads.local(tp)
+        ref_qkv = R.linear(xn_in, pw["w_qkv"], pw["w_qkv_scale"])
+        rq, rk, rv = R.heads_prefill(ref_qkv, qh, kh, heads.head_dim, pw["w_qn"],
+                                     pw["w_kn"], cos, sin, heads.rotary_dim, shape.eps)
+        e_q = R.rel_fro(got["q"], rq)
+        e_k = R.rel_fro(got["k"].float(), R.to_e4m3_sat(rk).float())
+        e_v = R.rel_fro(got["v"].float(), R.to_e4m3_sat(rv).float())
+        lay_ok = e_out <= tol and e_norm <= tol and routes_equal and e_q <= tol
+        good = good and lay_ok
+        case["layers"].append({"layer": i, "rel_fro_out": e_out, "rel_fro_norm": e_norm,
+                               "chained_rel_fro_out": c_out,
+                               "routes_equal": routes_equal,
+                               "rows_with_clear_margin": int(clear.sum()),
+                               "rel_fro_q": e_q, "rel_fro_k_e4m3": e_k,
+                               "rel_fro_v_e4m3": e_v, "ok": lay_ok})
+        res_ref, res_in, xn_in = chain_out, got["out"], got["norm"]
+    case["ok"] = good
+    return case
+
+
+def slice_parity(args, tp, rank, dev, group, rows_list=(1, 4)):
+    """One untimed step of the 4-layer slice per row count (expert bank cut to 16 experts),
+    checked on rank 0 layer by layer: the chained layer outputs against the reference's
+    algebra applied four times over ALL ranks' shards (the oracle carries its own residual
+    from layer to layer; the routes are the kernel's, checked against the reference's rule
+    where the margin is clear), and this rank's prologue (q, and the cache rows through the
+    same heads step) against the reference's algebra on the norm the kernel handed it.
+    Gated per layer on that layer's own inputs (the bar is a per-layer one); the error of
+    the whole chain against the oracle's own chain is reported beside it."""
+    import torch
+    import torch.distributed as dist
+    from iquestrt_b200 import synth
+    from iquestrt_b200.layer import DecodeSlice
+    tol = 2e-2
+    L = SLICE_LAYERS
+    shape = synth.LayerShape(n_experts=16)
+    heads = synth.HEADS
+    report = {"tol": tol, "oracle": f"reference torch algebra chained over {L} layers, all {tp} "
+                                    "rank shards, 16-expert bank; prologue on rank 0's heads",
+              "cases": []}
+    ok = True
+    for rows in rows_list:
+        lws = [[synth.make_layer(shape, tp=tp, rank=r, device=dev, seed=0, layer=i)
+                for r in range(tp)] for i in range(L)]
+        pws = [synth.make_prologue(shape, heads, tp=tp, rank=rank, device=dev, seed=0, layer=i)
+               for i in range(L)]
+        sl = DecodeSlice(shape, [(lws[i][rank], pws[i]) for i in range(L)], q_len=rows, tp=tp,
+                         group=group, device=dev, use_multicast=not args.no_multicast,
+                         protocol=args.protocol)
+        ins = [slice_inputs(synth, shape, rows, tp, r, dev, L) for r in range(tp)]
+        aos, res0, xn0 = ins[rank]
+        seen = []
+
+        def visit(i, q, out, norm):
+            lay = sl.layer
+            seen.append({"q": q.clone(), "out": out.clone(), "norm": norm.clone(),
+                         "sel": lay.router.sel.clone(), "wt": lay.router.wt.clone(),
+                         "x_pad": lay.moe.x_pad[:rows].clone(),
+                         "k": sl.k_cache[i][sl.slot].clone(), "v": sl.v_cache[i][sl.slot].clone()})
+        sl.step(res0, xn0, aos)                             # (both alternating slots warm)
+        seen.clear()
+        out, norm = sl.step(res0, xn0, aos, visit=visit)
+        sl.check()
+        out, norm = out.clone(), norm.clone()
+        same = True
+        if tp > 1:
+            both = torch.cat([out.contiguous().view(torch.uint8).flatten(),
+                              norm.contiguous().view(torch.uint8).flatten()])
+            gathered = [torch.empty_like(both) for _ in range(tp)]
+            dist.all_gather(gathered, both)
+            same = all(torch.equal(g, both) for g in gathered)
+        if rank == 0:
+            case = slice_check(rows, tp, shape, heads, seen, lws, pws, ins, sl.cos.cpu(),
+                               sl.sin.cpu(), same, tol)
+            ok = ok and case["ok"]
+            report["cases"].append(case)
+        del sl, lws, pws
+    if rank != 0:
+        return None
+    every = [l for c in report["cases"] for l in c["layers"]]
+    report["rel_fro_out"] = max(l["rel_fro_out"] for l in every)
+    report["rel_fro_norm"] = max(l["rel_fro_norm"] for l in every)
+    report["rel_fro_q"] = max(l["rel_fro_q"] for l in every)
+    report["routes_equal"] = all(l["routes_equal"] for l in every)
+    report["chained_rel_fro_out"] = max(l["chained_rel_fro_out"] for l in every)
+    report["gated"] = ("per layer: out, norm and q within tol of the reference's algebra on the "
+                       "layer's own inputs, routes equal under the margin rule, ranks "
+                       "bit-identical; reported only: the chained figure and the e4m3 cache rows")
+    report["ok"] = ok
+    return report
+
+
+def run_slice(args):
+    """`--workload slice4`: us per 4-layer step and tokens/s of the chained slice."""
+    import torch
+    import torch.distributed as dist
+    from iquestrt_b200 import _build, synth
+    from iquestrt_b200.layer import DecodeSlice
+
+    tp = args.gpus
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != tp:
+        raise SystemExit(f"--gpus {tp} needs WORLD_SIZE={tp} (launch with torchrun), got {world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    group = None
+    if tp > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD.group_name
+    _build.build()
+    parity = None if args.no_parity else slice_parity(args, tp, rank, dev, group)
+
+    L, rows = SLICE_LAYERS, args.rows
+    shape = synth.LayerShape(n_experts=args.experts)
+    heads = synth.HEADS
+    shard_of = args.shard_of if tp == 1 else 0
+    if shard_of > 1:
+        # one rank's slice of every sharded dimension (heads included), as a model of its own
+        ql, il = shape.local(shard_of)
+        shape = synth.LayerShape(hidden=shape.hidden, q_dim=ql, n_experts=shape.n_experts,
+                                 top_k=shape.top_k, inter=il, n_shared=shape.n_shared,
+                                 eps=shape.eps)
+        qh_s, kh_s = heads.local(shard_of)
+        heads = synth.HeadShape(q_heads=qh_s, kv_heads=kh_s, head_dim=heads.head_dim,
+                                rotary_dim=heads.rotary_dim, theta=heads.theta)
+    qh, kh = heads.local(tp)
+    qkv_bytes = (qh + 2 * kh) * heads.head_dim * shape.hidden
+    by = layer_bytes(shape, tp, rows, shape.top_k if rows == 1 else min(shape.n_experts,
+                                                                        rows * shape.top_k))
+    step_bytes = L * (by["total"] + qkv_bytes)
+    # Weight sets: one slice is larger than L2 several times over except at TP=8, where two
+    # sets alternate from step to step.
+    n_sets = 1 if step_bytes >= 3 * 126e6 else 2
+    sets = [[(synth.make_layer(shape, tp=tp, rank=rank, device=dev, seed=0, layer=s * L + i),
+              synth.make_prologue(shape, heads, tp=tp, rank=rank, device=dev, seed=0,
+                                  layer=s * L + i)) for i in range(L)] for s in range(n_sets)]
+    sl = DecodeSlice(shape, sets[0], heads=heads, q_len=rows, tp=tp, group=group, device=dev,
+                     use_multicast=not args.no_multicast, protocol=args.protocol)
+    aos, res0, xn0 = slice_inputs(synth, shape, rows, tp, rank, dev, L)
+    K, W = max(1, args.steps), max(3, args.warmup)
+
+    def call(j):
+        sl.layers = sets[j % n_sets]
+        return sl.step(res0, xn0, aos)
+
+    def barrier():
+        if tp > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if tp == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    stream = torch.cuda.Stream(device=dev)
+    chunk = 32
+    with torch.cuda.stream(stream):
+        for j in range(W):
+            call(j)
+        stream.synchronize()
+        sl.check()
+
+        def capture(n):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for j in range(n):
+                    call(j)
+            return g
+
+        unit = K * (2 if (K % 2 and n_sets > 1) else 1)      # whole cycles of the weight sets
+        graphs = []
+        if unit >= chunk:
+            graphs += [capture(chunk)] * (unit // chunk)
+        if unit % chunk:
+            graphs.append(capture(unit % chunk))
+
+        def run_pass():
+            for g in graphs:
+                g.replay()
+
+        run_pass()
+        stream.synchronize()
+        probe = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        probe[0].record(stream)
+        run_pass()
+        probe[1].record(stream)
+        stream.synchronize()
+        est_ms = max(probe[0].elapsed_time(probe[1]), 1e-3)
+        passes = args.passes or int(min(501, max(11, 50.0 / est_ms + 2)))
+        passes = int(max_over_ranks(float(passes)))
+        barrier()
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(passes + 1)]
+        with ClockSampler(local_rank) as clocks:
+            marks[0].record(stream)
+            for j in range(passes):
+                run_pass()
+                marks[j + 1].record(stream)
+            stream.synchronize()
+        barrier()
+        pass_ms = [marks[j].elapsed_time(marks[j + 1]) * K / unit for j in range(1, passes)]
+        sl.check()
+
+    med_ms = max_over_ranks(statistics.median(pass_ms))
+    min_ms = max_over_ranks(min(pass_ms))
+    max_ms = max_over_ranks(max(pass_ms))
+    failed = False
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        us = med_ms * 1e3 / K
+        launches = L * sl.launches_per_layer
+        line = {
+            "metric": "us per 4-layer decode step (attention core left out)", "value": us,
+            "unit": "us/step", "n_gpus": tp, "steps": K, "warmup": W, "ms_per_step": med_ms / K,
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "e4m3 x e4m3 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": SLICE_WORKLOAD, "rows": rows, "tp": tp, "layers": L,
+                       "launches_per_step": launches, "experts_in_bank": args.experts,
+                       "shard_of": shard_of or None,
+                       "timing": f"{passes} passes of {K} steps back to back, first dropped, "
+                                 "median pass",
+                       "l2": f"{n_sets} set(s) of {L} distinct layers, "
+                             f"{step_bytes * n_sets / 1e6:.0f} MB touched per cycle, L2 is 126 MB",
+                       "all_reduce": "none (TP=1)" if tp == 1 else
+                                     f"{args.protocol}, " +
+                                     ("peer stores/loads" if args.no_multicast else "NVLS multimem")},
+            "clocks": clocks.summary(),
+            "e2e": None,
+            "gpu_launches": launches * unit * (passes - 1),
+            "passes_timed": passes - 1,
+            "us_per_layer": us / L,
+            "tokens_per_s": rows / (us * 1e-6),
+            "roofline": {"bound": "hbm", "kernel": "whole step (24 launches)",
+                         "achieved": step_bytes / (us * 1e-6) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": step_bytes / (us * 1e-6) / 1e9 / peak, "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_step": step_bytes, "traffic": None},
+            "spread_us": {"passes": passes - 1, "min": min_ms * 1e3 / K,
+                          "median": med_ms * 1e3 / K, "max": max_ms * 1e3 / K},
+            "parity": parity,
+            "cpu_baseline": None,
+        }
+        print(json.dumps(line))
+        failed = parity is not None and not parity["ok"]
+    if tp > 1:
+        flag = torch.tensor([int(failed)], device=dev)
+        dist.broadcast(flag, src=0)
+        failed = bool(flag.item())
+        dist.barrier()
+        dist.destroy_process_group()
+    if failed:
+        raise SystemExit("parity check failed (see the `parity` object of the JSON line)")
+
+
 # ------------------------------------------------------------------------------ reference GPU arm
 
 def run_reference_gpu(args):
@@ -729,6 +1044,8 @@ def main():
         run_reference(args)
     elif args.impl == "reference-gpu":
         run_reference_gpu(args)
+    elif args.workload == "slice4":
+        run_slice(args)
     else:
         run_ours(args)
 

@@ -25,8 +25,8 @@ import torch
 
 from . import ops
 from .kernels import (MoeDecodeKernels, MultimemARTail, MultimemMLPTail, OProjGemv,
-                      RouterSelect, TailKernels)
-from .synth import LayerShape
+                      PrologueKernels, RouterSelect, TailKernels)
+from .synth import HEADS, HeadShape, LayerShape, rope_tables
 from .workspace import Workspace
 
 
@@ -161,6 +161,71 @@ class DecodeLayer:
     def check(self) -> None:
         """Synchronises and raises if any launch recorded a device-side error."""
         self.scratch.raise_on_error("decode layer")
+
+
+class DecodeSlice:
+    """Consecutive decoder layers of one TP rank as one chain of launches: per layer the
+    attention prologue (column-parallel QKV product, q/k norm, rotary embedding, KV-cache
+    write), then the `DecodeLayer` (o_proj + attention tail, router, expert Gate, expert
+    Down + MLP tail).  The attention core between the two is not part of this library: the
+    layer's `ao` is a stand-in the caller supplies per layer, and the prologue's q and the
+    cache rows it writes are outputs nobody consumes here.  Everything else is chained as in
+    the model: layer i's output is layer i+1's residual, and its norm (under layer i+1's
+    attention norm) is what layer i+1's QKV product reads.
+
+    `layers` is a list of `(lw, pw)`: `synth.make_layer` and `synth.make_prologue` dicts.  An
+    even number of layers keeps the alternating all-reduce outputs in step with a captured
+    graph."""
+
+    def __init__(self, shape: LayerShape, layers, *, heads: HeadShape = HEADS, q_len: int = 1,
+                 tp: int = 1, group=None, device="cuda", cache_rows: int = 4096,
+                 positions=None, **layer_kwargs):
+        self.layers = list(layers)
+        self.layer = DecodeLayer(shape, q_len=q_len, tp=tp, group=group, device=device,
+                                 formats="benchmark", **layer_kwargs)
+        qh, kh = heads.local(tp)
+        self.heads, self.q_heads, self.kv_heads = heads, qh, kh
+        self._ws = Workspace(device=device)
+        self.prologue = PrologueKernels(shape.hidden, qh, kh, heads.head_dim, heads.rotary_dim,
+                                        shape.eps, ws=self._ws, q_len=q_len,
+                                        scratch=self.layer.scratch)
+        self._ws.freeze()
+        if positions is None:
+            positions = [32000 + r for r in range(q_len)]
+        self.cos, self.sin = rope_tables(positions, heads, device=device)
+        self.slot = torch.arange(100, 100 + q_len, dtype=torch.int64, device=device)
+        e4m3 = torch.float8_e4m3fn
+        self.k_cache = [torch.zeros(cache_rows, kh, heads.head_dim, dtype=e4m3, device=device)
+                        for _ in self.layers]
+        self.v_cache = [torch.zeros_like(k) for k in self.k_cache]
+
+    def prologue_step(self, i, xn, *, pdl=True):
+        """Layer `i`'s prologue on `xn [q, hidden]`: returns q `[q, q_heads, D]` (one buffer,
+        overwritten by the next layer); k and v go into the layer's cache rows."""
+        pw = self.layers[i][1]
+        _, q = self.prologue.call_prenorm(xn, pw["w_qkv"], pw["w_qkv_scale"], pw["w_qn"],
+                                          pw["w_kn"], self.cos, self.sin, self.slot,
+                                          self.k_cache[i], self.v_cache[i], pdl=pdl)
+        return q
+
+    def step(self, residual, xn, aos, *, pdl=True, visit=None):
+        """One token step through every layer.  `residual`, `xn` `[q, hidden]` bf16: the
+        stream entering layer 0 and its norm; `aos[i]` the stand-in attention output of
+        layer i (`[q, q_dim/tp]` bf16).  Returns the last layer's `(out, norm_out)`.
+        `visit(i, q, out, norm_out)` is called after each layer's launches are enqueued."""
+        for i, (lw, _) in enumerate(self.layers):
+            q = self.prologue_step(i, xn, pdl=pdl)
+            residual, xn = self.layer.step(aos[i], residual, lw, pdl=pdl)
+            if visit is not None:
+                visit(i, q, residual, xn)
+        return residual, xn
+
+    @property
+    def launches_per_layer(self):
+        return 6
+
+    def check(self) -> None:
+        self.layer.check()
 
 
 class CapturedSteps:

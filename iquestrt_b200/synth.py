@@ -124,6 +124,58 @@ def make_layer(shape: LayerShape, *, tp=1, rank=0, device="cuda", seed=0, layer=
     return out
 
 
+@dataclass(frozen=True)
+class HeadShape:
+    """Attention heads of the benchmark's decoder slice: 64 query and 8 key/value heads of
+    128 channels, rotary embedding on the first 32."""
+    q_heads: int = 64
+    kv_heads: int = 8
+    head_dim: int = 128
+    rotary_dim: int = 32
+    theta: float = 10000.0
+
+    def local(self, tp: int):
+        if self.q_heads % tp or self.kv_heads % tp:
+            raise ValueError(f"TP={tp} does not divide {self.q_heads} / {self.kv_heads} heads")
+        return self.q_heads // tp, self.kv_heads // tp
+
+
+HEADS = HeadShape()
+
+
+def make_prologue(shape: LayerShape, heads: HeadShape = HEADS, *, tp=1, rank=0, device="cuda",
+                  seed=0, layer=0):
+    """Rank-local weights of one layer's attention prologue: the column-parallel QKV weight
+    (this rank's query heads, then its key heads, then its value heads: rows of the global
+    [q | k | v] matrix) with its block scales, and the q / k norm weights."""
+    qh, kh = heads.local(tp)
+    d, h = heads.head_dim, shape.hidden
+    g = _gen(device, seed, layer, 7)
+    parts, scales = [], []
+    # (one global tensor per projection, generated whole so that every TP degree sees the
+    # same problem; a rank keeps its heads' rows)
+    for n_heads, mine in ((heads.q_heads, qh), (heads.kv_heads, kh), (heads.kv_heads, kh)):
+        w = fp8_weight(n_heads * d, h, g, device)
+        sc = block_scales(n_heads * d, h, g, device)
+        r0, n = rank * mine * d, mine * d
+        parts.append(w[r0:r0 + n])
+        scales.append(shard_scale(sc, 0, r0, n, BLOCK))
+    return {"w_qkv": torch.cat(parts, 0).contiguous(),
+            "w_qkv_scale": torch.cat(scales, 0).contiguous(),
+            "w_qn": 0.5 + torch.rand(d, generator=g, device=device, dtype=torch.float32),
+            "w_kn": 0.5 + torch.rand(d, generator=g, device=device, dtype=torch.float32)}
+
+
+def rope_tables(positions, heads: HeadShape = HEADS, *, device="cuda"):
+    """bf16 (cos, sin) `[len(positions), rotary_dim]` of the partial rotary embedding (the
+    two halves of the rotated channels share their angles)."""
+    rot = heads.rotary_dim
+    pos = torch.as_tensor(positions, dtype=torch.float32)
+    inv = heads.theta ** (-torch.arange(0, rot, 2, dtype=torch.float32) / rot)
+    ang = torch.cat([pos[:, None] * inv[None, :]] * 2, dim=-1)
+    return ang.cos().bfloat16().to(device), ang.sin().bfloat16().to(device)
+
+
 def make_step_inputs(shape: LayerShape, m, *, tp=1, rank=0, device="cuda", seed=0, step=0):
     """Activations of one decode step: the attention output `ao [m, q_dim/tp]` (this rank's
     head slice of a global N(0,1) tensor) and the residual `[m, hidden]`, both bf16."""

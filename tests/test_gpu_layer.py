@@ -226,3 +226,46 @@ def test_host_step_matches_device_step():
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))
     layer.check()
     assert hs.h2d_bytes == 2 * (ao.numel() + res.numel()) and hs.d2h_bytes == 2 * want.numel()
+
+
+def test_decode_slice_chain_against_oracle():
+    """Four chained layers with their attention prologues (`DecodeSlice`, the attention core
+    a stand-in): every layer's out / norm / q within the path tolerance of the reference's
+    algebra on that layer's inputs, routes equal under the margin rule (the check the bench's
+    `--workload slice4` prints), and a CUDA-graph replay of the step bit-identical to the
+    eager step."""
+    import types
+    import bench
+    from iquestrt_b200 import synth
+    from iquestrt_b200.layer import DecodeSlice
+    args = types.SimpleNamespace(no_multicast=False, protocol="push")
+    report = bench.slice_parity(args, 1, 0, torch.device("cuda", 0), None, rows_list=(2,))
+    assert report["ok"], report
+    assert report["rel_fro_out"] <= PATH_TOL and report["rel_fro_q"] <= PATH_TOL
+
+    shape = synth.LayerShape(n_experts=16)
+    ql, il = shape.local(8)
+    shard = synth.LayerShape(hidden=shape.hidden, q_dim=ql, n_experts=16, inter=il)
+    heads = synth.HeadShape(q_heads=8, kv_heads=1)
+    layers = [(synth.make_layer(shard, device="cuda", seed=5, layer=i),
+               synth.make_prologue(shard, heads, device="cuda", seed=5, layer=i))
+              for i in range(4)]
+    sl = DecodeSlice(shard, layers, heads=heads, q_len=1)
+    aos, res0, xn0 = bench.slice_inputs(synth, shard, 1, 1, 0, "cuda", 4)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            out, norm = sl.step(res0, xn0, aos)
+        stream.synchronize()
+        want = (out.clone(), norm.clone(), sl.k_cache[3][sl.slot].clone())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for _ in range(4):
+                out_g, norm_g = sl.step(res0, xn0, aos)
+        for _ in range(3):
+            g.replay()
+        stream.synchronize()
+    sl.check()
+    assert torch.equal(out_g.view(torch.int16), want[0].view(torch.int16))
+    assert torch.equal(norm_g.view(torch.int16), want[1].view(torch.int16))
+    assert torch.equal(sl.k_cache[3][sl.slot].view(torch.uint8), want[2].view(torch.uint8))
