@@ -775,7 +775,7 @@ def run_slice(args):
     import torch
     import torch.distributed as dist
     from iquestrt_b200 import _build, synth
-    from iquestrt_b200.layer import DecodeSlice
+    from iquestrt_b200.layer import DecodeSlice, HostSliceStep
 
     tp = args.gpus
     rank = int(os.environ.get("RANK", "0"))
@@ -885,6 +885,31 @@ def run_slice(args):
         pass_ms = [marks[j].elapsed_time(marks[j + 1]) * K / unit for j in range(1, passes)]
         sl.check()
 
+        # ---- end to end from HOST buffers: one graph launch per step (`HostSliceStep`: the
+        # H2D copies of the entering stream and its norm, the 24 launches, the D2H copy of
+        # the output), one synchronise per step.
+        n_e2e, e2e_ms, h2d_bytes, d2h_bytes = min(K, 64), float("nan"), 0, 0
+        if not args.no_e2e:
+            hosts = []
+            for s_ in range(n_sets):
+                sl.layers = sets[s_]
+                hosts.append(HostSliceStep(sl, aos))
+            res_h, xn_h = res0.cpu(), xn0.cpu()
+            for j in range(4):
+                last = hosts[j % n_sets](res_h, xn_h)
+            want, _ = call((4 - 1) % n_sets)
+            stream.synchronize()
+            if not torch.equal(last.view(torch.int16), want.cpu().view(torch.int16)):
+                raise SystemExit("the host-buffer step and the device step disagree")
+            barrier()
+            t_e2e = time.perf_counter()
+            for j in range(n_e2e):
+                hosts[j % n_sets](res_h, xn_h)
+            e2e_ms = (time.perf_counter() - t_e2e) * 1e3
+            h2d_bytes, d2h_bytes = hosts[0].h2d_bytes, hosts[0].d2h_bytes
+            sl.check()
+
+    e2e_ms = max_over_ranks(e2e_ms)
     med_ms = max_over_ranks(statistics.median(pass_ms))
     min_ms = max_over_ranks(min(pass_ms))
     max_ms = max_over_ranks(max(pass_ms))
@@ -909,7 +934,9 @@ def run_slice(args):
                                      f"{args.protocol}, " +
                                      ("peer stores/loads" if args.no_multicast else "NVLS multimem")},
             "clocks": clocks.summary(),
-            "e2e": None,
+            "e2e": None if args.no_e2e else
+                   {"value": e2e_ms * 1e3 / n_e2e, "unit": "us/step", "steps": n_e2e,
+                    "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": int(d2h_bytes)},
             "gpu_launches": launches * unit * (passes - 1),
             "passes_timed": passes - 1,
             "us_per_layer": us / L,

@@ -228,6 +228,50 @@ class DecodeSlice:
         self.layer.check()
 
 
+class HostSliceStep:
+    """One `DecodeSlice.step` from HOST buffers as a single CUDA-graph launch: the copies of
+    the stream entering layer 0 and its norm from pinned host memory, every layer's
+    launches, and the copy of the last layer's output back to pinned host memory (`HostStep`
+    for the slice).  The stand-in attention outputs `aos` stay on the device, where an
+    attention kernel would have written them.  Captures the slice's CURRENT `layers`."""
+
+    def __init__(self, sl: DecodeSlice, aos, *, pdl: bool = True):
+        layer = sl.layer
+        dev = layer.norm_out.device
+        q, h = layer.q_len, layer.shape.hidden
+        self.stream = torch.cuda.Stream(device=dev)
+        self.res_pin = torch.zeros(q, h, dtype=torch.bfloat16).pin_memory()
+        self.xn_pin = torch.zeros(q, h, dtype=torch.bfloat16).pin_memory()
+        self.out_pin = torch.empty(q, h, dtype=torch.bfloat16).pin_memory()
+        self.res_dev = torch.empty(q, h, dtype=torch.bfloat16, device=dev)
+        self.xn_dev = torch.empty(q, h, dtype=torch.bfloat16, device=dev)
+
+        def body():
+            self.res_dev.copy_(self.res_pin, non_blocking=True)
+            self.xn_dev.copy_(self.xn_pin, non_blocking=True)
+            out, _ = sl.step(self.res_dev, self.xn_dev, aos, pdl=pdl)
+            self.out_pin.copy_(out, non_blocking=True)
+
+        with torch.cuda.stream(self.stream):
+            body()
+            self.stream.synchronize()
+            sl.check()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self.stream):
+                body()
+        self.stream.synchronize()
+        self.h2d_bytes = 2 * (self.res_pin.numel() + self.xn_pin.numel())
+        self.d2h_bytes = 2 * self.out_pin.numel()
+
+    def __call__(self, residual_host, xn_host):
+        self.res_pin.copy_(residual_host)
+        self.xn_pin.copy_(xn_host)
+        with torch.cuda.stream(self.stream):
+            self.graph.replay()
+        self.stream.synchronize()
+        return self.out_pin
+
+
 class CapturedSteps:
     """`n` consecutive `DecodeLayer.step` calls recorded into one CUDA graph (the
     reference captures its whole step the same way, iquestrt/engine.py:677-772)."""
