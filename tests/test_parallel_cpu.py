@@ -3,7 +3,8 @@
 Covers what needs no GPU: every rank derives its shard from the same seeded global
 tensors, the rank-local scale tables follow the reference's `shard_scale` rule, and the
 sum over ranks of the row-parallel partial products (the all-reduce, here gloo's) equals
-the unsharded product -- for o_proj and for the expert Down."""
+the unsharded product -- for o_proj and for the expert Down; the column-parallel QKV
+shards of the attention prologue, gathered, equal the unsharded product."""
 
 import os
 
@@ -55,6 +56,26 @@ def _worker(rank, world, port, results):
         d = act[:, rank * il:(rank + 1) * il] @ w_loc.t()
         dist.all_reduce(d)
         assert torch.allclose(d, act @ w_all.t(), rtol=1e-4, atol=1e-6)
+        # attention prologue: column-parallel QKV (no reduction): the ranks' head shards,
+        # gathered, are the unsharded [q | k | v] product and its heads
+        heads = synth.HeadShape(q_heads=4, kv_heads=2)
+        pw = synth.make_prologue(shape, heads, tp=world, rank=rank, device="cpu", seed=7)
+        pf = synth.make_prologue(shape, heads, tp=1, rank=0, device="cpu", seed=7)
+        assert torch.equal(pw["w_qn"], pf["w_qn"]) and torch.equal(pw["w_kn"], pf["w_kn"])
+        xn = res_full
+        mine = R.linear(xn, pw["w_qkv"], pw["w_qkv_scale"])
+        both = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(both, mine)
+        whole = R.linear(xn, pf["w_qkv"], pf["w_qkv_scale"])
+        qh, kh = heads.local(world)
+        d_ = heads.head_dim
+        q_all = torch.cat([b[:, :qh * d_] for b in both], 1)
+        k_all = torch.cat([b[:, qh * d_:(qh + kh) * d_] for b in both], 1)
+        v_all = torch.cat([b[:, (qh + kh) * d_:] for b in both], 1)
+        nq, nk = heads.q_heads * d_, heads.kv_heads * d_
+        assert torch.equal(q_all, whole[:, :nq])
+        assert torch.equal(k_all, whole[:, nq:nq + nk])
+        assert torch.equal(v_all, whole[:, nq + nk:])
         results[rank] = "ok"
     finally:
         dist.destroy_process_group()
