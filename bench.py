@@ -5,6 +5,8 @@
     python bench.py --impl reference --gpus N ...            # the reference's CPU algebra
     python bench.py --impl reference-gpu                     # the reference's own SM100 kernels
                                                              # beside this build's, one GPU
+    python bench.py --workload slice4 [--gpus N]             # four chained layers with their
+                                                             # attention prologues (see run_slice)
 
 N is the tensor-parallel degree (one process per GPU; under torchrun for N > 1).  A step
 is one pass of the hot path of ONE decode layer at batch 1 over one synthetic input:
