@@ -266,3 +266,46 @@ def test_abi_rejects_null_arguments_without_a_gpu():
     assert lib.iq_linear_static_status(null, null) == _lib.IQ_ERR_ARG
     assert lib.iq_status_read(null, null, 0, null) == _lib.IQ_ERR_ARG
     assert lib.iq_scratch_bytes() >= 4 * 1024 * 1024
+
+
+def test_slice_checker_accepts_the_oracle_chain_and_rejects_a_wrong_layer():
+    """`bench.slice_check` (the parity gate of `--workload slice4`) on fabricated kernel
+    outputs: the oracle's own four-layer chain over two simulated ranks passes with zero
+    error; the same chain with one layer's output disturbed by 5 % fails at that layer."""
+    import bench
+    from iquestrt_b200 import synth
+    from oracle.cpu_layer import layer_cpu
+    torch.set_num_threads(4)
+    shape = synth.LayerShape(hidden=1024, q_dim=1024, n_experts=16, inter=256)
+    heads = synth.HeadShape(q_heads=8, kv_heads=2)
+    tp, rows, n_layers = 2, 2, 4
+    lws = [[synth.make_layer(shape, tp=tp, rank=r, device="cpu", layer=i) for r in range(tp)]
+           for i in range(n_layers)]
+    pws = [synth.make_prologue(shape, heads, tp=tp, rank=0, device="cpu", layer=i)
+           for i in range(n_layers)]
+    ins = [bench.slice_inputs(synth, shape, rows, tp, r, "cpu", n_layers) for r in range(tp)]
+    cos, sin = synth.rope_tables([5, 6], heads, device="cpu")
+    res, xn = ins[0][1], ins[0][2]
+    seen = []
+    qh, kh = heads.local(tp)
+    for i in range(n_layers):
+        aos = [ins[r][0][i] for r in range(tp)]
+        out, norm, sel, wt = layer_cpu(lws[i], aos, res, top_k=shape.top_k, n_shared=1,
+                                       eps=shape.eps, score="sigmoid")
+        parts = [R.linear(a, lw["o_proj"], lw["o_scale"]) for a, lw in zip(aos, lws[i])]
+        _, hn = R.layer_residual_algebra(parts, res, lws[i][0]["attn_out_norm"],
+                                         lws[i][0]["feed_forward_norm"], 1.0, shape.eps)
+        qkv = R.linear(xn, pws[i]["w_qkv"], pws[i]["w_qkv_scale"])
+        q, k, v = R.heads_prefill(qkv, qh, kh, heads.head_dim, pws[i]["w_qn"], pws[i]["w_kn"],
+                                  cos, sin, heads.rotary_dim, shape.eps)
+        seen.append({"q": q, "out": out, "norm": norm, "sel": sel.int().flatten(),
+                     "wt": wt.flatten(), "x_pad": hn, "k": R.to_e4m3_sat(k),
+                     "v": R.to_e4m3_sat(v)})
+        res, xn = out, norm
+    case = bench.slice_check(rows, tp, shape, heads, seen, lws, pws, ins, cos, sin, True, 2e-2)
+    assert case["ok"] and all(l["rel_fro_out"] == 0.0 and l["rel_fro_q"] == 0.0
+                              for l in case["layers"])
+    seen[2]["out"] = (seen[2]["out"].float() * 1.05).bfloat16()
+    case = bench.slice_check(rows, tp, shape, heads, seen, lws, pws, ins, cos, sin, True, 2e-2)
+    assert not case["ok"]
+    assert [l["ok"] for l in case["layers"]][:3] == [True, True, False]
